@@ -1,0 +1,211 @@
+/*
+ * tqb200.h - C ABI of libtqb200.so: the TurboQuant / PolarQuant packed-KV hot
+ * path as hand-written sm_100a CUDA kernels.
+ *
+ * Conventions
+ *   - Every function returns 0 (TQ_OK) or a negative tq_status; the message of
+ *     the last failure on the calling thread is tq_last_error_string().
+ *   - Tensor arguments (vectors, packed words, norms, queries, weights,
+ *     outputs, workspace) are DEVICE pointers owned by the caller.  The library
+ *     never allocates or frees device memory.
+ *   - Codebook-sized parameters (signs[dim], boundaries[2^bits-1],
+ *     centroids[2^bits]) are HOST pointers to float32; they are copied into the
+ *     kernel's parameter block at launch.  signs must be exactly +1 or -1.
+ *   - `stream` is a cudaStream_t passed as void*; launches are asynchronous and
+ *     stream-ordered, nothing synchronises.
+ *   - Strides are in elements of the pointed-to type unless stated otherwise.
+ *   - Packed layout (reference turboquant_mlx/packing.py:16-56): element j of a
+ *     vector lives in word j / vpw at bit (j % vpw) * bits, vpw = {1:32, 2:16,
+ *     3:10, 4:8}[bits]; a vector of `dim` elements takes ceil(dim / vpw) words.
+ *
+ * Each entry point cites the reference interface it replaces (path:line inside
+ * the reference project).
+ */
+#ifndef TQB200_H
+#define TQB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum tq_status {
+  TQ_OK = 0,
+  TQ_ERR_BAD_DIM = -1,        /* dim not a power of two or out of range */
+  TQ_ERR_BAD_BITS = -2,       /* bits outside 1..4 (8 / 4 for affine) */
+  TQ_ERR_HEAD_MISMATCH = -3,  /* n_q_heads != n_kv_heads * n_rep */
+  TQ_ERR_MISALIGNED = -4,     /* pointer or stride breaks an alignment rule */
+  TQ_ERR_WORKSPACE = -5,      /* workspace missing or too small */
+  TQ_ERR_LAUNCH = -6,         /* CUDA reported a launch/runtime error */
+  TQ_ERR_BAD_ARG = -7,        /* any other invalid argument */
+  TQ_ERR_UNSUPPORTED = -8     /* valid request this build has no kernel for */
+} tq_status;
+
+typedef enum tq_dtype { TQ_F32 = 0, TQ_F16 = 1, TQ_BF16 = 2 } tq_dtype;
+
+/* K / V storage formats understood by tq_flash_decode. */
+typedef enum tq_kv_format {
+  TQ_KV_POLAR = 0,   /* packed PolarQuant words + float32 norms */
+  TQ_KV_DENSE = 1,   /* plain fp16 / bf16 / fp32 rows (keys of the V-only cache) */
+  TQ_KV_AFFINE = 2   /* group-wise affine codes + fp16 scale / bias per group */
+} tq_kv_format;
+
+int tq_version(void);                      /* major * 10000 + minor * 100 + patch */
+const char* tq_last_error_string(void);    /* thread-local, never NULL */
+
+/* ---- fused quantize ------------------------------------------------------
+ * Replaces fused_quantize (turboquant_mlx/metal.py:147-196) with the rounding
+ * of PolarQuantizer.quantize + pack_indices (quantizer.py:75-106,
+ * packing.py:26-56): per-vector L2 norm, x / max(norm, 1e-8), sign flip, raw
+ * Walsh-Hadamard butterfly, *s then /s with s = float32(1/sqrt(dim)), strict
+ * compare with the boundaries, pack.
+ * Vector (o, i), o < n_outer, i < n_inner, is read at
+ *   x + o * x_outer_stride + i * dim
+ * and written at packed + o * packed_outer_stride + i * packed_dim and
+ * norms + o * norms_outer_stride + i, so a (B, H, S, D) insert can land
+ * directly inside a (B, H, n_alloc, .) cache at a row offset. */
+int tq_quantize(const void* x, int x_dtype, int64_t n_outer, int64_t n_inner,
+                int64_t x_outer_stride, int dim, int bits,
+                const float* signs_host, const float* boundaries_host,
+                uint32_t* packed, int64_t packed_outer_stride,
+                float* norms, int64_t norms_outer_stride, void* stream);
+
+/* ---- dequantize ----------------------------------------------------------
+ * Replaces dequant_fp16 (metal.py:199-232) and packed_dequantize
+ * (kernels.py:123-155): unpack, centroid * s, raw butterfly, * s * signs *
+ * norm, cast to out_dtype.  Addressing mirrors tq_quantize. */
+int tq_dequantize(const uint32_t* packed, int64_t packed_outer_stride,
+                  const float* norms, int64_t norms_outer_stride,
+                  int64_t n_outer, int64_t n_inner, int dim, int bits,
+                  const float* centroids_host, const float* signs_host,
+                  void* out, int out_dtype, int64_t out_outer_stride, void* stream);
+
+/* ---- pre-rotated query ---------------------------------------------------
+ * Replaces prerotate_query (metal_kernels_v4.py:119-150):
+ * out[h] = raw_butterfly(q[h] * signs), float32, no 1/sqrt(dim). */
+int tq_prerotate_query(const void* q, int q_dtype, int64_t n_heads, int64_t q_head_stride,
+                       int dim, const float* signs_host, float* out, void* stream);
+
+/* Replaces walsh_hadamard_transform / randomized_hadamard_transform /
+ * inverse_randomized_hadamard (rotation.py:7-80) for float32 rows:
+ * out = (bfly(x * pre) * s) * post, pre/post optional (NULL = ones). */
+int tq_hadamard(const float* x, int64_t n_rows, int dim, const float* pre_signs_host,
+                const float* post_signs_host, int normalize, float* out, void* stream);
+
+/* ---- Q.K scores with a pre-rotated query -----------------------------------
+ * Replaces prerot_fused_qk_scores (metal_kernels_v4.py:153-221):
+ * out[h, p] = (sum_e c[idx[h / n_rep, p, e]] * q_rot[h, e]) * norm[h / n_rep, p] / dim.
+ * k_packed head stride in words, k_norms head stride in floats; out is
+ * (n_kv * n_rep, seq_len) contiguous float32. */
+int tq_prerot_qk_scores(const float* q_rot, const uint32_t* k_packed, int64_t k_head_stride,
+                        const float* k_norms, int64_t kn_head_stride, int n_kv_heads,
+                        int64_t seq_len, const float* centroids_host, int dim, int bits,
+                        int n_rep, float* out, void* stream);
+
+/* Replaces packed_fused_qk_scores (kernels.py:158-196): per-position dequant
+ * then dot with the un-rotated query (multi-head only).  Comparator. */
+int tq_packed_qk_scores(const float* query, const uint32_t* k_packed, int64_t k_head_stride,
+                        const float* k_norms, int64_t kn_head_stride, int n_heads,
+                        int64_t seq_len, const float* centroids_host, const float* signs_host,
+                        int dim, int bits, float* out, void* stream);
+
+/* ---- weighted V sum, butterfly pulled out ----------------------------------
+ * Replaces sparse_v_matvec (sparse_v.py:94-186):
+ * out[h] = signs * bfly(sum_{p : w[h,p] >= thr} w[h,p] * norm[p] * c[idx[p]]) / dim,
+ * thr = max(threshold, 0).  Needs tq_sparse_v_workspace_bytes() of workspace. */
+size_t tq_sparse_v_workspace_bytes(int n_q_heads, int64_t seq_len, int dim);
+int tq_sparse_v_matvec(const float* weights, int64_t w_head_stride,
+                       const uint32_t* v_packed, int64_t v_head_stride,
+                       const float* v_norms, int64_t vn_head_stride, int n_kv_heads,
+                       int64_t seq_len, const float* centroids_host, const float* signs_host,
+                       int dim, int bits, float threshold, int n_rep, float* out,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- split-K flash decoding over packed KV ----------------------------------
+ * One query token per sequence.  Replaces flash_attention_turboquant
+ * (flash_attention.py:168-274) and the composition turboquant_attention
+ * (fused_attention.py:20-125) = prerotate_query -> prerot_fused_qk_scores ->
+ * scale/mask -> softmax -> sparse_v_matvec, and for dense / affine keys the
+ * composition of hybrid_attention.py:45-88, with a batch dimension, split-K
+ * over the sequence and grouped-query heads sharing one read of K/V. */
+typedef struct tq_flash_params {
+  int32_t struct_bytes;        /* sizeof(tq_flash_params) */
+  int32_t batch, n_q_heads, n_kv_heads, dim;
+  int64_t seq_len;
+
+  const void* q;               /* (batch, n_q_heads, dim) */
+  int32_t q_dtype;
+  int32_t q_prerotated;        /* 1: q already holds raw_butterfly(q * k_signs) */
+  int64_t q_batch_stride, q_head_stride;
+
+  int32_t k_format, k_bits, k_dtype, k_group;   /* k_dtype: dense only; k_group: affine only */
+  const void* k_data;          /* polar: uint32 words; dense: elements; affine: uint8 codes */
+  int64_t k_batch_stride, k_head_stride;        /* in units of k_data's element type */
+  const float* k_norms;        /* polar only */
+  int64_t kn_batch_stride, kn_head_stride;
+  const void* k_scales;        /* affine only: fp16 (.., seq, dim / group) */
+  const void* k_biases;
+  int64_t ks_batch_stride, ks_head_stride;
+  const float* k_centroids_host;
+  const float* k_signs_host;
+
+  int32_t v_format, v_bits, v_group, v_reserved;
+  const void* v_data;
+  int64_t v_batch_stride, v_head_stride;
+  const float* v_norms;
+  int64_t vn_batch_stride, vn_head_stride;
+  const void* v_scales;
+  const void* v_biases;
+  int64_t vs_batch_stride, vs_head_stride;
+  const float* v_centroids_host;
+  const float* v_signs_host;
+
+  float attn_scale;
+  int32_t num_splits;          /* 0 = choose from the SM count */
+  const float* mask;           /* optional additive mask, element [b, h, p] */
+  int64_t mask_batch_stride, mask_head_stride;  /* 0 broadcasts */
+
+  void* workspace;             /* tq_flash_decode_workspace_bytes() */
+  int64_t workspace_bytes;
+
+  int32_t out_mode;            /* 0: final output; 1: merged partials (m, l, S) */
+  int32_t out_dtype;
+  void* out;                   /* mode 0: (batch, n_q_heads, dim) */
+  int64_t out_batch_stride, out_head_stride;
+  float* part_m;               /* mode 1: (batch * n_q_heads) */
+  float* part_l;               /* mode 1: (batch * n_q_heads) */
+  float* part_acc;             /* mode 1: (batch * n_q_heads, dim), before the butterfly */
+  void* stream;
+} tq_flash_params;
+
+int64_t tq_flash_decode_workspace_bytes(const tq_flash_params* p);
+int tq_flash_decode(const tq_flash_params* p);
+
+/* Merge n_parts partial states (split-K chunks or ranks) laid out
+ * (n_parts, n_rows[, dim]) contiguous: m* = max m_i, l* = sum l_i e^(m_i - m*),
+ * acc* likewise; out = post(acc*) / l* with post = signs * bfly(.) / dim when
+ * v_signs_host is given, identity when NULL.  No reference counterpart: the
+ * reference runs on one device without split-K. */
+int tq_merge_partials(const float* part_m, const float* part_l, const float* part_acc,
+                      int n_parts, int64_t n_rows, int dim, const float* v_signs_host,
+                      void* out, int out_dtype, int64_t out_row_stride, void* stream);
+
+/* ---- group-wise affine quantisation (K8 / V4) -------------------------------
+ * Stands in for KVCache.to_quantized(group_size, bits) as used at
+ * hybrid_cache.py:57-63; the arithmetic of the reference lives in the mlx
+ * library and is not available, so the format is this library's own:
+ * scale = fp16((max - min) / (2^bits - 1)), bias = fp16(min) per group,
+ * code = clip(rint((x - bias) / scale), 0, 2^bits - 1); 4-bit codes two per
+ * byte, low nibble first. */
+int tq_affine_quantize(const void* x, int x_dtype, int64_t n_rows, int dim, int group, int bits,
+                       uint8_t* codes, void* scales_f16, void* biases_f16, void* stream);
+int tq_affine_dequantize(const uint8_t* codes, const void* scales_f16, const void* biases_f16,
+                         int64_t n_rows, int dim, int group, int bits, void* out, int out_dtype,
+                         void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TQB200_H */

@@ -1,0 +1,84 @@
+"""Host-side logic that needs no GPU: packing utilities, codebooks, the sign
+generator, the plain KV cache and the mask helpers."""
+
+import numpy as np
+import pytest
+import torch
+
+
+def test_packing_matches_oracle(tq, oracle):
+    rng = np.random.default_rng(0)
+    for bits, dim in ((1, 64), (2, 32), (3, 128), (4, 64), (3, 50)):
+        idx = rng.integers(0, 1 << bits, size=(3, 9, dim)).astype(np.uint8)
+        p = tq.pack_indices(torch.from_numpy(idx), bits)
+        assert p.dtype == torch.uint32
+        assert np.array_equal(p.numpy(), oracle.pack_indices(idx, bits))
+        assert np.array_equal(tq.unpack_indices(p, bits, dim).numpy(), idx)
+        assert tq.packed_dim(dim, bits) == oracle.packed_dim(dim, bits)
+
+
+def test_codebooks_boundaries_and_signs_match_oracle(tq, oracle):
+    from turboquant_mlx_b200 import quantizer, rotation
+    for bits in (1, 2, 3, 4):
+        c = quantizer.codebook_values(bits)
+        assert np.array_equal(np.asarray(c, np.float32), oracle.codebook(bits))
+        assert np.array_equal(np.asarray(quantizer.boundary_values(c), np.float32),
+                              oracle.boundaries(oracle.codebook(bits)))
+    with pytest.raises(ValueError, match="Unsupported bit width"):
+        quantizer.codebook_values(5)
+    for d, seed in ((128, 42), (128, 43), (64, 7)):
+        assert np.array_equal(np.asarray(rotation.sign_values(d, seed), np.float32),
+                              oracle.signs_from_seed(d, seed))
+
+
+def test_plain_kv_cache_and_masks(tq):
+    from turboquant_mlx_b200.base import KVCache, create_causal_mask
+    c = KVCache()
+    assert c.empty() and c.make_mask(1) is None and c.make_mask(5) == "causal"
+    k = torch.randn(1, 2, 5, 8)
+    ko, vo = c.update_and_fetch(k, k * 2)
+    assert ko.shape == (1, 2, 5, 8) and c.offset == 5 and c.keys.shape[2] == 256
+    ko, _ = c.update_and_fetch(k[:, :, :1], k[:, :, :1])
+    assert ko.shape[2] == 6 and torch.equal(ko[:, :, :5], k)
+    assert c.trim(2) == 2 and c.size() == 4
+    m = create_causal_mask(3, offset=2)
+    assert m.shape == (3, 5) and bool(m[0, 2]) and not bool(m[0, 3])
+    m = c.make_mask(3, return_array=True)
+    assert m.shape == (3, 7)
+
+
+def test_mask_broadcast_rules(tq):
+    from turboquant_mlx_b200.fused_attention import _mask_3d
+    B, H, T = 3, 4, 10
+    assert _mask_3d(torch.zeros(B, 1, 1, T), B, H, T).shape == (B, 1, T)
+    assert _mask_3d(torch.zeros(1, H, 1, T), B, H, T).shape == (1, H, T)
+    assert _mask_3d(torch.zeros(1, 1, T), B, H, T).shape == (1, 1, T)
+    assert _mask_3d(torch.zeros(2, 1, 1, T), B, H, T).shape == (B, 1, T)  # index min(b, M-1)
+
+
+def test_patch_swaps_and_restores_symbol(tq):
+    from turboquant_mlx_b200 import base, patch
+    orig = base.scaled_dot_product_attention
+    tq.apply_patch()
+    assert base.scaled_dot_product_attention is patch._patched_sdpa
+    tq.apply_patch()  # idempotent
+    tq.remove_patch()
+    assert base.scaled_dot_product_attention is orig
+    q = torch.randn(1, 4, 1, 8)
+    k = torch.randn(1, 2, 6, 8)
+    out = base.scaled_dot_product_attention(q, k, k, None, 0.3, None)
+    assert out.shape == (1, 4, 1, 8)
+
+
+def test_meta_state_format(tq):
+    c = tq.TurboQuantKVCache(bits=3, seed=42)
+    assert c.meta_state == "0,3,42,0,0,float16"
+    c.meta_state = "12,3,42,128,128,bfloat16"
+    assert c.offset == 12 and c._dtype == torch.bfloat16 and c._k_dim == 128
+    c2 = tq.TurboQuantKVCache(bits=3, k_bits=4, v_bits=3)
+    assert c2.meta_state.endswith(",4,3")
+    v = tq.VOnlyTurboQuantCache(bits=3)
+    assert v.meta_state.startswith("VOnlyTQ,3,")
+    assert v.empty() and v.is_trimmable() and tq.TurboQuantKVCache().empty()
+    with pytest.raises(ValueError, match="Expected 2"):
+        c.state = [torch.zeros(1)] * 3

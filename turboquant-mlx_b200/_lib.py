@@ -1,0 +1,194 @@
+"""ctypes binding of libtqb200.so and the tensor <-> pointer marshalling.
+
+The shared library is the product; this module only loads it, turns
+`torch.Tensor`s (CUDA) into raw pointers, sizes and strides, and maps status
+codes to exceptions.  There is no CPU implementation behind it: a missing
+library or a non-CUDA tensor raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libtqb200.so")
+
+TQ_F32, TQ_F16, TQ_BF16 = 0, 1, 2
+TQ_KV_POLAR, TQ_KV_DENSE, TQ_KV_AFFINE = 0, 1, 2
+_DTYPES = {torch.float32: TQ_F32, torch.float16: TQ_F16, torch.bfloat16: TQ_BF16}
+
+# status codes that mean "the caller passed something invalid" -> ValueError
+_VALUE_ERRORS = {-1, -2, -3, -4, -5, -7, -8}
+
+
+class FlashParams(ctypes.Structure):
+    """Mirror of `tq_flash_params` (include/tqb200.h)."""
+
+    _fields_ = [
+        ("struct_bytes", c_int32),
+        ("batch", c_int32), ("n_q_heads", c_int32), ("n_kv_heads", c_int32), ("dim", c_int32),
+        ("seq_len", c_int64),
+        ("q", c_void_p), ("q_dtype", c_int32), ("q_prerotated", c_int32),
+        ("q_batch_stride", c_int64), ("q_head_stride", c_int64),
+        ("k_format", c_int32), ("k_bits", c_int32), ("k_dtype", c_int32), ("k_group", c_int32),
+        ("k_data", c_void_p), ("k_batch_stride", c_int64), ("k_head_stride", c_int64),
+        ("k_norms", c_void_p), ("kn_batch_stride", c_int64), ("kn_head_stride", c_int64),
+        ("k_scales", c_void_p), ("k_biases", c_void_p),
+        ("ks_batch_stride", c_int64), ("ks_head_stride", c_int64),
+        ("k_centroids_host", POINTER(c_float)), ("k_signs_host", POINTER(c_float)),
+        ("v_format", c_int32), ("v_bits", c_int32), ("v_group", c_int32), ("v_reserved", c_int32),
+        ("v_data", c_void_p), ("v_batch_stride", c_int64), ("v_head_stride", c_int64),
+        ("v_norms", c_void_p), ("vn_batch_stride", c_int64), ("vn_head_stride", c_int64),
+        ("v_scales", c_void_p), ("v_biases", c_void_p),
+        ("vs_batch_stride", c_int64), ("vs_head_stride", c_int64),
+        ("v_centroids_host", POINTER(c_float)), ("v_signs_host", POINTER(c_float)),
+        ("attn_scale", c_float), ("num_splits", c_int32),
+        ("mask", c_void_p), ("mask_batch_stride", c_int64), ("mask_head_stride", c_int64),
+        ("workspace", c_void_p), ("workspace_bytes", c_int64),
+        ("out_mode", c_int32), ("out_dtype", c_int32),
+        ("out", c_void_p), ("out_batch_stride", c_int64), ("out_head_stride", c_int64),
+        ("part_m", c_void_p), ("part_l", c_void_p), ("part_acc", c_void_p),
+        ("stream", c_void_p),
+    ]
+
+
+_lib = None
+
+_FP = POINTER(c_float)
+_SIGNATURES = {
+    "tq_version": (c_int, []),
+    "tq_last_error_string": (c_char_p, []),
+    "tq_quantize": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, _FP, _FP,
+                            c_void_p, c_int64, c_void_p, c_int64, c_void_p]),
+    "tq_dequantize": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int, c_int,
+                              _FP, _FP, c_void_p, c_int, c_int64, c_void_p]),
+    "tq_prerotate_query": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, _FP, c_void_p, c_void_p]),
+    "tq_hadamard": (c_int, [c_void_p, c_int64, c_int, _FP, _FP, c_int, c_void_p, c_void_p]),
+    "tq_prerot_qk_scores": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int64,
+                                    _FP, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "tq_packed_qk_scores": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int64,
+                                    _FP, _FP, c_int, c_int, c_void_p, c_void_p]),
+    "tq_sparse_v_workspace_bytes": (c_size_t, [c_int, c_int64, c_int]),
+    "tq_sparse_v_matvec": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int,
+                                   c_int64, _FP, _FP, c_int, c_int, c_float, c_int, c_void_p,
+                                   c_void_p, c_size_t, c_void_p]),
+    "tq_flash_decode_workspace_bytes": (c_int64, [POINTER(FlashParams)]),
+    "tq_flash_decode": (c_int, [POINTER(FlashParams)]),
+    "tq_merge_partials": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, _FP,
+                                  c_void_p, c_int, c_int64, c_void_p]),
+    "tq_affine_quantize": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p,
+                                   c_void_p, c_void_p, c_void_p]),
+    "tq_affine_dequantize": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,
+                                     c_void_p, c_int, c_void_p]),
+}
+
+
+def lib() -> ctypes.CDLL:
+    """Load libtqb200.so (once).  Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `make -C {_HERE}` "
+                "(nvcc, sm_100a).  There is no fallback implementation.")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def exported_symbols():
+    return sorted(_SIGNATURES)
+
+
+def check(status: int) -> None:
+    if status == 0:
+        return
+    msg = lib().tq_last_error_string().decode("utf-8", "replace")
+    if status in _VALUE_ERRORS:
+        raise ValueError(msg)
+    raise RuntimeError(f"libtqb200 error {status}: {msg}")
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPES[dtype]
+    except KeyError:
+        raise ValueError(f"unsupported dtype {dtype}; use float32, float16 or bfloat16") from None
+
+
+def ptr(t: torch.Tensor | None) -> c_void_p:
+    if t is None:
+        return c_void_p(0)
+    if not t.is_cuda:
+        raise RuntimeError("libtqb200 operates on CUDA tensors only (no CPU path)")
+    return c_void_p(t.data_ptr())
+
+
+def stream_ptr(device=None) -> c_void_p:
+    return c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+# ---------------------------------------------------------------------------
+# codebook-sized parameters: the C ABI takes them as host float arrays
+# ---------------------------------------------------------------------------
+_host_cache: dict = {}
+
+
+def register_host_values(t: torch.Tensor, values) -> None:
+    """Remember the host copy of a small device tensor (signs, centroids,
+    boundaries) so that passing the tensor later costs no device read."""
+    arr = (c_float * len(values))(*[float(v) for v in values])
+    _host_cache[(t.data_ptr(), t._version, t.numel(), str(t.device))] = arr
+    if len(_host_cache) > 4096:
+        for k in list(_host_cache)[:1024]:
+            del _host_cache[k]
+
+
+def host_floats(x):
+    """ctypes float array for a codebook-sized parameter given as a tensor,
+    numpy array or sequence.  A device tensor seen for the first time is read
+    back once (this synchronises) and cached by (address, version)."""
+    if x is None:
+        return None
+    if isinstance(x, torch.Tensor):
+        key = (x.data_ptr(), x._version, x.numel(), str(x.device))
+        arr = _host_cache.get(key)
+        if arr is None:
+            vals = x.detach().to(torch.float32).reshape(-1).cpu().tolist()
+            arr = (c_float * len(vals))(*vals)
+            _host_cache[key] = arr
+        return arr
+    vals = [float(v) for v in x]
+    return (c_float * len(vals))(*vals)
+
+
+# ---------------------------------------------------------------------------
+# scratch memory: allocated by torch (the library never allocates), cached per
+# (device, stream) so stream-ordered reuse is safe
+# ---------------------------------------------------------------------------
+_workspaces: dict = {}
+
+
+def workspace(nbytes: int, device) -> torch.Tensor | None:
+    if nbytes <= 0:
+        return None
+    key = (str(device), torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def require_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("libtqb200 operates on CUDA tensors only (no CPU path)")

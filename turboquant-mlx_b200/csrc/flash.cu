@@ -1,0 +1,201 @@
+// tq_flash_decode: argument validation, split-K planning, kernel choice, merge.
+#include <math.h>
+#include <string.h>
+
+#include "common.cuh"
+#include "flash.cuh"
+
+namespace tq {
+
+struct Plan {
+  int splits;
+  int64_t chunk;
+  bool mma;
+};
+
+static int validate(const tq_flash_params* p) {
+  TQ_REQUIRE(p != nullptr, TQ_ERR_BAD_ARG, "params pointer is NULL");
+  TQ_REQUIRE(p->struct_bytes == (int32_t)sizeof(tq_flash_params), TQ_ERR_BAD_ARG,
+             "struct_bytes %d does not match this library (%zu)", p->struct_bytes,
+             sizeof(tq_flash_params));
+  TQ_REQUIRE(p->dim >= 32 && p->dim <= 256 && !(p->dim & (p->dim - 1)), TQ_ERR_BAD_DIM,
+             "dim must be a power of 2 in [32, 256], got %d", p->dim);
+  TQ_REQUIRE(p->batch > 0 && p->n_q_heads > 0 && p->n_kv_heads > 0, TQ_ERR_BAD_ARG,
+             "batch and head counts must be positive");
+  TQ_REQUIRE(p->n_q_heads % p->n_kv_heads == 0, TQ_ERR_HEAD_MISMATCH,
+             "n_q_heads (%d) must equal n_kv_heads (%d) * n_rep", p->n_q_heads, p->n_kv_heads);
+  TQ_REQUIRE(p->seq_len > 0, TQ_ERR_BAD_ARG, "seq_len must be positive, got %lld",
+             (long long)p->seq_len);
+  TQ_REQUIRE(p->q_dtype >= TQ_F32 && p->q_dtype <= TQ_BF16, TQ_ERR_BAD_ARG, "bad q_dtype");
+  switch (p->k_format) {
+    case TQ_KV_POLAR:
+      TQ_REQUIRE(p->k_bits >= 1 && p->k_bits <= 4, TQ_ERR_BAD_BITS,
+                 "Unsupported bit width: %d. Use 1-4.", p->k_bits);
+      TQ_REQUIRE(p->k_norms && p->k_centroids_host, TQ_ERR_BAD_ARG, "polar K needs norms and centroids");
+      TQ_REQUIRE(p->q_prerotated || p->k_signs_host, TQ_ERR_BAD_ARG, "polar K needs k_signs unless q is pre-rotated");
+      break;
+    case TQ_KV_DENSE:
+      TQ_REQUIRE(p->k_dtype >= TQ_F32 && p->k_dtype <= TQ_BF16, TQ_ERR_BAD_ARG, "bad k_dtype");
+      break;
+    case TQ_KV_AFFINE:
+      TQ_REQUIRE(p->k_bits == 8, TQ_ERR_BAD_BITS, "affine K supports 8-bit codes, got %d", p->k_bits);
+      TQ_REQUIRE(p->k_group > 0 && p->dim % p->k_group == 0, TQ_ERR_BAD_ARG, "bad k_group %d", p->k_group);
+      TQ_REQUIRE(p->k_scales && p->k_biases, TQ_ERR_BAD_ARG, "affine K needs scales and biases");
+      break;
+    default: return set_error(TQ_ERR_BAD_ARG, "unknown k_format %d", p->k_format);
+  }
+  switch (p->v_format) {
+    case TQ_KV_POLAR:
+      TQ_REQUIRE(p->v_bits >= 1 && p->v_bits <= 4, TQ_ERR_BAD_BITS,
+                 "Unsupported bit width: %d. Use 1-4.", p->v_bits);
+      TQ_REQUIRE(p->v_norms && p->v_centroids_host && p->v_signs_host, TQ_ERR_BAD_ARG,
+                 "polar V needs norms, centroids and signs");
+      break;
+    case TQ_KV_AFFINE:
+      TQ_REQUIRE(p->v_bits == 4 || p->v_bits == 8, TQ_ERR_BAD_BITS,
+                 "affine V supports 4- or 8-bit codes, got %d", p->v_bits);
+      TQ_REQUIRE(p->v_group > 0 && p->dim % p->v_group == 0, TQ_ERR_BAD_ARG, "bad v_group %d", p->v_group);
+      TQ_REQUIRE(p->v_scales && p->v_biases, TQ_ERR_BAD_ARG, "affine V needs scales and biases");
+      break;
+    default: return set_error(TQ_ERR_BAD_ARG, "unknown v_format %d", p->v_format);
+  }
+  TQ_REQUIRE(p->q && p->k_data && p->v_data, TQ_ERR_BAD_ARG, "NULL tensor pointer");
+  TQ_REQUIRE(p->out_mode == 0 || p->out_mode == 1, TQ_ERR_BAD_ARG, "bad out_mode %d", p->out_mode);
+  if (p->out_mode == 0)
+    TQ_REQUIRE(p->out && p->out_dtype >= TQ_F32 && p->out_dtype <= TQ_BF16, TQ_ERR_BAD_ARG,
+               "mode 0 needs out and a valid out_dtype");
+  else
+    TQ_REQUIRE(p->part_m && p->part_l && p->part_acc, TQ_ERR_BAD_ARG,
+               "mode 1 needs part_m, part_l and part_acc");
+  return TQ_OK;
+}
+
+static int fill_args(const tq_flash_params* p, FlashArgs* a) {
+  memset(a, 0, sizeof(*a));
+  a->batch = p->batch;
+  a->n_q_heads = p->n_q_heads;
+  a->n_kv_heads = p->n_kv_heads;
+  a->n_rep = p->n_q_heads / p->n_kv_heads;
+  a->dim = p->dim;
+  a->seq_len = p->seq_len;
+  a->q = p->q;
+  a->q_dtype = p->q_dtype;
+  a->q_prerotated = p->q_prerotated;
+  a->q_batch_stride = p->q_batch_stride;
+  a->q_head_stride = p->q_head_stride;
+  a->k_format = p->k_format;
+  a->k_bits = p->k_format == TQ_KV_POLAR ? p->k_bits : 4;
+  a->k_dtype = p->k_dtype;
+  a->k_group = p->k_group > 0 ? p->k_group : p->dim;
+  a->k_data = p->k_data;
+  a->k_batch_stride = p->k_batch_stride;
+  a->k_head_stride = p->k_head_stride;
+  a->k_norms = p->k_norms;
+  a->kn_batch_stride = p->kn_batch_stride;
+  a->kn_head_stride = p->kn_head_stride;
+  a->k_scales = p->k_scales;
+  a->k_biases = p->k_biases;
+  a->ks_batch_stride = p->ks_batch_stride;
+  a->ks_head_stride = p->ks_head_stride;
+  a->v_format = p->v_format;
+  a->v_bits = p->v_bits;
+  a->v_group = p->v_group > 0 ? p->v_group : p->dim;
+  a->v_data = p->v_data;
+  a->v_batch_stride = p->v_batch_stride;
+  a->v_head_stride = p->v_head_stride;
+  a->v_norms = p->v_norms;
+  a->vn_batch_stride = p->vn_batch_stride;
+  a->vn_head_stride = p->vn_head_stride;
+  a->v_scales = p->v_scales;
+  a->v_biases = p->v_biases;
+  a->vs_batch_stride = p->vs_batch_stride;
+  a->vs_head_stride = p->vs_head_stride;
+  a->attn_scale = p->attn_scale;
+  a->mask = p->mask;
+  a->mask_batch_stride = p->mask_batch_stride;
+  a->mask_head_stride = p->mask_head_stride;
+  int rc;
+  if (p->k_format == TQ_KV_POLAR) {
+    for (int i = 0; i < (1 << p->k_bits); ++i) a->k_cent.v[i] = p->k_centroids_host[i];
+    if (!p->q_prerotated && (rc = make_sign_mask(p->k_signs_host, p->dim, &a->k_signs))) return rc;
+  }
+  if (p->v_format == TQ_KV_POLAR) {
+    for (int i = 0; i < (1 << p->v_bits); ++i) a->v_cent.v[i] = p->v_centroids_host[i];
+    if ((rc = make_sign_mask(p->v_signs_host, p->dim, &a->v_signs))) return rc;
+  }
+  return TQ_OK;
+}
+
+static void make_plan(const tq_flash_params* p, const FlashArgs& a, Plan* plan) {
+  plan->mma = flash_mma_supported(a);
+  const int mult = plan->mma ? flash_mma_chunk_multiple() : 32;
+  const int rgroups = plan->mma ? 1 : (a.n_rep + 7) / 8;
+  const int64_t groups = (int64_t)a.batch * a.n_kv_heads * rgroups;
+  const int64_t max_splits = (a.seq_len + mult - 1) / mult;
+  int64_t splits = p->num_splits;
+  if (splits <= 0) {
+    const int64_t target = 2LL * num_sms();
+    splits = (target + groups - 1) / groups;
+    const int64_t by_len = (a.seq_len + 127) / 128;   // at least 128 positions per split
+    if (splits > by_len) splits = by_len;
+  }
+  if (splits > max_splits) splits = max_splits;
+  if (splits < 1) splits = 1;
+  int64_t chunk = (a.seq_len + splits - 1) / splits;
+  chunk = (chunk + mult - 1) / mult * mult;
+  plan->chunk = chunk;
+  plan->splits = (int)((a.seq_len + chunk - 1) / chunk);
+}
+
+static int64_t workspace_need(const tq_flash_params* p, const Plan& plan) {
+  if (p->out_mode == 1 && plan.splits == 1) return 0;
+  const int64_t rows = (int64_t)p->batch * p->n_q_heads;
+  return (int64_t)plan.splits * rows * (p->dim + 2) * (int64_t)sizeof(float);
+}
+
+}  // namespace tq
+
+using namespace tq;
+
+extern "C" int64_t tq_flash_decode_workspace_bytes(const tq_flash_params* p) {
+  int rc = validate(p);
+  if (rc) return rc;
+  FlashArgs a;
+  if ((rc = fill_args(p, &a))) return rc;
+  Plan plan;
+  make_plan(p, a, &plan);
+  return workspace_need(p, plan);
+}
+
+extern "C" int tq_flash_decode(const tq_flash_params* p) {
+  int rc = validate(p);
+  if (rc) return rc;
+  FlashArgs a;
+  if ((rc = fill_args(p, &a))) return rc;
+  Plan plan;
+  make_plan(p, a, &plan);
+  a.chunk = plan.chunk;
+  const int64_t need = workspace_need(p, plan);
+  TQ_REQUIRE(need == 0 || (p->workspace && p->workspace_bytes >= need), TQ_ERR_WORKSPACE,
+             "workspace of %lld bytes required, got %lld", (long long)need,
+             (long long)p->workspace_bytes);
+  const int64_t rows = (int64_t)p->batch * p->n_q_heads;
+  if (need == 0) {
+    a.part_m = p->part_m;
+    a.part_l = p->part_l;
+    a.part_acc = p->part_acc;
+  } else {
+    float* ws = (float*)p->workspace;
+    a.part_m = ws;
+    a.part_l = ws + (int64_t)plan.splits * rows;
+    a.part_acc = ws + 2 * (int64_t)plan.splits * rows;
+  }
+  cudaStream_t st = (cudaStream_t)p->stream;
+  rc = plan.mma ? launch_flash_mma(a, plan.splits, st) : launch_flash_generic(a, plan.splits, st);
+  if (rc) return rc;
+  if (need == 0) return TQ_OK;
+  const int rotate = p->v_format == TQ_KV_POLAR;
+  return launch_merge(a.part_m, a.part_l, a.part_acc, plan.splits, rows, p->dim, rotate, a.v_signs,
+                      p->out_mode == 0, p->out, p->out_dtype, p->out_head_stride, p->n_q_heads,
+                      p->out_batch_stride, p->part_m, p->part_l, p->part_acc, st);
+}

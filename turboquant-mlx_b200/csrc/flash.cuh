@@ -1,0 +1,62 @@
+// Internal argument block shared by the flash-decode kernels and their launcher.
+#pragma once
+
+#include "common.cuh"
+
+namespace tq {
+
+struct FlashArgs {
+  int batch, n_q_heads, n_kv_heads, n_rep, dim;
+  int64_t seq_len, chunk;          // chunk = positions per split
+
+  const void* q;
+  int q_dtype, q_prerotated;
+  int64_t q_batch_stride, q_head_stride;
+
+  int k_format, k_bits, k_dtype, k_group;
+  const void* k_data;
+  int64_t k_batch_stride, k_head_stride;
+  const float* k_norms;
+  int64_t kn_batch_stride, kn_head_stride;
+  const void* k_scales;
+  const void* k_biases;
+  int64_t ks_batch_stride, ks_head_stride;
+  Table16 k_cent;
+  SignMask k_signs;
+
+  int v_format, v_bits, v_group;
+  const void* v_data;
+  int64_t v_batch_stride, v_head_stride;
+  const float* v_norms;
+  int64_t vn_batch_stride, vn_head_stride;
+  const void* v_scales;
+  const void* v_biases;
+  int64_t vs_batch_stride, vs_head_stride;
+  Table16 v_cent;
+  SignMask v_signs;
+
+  float attn_scale;
+  const float* mask;
+  int64_t mask_batch_stride, mask_head_stride;
+
+  // per-split partial state, laid out (splits, batch * n_q_heads[, dim])
+  float* part_m;
+  float* part_l;
+  float* part_acc;
+};
+
+int launch_flash_generic(const FlashArgs& a, int splits, cudaStream_t st);
+
+// Tensor-core path (dim 128, polar or dense keys, polar values, no mask).
+// Returns TQ_ERR_UNSUPPORTED without launching when the arguments do not
+// qualify; the caller then takes the generic kernel.
+bool flash_mma_supported(const FlashArgs& a);
+int flash_mma_chunk_multiple();
+int launch_flash_mma(const FlashArgs& a, int splits, cudaStream_t st);
+
+int launch_merge(const float* pm, const float* pl, const float* pacc, int n_parts, int64_t n_rows,
+                 int dim, int rotate, const SignMask& signs, int finalize, void* out, int out_dtype,
+                 int64_t out_row_stride, int64_t rows_per_batch, int64_t out_batch_stride,
+                 float* om, float* ol, float* oacc, cudaStream_t st);
+
+}  // namespace tq

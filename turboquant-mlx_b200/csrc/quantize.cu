@@ -1,0 +1,362 @@
+// PolarQuant encode / decode kernels and the Hadamard rotation helpers.
+//
+// Generic layout: one warp per vector, lane l holds elements [EPL*l, EPL*l+EPL)
+// with EPL = dim / 32, so the butterfly runs log2(EPL) stages in registers and
+// five stages through warp shuffles.  All float32 steps that feed the index
+// compare use explicit round-to-nearest intrinsics (no FMA contraction) so the
+// packed words are bit-identical to a sequential float32 evaluation.
+#include "common.cuh"
+
+namespace tq {
+
+constexpr int kWarpsPerBlock = 8;
+
+struct QuantArgs {
+  const void* x;
+  int64_t n_vecs, n_inner, x_outer_stride;
+  uint32_t* packed;
+  int64_t packed_outer_stride;
+  float* norms;
+  int64_t norms_outer_stride;
+  SignMask signs;
+  Table16 thr;   // thresholds on the raw butterfly output
+  int n_thr;
+};
+
+template <typename T, int EPL, int BITS>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+quantize_warp_kernel(const QuantArgs a) {
+  constexpr int DIM = EPL * 32;
+  constexpr int VPW = vals_per_word(BITS);
+  constexpr int PDIM = packed_words(DIM, BITS);
+  __shared__ uint8_t idx_s[kWarpsPerBlock][DIM];
+
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int64_t warp_global = (int64_t)blockIdx.x * kWarpsPerBlock + warp;
+  const int64_t warp_stride = (int64_t)gridDim.x * kWarpsPerBlock;
+
+  uint32_t sbit[EPL];
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) sbit[j] = sign_bit_at(a.signs, lane * EPL + j);
+
+  for (int64_t v = warp_global; v < a.n_vecs; v += warp_stride) {
+    const int64_t o = v / a.n_inner, i = v - o * a.n_inner;
+    const T* row = reinterpret_cast<const T*>(a.x) + o * a.x_outer_stride + i * DIM + lane * EPL;
+    float x[EPL];
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) x[j] = to_f32<T>(row[j]);
+
+    // L2 norm: float32 squares, pairwise tree in natural index order.
+    float sq[EPL];
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) sq[j] = __fmul_rn(x[j], x[j]);
+#pragma unroll
+    for (int h = 1; h < EPL; h <<= 1) {
+#pragma unroll
+      for (int j = 0; j < EPL; j += 2 * h) sq[j] = __fadd_rn(sq[j], sq[j + h]);
+    }
+    float ss = sq[0];
+#pragma unroll
+    for (int k = 1; k < 32; k <<= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, k));
+    const float nrm = __fsqrt_rn(ss);
+    const float safe = fmaxf(nrm, 1e-8f);
+
+    float t[EPL];
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      float u = __fdiv_rn(x[j], safe);
+      t[j] = __uint_as_float(__float_as_uint(u) ^ sbit[j]);   // u * (+/-1), exact
+    }
+    warp_butterfly<EPL>(t, lane);
+
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      int idx = 0;
+#pragma unroll
+      for (int b = 0; b < (1 << BITS) - 1; ++b) idx += (t[j] > a.thr.v[b]) ? 1 : 0;
+      idx_s[warp][lane * EPL + j] = (uint8_t)idx;
+    }
+    __syncwarp();
+    uint32_t* prow = a.packed + o * a.packed_outer_stride + i * PDIM;
+    for (int w = lane; w < PDIM; w += 32) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int k = 0; k < VPW; ++k) {
+        const int e = w * VPW + k;
+        if (e < DIM) word |= (uint32_t)idx_s[warp][e] << (k * BITS);
+      }
+      prow[w] = word;
+    }
+    if (lane == 0) a.norms[o * a.norms_outer_stride + i] = nrm;
+    __syncwarp();
+  }
+}
+
+struct DequantArgs {
+  const uint32_t* packed;
+  int64_t packed_outer_stride;
+  const float* norms;
+  int64_t norms_outer_stride;
+  int64_t n_vecs, n_inner;
+  void* out;
+  int64_t out_outer_stride;
+  SignMask signs;
+  Table16 cs;    // centroid * s
+  float s;
+};
+
+template <typename T, int EPL, int BITS>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+dequantize_warp_kernel(const DequantArgs a) {
+  constexpr int DIM = EPL * 32;
+  constexpr int VPW = vals_per_word(BITS);
+  constexpr int PDIM = packed_words(DIM, BITS);
+  __shared__ float cs_s[16];
+  if (threadIdx.x < 16) cs_s[threadIdx.x] = a.cs.v[threadIdx.x];
+  __syncthreads();
+
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int64_t warp_global = (int64_t)blockIdx.x * kWarpsPerBlock + warp;
+  const int64_t warp_stride = (int64_t)gridDim.x * kWarpsPerBlock;
+
+  float sgn[EPL];
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) sgn[j] = sign_at(a.signs, lane * EPL + j);
+
+  for (int64_t v = warp_global; v < a.n_vecs; v += warp_stride) {
+    const int64_t o = v / a.n_inner, i = v - o * a.n_inner;
+    const uint32_t* prow = a.packed + o * a.packed_outer_stride + i * PDIM;
+    const float nrm = a.norms[o * a.norms_outer_stride + i];
+    float y[EPL];
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      const int e = lane * EPL + j;
+      const uint32_t word = __ldg(prow + e / VPW);
+      y[j] = cs_s[(word >> ((e % VPW) * BITS)) & ((1u << BITS) - 1u)];
+    }
+    warp_butterfly<EPL>(y, lane);
+    T* orow = reinterpret_cast<T*>(a.out) + o * a.out_outer_stride + i * DIM + lane * EPL;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      // ((bfly * s) * signs) * norm, left to right as the reference writes it
+      float r = __fmul_rn(__fmul_rn(__fmul_rn(y[j], a.s), sgn[j]), nrm);
+      orow[j] = from_f32<T>(r);
+    }
+  }
+}
+
+struct HadamardArgs {
+  const void* x;
+  int64_t n_rows, in_row_stride;
+  float* out;
+  SignMask pre, post;
+  int use_pre, use_post, normalize;
+  float s;
+};
+
+template <typename T, int EPL>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+hadamard_warp_kernel(const HadamardArgs a) {
+  constexpr int DIM = EPL * 32;
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int64_t warp_global = (int64_t)blockIdx.x * kWarpsPerBlock + warp;
+  const int64_t warp_stride = (int64_t)gridDim.x * kWarpsPerBlock;
+  for (int64_t v = warp_global; v < a.n_rows; v += warp_stride) {
+    const T* row = reinterpret_cast<const T*>(a.x) + v * a.in_row_stride + lane * EPL;
+    float t[EPL];
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      float x = to_f32<T>(row[j]);
+      t[j] = a.use_pre ? __fmul_rn(x, sign_at(a.pre, lane * EPL + j)) : x;
+    }
+    warp_butterfly<EPL>(t, lane);
+    float* orow = a.out + v * DIM + lane * EPL;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      float r = a.normalize ? __fmul_rn(t[j], a.s) : t[j];
+      if (a.use_post) r = __fmul_rn(r, sign_at(a.post, lane * EPL + j));
+      orow[j] = r;
+    }
+  }
+}
+
+static int grid_for(int64_t n_vecs) {
+  int64_t blocks = (n_vecs + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  int64_t cap = (int64_t)num_sms() * 8;
+  return (int)(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
+}
+
+template <typename T, int EPL>
+static int launch_quantize_bits(const QuantArgs& a, int bits, cudaStream_t st) {
+  const int grid = grid_for(a.n_vecs);
+  const int block = kWarpsPerBlock * 32;
+  switch (bits) {
+    case 1: quantize_warp_kernel<T, EPL, 1><<<grid, block, 0, st>>>(a); break;
+    case 2: quantize_warp_kernel<T, EPL, 2><<<grid, block, 0, st>>>(a); break;
+    case 3: quantize_warp_kernel<T, EPL, 3><<<grid, block, 0, st>>>(a); break;
+    default: quantize_warp_kernel<T, EPL, 4><<<grid, block, 0, st>>>(a); break;
+  }
+  return check_launch("tq_quantize");
+}
+template <typename T>
+static int launch_quantize(const QuantArgs& a, int dim, int bits, cudaStream_t st) {
+  switch (dim) {
+    case 32: return launch_quantize_bits<T, 1>(a, bits, st);
+    case 64: return launch_quantize_bits<T, 2>(a, bits, st);
+    case 128: return launch_quantize_bits<T, 4>(a, bits, st);
+    default: return launch_quantize_bits<T, 8>(a, bits, st);
+  }
+}
+
+template <typename T, int EPL>
+static int launch_dequantize_bits(const DequantArgs& a, int bits, cudaStream_t st) {
+  const int grid = grid_for(a.n_vecs);
+  const int block = kWarpsPerBlock * 32;
+  switch (bits) {
+    case 1: dequantize_warp_kernel<T, EPL, 1><<<grid, block, 0, st>>>(a); break;
+    case 2: dequantize_warp_kernel<T, EPL, 2><<<grid, block, 0, st>>>(a); break;
+    case 3: dequantize_warp_kernel<T, EPL, 3><<<grid, block, 0, st>>>(a); break;
+    default: dequantize_warp_kernel<T, EPL, 4><<<grid, block, 0, st>>>(a); break;
+  }
+  return check_launch("tq_dequantize");
+}
+template <typename T>
+static int launch_dequantize(const DequantArgs& a, int dim, int bits, cudaStream_t st) {
+  switch (dim) {
+    case 32: return launch_dequantize_bits<T, 1>(a, bits, st);
+    case 64: return launch_dequantize_bits<T, 2>(a, bits, st);
+    case 128: return launch_dequantize_bits<T, 4>(a, bits, st);
+    default: return launch_dequantize_bits<T, 8>(a, bits, st);
+  }
+}
+
+template <typename T>
+static int launch_hadamard(const HadamardArgs& a, int dim, cudaStream_t st) {
+  const int grid = grid_for(a.n_rows);
+  const int block = kWarpsPerBlock * 32;
+  switch (dim) {
+    case 32: hadamard_warp_kernel<T, 1><<<grid, block, 0, st>>>(a); break;
+    case 64: hadamard_warp_kernel<T, 2><<<grid, block, 0, st>>>(a); break;
+    case 128: hadamard_warp_kernel<T, 4><<<grid, block, 0, st>>>(a); break;
+    default: hadamard_warp_kernel<T, 8><<<grid, block, 0, st>>>(a); break;
+  }
+  return check_launch("tq_hadamard");
+}
+
+}  // namespace tq
+
+using namespace tq;
+
+extern "C" int tq_quantize(const void* x, int x_dtype, int64_t n_outer, int64_t n_inner,
+                           int64_t x_outer_stride, int dim, int bits, const float* signs_host,
+                           const float* boundaries_host, uint32_t* packed,
+                           int64_t packed_outer_stride, float* norms, int64_t norms_outer_stride,
+                           void* stream) {
+  int rc = check_dim_bits(dim, bits, 256);
+  if (rc) return rc;
+  TQ_REQUIRE(n_outer >= 0 && n_inner >= 0, TQ_ERR_BAD_ARG, "negative vector count");
+  TQ_REQUIRE(boundaries_host != nullptr, TQ_ERR_BAD_ARG, "boundaries pointer is NULL");
+  if (n_outer * n_inner == 0) return TQ_OK;
+  TQ_REQUIRE(x && packed && norms, TQ_ERR_BAD_ARG, "NULL tensor pointer");
+  QuantArgs a;
+  a.x = x;
+  a.n_vecs = n_outer * n_inner;
+  a.n_inner = n_inner;
+  a.x_outer_stride = x_outer_stride;
+  a.packed = packed;
+  a.packed_outer_stride = packed_outer_stride;
+  a.norms = norms;
+  a.norms_outer_stride = norms_outer_stride;
+  rc = make_sign_mask(signs_host, dim, &a.signs);
+  if (rc) return rc;
+  a.n_thr = (1 << bits) - 1;
+  make_raw_thresholds(boundaries_host, a.n_thr, dim, &a.thr);
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (x_dtype) {
+    case TQ_F32: return launch_quantize<float>(a, dim, bits, st);
+    case TQ_F16: return launch_quantize<__half>(a, dim, bits, st);
+    case TQ_BF16: return launch_quantize<__nv_bfloat16>(a, dim, bits, st);
+    default: return set_error(TQ_ERR_BAD_ARG, "unknown dtype %d", x_dtype);
+  }
+}
+
+extern "C" int tq_dequantize(const uint32_t* packed, int64_t packed_outer_stride,
+                             const float* norms, int64_t norms_outer_stride, int64_t n_outer,
+                             int64_t n_inner, int dim, int bits, const float* centroids_host,
+                             const float* signs_host, void* out, int out_dtype,
+                             int64_t out_outer_stride, void* stream) {
+  int rc = check_dim_bits(dim, bits, 256);
+  if (rc) return rc;
+  TQ_REQUIRE(n_outer >= 0 && n_inner >= 0, TQ_ERR_BAD_ARG, "negative vector count");
+  TQ_REQUIRE(centroids_host != nullptr, TQ_ERR_BAD_ARG, "centroids pointer is NULL");
+  if (n_outer * n_inner == 0) return TQ_OK;
+  TQ_REQUIRE(packed && norms && out, TQ_ERR_BAD_ARG, "NULL tensor pointer");
+  DequantArgs a;
+  a.packed = packed;
+  a.packed_outer_stride = packed_outer_stride;
+  a.norms = norms;
+  a.norms_outer_stride = norms_outer_stride;
+  a.n_vecs = n_outer * n_inner;
+  a.n_inner = n_inner;
+  a.out = out;
+  a.out_outer_stride = out_outer_stride;
+  rc = make_sign_mask(signs_host, dim, &a.signs);
+  if (rc) return rc;
+  a.s = (float)(1.0 / sqrt((double)dim));
+  for (int i = 0; i < 16; ++i) {
+    volatile float cs = (i < (1 << bits)) ? centroids_host[i] * a.s : 0.0f;
+    a.cs.v[i] = cs;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (out_dtype) {
+    case TQ_F32: return launch_dequantize<float>(a, dim, bits, st);
+    case TQ_F16: return launch_dequantize<__half>(a, dim, bits, st);
+    case TQ_BF16: return launch_dequantize<__nv_bfloat16>(a, dim, bits, st);
+    default: return set_error(TQ_ERR_BAD_ARG, "unknown dtype %d", out_dtype);
+  }
+}
+
+static int hadamard_common(const void* x, int dtype, int64_t n_rows, int64_t in_stride, int dim,
+                           const float* pre, const float* post, int normalize, float* out,
+                           void* stream, const char* who) {
+  int rc = check_dim_bits(dim, 3, 256);
+  if (rc) return rc;
+  if (n_rows <= 0) return TQ_OK;
+  TQ_REQUIRE(x && out, TQ_ERR_BAD_ARG, "%s: NULL tensor pointer", who);
+  HadamardArgs a;
+  a.x = x;
+  a.n_rows = n_rows;
+  a.in_row_stride = in_stride;
+  a.out = out;
+  a.use_pre = pre != nullptr;
+  a.use_post = post != nullptr;
+  a.normalize = normalize;
+  a.s = (float)(1.0 / sqrt((double)dim));
+  if (pre && (rc = make_sign_mask(pre, dim, &a.pre))) return rc;
+  if (post && (rc = make_sign_mask(post, dim, &a.post))) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (dtype) {
+    case TQ_F32: return launch_hadamard<float>(a, dim, st);
+    case TQ_F16: return launch_hadamard<__half>(a, dim, st);
+    case TQ_BF16: return launch_hadamard<__nv_bfloat16>(a, dim, st);
+    default: return set_error(TQ_ERR_BAD_ARG, "unknown dtype %d", dtype);
+  }
+}
+
+extern "C" int tq_prerotate_query(const void* q, int q_dtype, int64_t n_heads,
+                                  int64_t q_head_stride, int dim, const float* signs_host,
+                                  float* out, void* stream) {
+  TQ_REQUIRE(signs_host != nullptr, TQ_ERR_BAD_ARG, "signs pointer is NULL");
+  return hadamard_common(q, q_dtype, n_heads, q_head_stride, dim, signs_host, nullptr, 0, out,
+                         stream, "tq_prerotate_query");
+}
+
+extern "C" int tq_hadamard(const float* x, int64_t n_rows, int dim, const float* pre_signs_host,
+                           const float* post_signs_host, int normalize, float* out,
+                           void* stream) {
+  return hadamard_common(x, TQ_F32, n_rows, dim, dim, pre_signs_host, post_signs_host, normalize,
+                         out, stream, "tq_hadamard");
+}

@@ -1,0 +1,396 @@
+"""Kernel-level API with the reference's names and argument meaning, on CUDA
+`torch.Tensor`s.  Each function marshals pointers, sizes and strides into the
+C ABI of libtqb200.so and raises the reference's `ValueError`s.
+
+Reference entry points mirrored here (paths inside the reference project):
+  fused_quantize, dequant_fp16           turboquant_mlx/metal.py:147-232
+  packed_dequantize, packed_fused_qk_scores   turboquant_mlx/kernels.py:123-196
+  prerotate_query, prerot_fused_qk_scores     turboquant_mlx/metal_kernels_v4.py:119-221
+  sparse_v_matvec, count_active_positions     turboquant_mlx/sparse_v.py:94-191
+  flash_attention_turboquant                  turboquant_mlx/flash_attention.py:168-274
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from .packing import VALS_PER_WORD, packed_dim
+
+__all__ = [
+    "fused_quantize", "dequant_fp16", "packed_dequantize", "packed_fused_qk_scores",
+    "prerotate_query", "prerot_fused_qk_scores", "prerot_packed_dequantize",
+    "sparse_v_matvec", "count_active_positions", "flash_attention_turboquant",
+    "flash_decode", "merge_partials",
+]
+
+
+def _check_bits(bits: int) -> None:
+    if bits not in VALS_PER_WORD:
+        raise ValueError(f"Unsupported bit width: {bits}. Use 1-4.")
+
+
+# ---------------------------------------------------------------------------
+# quantize / dequantize
+# ---------------------------------------------------------------------------
+def quantize_into(x: torch.Tensor, signs, boundaries, dim: int, bits: int,
+                  packed_out: torch.Tensor, norms_out: torch.Tensor, row_offset: int = 0) -> None:
+    """Quantize x (n_outer, n_inner, dim) straight into rows
+    [row_offset, row_offset + n_inner) of packed_out (n_outer, n_alloc, pdim) /
+    norms_out (n_outer, n_alloc): the append a cache insert needs, with no
+    temporary and no copy."""
+    _check_bits(bits)
+    _lib.require_cuda(x, packed_out, norms_out)
+    n_outer, n_inner, d = x.shape
+    assert d == dim and x.is_contiguous()
+    assert packed_out.stride(-1) == 1 and packed_out.stride(-2) == packed_out.shape[-1]
+    pd = packed_out.shape[-1]
+    p_ptr = ctypes.c_void_p(packed_out.data_ptr() + row_offset * pd * 4)
+    n_ptr = ctypes.c_void_p(norms_out.data_ptr() + row_offset * 4)
+    _lib.check(_lib.lib().tq_quantize(
+        _lib.ptr(x), _lib.dtype_code(x.dtype), n_outer, n_inner, n_inner * dim, dim, bits,
+        _lib.host_floats(signs), _lib.host_floats(boundaries),
+        p_ptr, packed_out.stride(0), n_ptr, norms_out.stride(0), _lib.stream_ptr(x.device)))
+
+
+def fused_quantize(vectors: torch.Tensor, signs, boundaries, dim: int, bits: int):
+    """Raw vectors (n_vecs, dim) fp16/bf16/fp32 -> (packed (n_vecs, packed_dim)
+    uint32, norms (n_vecs,) float32) in one kernel."""
+    _check_bits(bits)
+    _lib.require_cuda(vectors)
+    n_vecs = vectors.shape[0]
+    x = vectors.reshape(n_vecs, dim).contiguous()
+    packed = torch.empty((1, n_vecs, packed_dim(dim, bits)), dtype=torch.uint32, device=x.device)
+    norms = torch.empty((1, n_vecs), dtype=torch.float32, device=x.device)
+    quantize_into(x.unsqueeze(0), signs, boundaries, dim, bits, packed, norms)
+    return packed[0], norms[0]
+
+
+def dequantize_into(packed: torch.Tensor, norms: torch.Tensor, centroids, signs, dim: int,
+                    bits: int, out: torch.Tensor, n_inner: int, src_row: int = 0,
+                    dst_row: int = 0) -> None:
+    """Dequantize rows [src_row, src_row + n_inner) of packed (n_outer, n_alloc,
+    pdim) into rows [dst_row, ...) of out (n_outer, n_alloc_out, dim)."""
+    _check_bits(bits)
+    _lib.require_cuda(packed, norms, out)
+    n_outer = packed.shape[0]
+    pd = packed.shape[-1]
+    p_ptr = ctypes.c_void_p(packed.data_ptr() + src_row * pd * 4)
+    n_ptr = ctypes.c_void_p(norms.data_ptr() + src_row * 4)
+    o_ptr = ctypes.c_void_p(out.data_ptr() + dst_row * dim * out.element_size())
+    _lib.check(_lib.lib().tq_dequantize(
+        p_ptr, packed.stride(0), n_ptr, norms.stride(0), n_outer, n_inner, dim, bits,
+        _lib.host_floats(centroids), _lib.host_floats(signs), o_ptr, _lib.dtype_code(out.dtype),
+        out.stride(0), _lib.stream_ptr(out.device)))
+
+
+def _dequant(packed, norms, centroids, signs, dim, bits, dtype):
+    n = norms.shape[0]
+    packed = packed.reshape(n, -1).contiguous()
+    norms = norms.reshape(n).to(torch.float32).contiguous()
+    out = torch.empty((1, n, dim), dtype=dtype, device=packed.device)
+    dequantize_into(packed.unsqueeze(0), norms.unsqueeze(0), centroids, signs, dim, bits, out, n)
+    return out[0]
+
+
+def dequant_fp16(packed, norms, centroids, signs, dim: int, bits: int) -> torch.Tensor:
+    """Packed rows -> (n, dim) float16."""
+    return _dequant(packed, norms, centroids, signs, dim, bits, torch.float16)
+
+
+def packed_dequantize(packed, norms, centroids, signs, dim: int, bits: int) -> torch.Tensor:
+    """Packed rows -> (n, dim) float32."""
+    return _dequant(packed, norms, centroids, signs, dim, bits, torch.float32)
+
+
+prerot_packed_dequantize = packed_dequantize
+
+
+# ---------------------------------------------------------------------------
+# scores
+# ---------------------------------------------------------------------------
+def prerotate_query(q: torch.Tensor, signs) -> torch.Tensor:
+    """(n_heads, dim) -> raw_butterfly(q * signs), float32, no 1/sqrt(dim)."""
+    if q.ndim != 2:
+        raise ValueError(f"prerotate_query expects (n_heads, dim), got {tuple(q.shape)}")
+    _lib.require_cuda(q)
+    n_heads, dim = q.shape
+    if q.stride(-1) != 1:
+        q = q.contiguous()
+    out = torch.empty((n_heads, dim), dtype=torch.float32, device=q.device)
+    _lib.check(_lib.lib().tq_prerotate_query(_lib.ptr(q), _lib.dtype_code(q.dtype), n_heads,
+                                             q.stride(0), dim, _lib.host_floats(signs),
+                                             _lib.ptr(out), _lib.stream_ptr(q.device)))
+    return out
+
+
+def _rows_view(t: torch.Tensor) -> torch.Tensor:
+    """(heads, seq, width) with contiguous rows; the head stride may be anything."""
+    if t.stride(-1) != 1 or t.stride(-2) != t.shape[-1]:
+        t = t.contiguous()
+    return t
+
+
+def _vec_view(t: torch.Tensor) -> torch.Tensor:
+    if t.stride(-1) != 1:
+        t = t.contiguous()
+    return t
+
+
+def prerot_fused_qk_scores(q_rot, k_packed, k_norms, centroids, dim: int, bits: int,
+                           n_rep: int = 1) -> torch.Tensor:
+    """(n_q, dim) x packed K (n_kv, seq, pdim) -> (n_q, seq) float32 raw scores."""
+    _check_bits(bits)
+    _lib.require_cuda(q_rot, k_packed, k_norms)
+    n_q = q_rot.shape[0]
+    n_kv, seq = k_norms.shape
+    if n_q != n_kv * n_rep:
+        raise ValueError(
+            f"n_q_heads ({n_q}) must equal n_kv_heads ({n_kv}) * n_rep ({n_rep})")
+    q_rot = q_rot.to(torch.float32).contiguous()
+    kp = _rows_view(k_packed)
+    kn = _vec_view(k_norms.to(torch.float32))
+    out = torch.empty((n_q, seq), dtype=torch.float32, device=q_rot.device)
+    _lib.check(_lib.lib().tq_prerot_qk_scores(
+        _lib.ptr(q_rot), _lib.ptr(kp), kp.stride(0), _lib.ptr(kn), kn.stride(0), n_kv, seq,
+        _lib.host_floats(centroids), dim, bits, n_rep, _lib.ptr(out),
+        _lib.stream_ptr(q_rot.device)))
+    return out
+
+
+def packed_fused_qk_scores(query, k_packed, k_norms, centroids, signs, dim: int,
+                           bits: int) -> torch.Tensor:
+    """Per-position dequant then dot with the un-rotated query (multi-head)."""
+    _check_bits(bits)
+    _lib.require_cuda(query, k_packed, k_norms)
+    n_heads, seq = k_norms.shape
+    query = query.to(torch.float32).contiguous()
+    kp = _rows_view(k_packed)
+    kn = _vec_view(k_norms.to(torch.float32))
+    out = torch.empty((n_heads, seq), dtype=torch.float32, device=query.device)
+    _lib.check(_lib.lib().tq_packed_qk_scores(
+        _lib.ptr(query), _lib.ptr(kp), kp.stride(0), _lib.ptr(kn), kn.stride(0), n_heads, seq,
+        _lib.host_floats(centroids), _lib.host_floats(signs), dim, bits, _lib.ptr(out),
+        _lib.stream_ptr(query.device)))
+    return out
+
+
+# ---------------------------------------------------------------------------
+# weighted V sum
+# ---------------------------------------------------------------------------
+def sparse_v_matvec(weights, v_packed, v_norms, centroids, signs, dim: int, bits: int,
+                    threshold: float = 1e-5, n_rep: int = 1) -> torch.Tensor:
+    """Weighted sum of dequantized V rows, (n_q, seq) x packed V -> (n_q, dim)
+    float32; positions with weight < threshold are skipped."""
+    if dim & (dim - 1):
+        raise ValueError(f"dim must be a power of 2, got {dim}")
+    if dim > 256:
+        raise ValueError(f"dim > 256 not supported by threadgroup layout, got {dim}")
+    _check_bits(bits)
+    _lib.require_cuda(weights, v_packed, v_norms)
+    n_q, seq = weights.shape
+    n_kv = v_packed.shape[0]
+    if n_q != n_kv * n_rep:
+        raise ValueError(
+            f"n_q_heads ({n_q}) must equal n_kv_heads ({n_kv}) * n_rep ({n_rep})")
+    w = _vec_view(weights.to(torch.float32))
+    vp = _rows_view(v_packed)
+    vn = _vec_view(v_norms.to(torch.float32))
+    out = torch.empty((n_q, dim), dtype=torch.float32, device=w.device)
+    L = _lib.lib()
+    need = L.tq_sparse_v_workspace_bytes(n_q, seq, dim)
+    ws = _lib.workspace(need, w.device)
+    _lib.check(L.tq_sparse_v_matvec(
+        _lib.ptr(w), w.stride(0), _lib.ptr(vp), vp.stride(0), _lib.ptr(vn), vn.stride(0), n_kv,
+        seq, _lib.host_floats(centroids), _lib.host_floats(signs), dim, bits, float(threshold),
+        n_rep, _lib.ptr(out), _lib.ptr(ws), need, _lib.stream_ptr(w.device)))
+    return out
+
+
+def count_active_positions(weights: torch.Tensor, threshold: float = 1e-5) -> int:
+    """Positions whose weight exceeds `threshold` (diagnostics only)."""
+    return int((weights > threshold).sum().item())
+
+
+# ---------------------------------------------------------------------------
+# flash decode
+# ---------------------------------------------------------------------------
+def _strides3(t: torch.Tensor, batched: bool):
+    """(batch_stride, head_stride) of a (B, H, ...) or (H, ...) tensor."""
+    if batched:
+        return t.stride(0), t.stride(1)
+    return 0, t.stride(0)
+
+
+def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerotated: bool = False,
+                 mask: torch.Tensor | None = None, num_splits: int = 0, out_dtype=None,
+                 partials: bool = False):
+    """Split-K flash decoding for one query token per sequence.
+
+    q: (B, n_q, dim).  k / v: dicts describing the stored keys / values:
+      polar : dict(format="polar", packed (B, n_kv, S, pdim) uint32, norms (B, n_kv, S),
+                   centroids, signs, bits)
+      dense : dict(format="dense", data (B, n_kv, S, dim) fp16/bf16/fp32)       [keys only]
+      affine: dict(format="affine", codes (B, n_kv, S, bytes) uint8, scales, biases
+                   (B, n_kv, S, dim/group) fp16, bits, group)
+    The sequence dimension may be a view of a longer allocation (head and batch
+    strides are passed through).  mask: optional additive float mask
+    broadcastable to (B, n_q, S).  Returns (B, n_q, dim) in out_dtype (default
+    q.dtype), or with partials=True the merged state (m (B, n_q), l (B, n_q),
+    acc (B, n_q, dim)) before the final butterfly / normalisation.
+    """
+    _lib.require_cuda(q)
+    B, n_q, dim = q.shape
+    if q.stride(-1) != 1:
+        q = q.contiguous()
+    P = _lib.FlashParams()
+    P.struct_bytes = ctypes.sizeof(_lib.FlashParams)
+    P.batch, P.n_q_heads, P.dim = B, n_q, dim
+    P.q, P.q_dtype, P.q_prerotated = q.data_ptr(), _lib.dtype_code(q.dtype), int(q_prerotated)
+    P.q_batch_stride, P.q_head_stride = q.stride(0), q.stride(1)
+    keep = []  # keeps converted tensors / host arrays alive until the launch returns
+
+    def rows(t):
+        t = _rows_view(t)
+        keep.append(t)
+        return t
+
+    kf = k["format"]
+    if kf == "polar":
+        kp, kn = rows(k["packed"]), k["norms"]
+        if kn.stride(-1) != 1:
+            kn = kn.contiguous()
+        keep.append(kn)
+        n_kv, S = kn.shape[1], kn.shape[2]
+        P.k_format, P.k_bits = _lib.TQ_KV_POLAR, int(k["bits"])
+        _check_bits(P.k_bits)
+        P.k_data, P.k_batch_stride, P.k_head_stride = kp.data_ptr(), kp.stride(0), kp.stride(1)
+        P.k_norms, P.kn_batch_stride, P.kn_head_stride = kn.data_ptr(), kn.stride(0), kn.stride(1)
+        kc = _lib.host_floats(k["centroids"])
+        ks = _lib.host_floats(k.get("signs"))
+        keep += [kc, ks]
+        P.k_centroids_host = kc
+        if ks is not None:
+            P.k_signs_host = ks
+    elif kf == "dense":
+        kd = rows(k["data"])
+        n_kv, S = kd.shape[1], kd.shape[2]
+        P.k_format, P.k_dtype = _lib.TQ_KV_DENSE, _lib.dtype_code(kd.dtype)
+        P.k_data, P.k_batch_stride, P.k_head_stride = kd.data_ptr(), kd.stride(0), kd.stride(1)
+    elif kf == "affine":
+        kc_, ksc, kbi = rows(k["codes"]), rows(k["scales"]), rows(k["biases"])
+        n_kv, S = kc_.shape[1], kc_.shape[2]
+        P.k_format, P.k_bits, P.k_group = _lib.TQ_KV_AFFINE, int(k["bits"]), int(k["group"])
+        P.k_data, P.k_batch_stride, P.k_head_stride = kc_.data_ptr(), kc_.stride(0), kc_.stride(1)
+        P.k_scales, P.k_biases = ksc.data_ptr(), kbi.data_ptr()
+        P.ks_batch_stride, P.ks_head_stride = ksc.stride(0), ksc.stride(1)
+    else:
+        raise ValueError(f"unknown key format {kf!r}")
+
+    vf = v["format"]
+    if vf == "polar":
+        vp, vn = rows(v["packed"]), v["norms"]
+        if vn.stride(-1) != 1:
+            vn = vn.contiguous()
+        keep.append(vn)
+        P.v_format, P.v_bits = _lib.TQ_KV_POLAR, int(v["bits"])
+        _check_bits(P.v_bits)
+        P.v_data, P.v_batch_stride, P.v_head_stride = vp.data_ptr(), vp.stride(0), vp.stride(1)
+        P.v_norms, P.vn_batch_stride, P.vn_head_stride = vn.data_ptr(), vn.stride(0), vn.stride(1)
+        vc, vs = _lib.host_floats(v["centroids"]), _lib.host_floats(v["signs"])
+        keep += [vc, vs]
+        P.v_centroids_host, P.v_signs_host = vc, vs
+        v_heads, v_seq = vn.shape[1], vn.shape[2]
+    elif vf == "affine":
+        vc_, vsc, vbi = rows(v["codes"]), rows(v["scales"]), rows(v["biases"])
+        P.v_format, P.v_bits, P.v_group = _lib.TQ_KV_AFFINE, int(v["bits"]), int(v["group"])
+        P.v_data, P.v_batch_stride, P.v_head_stride = vc_.data_ptr(), vc_.stride(0), vc_.stride(1)
+        P.v_scales, P.v_biases = vsc.data_ptr(), vbi.data_ptr()
+        P.vs_batch_stride, P.vs_head_stride = vsc.stride(0), vsc.stride(1)
+        v_heads, v_seq = vc_.shape[1], vc_.shape[2]
+    else:
+        raise ValueError(f"unknown value format {vf!r}")
+    if v_heads != n_kv or v_seq != S:
+        raise ValueError(f"K ({n_kv} heads, {S} positions) and V ({v_heads}, {v_seq}) disagree")
+    if n_q % n_kv:
+        raise ValueError(f"n_q_heads ({n_q}) must equal n_kv_heads ({n_kv}) * n_rep")
+    P.n_kv_heads, P.seq_len = n_kv, S
+    P.attn_scale, P.num_splits = float(attn_scale), int(num_splits)
+
+    if mask is not None:
+        m = mask.to(torch.float32)
+        while m.ndim < 3:
+            m = m.unsqueeze(0)
+        if m.shape[-1] != S or m.shape[0] not in (1, B) or m.shape[1] not in (1, n_q):
+            raise ValueError(f"mask shape {tuple(mask.shape)} does not broadcast to ({B}, {n_q}, {S})")
+        if m.stride(-1) != 1:
+            m = m.contiguous()
+        keep.append(m)
+        P.mask = m.data_ptr()
+        P.mask_batch_stride = 0 if m.shape[0] == 1 else m.stride(0)
+        P.mask_head_stride = 0 if m.shape[1] == 1 else m.stride(1)
+
+    dev = q.device
+    if partials:
+        P.out_mode = 1
+        pm = torch.empty((B, n_q), dtype=torch.float32, device=dev)
+        pl = torch.empty((B, n_q), dtype=torch.float32, device=dev)
+        pa = torch.empty((B, n_q, dim), dtype=torch.float32, device=dev)
+        P.part_m, P.part_l, P.part_acc = pm.data_ptr(), pl.data_ptr(), pa.data_ptr()
+    else:
+        P.out_mode = 0
+        out = torch.empty((B, n_q, dim), dtype=out_dtype or q.dtype, device=dev)
+        P.out, P.out_dtype = out.data_ptr(), _lib.dtype_code(out.dtype)
+        P.out_batch_stride, P.out_head_stride = out.stride(0), out.stride(1)
+    P.stream = torch.cuda.current_stream(dev).cuda_stream
+    L = _lib.lib()
+    need = L.tq_flash_decode_workspace_bytes(ctypes.byref(P))
+    if need < 0:
+        _lib.check(int(need))
+    ws = _lib.workspace(need, dev)
+    if ws is not None:
+        P.workspace, P.workspace_bytes = ws.data_ptr(), ws.numel()
+    _lib.check(L.tq_flash_decode(ctypes.byref(P)))
+    del keep
+    return (pm, pl, pa) if partials else out
+
+
+def flash_attention_turboquant(q_rot, k_packed, k_norms, v_packed, v_norms, k_centroids,
+                               v_centroids, v_signs, dim: int, bits: int, attn_scale: float,
+                               block_size: int = 16, n_rep: int = 1, v_bits: int | None = None):
+    """Fused SDPA over packed K/V for one pre-rotated query per head:
+    (n_q, dim) -> (n_q, dim) float32.  `block_size` is validated for
+    compatibility; the kernel picks its own tiling and splits the sequence
+    across CTAs.  `v_bits` (default: bits) allows a different width for V."""
+    if dim > 128 or dim & (dim - 1):
+        raise ValueError(f"dim must be a power of 2 and <= 128, got {dim}")
+    if block_size < 1 or block_size > 32:
+        raise ValueError(f"block_size must be in 1..32, got {block_size}")
+    n_q = q_rot.shape[0]
+    n_kv, seq = k_norms.shape
+    if n_q != n_kv * n_rep:
+        raise ValueError(
+            f"n_q_heads ({n_q}) must equal n_kv_heads ({n_kv}) * n_rep ({n_rep})")
+    k = dict(format="polar", packed=k_packed.unsqueeze(0), norms=k_norms.to(torch.float32).unsqueeze(0),
+             centroids=k_centroids, bits=bits)
+    v = dict(format="polar", packed=v_packed.unsqueeze(0), norms=v_norms.to(torch.float32).unsqueeze(0),
+             centroids=v_centroids, signs=v_signs, bits=bits if v_bits is None else v_bits)
+    out = flash_decode(q_rot.to(torch.float32).unsqueeze(0), k=k, v=v, attn_scale=attn_scale,
+                       q_prerotated=True, out_dtype=torch.float32)
+    return out[0]
+
+
+def merge_partials(part_m, part_l, part_acc, v_signs, out_dtype=torch.float32) -> torch.Tensor:
+    """Merge (n_parts, rows) / (n_parts, rows, dim) partial states from sequence
+    chunks or ranks into the final (rows, dim) output."""
+    _lib.require_cuda(part_m, part_l, part_acc)
+    n_parts, rows, dim = part_acc.shape
+    pm, pl, pa = part_m.contiguous(), part_l.contiguous(), part_acc.contiguous()
+    out = torch.empty((rows, dim), dtype=out_dtype, device=pa.device)
+    _lib.check(_lib.lib().tq_merge_partials(_lib.ptr(pm), _lib.ptr(pl), _lib.ptr(pa), n_parts, rows,
+                                            dim, _lib.host_floats(v_signs), _lib.ptr(out),
+                                            _lib.dtype_code(out_dtype), dim,
+                                            _lib.stream_ptr(pa.device)))
+    return out

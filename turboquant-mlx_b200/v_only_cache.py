@@ -1,0 +1,110 @@
+"""V-only TurboQuant cache: keys stay fp16/bf16, values are PolarQuant-packed
+(reference turboquant_mlx/v_only_cache.py:24-127).
+
+With `fused=False` (the reference's behaviour) values are dequantized into an
+incremental buffer and attention runs on plain tensors.  With `fused=True`
+decode attention reads the dense keys and the packed values in one
+flash-decode launch (`v_only_attention`), and no dequantized V buffer exists."""
+
+from __future__ import annotations
+
+import torch
+
+from .base import KVCache
+from .cache import TurboQuantKVCache
+from .kernels import flash_decode
+
+
+class VOnlyTurboQuantCache:
+    """KV cache with un-quantized keys and TurboQuant-compressed values.
+
+    Does not expose `.bits` / `.group_size`, so an attention router treats it
+    as a plain cache unless `fused` is set."""
+
+    def __init__(self, bits: int = 3, seed: int = 42, no_v_buffer: bool = False,
+                 fused: bool = False):
+        self._k_cache = KVCache()
+        self._v_tq = TurboQuantKVCache(bits=bits, seed=seed, v_only=True, fused=fused)
+        self._v_bits = bits
+        self._no_v_buffer = no_v_buffer
+        self.fused = fused
+
+    def update_and_fetch(self, keys, values):
+        """Store K as is, compress V, return (K, V_dequant)."""
+        k_out, _ = self._k_cache.update_and_fetch(keys, values)
+        if self._no_v_buffer and not self.fused:
+            # quantize, then re-dequantize everything from packed storage each call
+            tq = self._v_tq
+            B, H, S, v_dim = values.shape
+            tq._dtype = keys.dtype
+            tq._ensure_quantizer(keys.shape[-1], v_dim, values.device)
+            tq._ensure_storage(B, H, S, values.device)
+            tq._insert(values, tq._v_q, tq.v_packed, tq.v_norms, tq.offset)
+            tq.offset += S
+            _, v_out = tq.dequantized(values.dtype)
+        else:
+            _, v_out = self._v_tq.update_and_fetch(keys, values)
+        return k_out, v_out
+
+    @property
+    def offset(self):
+        return self._k_cache.offset
+
+    @property
+    def state(self):
+        k_state = list(self._k_cache.state) if self._k_cache.state else []
+        v_state = list(self._v_tq.state) if self._v_tq.state else []
+        return k_state + v_state
+
+    @property
+    def meta_state(self):
+        return f"VOnlyTQ,{self._v_bits},{self._v_tq.seed},{self._v_tq.meta_state}"
+
+    @classmethod
+    def from_state(cls, state, meta_state):
+        parts = meta_state.split(",", 3)
+        obj = cls(bits=int(parts[1]), seed=int(parts[2]))
+        if len(state) >= 2:
+            obj._k_cache.keys = state[0].contiguous()
+            obj._k_cache.values = state[1].contiguous()
+            obj._k_cache.offset = state[0].shape[2]
+        if len(state) > 2:
+            obj._v_tq.state = state[2:]
+            obj._v_tq.meta_state = parts[3]
+            obj._v_tq._v_pdim = obj._v_tq.v_packed.shape[-1]
+        return obj
+
+    def make_mask(self, *args, **kwargs):
+        return self._k_cache.make_mask(*args, **kwargs)
+
+    def empty(self):
+        return self._k_cache.offset == 0
+
+    def is_trimmable(self):
+        return True
+
+    def trim(self, n):
+        self._k_cache.trim(n)
+        return self._v_tq.trim(n)
+
+    def size(self):
+        return self._k_cache.offset
+
+
+def v_only_attention(queries, cache: VOnlyTurboQuantCache, attn_scale: float, mask=None):
+    """Decode attention for a fused V-only cache: queries (B, n_q, 1, dim),
+    dense K and packed V read once per KV head -> (B, n_q, 1, dim)."""
+    total = cache.offset
+    tq = cache._v_tq
+    k = dict(format="dense", data=cache._k_cache.keys[:, :, :total, :])
+    v = dict(format="polar", packed=tq.v_packed[:, :, :total, :], norms=tq.v_norms[:, :, :total],
+             centroids=tq._v_q.centroids, signs=tq._v_q.signs, bits=tq._v_q.bits)
+    m3 = None
+    if mask is not None and not isinstance(mask, str):
+        from .fused_attention import _mask_3d
+        if mask.dtype == torch.bool:
+            mask = torch.where(mask, 0.0, float("-inf"))
+        m3 = _mask_3d(mask, queries.shape[0], queries.shape[1], total)
+    out = flash_decode(queries[:, :, 0, :], k=k, v=v, attn_scale=attn_scale, mask=m3,
+                       out_dtype=queries.dtype)
+    return out.unsqueeze(2)
