@@ -1,0 +1,279 @@
+"""GPU parity of the attention-side kernels against the oracle: re-expression
+of the reference's tests/test_prerot.py, test_sparse_v.py and
+test_flash_attention.py with the oracle as the comparator, plus the cases the
+reference lacks (dense and affine keys, batch, masks, split-K partials, ragged
+lengths).  Tolerance for attention outputs: 2e-3 max relative error."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ATT_TOL = 2e-3
+
+
+def _rel(a, b):
+    return np.abs(a - b).max() / max(np.abs(b).max(), 1e-30)
+
+
+def _t(x, dev):
+    return torch.from_numpy(np.ascontiguousarray(x)).to(dev)
+
+
+def _packed(rng, oracle, shape, bits):
+    return oracle.pack_indices(rng.integers(0, 1 << bits, shape).astype(np.uint8), bits)
+
+
+@pytest.mark.parametrize("n_heads,dim", [(4, 128), (8, 64), (1, 32), (32, 128)])
+def test_prerotate_query(tq, oracle, dev, n_heads, dim):
+    rng = np.random.default_rng(0)
+    q = rng.standard_normal((n_heads, dim)).astype(np.float32)
+    s = tq.random_diagonal_sign(dim, 42, device=dev)
+    out = tq.prerotate_query(_t(q, dev), s)
+    assert np.array_equal(out.cpu().numpy(), oracle.prerotate_query(q, s.cpu().numpy()))
+    with pytest.raises(ValueError):
+        tq.prerotate_query(_t(q, dev).unsqueeze(0), s)
+
+
+@pytest.mark.parametrize("H,S,D,bits", [(4, 64, 128, 3), (8, 256, 128, 3), (2, 16, 64, 4), (1, 128, 32, 2),
+                                        (3, 77, 128, 4)])
+def test_prerot_scores(tq, oracle, dev, H, S, D, bits):
+    rng = np.random.default_rng(1)
+    pq = tq.PolarQuantizer(D, bits, seed=42, device=dev)
+    signs, c = pq.signs.cpu().numpy(), oracle.codebook(bits)
+    kp = _packed(rng, oracle, (H, S, D), bits)
+    kn = (rng.random((H, S)) * 5 + 0.1).astype(np.float32)
+    q = rng.standard_normal((H, D)).astype(np.float32)
+    q_rot = tq.prerotate_query(_t(q, dev), pq.signs)
+    got = tq.prerot_fused_qk_scores(q_rot, _t(kp, dev), _t(kn, dev), pq.centroids, D, bits)
+    ref = oracle.prerot_fused_qk_scores(oracle.prerotate_query(q, signs), kp, kn, c, D, bits)
+    assert np.abs(got.cpu().numpy() - ref).max() < 1e-4 * max(1.0, np.abs(ref).max())
+    legacy = tq.packed_fused_qk_scores(_t(q, dev), _t(kp, dev), _t(kn, dev), pq.centroids, pq.signs, D, bits)
+    assert np.abs(legacy.cpu().numpy() - ref).max() < 1e-4 * max(1.0, np.abs(ref).max())
+
+
+@pytest.mark.parametrize("n_kv,n_rep", [(4, 2), (2, 4), (4, 7), (2, 9)])
+def test_prerot_scores_gqa(tq, oracle, dev, n_kv, n_rep):
+    rng = np.random.default_rng(2)
+    S, D, bits = 128, 128, 3
+    pq = tq.PolarQuantizer(D, bits, seed=42, device=dev)
+    kp = _packed(rng, oracle, (n_kv, S, D), bits)
+    kn = (rng.random((n_kv, S)) * 5 + 0.1).astype(np.float32)
+    q_rot = rng.standard_normal((n_kv * n_rep, D)).astype(np.float32) * 10
+    got = tq.prerot_fused_qk_scores(_t(q_rot, dev), _t(kp, dev), _t(kn, dev), pq.centroids, D, bits, n_rep=n_rep)
+    ref = oracle.prerot_fused_qk_scores(q_rot, kp, kn, oracle.codebook(bits), D, bits, n_rep)
+    assert np.abs(got.cpu().numpy() - ref).max() < 1e-4 * max(1.0, np.abs(ref).max())
+    with pytest.raises(ValueError, match="must equal n_kv_heads"):
+        tq.prerot_fused_qk_scores(_t(q_rot, dev), _t(kp, dev), _t(kn, dev), pq.centroids, D, bits, n_rep=n_rep + 1)
+
+
+@pytest.mark.parametrize("H,S,D,bits", [(4, 128, 128, 3), (2, 512, 128, 3), (8, 64, 64, 4), (2, 1000, 128, 3),
+                                        (1, 40, 256, 2)])
+def test_sparse_v_threshold_zero_matches_dense(tq, oracle, dev, H, S, D, bits):
+    rng = np.random.default_rng(3)
+    pq = tq.PolarQuantizer(D, bits, seed=42, device=dev)
+    vp = _packed(rng, oracle, (H, S, D), bits)
+    vn = (rng.random((H, S)) + 0.1).astype(np.float32)
+    w = oracle.softmax(rng.standard_normal((H, S)) * 3)
+    got = tq.sparse_v_matvec(_t(w, dev), _t(vp, dev), _t(vn, dev), pq.centroids, pq.signs, D, bits, threshold=0.0)
+    dense = np.einsum("hp,hpe->he", w.astype(np.float64),
+                      oracle.packed_dequantize(vp, vn, oracle.codebook(bits), pq.signs.cpu().numpy(), D, bits))
+    assert _rel(got.cpu().numpy(), dense) < 1e-5
+
+
+def test_sparse_v_threshold_and_gqa(tq, oracle, dev):
+    rng = np.random.default_rng(4)
+    S, D, bits = 512, 128, 3
+    pq = tq.PolarQuantizer(D, bits, seed=42, device=dev)
+    signs, c = pq.signs.cpu().numpy(), oracle.codebook(bits)
+    for n_kv, n_rep in ((4, 1), (4, 2), (2, 4), (4, 7), (1, 12)):
+        vp = _packed(rng, oracle, (n_kv, S, D), bits)
+        vn = (rng.random((n_kv, S)) + 0.1).astype(np.float32)
+        w = oracle.softmax(rng.standard_normal((n_kv * n_rep, S)) * 3)
+        for thr in (0.0, 1e-5, 1e-3):
+            got = tq.sparse_v_matvec(_t(w, dev), _t(vp, dev), _t(vn, dev), pq.centroids, pq.signs, D, bits,
+                                     threshold=thr, n_rep=n_rep)
+            ref = oracle.sparse_v_matvec(w, vp, vn, c, signs, D, bits, threshold=thr, n_rep=n_rep)
+            assert _rel(got.cpu().numpy(), ref) < 1e-5
+        zero = tq.sparse_v_matvec(_t(w, dev), _t(vp, dev), _t(vn, dev), pq.centroids, pq.signs, D, bits,
+                                  threshold=float(w.max()) * 2 + 1, n_rep=n_rep)
+        assert float(zero.abs().max()) == 0.0
+    assert tq.count_active_positions(_t(w, dev), 1e-5) == oracle.count_active_positions(w, 1e-5)
+    with pytest.raises(ValueError, match="power of 2"):
+        tq.sparse_v_matvec(_t(w, dev), _t(vp, dev), _t(vn, dev), pq.centroids, pq.signs, 100, bits)
+    with pytest.raises(ValueError, match="dim > 256"):
+        tq.sparse_v_matvec(_t(w, dev), _t(vp, dev), _t(vn, dev), pq.centroids, pq.signs, 512, bits)
+
+
+@pytest.mark.parametrize("n_kv,n_rep,S,D,bits,bc", [(4, 1, 32, 128, 3, 8), (4, 1, 128, 128, 3, 16),
+                                                   (8, 1, 256, 128, 3, 16), (2, 1, 64, 64, 4, 8),
+                                                   (4, 1, 96, 128, 3, 32), (4, 2, 128, 128, 3, 16),
+                                                   (2, 4, 128, 128, 3, 16), (4, 7, 1000, 128, 3, 16),
+                                                   (2, 8, 4099, 128, 4, 16), (1, 12, 300, 128, 2, 16)])
+def test_flash_matches_composed(tq, oracle, dev, n_kv, n_rep, S, D, bits, bc):
+    rng = np.random.default_rng(5)
+    kq = tq.PolarQuantizer(D, bits, seed=42, device=dev)
+    vq = tq.PolarQuantizer(D, bits, seed=43, device=dev)
+    c = oracle.codebook(bits)
+    kp, vp = _packed(rng, oracle, (n_kv, S, D), bits), _packed(rng, oracle, (n_kv, S, D), bits)
+    kn = (rng.random((n_kv, S)) * 5 + 0.1).astype(np.float32)
+    vn = (rng.random((n_kv, S)) * 5 + 0.1).astype(np.float32)
+    q = rng.standard_normal((n_kv * n_rep, D)).astype(np.float32)
+    scale = 1.0 / math.sqrt(D)
+    q_rot = tq.prerotate_query(_t(q, dev), kq.signs)
+    got = tq.flash_attention_turboquant(q_rot, _t(kp, dev), _t(kn, dev), _t(vp, dev), _t(vn, dev),
+                                        kq.centroids, vq.centroids, vq.signs, D, bits, scale,
+                                        block_size=bc, n_rep=n_rep)
+    ref, _ = oracle.decode_attention(
+        q, k_polar=dict(packed=kp, norms=kn, centroids=c, signs=kq.signs.cpu().numpy(), bits=bits),
+        v_polar=dict(packed=vp, norms=vn, centroids=c, signs=vq.signs.cpu().numpy(), bits=bits),
+        attn_scale=scale, n_rep=n_rep)
+    assert got.shape == (n_kv * n_rep, D) and got.dtype == torch.float32
+    assert _rel(got.cpu().numpy(), ref) < 1e-3
+    # composed GPU path (scores -> softmax -> sparse_v) agrees too
+    sc = tq.prerot_fused_qk_scores(q_rot, _t(kp, dev), _t(kn, dev), kq.centroids, D, bits, n_rep=n_rep)
+    w = torch.softmax(sc * scale, dim=-1)
+    comp = tq.sparse_v_matvec(w, _t(vp, dev), _t(vn, dev), vq.centroids, vq.signs, D, bits, threshold=0.0, n_rep=n_rep)
+    assert _rel(got.cpu().numpy(), comp.cpu().numpy()) < 1e-3
+
+
+def test_flash_argument_errors(tq, dev):
+    z = torch.zeros((4, 128), device=dev)
+    zp = torch.zeros((4, 8, 13), dtype=torch.uint32, device=dev)
+    zn = torch.ones((4, 8), device=dev)
+    c = [0.0] * 8
+    s = [1.0] * 128
+    with pytest.raises(ValueError, match="<= 128"):
+        tq.flash_attention_turboquant(z, zp, zn, zp, zn, c, c, s, 256, 3, 1.0)
+    with pytest.raises(ValueError, match="block_size"):
+        tq.flash_attention_turboquant(z, zp, zn, zp, zn, c, c, s, 128, 3, 1.0, block_size=0)
+    with pytest.raises(ValueError, match="must equal n_kv_heads"):
+        tq.flash_attention_turboquant(z, zp, zn, zp, zn, c, c, s, 128, 3, 1.0, n_rep=2)
+
+
+def _golden_dense_case(tq, golden, dev):
+    g = golden
+    vq = tq.PolarQuantizer(128, 3, seed=43, device=dev)
+    k = dict(format="dense", data=_t(g["att_kd"], dev).unsqueeze(0))
+    v = dict(format="polar", packed=_t(g["att_vp"], dev).unsqueeze(0), norms=_t(g["att_vn"], dev).unsqueeze(0),
+             centroids=vq.centroids, signs=vq.signs, bits=3)
+    return k, v
+
+
+def test_flash_decode_golden_dense_and_polar(tq, golden, dev):
+    g = golden
+    scale = 1.0 / math.sqrt(128)
+    q = _t(g["att_q"], dev).unsqueeze(0)
+    k, v = _golden_dense_case(tq, golden, dev)
+    out = tq.flash_decode(q, k=k, v=v, attn_scale=scale, out_dtype=torch.float32)
+    assert _rel(out[0].cpu().numpy(), g["att_out_dense"]) < ATT_TOL
+    out16 = tq.flash_decode(q, k=k, v=v, attn_scale=scale)
+    assert out16.dtype == torch.float16
+    assert _rel(out16[0].float().cpu().numpy(), g["att_out_dense"]) < ATT_TOL
+    kq = tq.PolarQuantizer(128, 4, seed=42, device=dev)
+    kpol = dict(format="polar", packed=_t(g["att_kp"], dev).unsqueeze(0), norms=_t(g["att_kn"], dev).unsqueeze(0),
+                centroids=kq.centroids, signs=kq.signs, bits=4)
+    out2 = tq.flash_decode(q, k=kpol, v=v, attn_scale=scale, out_dtype=torch.float32)
+    assert _rel(out2[0].cpu().numpy(), g["att_out_polar"]) < ATT_TOL
+    q_rot = tq.prerotate_query(q[0], kq.signs)
+    assert np.array_equal(q_rot.cpu().numpy(), g["q_rot"])
+    sc = tq.prerot_fused_qk_scores(q_rot, kpol["packed"][0], kpol["norms"][0], kq.centroids, 128, 4, n_rep=7)
+    assert np.abs(sc.cpu().numpy() - g["scores_polar"]).max() < 1e-4 * np.abs(g["scores_polar"]).max()
+
+
+@pytest.mark.parametrize("splits", [0, 1, 3, 16])
+def test_flash_decode_batch_splits_mask_strides(tq, oracle, dev, splits):
+    """Batch of 3, K/V are views of a longer allocation (stride != length), an
+    additive mask hides a ragged tail per sequence, bf16 dense keys."""
+    rng = np.random.default_rng(6)
+    B, n_kv, n_rep, n_alloc, S, D = 3, 2, 4, 768, 531, 128
+    vq = tq.PolarQuantizer(D, 3, seed=43, device=dev)
+    signs = vq.signs.cpu().numpy()
+    kd = torch.from_numpy(rng.standard_normal((B, n_kv, n_alloc, D)).astype(np.float32)).to(torch.bfloat16)
+    vraw = (rng.standard_normal((B, n_kv, n_alloc, D)) * rng.lognormal(0, 0.5, (B, n_kv, n_alloc, 1))).astype(np.float16)
+    vp, vn = oracle.quantize_packed(vraw, signs, 3)
+    q = rng.standard_normal((B, n_kv * n_rep, D)).astype(np.float16)
+    lens = [531, 200, 17]
+    mask = np.zeros((B, 1, S), np.float32)
+    for b, L in enumerate(lens):
+        mask[b, 0, L:] = -np.inf
+    scale = 1.0 / math.sqrt(D)
+    k = dict(format="dense", data=kd.to(dev)[:, :, :S])
+    v = dict(format="polar", packed=_t(vp, dev)[:, :, :S], norms=_t(vn, dev)[:, :, :S],
+             centroids=vq.centroids, signs=vq.signs, bits=3)
+    out = tq.flash_decode(_t(q, dev), k=k, v=v, attn_scale=scale, mask=_t(mask, dev), num_splits=splits,
+                          out_dtype=torch.float32)
+    for b in range(B):
+        ref, _ = oracle.decode_attention(
+            q[b], k_dense=kd[b, :, :S].float().numpy(),
+            v_polar=dict(packed=vp[b, :, :S], norms=vn[b, :, :S], centroids=oracle.codebook(3), signs=signs, bits=3),
+            attn_scale=scale, n_rep=n_rep, mask=np.broadcast_to(mask[b], (n_kv * n_rep, S)))
+        assert _rel(out[b].cpu().numpy(), ref) < ATT_TOL
+
+
+def test_partials_merge_across_chunks_equals_whole(tq, oracle, golden, dev):
+    """Sequence chunks processed separately (as ranks would) and merged with
+    tq_merge_partials equal the single-pass output; an empty chunk is a no-op."""
+    g = golden
+    scale = 1.0 / math.sqrt(128)
+    q = _t(g["att_q"], dev).unsqueeze(0)
+    k, v = _golden_dense_case(tq, golden, dev)
+    whole = tq.flash_decode(q, k=k, v=v, attn_scale=scale, out_dtype=torch.float32)
+    cuts = [0, 64, 65, 160]
+    ms, ls, accs = [], [], []
+    for a, b in zip(cuts[:-1], cuts[1:]):
+        kk = dict(k, data=k["data"][:, :, a:b])
+        vv = dict(v, packed=v["packed"][:, :, a:b], norms=v["norms"][:, :, a:b])
+        m, l, acc = tq.flash_decode(q, k=kk, v=vv, attn_scale=scale, partials=True)
+        ms.append(m[0]); ls.append(l[0]); accs.append(acc[0])
+    ms.append(torch.zeros_like(ms[0])); ls.append(torch.zeros_like(ls[0])); accs.append(torch.zeros_like(accs[0]))
+    merged = tq.merge_partials(torch.stack(ms), torch.stack(ls), torch.stack(accs), v["signs"])
+    assert _rel(merged.cpu().numpy(), whole[0].cpu().numpy()) < 1e-5
+    assert _rel(merged.cpu().numpy(), g["att_out_dense"]) < ATT_TOL
+    ref = oracle.merge_partials(torch.stack(ms).cpu().numpy(), torch.stack(ls).cpu().numpy(),
+                                torch.stack(accs).cpu().numpy(), g["signs_43"], 128)
+    assert _rel(merged.cpu().numpy(), ref) < 1e-5
+
+
+@pytest.mark.parametrize("v_bits", [4, 8])
+def test_affine_k8_with_polar_and_affine_values(tq, oracle, dev, v_bits):
+    rng = np.random.default_rng(7)
+    B, n_kv, n_rep, S, D, G = 2, 2, 4, 300, 128, 64
+    kraw = rng.standard_normal((B, n_kv, S, D)).astype(np.float16)
+    vraw = rng.standard_normal((B, n_kv, S, D)).astype(np.float16)
+    q = rng.standard_normal((B, n_kv * n_rep, D)).astype(np.float16)
+    kc, ks, kb = oracle.affine_quantize(kraw, G, 8)
+    vc, vs, vb = oracle.affine_quantize(vraw, G, v_bits)
+    from turboquant_mlx_b200 import affine
+    gkc, gks, gkb = affine.affine_quantize(_t(kraw, dev), G, 8)
+    assert np.array_equal(gkc.cpu().numpy(), kc) and np.array_equal(gks.cpu().numpy(), ks)
+    assert np.array_equal(gkb.cpu().numpy(), kb)
+    gvc, gvs, gvb = affine.affine_quantize(_t(vraw, dev), G, v_bits)
+    assert np.array_equal(gvc.cpu().numpy(), vc)
+    deq = affine.affine_dequantize(gvc, gvs, gvb, G, v_bits, torch.float32)
+    assert np.array_equal(deq.cpu().numpy(), oracle.affine_dequantize(vc, vs, vb, G, v_bits))
+    scale = 1.0 / math.sqrt(D)
+    k = dict(format="affine", codes=gkc, scales=gks, biases=gkb, bits=8, group=G)
+    v = dict(format="affine", codes=gvc, scales=gvs, biases=gvb, bits=v_bits, group=G)
+    out = tq.flash_decode(_t(q, dev), k=k, v=v, attn_scale=scale, out_dtype=torch.float32)
+    kd = oracle.affine_dequantize(kc, ks, kb, G, 8)
+    vd = oracle.affine_dequantize(vc, vs, vb, G, v_bits)
+    for b in range(B):
+        kv = np.arange(n_kv * n_rep) // n_rep
+        sc = np.einsum("hpe,he->hp", kd[b][kv].astype(np.float64), q[b].astype(np.float64)) * scale
+        w = oracle.softmax(sc)
+        ref = np.einsum("hp,hpe->he", w.astype(np.float64), vd[b][kv].astype(np.float64))
+        assert _rel(out[b].cpu().numpy(), ref) < ATT_TOL
+    # affine K8 + PolarQuant V3 (the long-context sharded layout)
+    vq = tq.PolarQuantizer(D, 3, seed=43, device=dev)
+    vp, vn = oracle.quantize_packed(vraw, vq.signs.cpu().numpy(), 3)
+    vpol = dict(format="polar", packed=_t(vp, dev), norms=_t(vn, dev), centroids=vq.centroids, signs=vq.signs, bits=3)
+    out2 = tq.flash_decode(_t(q, dev), k=k, v=vpol, attn_scale=scale, out_dtype=torch.float32)
+    for b in range(B):
+        ref, _ = oracle.decode_attention(q[b], k_dense=kd[b], attn_scale=scale, n_rep=n_rep,
+                                         v_polar=dict(packed=vp[b], norms=vn[b], centroids=oracle.codebook(3),
+                                                      signs=vq.signs.cpu().numpy(), bits=3))
+        assert _rel(out2[b].cpu().numpy(), ref) < ATT_TOL

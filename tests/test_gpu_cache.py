@@ -1,0 +1,198 @@
+"""GPU tests of the cache classes and the attention hook: re-expression of the
+reference's tests/test_core.py (cache part), test_fused_attn.py and
+test_v_only_cache.py on CUDA tensors."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _cos(a, b):
+    return torch.nn.functional.cosine_similarity(a.float().reshape(-1, a.shape[-1]),
+                                                 b.float().reshape(-1, b.shape[-1]), dim=-1).mean().item()
+
+
+def test_cache_shapes_offsets_and_quality(tq, dev):
+    torch.manual_seed(0)
+    c = tq.TurboQuantKVCache(bits=3)
+    k = torch.randn(1, 4, 1, 128, device=dev, dtype=torch.float16)
+    ko, vo = c.update_and_fetch(k, k)
+    assert ko.shape == (1, 4, 1, 128) and c.offset == 1 and not c.empty()
+    assert c.k_packed.dtype == torch.uint32 and c.k_packed.shape == (1, 4, 256, 13)
+    k64 = torch.randn(1, 4, 64, 128, device=dev, dtype=torch.float16)
+    v64 = torch.randn(1, 4, 64, 128, device=dev, dtype=torch.float16)
+    ko, vo = c.update_and_fetch(k64, v64)
+    assert ko.shape == (1, 4, 65, 128) and vo.dtype == torch.float16 and c.offset == 65
+    assert _cos(ko[:, :, 1:], k64) > 0.7 and _cos(vo[:, :, 1:], v64) > 0.7
+    assert c.compression_ratio > 1.5 and c.nbytes == 2 * 4 * 65 * 56
+    for _ in range(3):   # incremental decode path (S <= 4)
+        k1 = torch.randn(1, 4, 1, 128, device=dev, dtype=torch.float16)
+        ko2, vo2 = c.update_and_fetch(k1, k1)
+    assert ko2.shape[2] == 68 and torch.equal(ko2[:, :, :65], ko)
+    assert _cos(ko2[:, :, -1:], k1) > 0.7
+    assert c.trim(8) == 8 and c.offset == 60 and c.size() == 60
+
+
+def test_cache_insert_matches_oracle_and_grows(tq, oracle, dev):
+    rng = np.random.default_rng(1)
+    c = tq.TurboQuantKVCache(bits=3, seed=42, fused=True, k_bits=4, v_bits=3)
+    ks, vs = oracle.signs_from_seed(128, 42), oracle.signs_from_seed(128, 43)
+    chunks, all_k, all_v = [200, 1, 1, 3, 300, 1], [], []
+    for S in chunks:
+        k = rng.standard_normal((2, 3, S, 128)).astype(np.float16)
+        v = rng.standard_normal((2, 3, S, 128)).astype(np.float16)
+        zk, zv = c.update_and_fetch(torch.from_numpy(k).to(dev), torch.from_numpy(v).to(dev))
+        assert zk.shape == (2, 3, c.offset, 128) and float(zk.abs().max()) == 0.0
+        all_k.append(k); all_v.append(v)
+    K, V = np.concatenate(all_k, 2), np.concatenate(all_v, 2)
+    total = sum(chunks)
+    assert c.offset == total and c.k_packed.shape[2] % 256 == 0 and c.k_packed.shape[3] == 16
+    kp, kn = oracle.quantize_packed(K, ks, 4)
+    vp, vn = oracle.quantize_packed(V, vs, 3)
+    assert np.array_equal(c.k_packed[:, :, :total].cpu().numpy(), kp)
+    assert np.array_equal(c.v_packed[:, :, :total].cpu().numpy(), vp)
+    assert np.array_equal(c.k_norms[:, :, :total].cpu().numpy(), kn)
+    assert np.array_equal(c.v_norms[:, :, :total].cpu().numpy(), vn)
+
+
+def test_state_round_trip_and_extend(tq, dev):
+    torch.manual_seed(2)
+    c = tq.TurboQuantKVCache(bits=3, seed=42)
+    k = torch.randn(1, 4, 10, 128, device=dev, dtype=torch.float16)
+    c.update_and_fetch(k, k)
+    st, meta = c.state, c.meta_state
+    assert len(st) == 4 and meta == "10,3,42,128,128,float16"
+    assert len(c.state_with_signs) == 6
+    r = tq.TurboQuantKVCache.from_state(st, meta)
+    assert r.offset == 10 and torch.equal(r.k_packed.view(torch.int32), st[0].view(torch.int32))
+    k2 = torch.randn(1, 4, 2, 128, device=dev, dtype=torch.float16)
+    ko, vo = r.update_and_fetch(k2, k2)
+    assert r.offset == 12 and ko.shape == (1, 4, 12, 128)
+    assert torch.equal(r.k_packed[:, :, :10].view(torch.int32), st[0].view(torch.int32))
+
+
+def _filled_cache(tq, dev, B, n_kv, S, fused=True, **kw):
+    torch.manual_seed(3)
+    c = tq.TurboQuantKVCache(bits=3, fused=fused, **kw)
+    k = torch.randn(B, n_kv, S, 128, device=dev, dtype=torch.float16)
+    v = torch.randn(B, n_kv, S, 128, device=dev, dtype=torch.float16)
+    c.update_and_fetch(k, v)
+    return c
+
+
+@pytest.mark.parametrize("S,thr,B,n_rep", [(128, None, 1, 1), (512, 1e-5, 2, 4), (300, 0.0, 3, 7)])
+def test_turboquant_attention_vs_dense_sdpa(tq, dev, S, thr, B, n_rep):
+    n_kv = 4
+    c = _filled_cache(tq, dev, B, n_kv, S)
+    q = torch.randn(B, n_kv * n_rep, 1, 128, device=dev, dtype=torch.float16)
+    scale = 1.0 / math.sqrt(128)
+    out = tq.turboquant_attention(q, c, scale, sparse_v_threshold=thr)
+    assert out.shape == q.shape and out.dtype == q.dtype
+    kd, vd = c.dequantized(torch.float32)
+    kd = kd.repeat_interleave(n_rep, 1); vd = vd.repeat_interleave(n_rep, 1)
+    ref = torch.nn.functional.scaled_dot_product_attention(q.float(), kd, vd, scale=scale)
+    assert _cos(out, ref) > 0.999
+    if thr is None or thr == 0.0:
+        rel = (out.float() - ref).abs().max() / ref.abs().max()
+        assert rel < 3e-3   # fp16 output rounding included
+    # scores on cached K equal sum(dequant(K) * q)
+    q_rot = tq.prerotate_query(q[0, :, 0, :], c._k_q.signs)
+    sc = tq.prerot_fused_qk_scores(q_rot, c.k_packed[0, :, :S], c.k_norms[0, :, :S], c._k_q.centroids,
+                                   128, c.quant_bits, n_rep=n_rep)
+    ref_sc = torch.einsum("hpe,he->hp", kd[0], q[0, :, 0, :].float())
+    assert ((sc - ref_sc).abs().max() / ref_sc.abs().max()) < 1e-3
+
+
+def test_turboquant_attention_mask_and_v_buffer(tq, dev):
+    B, n_kv, n_rep, S = 2, 2, 2, 200
+    c = _filled_cache(tq, dev, B, n_kv, S)
+    q = torch.randn(B, n_kv * n_rep, 1, 128, device=dev, dtype=torch.float16)
+    scale = 1.0 / math.sqrt(128)
+    mask = torch.zeros(B, 1, 1, S, device=dev)
+    mask[0, :, :, 150:] = float("-inf")
+    out = tq.turboquant_attention(q, c, scale, mask=mask)
+    kd, vd = c.dequantized(torch.float32)
+    ref = torch.nn.functional.scaled_dot_product_attention(
+        q.float(), kd.repeat_interleave(n_rep, 1), vd.repeat_interleave(n_rep, 1), attn_mask=mask, scale=scale)
+    assert ((out.float() - ref).abs().max() / ref.abs().max()) < 3e-3
+    out_thr = tq.turboquant_attention(q, c, scale, mask=mask, sparse_v_threshold=1e-6)
+    assert _cos(out_thr, ref) > 0.999
+    out_vb = tq.turboquant_attention(q, c, scale, mask=mask, v_buffer=vd.half())
+    assert _cos(out_vb, ref) > 0.999
+
+
+def test_patched_sdpa_routes_fused_decode_and_prefill(tq, dev):
+    from turboquant_mlx_b200 import base
+    tq.apply_patch()
+    try:
+        B, n_kv, n_rep = 1, 2, 2
+        c = tq.TurboQuantKVCache(bits=4, fused=True)
+        k = torch.randn(B, n_kv, 40, 128, device=dev, dtype=torch.float16)
+        q = torch.randn(B, n_kv * n_rep, 40, 128, device=dev, dtype=torch.float16)
+        zk, zv = c.update_and_fetch(k, k)
+        scale = 1.0 / math.sqrt(128)
+        out = base.scaled_dot_product_attention(q, zk, zv, c, scale, "causal")   # prefill on fused cache
+        kd, vd = c.dequantized(torch.float16)
+        ref = base._dense_sdpa(q, kd, vd, scale, "causal")
+        assert torch.allclose(out, ref, atol=1e-3, rtol=1e-2) and float(out.abs().max()) > 0
+        q1 = torch.randn(B, n_kv * n_rep, 1, 128, device=dev, dtype=torch.float16)
+        zk, zv = c.update_and_fetch(k[:, :, :1], k[:, :, :1])
+        out1 = base.scaled_dot_product_attention(q1, zk, zv, c, scale, None)
+        kd, vd = c.dequantized(torch.float32)
+        ref1 = base._dense_sdpa(q1.float(), kd, vd, scale, None)
+        assert ((out1.float() - ref1).abs().max() / ref1.abs().max()) < 3e-3
+    finally:
+        tq.remove_patch()
+
+
+def test_v_only_cache(tq, dev):
+    torch.manual_seed(4)
+    for kwargs in ({}, {"no_v_buffer": True}):
+        c = tq.VOnlyTurboQuantCache(bits=3, **kwargs)
+        assert c.empty() and c.offset == 0
+        k = torch.randn(1, 4, 10, 128, device=dev, dtype=torch.float16)
+        v = torch.randn(1, 4, 10, 128, device=dev, dtype=torch.float16)
+        ko, vo = c.update_and_fetch(k, v)
+        assert _cos(ko, k) > 0.999 and _cos(vo, v) > 0.95 and c.offset == 10 and not c.empty()
+        ko, vo = c.update_and_fetch(k[:, :, :1], v[:, :, :1])
+        assert ko.shape == (1, 4, 11, 128) and vo.shape == (1, 4, 11, 128) and _cos(vo[:, :, :10], v) > 0.95
+        assert len(c.state) >= 4 and c.meta_state.startswith("VOnlyTQ,3,")
+        assert c.trim(1) == 1 and c.size() == 10
+    c = tq.VOnlyTurboQuantCache(bits=3)
+    c.update_and_fetch(k, v)
+    r = tq.VOnlyTurboQuantCache.from_state(c.state, c.meta_state)
+    assert r.offset == 10 and torch.equal(r._v_tq.v_packed.view(torch.int32), c.state[2].view(torch.int32))
+    ko, vo = r.update_and_fetch(k[:, :, :2], v[:, :, :2])
+    assert r.offset == 12 and vo.shape == (1, 4, 12, 128)
+
+
+def test_v_only_fused_decode_attention(tq, dev):
+    from turboquant_mlx_b200 import base
+    torch.manual_seed(5)
+    B, n_kv, n_rep, S = 2, 4, 7, 700
+    c = tq.VOnlyTurboQuantCache(bits=3, fused=True)
+    k = torch.randn(B, n_kv, S, 128, device=dev, dtype=torch.float16)
+    v = torch.randn(B, n_kv, S, 128, device=dev, dtype=torch.float16)
+    ko, _ = c.update_and_fetch(k, v)
+    q = torch.randn(B, n_kv * n_rep, 1, 128, device=dev, dtype=torch.float16)
+    scale = 1.0 / math.sqrt(128)
+    tq.apply_patch()
+    try:
+        out = base.scaled_dot_product_attention(q, ko, None, c, scale, None)
+    finally:
+        tq.remove_patch()
+    _, vd = c._v_tq.dequantized(torch.float32)
+    ref = base._dense_sdpa(q.float(), k.float(), vd, scale, None)
+    assert ((out.float() - ref).abs().max() / ref.abs().max()) < 3e-3
+
+
+def test_adaptive_cache_layout(tq):
+    from turboquant_mlx_b200.base import KVCache
+    caches = tq.make_adaptive_cache(12, bits=3, fp16_layers=2)
+    assert len(caches) == 12
+    assert all(isinstance(c, KVCache) for c in caches[:2] + caches[-2:])
+    assert all(isinstance(c, tq.TurboQuantKVCache) for c in caches[2:-2])

@@ -1,0 +1,47 @@
+"""Group-wise affine quantisation helpers (K8 / V4) over libtqb200.
+
+Format: per group of `group` consecutive elements scale = fp16((max - min) /
+(2^bits - 1)) and bias = fp16(min); code = clip(rint((x - bias) / scale), 0,
+2^bits - 1); 4-bit codes are packed two per byte, low nibble first.  This stands
+in for `KVCache.to_quantized(group_size, bits)` as the reference uses it
+(turboquant_mlx/hybrid_cache.py:57-63); the reference's arithmetic lives in the
+mlx library, so the format is this library's own."""
+
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+
+def affine_quantize(x: torch.Tensor, group: int = 64, bits: int = 8):
+    """(..., dim) -> codes (..., dim or dim/2) uint8, scales, biases (..., dim/group) fp16."""
+    _lib.require_cuda(x)
+    dim = x.shape[-1]
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, dim).contiguous()
+    n = x2.shape[0]
+    width = dim if bits == 8 else dim // 2
+    codes = torch.empty((n, width), dtype=torch.uint8, device=x.device)
+    scales = torch.empty((n, dim // group), dtype=torch.float16, device=x.device)
+    biases = torch.empty((n, dim // group), dtype=torch.float16, device=x.device)
+    _lib.check(_lib.lib().tq_affine_quantize(_lib.ptr(x2), _lib.dtype_code(x2.dtype), n, dim, group,
+                                             bits, _lib.ptr(codes), _lib.ptr(scales),
+                                             _lib.ptr(biases), _lib.stream_ptr(x.device)))
+    return (codes.reshape(*lead, width), scales.reshape(*lead, dim // group),
+            biases.reshape(*lead, dim // group))
+
+
+def affine_dequantize(codes, scales, biases, group: int = 64, bits: int = 8,
+                      dtype=torch.float16) -> torch.Tensor:
+    _lib.require_cuda(codes, scales, biases)
+    dim = codes.shape[-1] * (1 if bits == 8 else 2)
+    lead = codes.shape[:-1]
+    c2 = codes.reshape(-1, codes.shape[-1]).contiguous()
+    n = c2.shape[0]
+    out = torch.empty((n, dim), dtype=dtype, device=codes.device)
+    _lib.check(_lib.lib().tq_affine_dequantize(_lib.ptr(c2), _lib.ptr(scales.contiguous()),
+                                               _lib.ptr(biases.contiguous()), n, dim, group, bits,
+                                               _lib.ptr(out), _lib.dtype_code(dtype),
+                                               _lib.stream_ptr(codes.device)))
+    return out.reshape(*lead, dim)

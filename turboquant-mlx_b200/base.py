@@ -24,27 +24,31 @@ class KVCache:
 
     step = 256
 
-    def __init__(self):
+    def __init__(self, keys_only: bool = False):
         self.keys = None
         self.values = None
         self.offset = 0
+        # keys_only: the values live elsewhere (a V-only TurboQuant cache keeps
+        # them packed), so no full-precision copy of V is stored here
+        self.keys_only = keys_only
 
     def update_and_fetch(self, keys, values):
         B, H, S, Dk = keys.shape
-        Dv = values.shape[3]
+        Dv = 0 if self.keys_only else values.shape[3]
         prev = self.offset
         if self.keys is None or prev + S > self.keys.shape[2]:
             n = ((prev + S + self.step - 1) // self.step) * self.step
             if self.keys is not None:
                 n = max(n, 2 * self.keys.shape[2])
             new_k = torch.zeros((B, H, n, Dk), dtype=keys.dtype, device=keys.device)
-            new_v = torch.zeros((B, H, n, Dv), dtype=values.dtype, device=values.device)
+            new_v = torch.zeros((B, H, n, Dv), dtype=keys.dtype, device=keys.device)
             if self.keys is not None:
                 new_k[..., :prev, :] = self.keys[..., :prev, :]
                 new_v[..., :prev, :] = self.values[..., :prev, :]
             self.keys, self.values = new_k, new_v
         self.keys[..., prev:prev + S, :] = keys
-        self.values[..., prev:prev + S, :] = values
+        if not self.keys_only:
+            self.values[..., prev:prev + S, :] = values
         self.offset = prev + S
         return self.keys[..., :self.offset, :], self.values[..., :self.offset, :]
 

@@ -1,9 +1,647 @@
-// Tensor-core flash-decode path (placeholder until the kernel lands).
+// Split-K flash decoding for head_dim 128 on tensor cores (sm_100a).
+//
+// One CTA = one (batch, kv head, sequence chunk).  All n_rep <= 8 query heads of
+// the group consume the same K/V bytes, so every KV byte is read once.
+//
+//   producer warp : streams 64-position tiles of K / V (and their norms) into a
+//                   4-stage shared-memory ring with cp.async.bulk (TMA, 1-D) and
+//                   mbarrier transaction counts; no multicast, local memory only.
+//   4 consumer warps: each owns 16 positions of a tile and keeps its own online
+//                   softmax state, so the main loop has no CTA-wide barrier.
+//       scores  : mma.sync m16n8k16 (f16 x f16 -> f32).  A = query rows (rows 0-7
+//                 the f16 high part, rows 8-15 the f16 residual, summed after the
+//                 MMA, so the query keeps ~22 bits), B = K^T built in registers:
+//                 fp16 keys come straight from shared memory; packed keys are
+//                 decoded two elements at a time through a lane-replicated pair
+//                 LUT in shared memory (conflict-free: entry * 32 + lane).
+//       values  : out^T[e][head] += Vc^T[e][p] * P[p][head]; Vc pairs come from the
+//                 same kind of LUT, position pairs are zipped with PRMT.
+//       The V norm is folded into the softmax exponent (log2 domain) so P stays
+//       <= 2^8 in f16 whatever the norms are; l is accumulated without it.
+//   The accumulator stays in the rotated domain; (m, l, acc) per split go to the
+//   workspace and the shared merge kernel applies butterfly * signs / dim / l.
+//
+// The element <-> MMA k-slot assignment is a free permutation as long as the
+// query fragments use the same one; it is chosen per key format so that each
+// thread reads contiguous bytes of a row (see kslot_element()).
+#include <cuda_fp16.h>
+
+#include <mutex>
+
 #include "flash.cuh"
+
 namespace tq {
-bool flash_mma_supported(const FlashArgs&) { return false; }
-int flash_mma_chunk_multiple() { return 64; }
-int launch_flash_mma(const FlashArgs&, int, cudaStream_t) {
-  return set_error(TQ_ERR_UNSUPPORTED, "tensor-core flash decode not built");
+namespace {
+
+constexpr int kDim = 128;
+constexpr int kTile = 64;              // positions per stage
+constexpr int kConsumerWarps = 4;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr int kStages = 4;
+constexpr int kDenseRowBytes = 320;    // 256 B of data + 64 B pad: odd rows shift by 64 B mod 128
+constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleThreshold = 8.0f;   // log2 units; P stays <= 2^8
+
+enum : int { KF_DENSE = 0, KF_POLAR3 = 3, KF_POLAR4 = 4 };
+
+struct MmaTables {
+  uint16_t k_c16[16];   // beta_k-scaled centroids as f16 bits
+  uint16_t v_c16[16];
+  float k_post;         // multiplies the raw MMA score: attn_scale * log2(e) [/ (dim * beta_k)]
+  float v_post;         // multiplies the accumulator when it is written: 1 / beta_v
+  int* status;          // set non-zero if a bounded wait gives up
+};
+
+template <int KF> struct KGeom;
+template <> struct KGeom<KF_DENSE> { static constexpr int row = kDenseRowBytes, lut = 0, norms = 0; };
+template <> struct KGeom<KF_POLAR3> { static constexpr int row = 52, lut = 64 * 32 * 4, norms = 256; };
+template <> struct KGeom<KF_POLAR4> { static constexpr int row = 64, lut = 256 * 32 * 4, norms = 256; };
+template <int VB> struct VGeom;
+template <> struct VGeom<3> { static constexpr int row = 52, lut = 64 * 32 * 4; };
+template <> struct VGeom<4> { static constexpr int row = 64, lut = 256 * 32 * 4; };
+
+template <int KF, int VB> struct Layout {
+  static constexpr int bars = 0;                         // 2 * kStages * 8 bytes
+  static constexpr int q = 128;                          // 16 rows x 128 halfs
+  static constexpr int klut = q + 16 * kDim * 2;
+  static constexpr int vlut = klut + KGeom<KF>::lut;
+  static constexpr int stage0 = vlut + VGeom<VB>::lut;
+  static constexpr int k_off = 0;
+  static constexpr int kn_off = kTile * KGeom<KF>::row;
+  static constexpr int v_off = kn_off + KGeom<KF>::norms;
+  static constexpr int vn_off = v_off + kTile * VGeom<VB>::row;
+  static constexpr int stage_bytes = vn_off + 256;
+  static constexpr int total = stage0 + kStages * stage_bytes;
+  static_assert(stage_bytes % 16 == 0 && stage0 % 16 == 0, "stage alignment");
+  static_assert(kStages * stage_bytes >= kConsumerWarps * (8 * kDim + 16) * 4, "epilogue reuse");
+};
+
+// ---- PTX wrappers -----------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
 }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+// Bounded wait: false when the phase did not complete within the spin limit.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float lg2(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float lds_f32(uint32_t addr) { return __uint_as_float(lds32(addr)); }
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Element of the head dimension that MMA k-step `ks`, k-slot `s` (0..15) stands
+// for, per key format.  Slots (2t, 2t+1) and (2t+8, 2t+9) belong to thread t of a
+// quad; the two slots of a pair are consecutive elements.
+template <int KF>
+__device__ __forceinline__ int kslot_element(int ks, int s) {
+  const int tt = (s & 7) >> 1, lo = s & 1, up = s >> 3;
+  if (KF == KF_DENSE) return 8 * (4 * (ks >> 1) + tt) + 4 * (ks & 1) + 2 * up + lo;
+  if (KF == KF_POLAR4) return 32 * tt + 4 * ks + 2 * up + lo;
+  const int pi = 2 * ks + up;   // pair index within the thread: 15 pairs in words 3t..3t+2, one in word 12
+  return (pi < 15 ? 30 * tt + 2 * pi : 120 + 2 * tt) + lo;
+}
+
+template <typename T>
+__device__ __forceinline__ float load_q(const void* base, int64_t idx) {
+  return to_f32<T>(reinterpret_cast<const T*>(base)[idx]);
+}
+
+// ---- the kernel ---------------------------------------------------------------------
+template <int KF, int VB>
+__global__ void __launch_bounds__(kThreads, 2)
+flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
+  using L = Layout<KF, VB>;
+  extern __shared__ __align__(128) uint8_t smem[];
+  const uint32_t sbase = smem_u32(smem);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int64_t pb = (int64_t)split * a.chunk;
+  const int64_t pe = min(a.seq_len, pb + a.chunk);
+  const int n_tiles = (int)((pe - pb + kTile - 1) / kTile);
+  const int h0 = kvh * a.n_rep;
+
+  auto full_bar = [&](int s) { return sbase + L::bars + 8 * s; };
+  auto empty_bar = [&](int s) { return sbase + L::bars + 8 * (kStages + s); };
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), kConsumerWarps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // pair LUTs: entry (i0 | i1 << bits) replicated per lane -> word index entry * 32 + lane
+  {
+    uint32_t* vl = reinterpret_cast<uint32_t*>(smem + L::vlut);
+    constexpr int nv = 1 << (2 * VB);
+    for (int i = tid; i < nv * 32; i += kThreads) {
+      const int e = i >> 5;
+      vl[i] = (uint32_t)tb.v_c16[e & ((1 << VB) - 1)] | ((uint32_t)tb.v_c16[e >> VB] << 16);
+    }
+    if (KF != KF_DENSE) {
+      constexpr int KB = KF == KF_POLAR3 ? 3 : 4;
+      uint32_t* kl = reinterpret_cast<uint32_t*>(smem + L::klut);
+      constexpr int nk = 1 << (2 * KB);
+      for (int i = tid; i < nk * 32; i += kThreads) {
+        const int e = i >> 5;
+        kl[i] = (uint32_t)tb.k_c16[e & ((1 << KB) - 1)] | ((uint32_t)tb.k_c16[e >> KB] << 16);
+      }
+    }
+  }
+  // query rows -> shared f16: row r = high part of head r, row 8 + r = residual
+  if (warp < kConsumerWarps) {
+    __half* qs = reinterpret_cast<__half*>(smem + L::q);
+    for (int r = warp; r < 8; r += kConsumerWarps) {
+      float v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float x = 0.f;
+        if (r < a.n_rep) {
+          const int64_t off = b * a.q_batch_stride + (int64_t)(h0 + r) * a.q_head_stride + lane * 4 + j;
+          x = a.q_dtype == TQ_F32 ? load_q<float>(a.q, off)
+              : a.q_dtype == TQ_F16 ? load_q<__half>(a.q, off)
+                                    : load_q<__nv_bfloat16>(a.q, off);
+        }
+        v[j] = x;
+      }
+      if (KF != KF_DENSE && !a.q_prerotated) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] *= sign_at(a.k_signs, lane * 4 + j);
+        warp_butterfly<4>(v, lane);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __half hi = __float2half_rn(v[j]);
+        const __half lo = __float2half_rn(v[j] - __half2float(hi));
+        qs[r * kDim + lane * 4 + j] = hi;
+        qs[(8 + r) * kDim + lane * 4 + j] = lo;
+      }
+    }
+  }
+  __syncthreads();
+
+  const uint8_t* kbase;
+  if (KF == KF_DENSE)
+    kbase = reinterpret_cast<const uint8_t*>(a.k_data) + (b * a.k_batch_stride + kvh * a.k_head_stride) * 2;
+  else
+    kbase = reinterpret_cast<const uint8_t*>(a.k_data) + (b * a.k_batch_stride + kvh * a.k_head_stride) * 4;
+  const uint8_t* vbase = reinterpret_cast<const uint8_t*>(a.v_data) + (b * a.v_batch_stride + kvh * a.v_head_stride) * 4;
+  const float* knbase = KF == KF_DENSE ? nullptr : a.k_norms + b * a.kn_batch_stride + kvh * a.kn_head_stride;
+  const float* vnbase = a.v_norms + b * a.vn_batch_stride + kvh * a.vn_head_stride;
+
+  // =============================== producer ===============================
+  if (warp == kConsumerWarps) {
+    for (int i = 0; i < n_tiles; ++i) {
+      const int s = i % kStages;
+      const uint32_t ph = (i / kStages) & 1;
+      if (i >= kStages && !mbar_wait(empty_bar(s), ph ^ 1)) {
+        if (lane == 0) atomicExch(tb.status, 1);
+        break;
+      }
+      const int64_t p0 = pb + (int64_t)i * kTile;
+      const int nvp = (int)min((int64_t)kTile, pe - p0);
+      const uint32_t st = sbase + L::stage0 + s * L::stage_bytes;
+      uint8_t* stg = smem + L::stage0 + s * L::stage_bytes;
+      // byte counts moved by bulk copies (multiples of 16); ragged remainders by plain loads
+      const uint32_t v_total = nvp * VGeom<VB>::row, v_bulk = v_total & ~15u;
+      const uint32_t n_total = nvp * 4, n_bulk = n_total & ~15u;
+      const uint32_t k_total = KF == KF_DENSE ? 0u : (uint32_t)nvp * KGeom<KF>::row, k_bulk = k_total & ~15u;
+      const uint8_t* vsrc = vbase + p0 * VGeom<VB>::row;
+      const uint8_t* ksrc = kbase + p0 * (KF == KF_DENSE ? 256 : KGeom<KF>::row);
+      {
+        const int w = lane;   // remainders are at most 3 words each
+        if (v_bulk + 4 * w < v_total)
+          *reinterpret_cast<uint32_t*>(stg + L::v_off + v_bulk + 4 * w) =
+              *reinterpret_cast<const uint32_t*>(vsrc + v_bulk + 4 * w);
+        if (n_bulk + 4 * w < n_total)
+          *reinterpret_cast<float*>(stg + L::vn_off + n_bulk + 4 * w) = vnbase[p0 + n_bulk / 4 + w];
+        if (KF != KF_DENSE) {
+          if (k_bulk + 4 * w < k_total)
+            *reinterpret_cast<uint32_t*>(stg + L::k_off + k_bulk + 4 * w) =
+                *reinterpret_cast<const uint32_t*>(ksrc + k_bulk + 4 * w);
+          if (n_bulk + 4 * w < n_total)
+            *reinterpret_cast<float*>(stg + L::kn_off + n_bulk + 4 * w) = knbase[p0 + n_bulk / 4 + w];
+        }
+      }
+      __syncwarp();
+      if (lane == 0) {
+        uint32_t tx = v_bulk + n_bulk;
+        tx += KF == KF_DENSE ? (uint32_t)nvp * 256u : k_bulk + n_bulk;
+        mbar_arrive_expect_tx(full_bar(s), tx);
+        if (v_bulk) bulk_g2s(st + L::v_off, vsrc, v_bulk, full_bar(s));
+        if (n_bulk) bulk_g2s(st + L::vn_off, vnbase + p0, n_bulk, full_bar(s));
+        if (KF != KF_DENSE) {
+          if (k_bulk) bulk_g2s(st + L::k_off, ksrc, k_bulk, full_bar(s));
+          if (n_bulk) bulk_g2s(st + L::kn_off, knbase + p0, n_bulk, full_bar(s));
+        }
+      }
+      __syncwarp();
+      if (KF == KF_DENSE) {
+        for (int r = lane; r < nvp; r += 32)
+          bulk_g2s(st + L::k_off + r * kDenseRowBytes, ksrc + (int64_t)r * 256, 256, full_bar(s));
+      }
+    }
+    return;
+  }
+
+  // =============================== consumers ===============================
+  // query fragments in the k-slot order of this key format
+  uint32_t aq[8][4];
+  {
+    const __half* qs = reinterpret_cast<const __half*>(smem + L::q);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const int e_lo = kslot_element<KF>(ks, 2 * t);
+      const int e_hi = kslot_element<KF>(ks, 2 * t + 8);
+      aq[ks][0] = *reinterpret_cast<const uint32_t*>(qs + g * kDim + e_lo);
+      aq[ks][1] = *reinterpret_cast<const uint32_t*>(qs + (g + 8) * kDim + e_lo);
+      aq[ks][2] = *reinterpret_cast<const uint32_t*>(qs + g * kDim + e_hi);
+      aq[ks][3] = *reinterpret_cast<const uint32_t*>(qs + (g + 8) * kDim + e_hi);
+    }
+  }
+  // V side: this thread's 16 elements are 16g .. 16g+15 (8 pairs)
+  const uint32_t lane4 = lane * 4;
+  const uint32_t vlut = sbase + L::vlut, klut = sbase + L::klut;
+  const int v_w0 = (16 * g) / 10;                       // first word holding element 16g (3-bit rows)
+  const int v_s0 = 3 * ((16 * g) % 10);                 // its bit offset inside that word
+  const int v_w2 = min(v_w0 + 2, 12);
+
+  float o[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;
+  const int pw = 16 * warp;   // first position of this warp inside a tile
+  bool ok = true;
+
+  for (int i = 0; i < n_tiles; ++i) {
+    const int s = i % kStages;
+    if (!mbar_wait(full_bar(s), (i / kStages) & 1)) {
+      if (lane == 0) atomicExch(tb.status, 2);
+      ok = false;
+      break;
+    }
+    const uint32_t st = sbase + L::stage0 + s * L::stage_bytes;
+    const int nvp = (int)min((int64_t)kTile, pe - (pb + (int64_t)i * kTile));
+
+    // ---------------- scores ----------------
+    float sc[2][4];
+#pragma unroll
+    for (int ng = 0; ng < 2; ++ng) {
+      sc[ng][0] = sc[ng][1] = sc[ng][2] = sc[ng][3] = 0.f;
+      const int prow = pw + 8 * ng + g;
+      if (KF == KF_DENSE) {
+        const uint32_t row = st + L::k_off + prow * kDenseRowBytes + t * 16;
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const uint4 r = lds128(row + it * 64);
+          mma16816(sc[ng], aq[2 * it], r.x, r.y);
+          mma16816(sc[ng], aq[2 * it + 1], r.z, r.w);
+        }
+      } else if (KF == KF_POLAR4) {
+        const uint4 w4 = lds128(st + L::k_off + prow * 64 + t * 16);
+        const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {
+          const uint32_t a0 = ((w[wi] << 7) & 0x7F80u) | lane4;
+          const uint32_t a1 = ((w[wi] >> 1) & 0x7F80u) | lane4;
+          const uint32_t a2 = ((w[wi] >> 9) & 0x7F80u) | lane4;
+          const uint32_t a3 = ((w[wi] >> 17) & 0x7F80u) | lane4;
+          mma16816(sc[ng], aq[2 * wi], lds32(klut + a0), lds32(klut + a1));
+          mma16816(sc[ng], aq[2 * wi + 1], lds32(klut + a2), lds32(klut + a3));
+        }
+      } else {
+        const uint32_t row = st + L::k_off + prow * 52;
+        uint32_t w[3];
+        w[0] = lds32(row + 12 * t);
+        w[1] = lds32(row + 12 * t + 4);
+        w[2] = lds32(row + 12 * t + 8);
+        const uint32_t w12 = lds32(row + 48) >> (6 * t);
+        uint32_t bq[16];
+#pragma unroll
+        for (int pi = 0; pi < 15; ++pi) {
+          const uint32_t ww = w[pi / 5];
+          const int sh = 6 * (pi % 5) - 7;
+          bq[pi] = ((sh >= 0 ? (ww >> sh) : (ww << (-sh))) & 0x1F80u) | lane4;
+        }
+        bq[15] = ((w12 << 7) & 0x1F80u) | lane4;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          mma16816(sc[ng], aq[ks], lds32(klut + bq[2 * ks]), lds32(klut + bq[2 * ks + 1]));
+      }
+    }
+
+    // ---------------- softmax (log2 domain) ----------------
+    // this thread: head g, positions pw + 8*ng + 2t + c
+    float s2[2][2], s2v[2][2];
+    float m_tile = -INFINITY;
+#pragma unroll
+    for (int ng = 0; ng < 2; ++ng)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int pos = pw + 8 * ng + 2 * t + c;
+        float v = (sc[ng][c] + sc[ng][c + 2]) * tb.k_post;
+        if (KF != KF_DENSE) v *= lds_f32(st + L::kn_off + pos * 4);
+        const float vn = lds_f32(st + L::vn_off + pos * 4);
+        const bool valid = pos < nvp;
+        s2[ng][c] = valid ? v : -INFINITY;
+        s2v[ng][c] = valid ? v + lg2(fmaxf(vn, 1e-26f)) : -INFINITY;
+        m_tile = fmaxf(m_tile, s2v[ng][c]);
+      }
+    m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 1));
+    m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 2));
+    const bool need = m_tile > m_run + kRescaleThreshold;   // also true for the first finite tile
+    if (__any_sync(0xffffffffu, need)) {
+      const float alpha = need ? (m_run == -INFINITY ? 0.f : ex2(m_run - m_tile)) : 1.f;
+      if (need) m_run = m_tile;
+      l_run *= alpha;
+      const float al0 = __shfl_sync(0xffffffffu, alpha, 8 * t);        // head 2t lives in lanes 8t..8t+3
+      const float al1 = __shfl_sync(0xffffffffu, alpha, 8 * t + 4);    // head 2t + 1
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o[j][0] *= al0; o[j][1] *= al1; o[j][2] *= al0; o[j][3] *= al1;
+      }
+    }
+    const float m_use = m_run == -INFINITY ? 0.f : m_run;
+    float pv[2][2];
+#pragma unroll
+    for (int ng = 0; ng < 2; ++ng)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        pv[ng][c] = ex2(s2v[ng][c] - m_use);
+        l_run += ex2(s2[ng][c] - m_use);
+      }
+    const uint32_t pb0 = pack_h2(pv[0][0], pv[0][1]);   // k = 2t, 2t+1      (positions pw + 2t ..)
+    const uint32_t pb1 = pack_h2(pv[1][0], pv[1][1]);   // k = 2t+8, 2t+9    (positions pw + 8 + 2t ..)
+
+    // ---------------- values ----------------
+    // positions handled by this thread as MMA k: pw + 2t, +1 and pw + 8 + 2t, +1
+    uint32_t xlo[4], xhi[4];
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) {
+      const int pos = pw + 2 * t + (q4 & 1) + 8 * (q4 >> 1);
+      if (VB == 3) {
+        const uint32_t row = st + L::v_off + pos * 52;
+        const uint32_t w0 = lds32(row + 4 * v_w0), w1 = lds32(row + 4 * v_w0 + 4), w2 = lds32(row + 4 * v_w2);
+        // 48-bit stream of this thread's 16 codes, element 16g first
+        xlo[q4] = (w0 >> v_s0) | (w1 << (30 - v_s0));
+        xhi[q4] = (w1 >> (2 + v_s0)) | (w2 << (28 - v_s0));
+      } else {
+        const uint2 w = lds64(st + L::v_off + pos * 64 + 8 * g);
+        xlo[q4] = w.x;
+        xhi[q4] = w.y;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      uint32_t lv[4];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        uint32_t addr;
+        if (VB == 3) {
+          // pair j = bits [6j, 6j+6) of the stream; LUT byte address = idx * 128 + lane * 4
+          if (j == 0) addr = (xlo[q4] << 7) & 0x1F80u;
+          else if (j == 1) addr = (xlo[q4] << 1) & 0x1F80u;
+          else if (j < 5) addr = (xlo[q4] >> (6 * j - 7)) & 0x1F80u;
+          else if (j == 5) addr = (__funnelshift_r(xlo[q4], xhi[q4], 23)) & 0x1F80u;
+          else addr = (xhi[q4] >> (6 * j - 32 - 7)) & 0x1F80u;
+        } else {
+          const uint32_t w = j < 4 ? xlo[q4] : xhi[q4];
+          const int sh = 8 * (j & 3) - 7;
+          addr = (sh >= 0 ? (w >> sh) : (w << 7)) & 0x7F80u;
+        }
+        lv[q4] = lds32(vlut + (addr | lane4));
+      }
+      uint32_t af[4];
+      af[0] = __byte_perm(lv[0], lv[1], 0x5410);   // element 16g+2j,   positions 2t, 2t+1
+      af[1] = __byte_perm(lv[0], lv[1], 0x7632);   // element 16g+2j+1, positions 2t, 2t+1
+      af[2] = __byte_perm(lv[2], lv[3], 0x5410);   // element 16g+2j,   positions 2t+8, 2t+9
+      af[3] = __byte_perm(lv[2], lv[3], 0x7632);
+      mma16816(o[j], af, pb0, pb1);
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty_bar(s));
+  }
+
+  // ---------------- CTA epilogue: merge the four warps, write the split's partial ----------------
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  asm volatile("bar.sync 1, 128;" ::: "memory");      // every consumer is done with the ring
+  float* red_o = reinterpret_cast<float*>(smem + L::stage0);             // [warp][head][128]
+  float* red_m = red_o + kConsumerWarps * 8 * kDim;                       // [warp][8]
+  float* red_l = red_m + kConsumerWarps * 8;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int e = 16 * g + 2 * j;
+    red_o[(warp * 8 + 2 * t) * kDim + e] = o[j][0];
+    red_o[(warp * 8 + 2 * t + 1) * kDim + e] = o[j][1];
+    red_o[(warp * 8 + 2 * t) * kDim + e + 1] = o[j][2];
+    red_o[(warp * 8 + 2 * t + 1) * kDim + e + 1] = o[j][3];
+  }
+  if (t == 0) {
+    red_m[warp * 8 + g] = m_run;
+    red_l[warp * 8 + g] = l_run;
+  }
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  if (!ok) return;
+  const int e = tid;   // 0..127
+  const int64_t n_rows = (int64_t)a.batch * a.n_q_heads;
+  for (int r = 0; r < a.n_rep; ++r) {
+    float m_star = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; ++w) m_star = fmaxf(m_star, red_m[w * 8 + r]);
+    float acc = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; ++w) {
+      const float mw = red_m[w * 8 + r];
+      const float f = mw == -INFINITY ? 0.f : ex2(mw - m_star);
+      acc += red_o[(w * 8 + r) * kDim + e] * f;
+      l += red_l[w * 8 + r] * f;
+    }
+    const int64_t row = (int64_t)b * a.n_q_heads + h0 + r;
+    a.part_acc[((int64_t)split * n_rows + row) * kDim + e] = acc * tb.v_post;
+    if (e == 0) {
+      a.part_m[(int64_t)split * n_rows + row] = m_star == -INFINITY ? -INFINITY : m_star * 0.6931471805599453f;
+      a.part_l[(int64_t)split * n_rows + row] = l;
+    }
+  }
+}
+
+// ---- host side: scaled f16 codebooks --------------------------------------------------
+struct ScaledBook {
+  float key[16];
+  int n;
+  uint16_t c16[16];
+  float beta;
+};
+
+// f16 has an 11-bit significand; rounding the centroids directly would leave a
+// fixed relative error of up to 2^-12 on each.  A common factor beta in [1, 2)
+// is searched so that every beta * c_i lands (almost) on an f16 value; 1/beta is
+// applied in float32 after the MMA.
+static void scale_codebook(const float* c, int n, ScaledBook* out) {
+  static std::mutex mu;
+  static ScaledBook cache[8];
+  static int n_cached = 0;
+  std::lock_guard<std::mutex> lock(mu);
+  for (int i = 0; i < n_cached; ++i) {
+    if (cache[i].n == n && memcmp(cache[i].key, c, n * sizeof(float)) == 0) {
+      *out = cache[i];
+      return;
+    }
+  }
+  float best_beta = 1.f;
+  double best_err = 1e30;
+  for (int step = 0; step < (1 << 16); ++step) {
+    const float beta = 1.0f + step * (1.0f / 65536.0f);
+    double worst = 0.0;
+    for (int i = 0; i < n && worst < best_err; ++i) {
+      if (c[i] == 0.f) continue;
+      const double exact = (double)beta * (double)c[i];
+      const double got = (double)__half2float(__float2half_rn((float)exact));
+      const double rel = fabs(got - exact) / fabs(exact);
+      if (rel > worst) worst = rel;
+    }
+    if (worst < best_err) {
+      best_err = worst;
+      best_beta = beta;
+    }
+  }
+  ScaledBook sb;
+  memset(&sb, 0, sizeof(sb));
+  sb.n = n;
+  memcpy(sb.key, c, n * sizeof(float));
+  sb.beta = best_beta;
+  for (int i = 0; i < n; ++i) {
+    const __half h = __float2half_rn(best_beta * c[i]);
+    sb.c16[i] = *reinterpret_cast<const uint16_t*>(&h);
+  }
+  if (n_cached < 8) cache[n_cached++] = sb;
+  *out = sb;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <int KF, int VB>
+static int launch_variant(const FlashArgs& a, const MmaTables& tb, int splits, cudaStream_t st) {
+  using L = Layout<KF, VB>;
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(flash_mma_kernel<KF, VB>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
+    if (e != cudaSuccess) return set_error(TQ_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    attr_done[dev] = true;
+  }
+  const dim3 grid(splits, a.n_kv_heads, a.batch);
+  flash_mma_kernel<KF, VB><<<grid, kThreads, L::total, st>>>(a, tb);
+  return check_launch("tq_flash_decode (mma)");
+}
+
+}  // namespace
+
+bool flash_mma_supported(const FlashArgs& a) {
+  if (a.dim != kDim || a.n_rep > 8 || a.mask != nullptr) return false;
+  if (a.v_format != TQ_KV_POLAR || (a.v_bits != 3 && a.v_bits != 4)) return false;
+  if (!aligned16(a.v_data) || a.v_batch_stride % 4 || a.v_head_stride % 4) return false;
+  if (!aligned16(a.v_norms) || a.vn_batch_stride % 4 || a.vn_head_stride % 4) return false;
+  if (a.k_format == TQ_KV_DENSE) {
+    if (a.k_dtype != TQ_F16) return false;
+    if (!aligned16(a.k_data) || a.k_batch_stride % 8 || a.k_head_stride % 8) return false;
+  } else if (a.k_format == TQ_KV_POLAR) {
+    if (a.k_bits != 3 && a.k_bits != 4) return false;
+    if (!aligned16(a.k_data) || a.k_batch_stride % 4 || a.k_head_stride % 4) return false;
+    if (!aligned16(a.k_norms) || a.kn_batch_stride % 4 || a.kn_head_stride % 4) return false;
+  } else {
+    return false;
+  }
+  return true;
+}
+
+int flash_mma_chunk_multiple() { return kTile; }
+
+int launch_flash_mma(const FlashArgs& a, int splits, int* status, cudaStream_t st) {
+  MmaTables tb;
+  memset(&tb, 0, sizeof(tb));
+  tb.status = status;
+  ScaledBook vb;
+  scale_codebook(a.v_cent.v, 1 << a.v_bits, &vb);
+  memcpy(tb.v_c16, vb.c16, sizeof(tb.v_c16));
+  tb.v_post = 1.0f / vb.beta;
+  tb.k_post = a.attn_scale * kLog2e;
+  int kf = KF_DENSE;
+  if (a.k_format == TQ_KV_POLAR) {
+    ScaledBook kb;
+    scale_codebook(a.k_cent.v, 1 << a.k_bits, &kb);
+    memcpy(tb.k_c16, kb.c16, sizeof(tb.k_c16));
+    tb.k_post = a.attn_scale * kLog2e / ((float)kDim * kb.beta);
+    kf = a.k_bits == 3 ? KF_POLAR3 : KF_POLAR4;
+  }
+  if (kf == KF_DENSE) return a.v_bits == 3 ? launch_variant<KF_DENSE, 3>(a, tb, splits, st) : launch_variant<KF_DENSE, 4>(a, tb, splits, st);
+  if (kf == KF_POLAR3) return a.v_bits == 3 ? launch_variant<KF_POLAR3, 3>(a, tb, splits, st) : launch_variant<KF_POLAR3, 4>(a, tb, splits, st);
+  return a.v_bits == 3 ? launch_variant<KF_POLAR4, 3>(a, tb, splits, st) : launch_variant<KF_POLAR4, 4>(a, tb, splits, st);
+}
+
 }  // namespace tq

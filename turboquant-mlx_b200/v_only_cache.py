@@ -23,11 +23,22 @@ class VOnlyTurboQuantCache:
 
     def __init__(self, bits: int = 3, seed: int = 42, no_v_buffer: bool = False,
                  fused: bool = False):
-        self._k_cache = KVCache()
+        self._k_cache = KVCache(keys_only=True)
         self._v_tq = TurboQuantKVCache(bits=bits, seed=seed, v_only=True, fused=fused)
         self._v_bits = bits
         self._no_v_buffer = no_v_buffer
         self.fused = fused
+
+    def reserve(self, B, H, n_positions, k_dim, v_dim, dtype=torch.float16, device=None):
+        """Pre-size K and V storage for `n_positions` so inserts never reallocate."""
+        self._v_tq.reserve(B, H, n_positions, k_dim, v_dim, device)
+        kc = self._k_cache
+        if kc.keys is None or kc.keys.shape[2] < n_positions:
+            new_k = torch.zeros((B, H, n_positions, k_dim), dtype=dtype, device=self._v_tq.v_packed.device)
+            if kc.keys is not None:
+                new_k[..., :kc.offset, :] = kc.keys[..., :kc.offset, :]
+            kc.keys = new_k
+            kc.values = torch.zeros((B, H, n_positions, 0), dtype=dtype, device=new_k.device)
 
     def update_and_fetch(self, keys, values):
         """Store K as is, compress V, return (K, V_dequant)."""
