@@ -203,6 +203,14 @@ def gpu_arm(args):
     # ---- device-resident step: 28 flash-decode launches, captured as one graph ----
     from turboquant_mlx_b200.v_only_cache import v_only_attention
 
+    if args.kernel_only:
+        for _ in range(args.warmup + args.steps):
+            for layer in range(N_LAYERS):
+                v_only_attention(q_dev[layer], caches[layer], scale)
+        torch.cuda.synchronize()
+        print(json.dumps({"kernel_only": True, "layers": N_LAYERS, "launches": (args.warmup + args.steps) * N_LAYERS}))
+        return
+
     def device_step():
         for layer in range(N_LAYERS):
             out_dev[layer].copy_(v_only_attention(q_dev[layer], caches[layer], scale))
@@ -316,11 +324,11 @@ def gpu_arm(args):
                    "e2e_path": "CUDA-graph replay of H2D(q,k,v) -> append -> hooked SDPA -> D2H, ctx held at 32768"},
         "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": ms_e2e},
-        "gpu_launches": args.steps * N_LAYERS * 2,
+        "gpu_launches": args.steps * N_LAYERS,
         "clocks": sampler.summary(),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind,
-                     "kernel": "flash decode (+ split merge)", "us_per_launch": launch_ms * 1e3,
+                     "kernel": "flash_mma_kernel (split-K flash decode, merge fused)", "us_per_launch": launch_ms * 1e3,
                      "bytes_per_launch": ALGO_BYTES_LAYER},
     }
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -336,13 +344,19 @@ def gpu_arm(args):
 
 
 def main():
+    global N_LAYERS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--layers", type=int, default=28,
+                    help="layers (independent KV buffers) per step; fewer for a profiler capture")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="plain launches of the flash-decode kernel only (no graph, no e2e): profiler case")
     args = ap.parse_args()
+    N_LAYERS = args.layers
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
         reference_arm(args)

@@ -180,8 +180,24 @@ typedef struct tq_flash_params {
   void* stream;
 } tq_flash_params;
 
+/* Workspace contract: 16-byte aligned, at least tq_flash_decode_workspace_bytes()
+ * bytes.  It starts with a header of tq_flash_decode_header_bytes(batch,
+ * n_kv_heads) bytes (a status block and split counters) that must be zero the
+ * first time the workspace is used; every call leaves the counters at zero, so
+ * a workspace can be reused by later calls with the same batch * n_kv_heads.
+ * Zero the header again before reusing the memory with a different
+ * batch * n_kv_heads or after any other use.  Calls that share a workspace must
+ * not overlap on the GPU. */
+int64_t tq_flash_decode_header_bytes(int batch, int n_kv_heads);
 int64_t tq_flash_decode_workspace_bytes(const tq_flash_params* p);
 int tq_flash_decode(const tq_flash_params* p);
+/* Which kernel the calling thread's last tq_flash_decode launched: 1 = tensor-core
+ * path (dim 128, n_rep <= 8, fp16 or 3/4-bit packed keys, 3/4-bit packed values,
+ * 16-byte aligned rows, no mask), 0 = general float32 path, -1 = none yet.  The
+ * workspace's first 16 bytes are a status header for the tensor-core path: the
+ * caller zero-fills it once; a kernel whose bounded wait gives up writes a
+ * non-zero word there.  Diagnostic, no reference counterpart. */
+int tq_flash_decode_last_kernel(void);
 
 /* Merge n_parts partial states (split-K chunks or ranks) laid out
  * (n_parts, n_rows[, dim]) contiguous: m* = max m_i, l* = sum l_i e^(m_i - m*),

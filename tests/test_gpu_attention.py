@@ -231,7 +231,8 @@ def test_partials_merge_across_chunks_equals_whole(tq, oracle, golden, dev):
         ms.append(m[0]); ls.append(l[0]); accs.append(acc[0])
     ms.append(torch.zeros_like(ms[0])); ls.append(torch.zeros_like(ls[0])); accs.append(torch.zeros_like(accs[0]))
     merged = tq.merge_partials(torch.stack(ms), torch.stack(ls), torch.stack(accs), v["signs"])
-    assert _rel(merged.cpu().numpy(), whole[0].cpu().numpy()) < 1e-5
+    # `whole` ran on the tensor-core kernel (f16 operands), the ragged chunks on the float32 one
+    assert _rel(merged.cpu().numpy(), whole[0].cpu().numpy()) < 1e-3
     assert _rel(merged.cpu().numpy(), g["att_out_dense"]) < ATT_TOL
     ref = oracle.merge_partials(torch.stack(ms).cpu().numpy(), torch.stack(ls).cpu().numpy(),
                                 torch.stack(accs).cpu().numpy(), g["signs_43"], 128)
@@ -277,3 +278,56 @@ def test_affine_k8_with_polar_and_affine_values(tq, oracle, dev, v_bits):
                                          v_polar=dict(packed=vp[b], norms=vn[b], centroids=oracle.codebook(3),
                                                       signs=vq.signs.cpu().numpy(), bits=3))
         assert _rel(out2[b].cpu().numpy(), ref) < ATT_TOL
+
+
+def test_tensor_core_path_is_taken_and_accurate(tq, oracle, dev):
+    """Shapes that qualify (dim 128, n_rep <= 8, aligned rows, no mask) must run
+    the tensor-core kernel; its result stays within tolerance of the oracle for
+    fp16 keys and for 3/4-bit packed keys, including a ragged last tile and
+    large / tiny V norms."""
+    L = tq._lib.lib()
+    rng = np.random.default_rng(21)
+    n_kv, n_rep, S, D = 2, 7, 1531, 128
+    scale = 1.0 / math.sqrt(D)
+    vq = tq.PolarQuantizer(D, 3, seed=43, device=dev)
+    vs = vq.signs.cpu().numpy()
+    vraw = (rng.standard_normal((n_kv, S, D)) * rng.lognormal(0, 1.5, (n_kv, S, 1))).astype(np.float32)
+    vraw[0, 5] = 0.0
+    vraw[1, 7] *= 3000.0
+    vp, vn = oracle.quantize_packed(vraw, vs, 3)
+
+    def alloc(x, n_alloc=1536):   # rows live in a longer allocation, as in a cache (16-byte aligned heads)
+        full = np.zeros((x.shape[0], n_alloc) + x.shape[2:], x.dtype)
+        full[:, :S] = x
+        return _t(full, dev)[:, :S].unsqueeze(0)
+
+    v = dict(format="polar", packed=alloc(vp), norms=alloc(vn), centroids=vq.centroids, signs=vq.signs, bits=3)
+    vdesc = dict(packed=vp, norms=vn, centroids=oracle.codebook(3), signs=vs, bits=3)
+    q = rng.standard_normal((n_kv * n_rep, D)).astype(np.float16)
+    kd = rng.standard_normal((n_kv, S, D)).astype(np.float16)
+    out = tq.flash_decode(_t(q, dev).unsqueeze(0), k=dict(format="dense", data=_t(kd, dev).unsqueeze(0)), v=v,
+                          attn_scale=scale, out_dtype=torch.float32)
+    assert L.tq_flash_decode_last_kernel() == 1
+    ref, _ = oracle.decode_attention(q, k_dense=kd, v_polar=vdesc, attn_scale=scale, n_rep=n_rep)
+    assert _rel(out[0].cpu().numpy(), ref) < ATT_TOL
+    for kbits in (3, 4):
+        kq = tq.PolarQuantizer(D, kbits, seed=42, device=dev)
+        ks = kq.signs.cpu().numpy()
+        kraw = (rng.standard_normal((n_kv, S, D)) * rng.lognormal(0, 0.5, (n_kv, S, 1))).astype(np.float16)
+        kp, kn = oracle.quantize_packed(kraw, ks, kbits)
+        kpol = dict(format="polar", packed=alloc(kp), norms=alloc(kn), centroids=kq.centroids, signs=kq.signs,
+                    bits=kbits)
+        out = tq.flash_decode(_t(q, dev).unsqueeze(0), k=kpol, v=v, attn_scale=scale, out_dtype=torch.float32)
+        assert L.tq_flash_decode_last_kernel() == 1
+        ref, _ = oracle.decode_attention(
+            q, k_polar=dict(packed=kp, norms=kn, centroids=oracle.codebook(kbits), signs=ks, bits=kbits),
+            v_polar=vdesc, attn_scale=scale, n_rep=n_rep)
+        assert _rel(out[0].cpu().numpy(), ref) < ATT_TOL
+    # a mask sends the same call down the general path
+    out = tq.flash_decode(_t(q, dev).unsqueeze(0), k=kpol, v=v, attn_scale=scale, out_dtype=torch.float32,
+                          mask=torch.zeros((1, 1, S), device=dev))
+    assert L.tq_flash_decode_last_kernel() == 0
+    assert _rel(out[0].cpu().numpy(), ref) < ATT_TOL
+    ws = tq._lib.workspace(16, dev, tag=f"flash{n_kv}")
+    hdr = L.tq_flash_decode_header_bytes(1, n_kv)
+    assert int(ws[:hdr].view(torch.int32).abs().sum()) == 0   # no bounded wait gave up, counters back at zero

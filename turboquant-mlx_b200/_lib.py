@@ -76,8 +76,10 @@ _SIGNATURES = {
     "tq_sparse_v_matvec": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int,
                                    c_int64, _FP, _FP, c_int, c_int, c_float, c_int, c_void_p,
                                    c_void_p, c_size_t, c_void_p]),
+    "tq_flash_decode_header_bytes": (c_int64, [c_int, c_int]),
     "tq_flash_decode_workspace_bytes": (c_int64, [POINTER(FlashParams)]),
     "tq_flash_decode": (c_int, [POINTER(FlashParams)]),
+    "tq_flash_decode_last_kernel": (c_int, []),
     "tq_merge_partials": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, _FP,
                                   c_void_p, c_int, c_int64, c_void_p]),
     "tq_affine_quantize": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p,
@@ -177,13 +179,16 @@ def host_floats(x):
 _workspaces: dict = {}
 
 
-def workspace(nbytes: int, device) -> torch.Tensor | None:
+def workspace(nbytes: int, device, tag: str = "flash") -> torch.Tensor | None:
+    """Zero-filled scratch tensor for one kind of call (`tag`): the flash-decode
+    workspace starts with counters that must stay zero between calls, so other
+    kernels never share it."""
     if nbytes <= 0:
         return None
-    key = (str(device), torch.cuda.current_stream(device).cuda_stream)
+    key = (tag, str(device), torch.cuda.current_stream(device).cuda_stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=device)
+        ws = torch.zeros(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
 

@@ -1,5 +1,6 @@
 // tq_flash_decode: argument validation, split-K planning, kernel choice, merge.
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -127,7 +128,8 @@ static int fill_args(const tq_flash_params* p, FlashArgs* a) {
 }
 
 static void make_plan(const tq_flash_params* p, const FlashArgs& a, Plan* plan) {
-  plan->mma = flash_mma_supported(a);
+  static const bool force_generic = getenv("TQ_FORCE_GENERIC") != nullptr;   // debugging aid
+  plan->mma = !force_generic && flash_mma_supported(a);
   const int mult = plan->mma ? flash_mma_chunk_multiple() : 32;
   const int rgroups = plan->mma ? 1 : (a.n_rep + 7) / 8;
   const int64_t groups = (int64_t)a.batch * a.n_kv_heads * rgroups;
@@ -140,6 +142,7 @@ static void make_plan(const tq_flash_params* p, const FlashArgs& a, Plan* plan) 
     if (splits > by_len) splits = by_len;
   }
   if (splits > max_splits) splits = max_splits;
+  if (plan->mma && splits > flash_mma_max_splits()) splits = flash_mma_max_splits();
   if (splits < 1) splits = 1;
   int64_t chunk = (a.seq_len + splits - 1) / splits;
   chunk = (chunk + mult - 1) / mult * mult;
@@ -147,15 +150,37 @@ static void make_plan(const tq_flash_params* p, const FlashArgs& a, Plan* plan) 
   plan->splits = (int)((a.seq_len + chunk - 1) / chunk);
 }
 
-static int64_t workspace_need(const tq_flash_params* p, const Plan& plan) {
-  if (p->out_mode == 1 && plan.splits == 1) return 0;
+// Workspace layout: [header][m][l][acc].  The header is a
+// 16-byte status block (word 0 is set non-zero by a kernel whose bounded wait
+// gave up) followed by one split counter per (batch, kv head); the caller
+// zero-fills the workspace once when it allocates it and the kernel leaves the
+// counters at zero after every call.
+static int64_t header_bytes(const tq_flash_params* p, const Plan&) {
+  return flash_mma_header_bytes(p->batch, p->n_kv_heads);   // reserved on both paths
+}
+static int64_t partial_bytes(const tq_flash_params* p, const Plan& plan) {
+  if (!plan.mma && p->out_mode == 1 && plan.splits == 1) return 0;
   const int64_t rows = (int64_t)p->batch * p->n_q_heads;
-  return (int64_t)plan.splits * rows * (p->dim + 2) * (int64_t)sizeof(float);
+  const int64_t parts = plan.splits + (plan.mma ? flash_mma_level1_parts() : 0);
+  return parts * rows * (p->dim + 2) * (int64_t)sizeof(float);
+}
+static int64_t workspace_need(const tq_flash_params* p, const Plan& plan) {
+  const int64_t part = partial_bytes(p, plan);
+  return (plan.mma || part > 0) ? header_bytes(p, plan) + part : 0;
 }
 
 }  // namespace tq
 
 using namespace tq;
+
+static thread_local int g_last_kernel = -1;
+
+extern "C" int tq_flash_decode_last_kernel(void) { return g_last_kernel; }
+
+extern "C" int64_t tq_flash_decode_header_bytes(int batch, int n_kv_heads) {
+  if (batch <= 0 || n_kv_heads <= 0) return 0;
+  return flash_mma_header_bytes(batch, n_kv_heads);
+}
 
 extern "C" int64_t tq_flash_decode_workspace_bytes(const tq_flash_params* p) {
   int rc = validate(p);
@@ -176,24 +201,52 @@ extern "C" int tq_flash_decode(const tq_flash_params* p) {
   make_plan(p, a, &plan);
   a.chunk = plan.chunk;
   const int64_t need = workspace_need(p, plan);
+  TQ_REQUIRE(need == 0 || ((uintptr_t)p->workspace & 15) == 0, TQ_ERR_MISALIGNED,
+             "workspace must be 16-byte aligned");
   TQ_REQUIRE(need == 0 || (p->workspace && p->workspace_bytes >= need), TQ_ERR_WORKSPACE,
              "workspace of %lld bytes required, got %lld", (long long)need,
              (long long)p->workspace_bytes);
   const int64_t rows = (int64_t)p->batch * p->n_q_heads;
-  if (need == 0) {
+  const bool direct = partial_bytes(p, plan) == 0;
+  float *l1_acc = nullptr, *l1_m = nullptr, *l1_l = nullptr;
+  if (direct) {
     a.part_m = p->part_m;
     a.part_l = p->part_l;
     a.part_acc = p->part_acc;
   } else {
-    float* ws = (float*)p->workspace;
-    a.part_m = ws;
-    a.part_l = ws + (int64_t)plan.splits * rows;
-    a.part_acc = ws + 2 * (int64_t)plan.splits * rows;
+    // [acc level 0][acc level 1][m0][l0][m1][l1]: both accumulator blocks stay 16-byte aligned
+    float* ws = (float*)((char*)p->workspace + header_bytes(p, plan));
+    const int64_t n1 = plan.mma ? flash_mma_level1_parts() : 0;
+    a.part_acc = ws;
+    l1_acc = ws + (int64_t)plan.splits * rows * p->dim;
+    float* sc = l1_acc + n1 * rows * p->dim;
+    a.part_m = sc;
+    a.part_l = sc + (int64_t)plan.splits * rows;
+    l1_m = sc + 2 * (int64_t)plan.splits * rows;
+    l1_l = l1_m + n1 * rows;
   }
   cudaStream_t st = (cudaStream_t)p->stream;
-  rc = plan.mma ? launch_flash_mma(a, plan.splits, st) : launch_flash_generic(a, plan.splits, st);
+  g_last_kernel = plan.mma ? 1 : 0;
+  if (plan.mma) {   // the kernel's last CTA per (batch, kv head) merges and writes the output
+    MmaOutput mo;
+    mo.status = (int*)p->workspace;
+    mo.counters = (int*)p->workspace + 4;
+    mo.out_mode = p->out_mode;
+    mo.out_dtype = p->out_dtype;
+    mo.out = p->out;
+    mo.out_batch_stride = p->out_batch_stride;
+    mo.out_head_stride = p->out_head_stride;
+    mo.om = p->part_m;
+    mo.ol = p->part_l;
+    mo.oacc = p->part_acc;
+    mo.l1_m = l1_m;
+    mo.l1_l = l1_l;
+    mo.l1_acc = l1_acc;
+    return launch_flash_mma(a, plan.splits, mo, st);
+  }
+  rc = launch_flash_generic(a, plan.splits, st);
   if (rc) return rc;
-  if (need == 0) return TQ_OK;
+  if (direct) return TQ_OK;
   const int rotate = p->v_format == TQ_KV_POLAR;
   return launch_merge(a.part_m, a.part_l, a.part_acc, plan.splits, rows, p->dim, rotate, a.v_signs,
                       p->out_mode == 0, p->out, p->out_dtype, p->out_head_stride, p->n_q_heads,

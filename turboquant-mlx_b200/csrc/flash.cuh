@@ -52,7 +52,23 @@ int launch_flash_generic(const FlashArgs& a, int splits, cudaStream_t st);
 // qualify; the caller then takes the generic kernel.
 bool flash_mma_supported(const FlashArgs& a);
 int flash_mma_chunk_multiple();
-int launch_flash_mma(const FlashArgs& a, int splits, cudaStream_t st);
+struct MmaOutput {       // where the tensor-core kernel's fused merge writes
+  int* status;           // workspace header word 0
+  int* counters;         // batch * n_kv_heads ints after the header, zero between calls
+  int out_mode, out_dtype;
+  void* out;
+  int64_t out_batch_stride, out_head_stride;
+  float* om;
+  float* ol;
+  float* oacc;
+  float* l1_m;           // level-1 partials: flash_mma_level1_parts() x rows [x dim]
+  float* l1_l;
+  float* l1_acc;
+};
+int64_t flash_mma_header_bytes(int batch, int n_kv_heads);
+int flash_mma_max_splits();
+int flash_mma_level1_parts();
+int launch_flash_mma(const FlashArgs& a, int splits, const MmaOutput& mo, cudaStream_t st);
 
 int launch_merge(const float* pm, const float* pl, const float* pacc, int n_parts, int64_t n_rows,
                  int dim, int rotate, const SignMask& signs, int finalize, void* out, int out_dtype,

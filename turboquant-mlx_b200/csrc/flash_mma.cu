@@ -38,10 +38,12 @@ constexpr int kTile = 64;              // positions per stage
 constexpr int kConsumerWarps = 4;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr int kStages = 4;
-constexpr int kDenseRowBytes = 320;    // 256 B of data + 64 B pad: odd rows shift by 64 B mod 128
+constexpr int kDenseRowBytes = 256;    // rows as in memory: one bulk copy per tile (2-way LDS.128 conflicts accepted)
 constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units; P stays <= 2^8
+constexpr int kMaxMerge = 16;               // partial states one merge call combines
+constexpr int kCtrPerGroup = kMaxMerge + 1; // level-1 counters + the top counter
 
 enum : int { KF_DENSE = 0, KF_POLAR3 = 3, KF_POLAR4 = 4 };
 
@@ -51,6 +53,19 @@ struct MmaTables {
   float k_post;         // multiplies the raw MMA score: attn_scale * log2(e) [/ (dim * beta_k)]
   float v_post;         // multiplies the accumulator when it is written: 1 / beta_v
   int* status;          // set non-zero if a bounded wait gives up
+  int* counters;        // kCtrPerGroup per (batch, kv head); zero between calls
+  int splits;           // level-0 partials per (batch, kv head)
+  int group;            // splits merged by one level-1 merge (<= kMaxMerge)
+  int n_groups;         // level-1 partials per (batch, kv head) (<= kMaxMerge); 1 = single level
+  float* l1_m;          // level-1 partial state (n_groups, rows[, dim])
+  float* l1_l;
+  float* l1_acc;
+  int out_mode, out_dtype;
+  void* out;
+  int64_t out_batch_stride, out_head_stride;
+  float* om;            // merged partial outputs (out_mode 1)
+  float* ol;
+  float* oacc;
 };
 
 template <int KF> struct KGeom;
@@ -167,6 +182,35 @@ __device__ __forceinline__ float load_q(const void* base, int64_t idx) {
   return to_f32<T>(reinterpret_cast<const T*>(base)[idx]);
 }
 
+// Merge `count` (<= kMaxMerge) partial states of one output row, one warp per row:
+// lane i owns the weight of part i, every lane owns 4 accumulator elements.  All
+// loads are issued before the first use so one L2 round trip covers the merge.
+__device__ __forceinline__ void merge_parts(const float* pm, const float* pl, const float* pacc,
+                                            int64_t n_rows, int64_t row, int first, int count,
+                                            int lane, float& m_star, float& l_star, float4& acc4) {
+  float mi = -INFINITY, li = 0.f;
+  if (lane < count) {
+    li = __ldcg(pl + (int64_t)(first + lane) * n_rows + row);
+    mi = __ldcg(pm + (int64_t)(first + lane) * n_rows + row);
+  }
+  float4 v[kMaxMerge];
+#pragma unroll
+  for (int i = 0; i < kMaxMerge; ++i) {
+    v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < count)
+      v[i] = __ldcg(reinterpret_cast<const float4*>(pacc + ((int64_t)(first + i) * n_rows + row) * kDim) + lane);
+  }
+  m_star = warp_max(li > 0.f ? mi : -INFINITY);
+  const float w = li > 0.f ? __expf(mi - m_star) : 0.f;
+  l_star = warp_sum(li * w);
+  acc4 = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int i = 0; i < kMaxMerge; ++i) {
+    const float wi = __shfl_sync(0xffffffffu, w, i);
+    acc4.x += v[i].x * wi; acc4.y += v[i].y * wi; acc4.z += v[i].z * wi; acc4.w += v[i].w * wi;
+  }
+}
+
 // ---- the kernel ---------------------------------------------------------------------
 template <int KF, int VB>
 __global__ void __launch_bounds__(kThreads, 2)
@@ -185,6 +229,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   auto full_bar = [&](int s) { return sbase + L::bars + 8 * s; };
   auto empty_bar = [&](int s) { return sbase + L::bars + 8 * (kStages + s); };
 
+  __shared__ uint16_t c16_s[32];
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(full_bar(s), 1);
@@ -192,21 +237,25 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  if (tid < 16) c16_s[tid] = tb.v_c16[tid];
+  else if (tid < 32) c16_s[tid] = tb.k_c16[tid - 16];
+  __syncthreads();   // barriers and codebooks visible; the producer leaves for its loop now
   // pair LUTs: entry (i0 | i1 << bits) replicated per lane -> word index entry * 32 + lane
-  {
+  if (warp < kConsumerWarps) {
+    constexpr int kCT = kConsumerWarps * 32;
     uint32_t* vl = reinterpret_cast<uint32_t*>(smem + L::vlut);
     constexpr int nv = 1 << (2 * VB);
-    for (int i = tid; i < nv * 32; i += kThreads) {
+    for (int i = tid; i < nv * 32; i += kCT) {
       const int e = i >> 5;
-      vl[i] = (uint32_t)tb.v_c16[e & ((1 << VB) - 1)] | ((uint32_t)tb.v_c16[e >> VB] << 16);
+      vl[i] = (uint32_t)c16_s[e & ((1 << VB) - 1)] | ((uint32_t)c16_s[e >> VB] << 16);
     }
     if (KF != KF_DENSE) {
       constexpr int KB = KF == KF_POLAR3 ? 3 : 4;
       uint32_t* kl = reinterpret_cast<uint32_t*>(smem + L::klut);
       constexpr int nk = 1 << (2 * KB);
-      for (int i = tid; i < nk * 32; i += kThreads) {
+      for (int i = tid; i < nk * 32; i += kCT) {
         const int e = i >> 5;
-        kl[i] = (uint32_t)tb.k_c16[e & ((1 << KB) - 1)] | ((uint32_t)tb.k_c16[e >> KB] << 16);
+        kl[i] = (uint32_t)c16_s[16 + (e & ((1 << KB) - 1))] | ((uint32_t)c16_s[16 + (e >> KB)] << 16);
       }
     }
   }
@@ -239,8 +288,8 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         qs[(8 + r) * kDim + lane * 4 + j] = lo;
       }
     }
+    asm volatile("bar.sync 1, 128;" ::: "memory");   // consumers only: tables and query rows ready
   }
-  __syncthreads();
 
   const uint8_t* kbase;
   if (KF == KF_DENSE)
@@ -278,7 +327,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         if (n_bulk + 4 * w < n_total)
           *reinterpret_cast<float*>(stg + L::vn_off + n_bulk + 4 * w) = vnbase[p0 + n_bulk / 4 + w];
         if (KF != KF_DENSE) {
-          if (k_bulk + 4 * w < k_total)
+          if (k_total != 0 && k_bulk + 4 * w < k_total)
             *reinterpret_cast<uint32_t*>(stg + L::k_off + k_bulk + 4 * w) =
                 *reinterpret_cast<const uint32_t*>(ksrc + k_bulk + 4 * w);
           if (n_bulk + 4 * w < n_total)
@@ -290,6 +339,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         uint32_t tx = v_bulk + n_bulk;
         tx += KF == KF_DENSE ? (uint32_t)nvp * 256u : k_bulk + n_bulk;
         mbar_arrive_expect_tx(full_bar(s), tx);
+        if (KF == KF_DENSE) bulk_g2s(st + L::k_off, ksrc, (uint32_t)nvp * 256u, full_bar(s));
         if (v_bulk) bulk_g2s(st + L::v_off, vsrc, v_bulk, full_bar(s));
         if (n_bulk) bulk_g2s(st + L::vn_off, vnbase + p0, n_bulk, full_bar(s));
         if (KF != KF_DENSE) {
@@ -298,10 +348,6 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         }
       }
       __syncwarp();
-      if (KF == KF_DENSE) {
-        for (int r = lane; r < nvp; r += 32)
-          bulk_g2s(st + L::k_off + r * kDenseRowBytes, ksrc + (int64_t)r * 256, 256, full_bar(s));
-      }
     }
     return;
   }
@@ -353,12 +399,17 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       const int prow = pw + 8 * ng + g;
       if (KF == KF_DENSE) {
         const uint32_t row = st + L::k_off + prow * kDenseRowBytes + t * 16;
+        float sc2[4] = {0.f, 0.f, 0.f, 0.f};   // second accumulator: two independent MMA chains
+        uint4 r[4];
+#pragma unroll
+        for (int it = 0; it < 4; ++it) r[it] = lds128(row + it * 64);
 #pragma unroll
         for (int it = 0; it < 4; ++it) {
-          const uint4 r = lds128(row + it * 64);
-          mma16816(sc[ng], aq[2 * it], r.x, r.y);
-          mma16816(sc[ng], aq[2 * it + 1], r.z, r.w);
+          mma16816(sc[ng], aq[2 * it], r[it].x, r[it].y);
+          mma16816(sc2, aq[2 * it + 1], r[it].z, r[it].w);
         }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) sc[ng][c] += sc2[c];
       } else if (KF == KF_POLAR4) {
         const uint4 w4 = lds128(st + L::k_off + prow * 64 + t * 16);
         const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
@@ -465,7 +516,8 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
           else if (j == 1) addr = (xlo[q4] << 1) & 0x1F80u;
           else if (j < 5) addr = (xlo[q4] >> (6 * j - 7)) & 0x1F80u;
           else if (j == 5) addr = (__funnelshift_r(xlo[q4], xhi[q4], 23)) & 0x1F80u;
-          else addr = (xhi[q4] >> (6 * j - 32 - 7)) & 0x1F80u;
+          else if (j == 6) addr = (xhi[q4] << 3) & 0x1F80u;     // stream bits 36..41 = xhi bits 4..9
+          else addr = (xhi[q4] >> 3) & 0x1F80u;                  // stream bits 42..47 = xhi bits 10..15
         } else {
           const uint32_t w = j < 4 ? xlo[q4] : xhi[q4];
           const int sh = 8 * (j & 3) - 7;
@@ -524,6 +576,84 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
     if (e == 0) {
       a.part_m[(int64_t)split * n_rows + row] = m_star == -INFINITY ? -INFINITY : m_star * 0.6931471805599453f;
       a.part_l[(int64_t)split * n_rows + row] = l;
+    }
+  }
+
+  // ---------------- two-level merge, no waiting anywhere ----------------
+  // Every CTA publishes its partial and bumps the counter of its group of `group`
+  // splits; the CTA that completes a group merges it into a level-1 partial and
+  // bumps the top counter; the CTA that completes the last group merges the
+  // level-1 partials, applies butterfly * signs / dim / l and writes the output.
+  // Counters are reset by whoever completes them, so they are zero between calls.
+  __shared__ int flag_s;
+  int* ctr = tb.counters + (b * a.n_kv_heads + kvh) * kCtrPerGroup;
+  const float* src_m = a.part_m;
+  const float* src_l = a.part_l;
+  const float* src_acc = a.part_acc;
+  int n_final = tb.splits;
+  if (tb.n_groups > 1) {
+    const int gi = split / tb.group;
+    const int gsize = min(tb.group, tb.splits - gi * tb.group);
+    __threadfence();
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (tid == 0) {
+      const int prev = atomicAdd(ctr + 1 + gi, 1);
+      flag_s = prev == gsize - 1;
+      if (flag_s) ctr[1 + gi] = 0;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (!flag_s) return;
+    __threadfence();
+    for (int r = warp; r < a.n_rep; r += kConsumerWarps) {
+      const int64_t row = (int64_t)b * a.n_q_heads + h0 + r;
+      float m_star, l_star;
+      float4 acc4;
+      merge_parts(a.part_m, a.part_l, a.part_acc, n_rows, row, gi * tb.group, gsize, lane, m_star, l_star, acc4);
+      reinterpret_cast<float4*>(tb.l1_acc + ((int64_t)gi * n_rows + row) * kDim)[lane] = acc4;
+      if (lane == 0) {
+        tb.l1_m[(int64_t)gi * n_rows + row] = m_star;
+        tb.l1_l[(int64_t)gi * n_rows + row] = l_star;
+      }
+    }
+    src_m = tb.l1_m;
+    src_l = tb.l1_l;
+    src_acc = tb.l1_acc;
+    n_final = tb.n_groups;
+  }
+  __threadfence();
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  const int n_arrivals = tb.n_groups > 1 ? tb.n_groups : tb.splits;
+  if (tid == 0) {
+    const int prev = atomicAdd(ctr, 1);
+    flag_s = prev == n_arrivals - 1;
+    if (flag_s) ctr[0] = 0;
+  }
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  if (!flag_s) return;
+  __threadfence();
+  for (int r = warp; r < a.n_rep; r += kConsumerWarps) {
+    const int64_t row = (int64_t)b * a.n_q_heads + h0 + r;
+    float m_star, l_star;
+    float4 acc4;
+    merge_parts(src_m, src_l, src_acc, n_rows, row, 0, n_final, lane, m_star, l_star, acc4);
+    if (tb.out_mode == 1) {
+      reinterpret_cast<float4*>(tb.oacc + row * kDim)[lane] = acc4;
+      if (lane == 0) {
+        tb.om[row] = m_star;
+        tb.ol[row] = l_star;
+      }
+      continue;
+    }
+    float v[4] = {acc4.x, acc4.y, acc4.z, acc4.w};
+    warp_butterfly<4>(v, lane);
+    const float inv = l_star > 0.f ? (1.0f / kDim) / l_star : 0.f;
+    const int64_t ooff = b * tb.out_batch_stride + (int64_t)(h0 + r) * tb.out_head_stride + lane * 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float res = v[j] * sign_at(a.v_signs, lane * 4 + j) * inv;
+      if (tb.out_dtype == TQ_F32) reinterpret_cast<float*>(tb.out)[ooff + j] = res;
+      else if (tb.out_dtype == TQ_F16) reinterpret_cast<__half*>(tb.out)[ooff + j] = __float2half_rn(res);
+      else reinterpret_cast<__nv_bfloat16*>(tb.out)[ooff + j] = __float2bfloat16_rn(res);
     }
   }
 }
@@ -622,10 +752,37 @@ bool flash_mma_supported(const FlashArgs& a) {
 
 int flash_mma_chunk_multiple() { return kTile; }
 
-int launch_flash_mma(const FlashArgs& a, int splits, int* status, cudaStream_t st) {
+int64_t flash_mma_header_bytes(int batch, int n_kv_heads) {
+  return ((16 + 4 * (int64_t)kCtrPerGroup * batch * n_kv_heads) + 15) / 16 * 16;
+}
+int flash_mma_max_splits() { return kMaxMerge * kMaxMerge; }
+int flash_mma_level1_parts() { return kMaxMerge; }
+
+int launch_flash_mma(const FlashArgs& a, int splits, const MmaOutput& mo, cudaStream_t st) {
   MmaTables tb;
   memset(&tb, 0, sizeof(tb));
-  tb.status = status;
+  tb.status = mo.status;
+  tb.counters = mo.counters;
+  tb.splits = splits;
+  if (splits <= kMaxMerge) {
+    tb.group = splits;
+    tb.n_groups = 1;
+  } else {
+    tb.group = 1;
+    while (tb.group * tb.group < splits) ++tb.group;          // ceil(sqrt(splits)) <= kMaxMerge
+    tb.n_groups = (splits + tb.group - 1) / tb.group;
+  }
+  tb.l1_m = mo.l1_m;
+  tb.l1_l = mo.l1_l;
+  tb.l1_acc = mo.l1_acc;
+  tb.out_mode = mo.out_mode;
+  tb.out_dtype = mo.out_dtype;
+  tb.out = mo.out;
+  tb.out_batch_stride = mo.out_batch_stride;
+  tb.out_head_stride = mo.out_head_stride;
+  tb.om = mo.om;
+  tb.ol = mo.ol;
+  tb.oacc = mo.oacc;
   ScaledBook vb;
   scale_codebook(a.v_cent.v, 1 << a.v_bits, &vb);
   memcpy(tb.v_c16, vb.c16, sizeof(tb.v_c16));

@@ -201,7 +201,7 @@ def sparse_v_matvec(weights, v_packed, v_norms, centroids, signs, dim: int, bits
     out = torch.empty((n_q, dim), dtype=torch.float32, device=w.device)
     L = _lib.lib()
     need = L.tq_sparse_v_workspace_bytes(n_q, seq, dim)
-    ws = _lib.workspace(need, w.device)
+    ws = _lib.workspace(need, w.device, tag="sparse_v")
     _lib.check(L.tq_sparse_v_matvec(
         _lib.ptr(w), w.stride(0), _lib.ptr(vp), vp.stride(0), _lib.ptr(vn), vn.stride(0), n_kv,
         seq, _lib.host_floats(centroids), _lib.host_floats(signs), dim, bits, float(threshold),
@@ -349,7 +349,7 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
     need = L.tq_flash_decode_workspace_bytes(ctypes.byref(P))
     if need < 0:
         _lib.check(int(need))
-    ws = _lib.workspace(need, dev)
+    ws = _lib.workspace(need, dev, tag=f"flash{B * n_kv}")   # counters: one layout per batch * n_kv
     if ws is not None:
         P.workspace, P.workspace_bytes = ws.data_ptr(), ws.numel()
     _lib.check(L.tq_flash_decode(ctypes.byref(P)))
