@@ -15,7 +15,7 @@ from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libtqb200.so")
+LIB_PATH = os.environ.get("TQB200_LIB", os.path.join(_HERE, "libtqb200.so"))   # override: alternate builds
 
 TQ_F32, TQ_F16, TQ_BF16 = 0, 1, 2
 TQ_KV_POLAR, TQ_KV_DENSE, TQ_KV_AFFINE = 0, 1, 2

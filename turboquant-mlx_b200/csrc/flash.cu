@@ -136,7 +136,7 @@ static void make_plan(const tq_flash_params* p, const FlashArgs& a, Plan* plan) 
   const int64_t max_splits = (a.seq_len + mult - 1) / mult;
   int64_t splits = p->num_splits;
   if (splits <= 0) {
-    const int64_t target = 2LL * num_sms();
+    const int64_t target = (plan->mma ? flash_mma_ctas_per_sm() : 2) * (int64_t)num_sms();
     splits = (target + groups - 1) / groups;
     const int64_t by_len = (a.seq_len + 127) / 128;   // at least 128 positions per split
     if (splits > by_len) splits = by_len;

@@ -52,6 +52,7 @@ int launch_flash_generic(const FlashArgs& a, int splits, cudaStream_t st);
 // qualify; the caller then takes the generic kernel.
 bool flash_mma_supported(const FlashArgs& a);
 int flash_mma_chunk_multiple();
+int flash_mma_ctas_per_sm();
 struct MmaOutput {       // where the tensor-core kernel's fused merge writes
   int* status;           // workspace header word 0
   int* counters;         // batch * n_kv_heads ints after the header, zero between calls

@@ -34,16 +34,20 @@ namespace tq {
 namespace {
 
 constexpr int kDim = 128;
-constexpr int kTile = 64;              // positions per stage
-constexpr int kConsumerWarps = 4;
-constexpr int kThreads = (kConsumerWarps + 1) * 32;
-constexpr int kStages = 4;
+constexpr int kConsumerWarps = 12;     // 1 CTA per SM: 12 compute warps + 1 producer at ~145 registers
+constexpr int kTile = 16 * kConsumerWarps;   // positions per stage (16 per warp)
+constexpr int kChunkMultiple = 64;     // split boundaries: keeps every tile start 16-byte aligned
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kThreads = kConsumerThreads + 32;
+constexpr int kStages = 3;
 constexpr int kDenseRowBytes = 256;    // rows as in memory: one bulk copy per tile (2-way LDS.128 conflicts accepted)
 constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units; P stays <= 2^8
-constexpr int kMaxMerge = 16;               // partial states one merge call combines
-constexpr int kCtrPerGroup = kMaxMerge + 1; // level-1 counters + the top counter
+constexpr int kMaxMerge = 16;               // accumulator loads in flight per lane during a merge
+constexpr int kMaxParts = 64;               // partial states one merge call combines
+constexpr int kMaxGroups = 16;              // level-1 groups when there are more than kMaxParts splits
+constexpr int kCtrPerGroup = kMaxGroups + 1; // level-1 counters + the top counter
 
 enum : int { KF_DENSE = 0, KF_POLAR3 = 3, KF_POLAR4 = 4 };
 
@@ -55,8 +59,8 @@ struct MmaTables {
   int* status;          // set non-zero if a bounded wait gives up
   int* counters;        // kCtrPerGroup per (batch, kv head); zero between calls
   int splits;           // level-0 partials per (batch, kv head)
-  int group;            // splits merged by one level-1 merge (<= kMaxMerge)
-  int n_groups;         // level-1 partials per (batch, kv head) (<= kMaxMerge); 1 = single level
+  int group;            // splits merged by one level-1 merge (<= kMaxParts)
+  int n_groups;         // level-1 partials per (batch, kv head) (<= kMaxGroups); 1 = single level
   float* l1_m;          // level-1 partial state (n_groups, rows[, dim])
   float* l1_l;
   float* l1_acc;
@@ -70,8 +74,8 @@ struct MmaTables {
 
 template <int KF> struct KGeom;
 template <> struct KGeom<KF_DENSE> { static constexpr int row = kDenseRowBytes, lut = 0, norms = 0; };
-template <> struct KGeom<KF_POLAR3> { static constexpr int row = 52, lut = 64 * 32 * 4, norms = 256; };
-template <> struct KGeom<KF_POLAR4> { static constexpr int row = 64, lut = 256 * 32 * 4, norms = 256; };
+template <> struct KGeom<KF_POLAR3> { static constexpr int row = 52, lut = 64 * 32 * 4, norms = kTile * 4; };
+template <> struct KGeom<KF_POLAR4> { static constexpr int row = 64, lut = 256 * 32 * 4, norms = kTile * 4; };
 template <int VB> struct VGeom;
 template <> struct VGeom<3> { static constexpr int row = 52, lut = 64 * 32 * 4; };
 template <> struct VGeom<4> { static constexpr int row = 64, lut = 256 * 32 * 4; };
@@ -86,7 +90,7 @@ template <int KF, int VB> struct Layout {
   static constexpr int kn_off = kTile * KGeom<KF>::row;
   static constexpr int v_off = kn_off + KGeom<KF>::norms;
   static constexpr int vn_off = v_off + kTile * VGeom<VB>::row;
-  static constexpr int stage_bytes = vn_off + 256;
+  static constexpr int stage_bytes = vn_off + kTile * 4;
   static constexpr int total = stage0 + kStages * stage_bytes;
   static_assert(stage_bytes % 16 == 0 && stage0 % 16 == 0, "stage alignment");
   static_assert(kStages * stage_bytes >= kConsumerWarps * (8 * kDim + 16) * 4, "epilogue reuse");
@@ -182,16 +186,23 @@ __device__ __forceinline__ float load_q(const void* base, int64_t idx) {
   return to_f32<T>(reinterpret_cast<const T*>(base)[idx]);
 }
 
-// Merge `count` (<= kMaxMerge) partial states of one output row, one warp per row:
-// lane i owns the weight of part i, every lane owns 4 accumulator elements.  All
-// loads are issued before the first use so one L2 round trip covers the merge.
+// Merge `count` (<= kMaxParts) partial states of one output row, one warp per row:
+// lane i owns the weights of parts i and i + 32, every lane owns 4 accumulator
+// elements.  Accumulator loads go out in batches of kMaxMerge before their first
+// use, so a merge costs about one L2 round trip per batch.
 __device__ __forceinline__ void merge_parts(const float* pm, const float* pl, const float* pacc,
                                             int64_t n_rows, int64_t row, int first, int count,
                                             int lane, float& m_star, float& l_star, float4& acc4) {
-  float mi = -INFINITY, li = 0.f;
-  if (lane < count) {
-    li = __ldcg(pl + (int64_t)(first + lane) * n_rows + row);
-    mi = __ldcg(pm + (int64_t)(first + lane) * n_rows + row);
+  float mi[2], li[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int i = lane + 32 * h;
+    li[h] = 0.f;
+    mi[h] = -INFINITY;
+    if (i < count) {
+      li[h] = __ldcg(pl + (int64_t)(first + i) * n_rows + row);
+      mi[h] = __ldcg(pm + (int64_t)(first + i) * n_rows + row);
+    }
   }
   float4 v[kMaxMerge];
 #pragma unroll
@@ -200,20 +211,46 @@ __device__ __forceinline__ void merge_parts(const float* pm, const float* pl, co
     if (i < count)
       v[i] = __ldcg(reinterpret_cast<const float4*>(pacc + ((int64_t)(first + i) * n_rows + row) * kDim) + lane);
   }
-  m_star = warp_max(li > 0.f ? mi : -INFINITY);
-  const float w = li > 0.f ? __expf(mi - m_star) : 0.f;
-  l_star = warp_sum(li * w);
-  acc4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  m_star = warp_max(fmaxf(li[0] > 0.f ? mi[0] : -INFINITY, li[1] > 0.f ? mi[1] : -INFINITY));
+  float w[2];
 #pragma unroll
-  for (int i = 0; i < kMaxMerge; ++i) {
-    const float wi = __shfl_sync(0xffffffffu, w, i);
-    acc4.x += v[i].x * wi; acc4.y += v[i].y * wi; acc4.z += v[i].z * wi; acc4.w += v[i].w * wi;
+  for (int h = 0; h < 2; ++h) w[h] = li[h] > 0.f ? __expf(mi[h] - m_star) : 0.f;
+  l_star = warp_sum(li[0] * w[0] + li[1] * w[1]);
+  acc4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int base = 0; base < count; base += kMaxMerge) {
+    if (base > 0) {
+#pragma unroll
+      for (int i = 0; i < kMaxMerge; ++i) {
+        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (base + i < count)
+          v[i] = __ldcg(reinterpret_cast<const float4*>(pacc + ((int64_t)(first + base + i) * n_rows + row) * kDim) + lane);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kMaxMerge; ++i) {
+      const int part = base + i;                       // parts >= count carry weight 0
+      const float wi = __shfl_sync(0xffffffffu, part < 32 ? w[0] : w[1], part & 31);
+      acc4.x += v[i].x * wi; acc4.y += v[i].y * wi; acc4.z += v[i].z * wi; acc4.w += v[i].w * wi;
+    }
   }
 }
 
+// Optional per-CTA cycle stamps for tuning (build with -DTQ_TIMING; the stamps land
+// 2 MiB into the workspace, which must be at least 3 MiB).  Off in normal builds.
+#ifdef TQ_TIMING
+#define TQ_STAMP(slot)                                                                   \
+  do {                                                                                   \
+    if (lane == 0 && (warp == 0 || warp == kConsumerWarps))                              \
+      reinterpret_cast<long long*>(reinterpret_cast<char*>(tb.status) + (2 << 20))       \
+          [((blockIdx.x + gridDim.x * blockIdx.y) * 2 + (warp == 0 ? 0 : 1)) * 32 + (slot)] = clock64(); \
+  } while (0)
+#else
+#define TQ_STAMP(slot) do { } while (0)
+#endif
+
 // ---- the kernel ---------------------------------------------------------------------
 template <int KF, int VB>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 1)
 flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   using L = Layout<KF, VB>;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -226,6 +263,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   const int n_tiles = (int)((pe - pb + kTile - 1) / kTile);
   const int h0 = kvh * a.n_rep;
 
+  TQ_STAMP(0);
   auto full_bar = [&](int s) { return sbase + L::bars + 8 * s; };
   auto empty_bar = [&](int s) { return sbase + L::bars + 8 * (kStages + s); };
 
@@ -242,7 +280,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   __syncthreads();   // barriers and codebooks visible; the producer leaves for its loop now
   // pair LUTs: entry (i0 | i1 << bits) replicated per lane -> word index entry * 32 + lane
   if (warp < kConsumerWarps) {
-    constexpr int kCT = kConsumerWarps * 32;
+    constexpr int kCT = kConsumerThreads;
     uint32_t* vl = reinterpret_cast<uint32_t*>(smem + L::vlut);
     constexpr int nv = 1 << (2 * VB);
     for (int i = tid; i < nv * 32; i += kCT) {
@@ -288,7 +326,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         qs[(8 + r) * kDim + lane * 4 + j] = lo;
       }
     }
-    asm volatile("bar.sync 1, 128;" ::: "memory");   // consumers only: tables and query rows ready
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");   // consumers only: tables and query rows ready
   }
 
   const uint8_t* kbase;
@@ -309,6 +347,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         if (lane == 0) atomicExch(tb.status, 1);
         break;
       }
+      TQ_STAMP(1 + i);   // producer: about to issue tile i
       const int64_t p0 = pb + (int64_t)i * kTile;
       const int nvp = (int)min((int64_t)kTile, pe - p0);
       const uint32_t st = sbase + L::stage0 + s * L::stage_bytes;
@@ -380,6 +419,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   float m_run = -INFINITY, l_run = 0.f;
   const int pw = 16 * warp;   // first position of this warp inside a tile
   bool ok = true;
+  TQ_STAMP(1);   // consumer: set-up done
 
   for (int i = 0; i < n_tiles; ++i) {
     const int s = i % kStages;
@@ -390,6 +430,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
     }
     const uint32_t st = sbase + L::stage0 + s * L::stage_bytes;
     const int nvp = (int)min((int64_t)kTile, pe - (pb + (int64_t)i * kTile));
+    TQ_STAMP(2 + 2 * i);   // consumer: tile i arrived
 
     // ---------------- scores ----------------
     float sc[2][4];
@@ -534,51 +575,78 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(empty_bar(s));
+    TQ_STAMP(3 + 2 * i);   // consumer: tile i done
   }
+  TQ_STAMP(20);
 
-  // ---------------- CTA epilogue: merge the four warps, write the split's partial ----------------
-  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-  asm volatile("bar.sync 1, 128;" ::: "memory");      // every consumer is done with the ring
-  float* red_o = reinterpret_cast<float*>(smem + L::stage0);             // [warp][head][128]
-  float* red_m = red_o + kConsumerWarps * 8 * kDim;                       // [warp][8]
-  float* red_l = red_m + kConsumerWarps * 8;
+  // ---------------- CTA epilogue: pairwise tree over the consumer warps ----------------
+  // Round by round the upper half of the live warps hands (m, l, o) to the lower
+  // half through shared memory, [slot][value][lane] so every access is conflict
+  // free; l stays a per-thread partial until the end (it is linear).
+  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");   // every consumer is done with the ring
+  {
+    float* xch = reinterpret_cast<float*>(smem + L::stage0);             // [slot][34][32]
+    int live = kConsumerWarps;
+    while (live > 1) {
+      const int half = (live + 1) / 2;          // receivers 0 .. half-1, senders half .. live-1
+      if (warp >= half && warp < live) {
+        float* dst = xch + (warp - half) * 34 * 32 + lane;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const int e = 16 * g + 2 * j;
-    red_o[(warp * 8 + 2 * t) * kDim + e] = o[j][0];
-    red_o[(warp * 8 + 2 * t + 1) * kDim + e] = o[j][1];
-    red_o[(warp * 8 + 2 * t) * kDim + e + 1] = o[j][2];
-    red_o[(warp * 8 + 2 * t + 1) * kDim + e + 1] = o[j][3];
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) dst[(j * 4 + c) * 32] = o[j][c];
+        dst[32 * 32] = m_run;
+        dst[33 * 32] = l_run;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+      if (warp < live - half) {
+        const float* src = xch + warp * 34 * 32 + lane;
+        const float m_b = src[32 * 32], l_b = src[33 * 32];
+        const float m_new = fmaxf(m_run, m_b);
+        const float fa = m_run == -INFINITY ? 0.f : ex2(m_run - m_new);
+        const float fb = m_b == -INFINITY ? 0.f : ex2(m_b - m_new);
+        l_run = l_run * fa + l_b * fb;
+        m_run = m_new;
+        const float fa0 = __shfl_sync(0xffffffffu, fa, 8 * t), fa1 = __shfl_sync(0xffffffffu, fa, 8 * t + 4);
+        const float fb0 = __shfl_sync(0xffffffffu, fb, 8 * t), fb1 = __shfl_sync(0xffffffffu, fb, 8 * t + 4);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          o[j][0] = o[j][0] * fa0 + src[(j * 4 + 0) * 32] * fb0;
+          o[j][1] = o[j][1] * fa1 + src[(j * 4 + 1) * 32] * fb1;
+          o[j][2] = o[j][2] * fa0 + src[(j * 4 + 2) * 32] * fb0;
+          o[j][3] = o[j][3] * fa1 + src[(j * 4 + 3) * 32] * fb1;
+        }
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");   // slots free for the next round
+      live = half;
+    }
   }
-  if (t == 0) {
-    red_m[warp * 8 + g] = m_run;
-    red_l[warp * 8 + g] = l_run;
-  }
-  asm volatile("bar.sync 1, 128;" ::: "memory");
+  TQ_STAMP(24);   // tree merge done
   if (!ok) return;
-  const int e = tid;   // 0..127
   const int64_t n_rows = (int64_t)a.batch * a.n_q_heads;
-  for (int r = 0; r < a.n_rep; ++r) {
-    float m_star = -INFINITY;
+  if (warp == 0) {   // warp 0 now holds the CTA's state: head g in lanes 4g..4g+3, o columns = heads 2t, 2t+1
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    const int64_t row0 = (int64_t)b * a.n_q_heads + h0;
+    float* acc0 = a.part_acc + ((int64_t)split * n_rows + row0) * kDim;
 #pragma unroll
-    for (int w = 0; w < kConsumerWarps; ++w) m_star = fmaxf(m_star, red_m[w * 8 + r]);
-    float acc = 0.f, l = 0.f;
-#pragma unroll
-    for (int w = 0; w < kConsumerWarps; ++w) {
-      const float mw = red_m[w * 8 + r];
-      const float f = mw == -INFINITY ? 0.f : ex2(mw - m_star);
-      acc += red_o[(w * 8 + r) * kDim + e] * f;
-      l += red_l[w * 8 + r] * f;
+    for (int j = 0; j < 8; ++j) {
+      const int e = 16 * g + 2 * j;
+      if (2 * t < a.n_rep) {
+        acc0[(2 * t) * kDim + e] = o[j][0] * tb.v_post;
+        acc0[(2 * t) * kDim + e + 1] = o[j][2] * tb.v_post;
+      }
+      if (2 * t + 1 < a.n_rep) {
+        acc0[(2 * t + 1) * kDim + e] = o[j][1] * tb.v_post;
+        acc0[(2 * t + 1) * kDim + e + 1] = o[j][3] * tb.v_post;
+      }
     }
-    const int64_t row = (int64_t)b * a.n_q_heads + h0 + r;
-    a.part_acc[((int64_t)split * n_rows + row) * kDim + e] = acc * tb.v_post;
-    if (e == 0) {
-      a.part_m[(int64_t)split * n_rows + row] = m_star == -INFINITY ? -INFINITY : m_star * 0.6931471805599453f;
-      a.part_l[(int64_t)split * n_rows + row] = l;
+    if (t == 0 && g < a.n_rep) {
+      a.part_m[(int64_t)split * n_rows + row0 + g] = m_run == -INFINITY ? -INFINITY : m_run * 0.6931471805599453f;
+      a.part_l[(int64_t)split * n_rows + row0 + g] = l_run;
     }
   }
-
+  TQ_STAMP(21);   // partial written
   // ---------------- two-level merge, no waiting anywhere ----------------
   // Every CTA publishes its partial and bumps the counter of its group of `group`
   // splits; the CTA that completes a group merges it into a level-1 partial and
@@ -595,13 +663,13 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
     const int gi = split / tb.group;
     const int gsize = min(tb.group, tb.splits - gi * tb.group);
     __threadfence();
-    asm volatile("bar.sync 1, 128;" ::: "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
     if (tid == 0) {
       const int prev = atomicAdd(ctr + 1 + gi, 1);
       flag_s = prev == gsize - 1;
       if (flag_s) ctr[1 + gi] = 0;
     }
-    asm volatile("bar.sync 1, 128;" ::: "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
     if (!flag_s) return;
     __threadfence();
     for (int r = warp; r < a.n_rep; r += kConsumerWarps) {
@@ -619,16 +687,17 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
     src_l = tb.l1_l;
     src_acc = tb.l1_acc;
     n_final = tb.n_groups;
+    TQ_STAMP(22);   // level-1 merge done
   }
   __threadfence();
-  asm volatile("bar.sync 1, 128;" ::: "memory");
+  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
   const int n_arrivals = tb.n_groups > 1 ? tb.n_groups : tb.splits;
   if (tid == 0) {
     const int prev = atomicAdd(ctr, 1);
     flag_s = prev == n_arrivals - 1;
     if (flag_s) ctr[0] = 0;
   }
-  asm volatile("bar.sync 1, 128;" ::: "memory");
+  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
   if (!flag_s) return;
   __threadfence();
   for (int r = warp; r < a.n_rep; r += kConsumerWarps) {
@@ -656,6 +725,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       else reinterpret_cast<__nv_bfloat16*>(tb.out)[ooff + j] = __float2bfloat16_rn(res);
     }
   }
+  TQ_STAMP(23);   // final merge done
 }
 
 // ---- host side: scaled f16 codebooks --------------------------------------------------
@@ -750,13 +820,14 @@ bool flash_mma_supported(const FlashArgs& a) {
   return true;
 }
 
-int flash_mma_chunk_multiple() { return kTile; }
+int flash_mma_chunk_multiple() { return kChunkMultiple; }
+int flash_mma_ctas_per_sm() { return 1; }
 
 int64_t flash_mma_header_bytes(int batch, int n_kv_heads) {
   return ((16 + 4 * (int64_t)kCtrPerGroup * batch * n_kv_heads) + 15) / 16 * 16;
 }
-int flash_mma_max_splits() { return kMaxMerge * kMaxMerge; }
-int flash_mma_level1_parts() { return kMaxMerge; }
+int flash_mma_max_splits() { return kMaxParts * kMaxGroups; }
+int flash_mma_level1_parts() { return kMaxGroups; }
 
 int launch_flash_mma(const FlashArgs& a, int splits, const MmaOutput& mo, cudaStream_t st) {
   MmaTables tb;
@@ -764,14 +835,8 @@ int launch_flash_mma(const FlashArgs& a, int splits, const MmaOutput& mo, cudaSt
   tb.status = mo.status;
   tb.counters = mo.counters;
   tb.splits = splits;
-  if (splits <= kMaxMerge) {
-    tb.group = splits;
-    tb.n_groups = 1;
-  } else {
-    tb.group = 1;
-    while (tb.group * tb.group < splits) ++tb.group;          // ceil(sqrt(splits)) <= kMaxMerge
-    tb.n_groups = (splits + tb.group - 1) / tb.group;
-  }
+  tb.n_groups = (splits + kMaxParts - 1) / kMaxParts;           // 1 up to kMaxParts splits
+  tb.group = (splits + tb.n_groups - 1) / tb.n_groups;
   tb.l1_m = mo.l1_m;
   tb.l1_l = mo.l1_l;
   tb.l1_acc = mo.l1_acc;
