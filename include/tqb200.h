@@ -123,6 +123,25 @@ int tq_sparse_v_matvec(const float* weights, int64_t w_head_stride,
                        int dim, int bits, float threshold, int n_rep, float* out,
                        void* workspace, size_t workspace_bytes, void* stream);
 
+/* No counterpart in the reference.  tq_sparse_v_matvec for callers that cannot
+ * hand over a workspace because they cannot allocate device memory themselves
+ * (a serving framework that owns all device memory and forbids cudaMalloc in
+ * plugin code, a foreign-language binding without an allocator, a decode loop
+ * where an allocation would stall the device).  The partial sums go to a fixed
+ * array built into the library, tq_sparse_v_noalloc_max_bytes() = 4 MiB per GPU,
+ * held by every process that loads the library until it exits; a call that would
+ * need more (tq_sparse_v_workspace_bytes() says how much) fails with
+ * TQ_ERR_WORKSPACE.  Calls share the array: do not let two of them overlap on
+ * the GPU.  The first call on each device looks up the array's address; make
+ * that call before any stream capture.  Allocates nothing, ever. */
+size_t tq_sparse_v_noalloc_max_bytes(void);
+int tq_sparse_v_matvec_noalloc(const float* weights, int64_t w_head_stride,
+                               const uint32_t* v_packed, int64_t v_head_stride,
+                               const float* v_norms, int64_t vn_head_stride, int n_kv_heads,
+                               int64_t seq_len, const float* centroids_host,
+                               const float* signs_host, int dim, int bits, float threshold,
+                               int n_rep, float* out, void* stream);
+
 /* ---- split-K flash decoding over packed KV ----------------------------------
  * One query token per sequence.  Replaces flash_attention_turboquant
  * (flash_attention.py:168-274) and the composition turboquant_attention

@@ -76,6 +76,10 @@ _SIGNATURES = {
     "tq_sparse_v_matvec": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int,
                                    c_int64, _FP, _FP, c_int, c_int, c_float, c_int, c_void_p,
                                    c_void_p, c_size_t, c_void_p]),
+    "tq_sparse_v_noalloc_max_bytes": (c_size_t, []),
+    "tq_sparse_v_matvec_noalloc": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int,
+                                           c_int64, _FP, _FP, c_int, c_int, c_float, c_int, c_void_p,
+                                           c_void_p]),
     "tq_flash_decode_header_bytes": (c_int64, [c_int, c_int]),
     "tq_flash_decode_workspace_bytes": (c_int64, [POINTER(FlashParams)]),
     "tq_flash_decode": (c_int, [POINTER(FlashParams)]),

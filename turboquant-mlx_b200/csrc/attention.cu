@@ -648,3 +648,101 @@ extern "C" int tq_merge_partials(const float* part_m, const float* part_l, const
                       1, out, out_dtype, out_row_stride, n_rows, 0, nullptr, nullptr, nullptr,
                       (cudaStream_t)stream);
 }
+
+// ---------------------------------------------------------------------------
+// tq_sparse_v_matvec_noalloc: the same two kernels as tq_sparse_v_matvec, with
+// the partial-sum scratch taken from a fixed array inside the library instead of
+// a caller-supplied workspace.  It exists for callers that are not in a position
+// to allocate device memory at all: code running under a serving framework that
+// owns every byte of device memory through its own arena and forbids plugins
+// from calling cudaMalloc, bindings from languages that can pass pointers they
+// were given but have no allocator of their own, and call sites where an
+// allocation would stall the device (cudaMalloc synchronises) in the middle of
+// a latency-critical decode loop.
+//
+// The array lives in every process that loads the library, on every GPU the
+// process touches, until exit - hence the modest, fixed size.  All calls share
+// it: two calls that overlap on the GPU (different streams, or different
+// threads) race on it and must be serialised by the caller.  It keeps whatever
+// the previous call left behind; that is harmless here because the first kernel
+// overwrites every word the second kernel reads, so nothing has to be cleared.
+// ---------------------------------------------------------------------------
+#define TQ_SPARSE_V_STATIC_BYTES (4u << 20)
+static __device__ __align__(256) unsigned char g_sparse_v_scratch[TQ_SPARSE_V_STATIC_BYTES];
+
+#include <mutex>
+
+// In host code the array's name is only a handle; the device address has to be
+// looked up, per device, with that device current.  Done on the first call that
+// runs on a device (so that call should come before any stream capture).
+static int sparse_v_static_scratch(float** out) {
+  static std::mutex mu;
+  static float* ptrs[64] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64)
+    return set_error(TQ_ERR_LAUNCH, "cudaGetDevice failed or device index %d out of range: %s", dev,
+                     cudaGetErrorString(e));
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_sparse_v_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return set_error(TQ_ERR_LAUNCH, "cudaGetSymbolAddress(scratch) on device %d: %s", dev,
+                       cudaGetErrorString(e));
+    ptrs[dev] = reinterpret_cast<float*>(p);
+  }
+  *out = ptrs[dev];
+  return TQ_OK;
+}
+
+extern "C" size_t tq_sparse_v_noalloc_max_bytes(void) { return TQ_SPARSE_V_STATIC_BYTES; }
+
+extern "C" int tq_sparse_v_matvec_noalloc(const float* weights, int64_t w_head_stride,
+                                          const uint32_t* v_packed, int64_t v_head_stride,
+                                          const float* v_norms, int64_t vn_head_stride,
+                                          int n_kv_heads, int64_t seq_len,
+                                          const float* centroids_host, const float* signs_host,
+                                          int dim, int bits, float threshold, int n_rep,
+                                          float* out, void* stream) {
+  if (dim <= 0 || (dim & (dim - 1)))
+    return set_error(TQ_ERR_BAD_DIM, "dim must be a power of 2, got %d", dim);
+  if (dim > 256)
+    return set_error(TQ_ERR_BAD_DIM, "dim > 256 not supported by threadgroup layout, got %d", dim);
+  int rc = check_dim_bits(dim, bits, 256);
+  if (rc) return rc;
+  TQ_REQUIRE(n_kv_heads > 0 && n_rep > 0 && seq_len >= 0, TQ_ERR_BAD_ARG, "bad head / seq count");
+  TQ_REQUIRE(centroids_host != nullptr, TQ_ERR_BAD_ARG, "centroids pointer is NULL");
+  TQ_REQUIRE(out != nullptr, TQ_ERR_BAD_ARG, "NULL output pointer");
+  const int n_q = n_kv_heads * n_rep;
+  const size_t need = tq_sparse_v_workspace_bytes(n_q, seq_len, dim);
+  TQ_REQUIRE(need <= TQ_SPARSE_V_STATIC_BYTES, TQ_ERR_WORKSPACE,
+             "this call needs %zu bytes of scratch but the built-in array holds %u; use "
+             "tq_sparse_v_matvec with a caller-provided workspace for this size",
+             need, (unsigned)TQ_SPARSE_V_STATIC_BYTES);
+  float* ws = nullptr;
+  if ((rc = sparse_v_static_scratch(&ws))) return rc;
+  SignMask sg;
+  if ((rc = make_sign_mask(signs_host, dim, &sg))) return rc;
+  Table16 cent;
+  fill_table(&cent, centroids_host, 1 << bits);
+  const int splits = sparse_v_splits(seq_len);
+  const int64_t chunk = (seq_len + splits - 1) / splits;
+  const float thr = threshold > 0.f ? threshold : 0.f;
+  cudaStream_t st = (cudaStream_t)stream;
+  const dim3 grid(splits, n_kv_heads, (n_rep + kSvRMax - 1) / kSvRMax);
+#define TQ_LAUNCH(B)                                                                             \
+  sparse_v_partial_kernel<B><<<grid, 256, 0, st>>>(weights, w_head_stride, v_packed, v_head_stride, \
+                                                   v_norms, vn_head_stride, seq_len,               \
+                                                   chunk > 0 ? chunk : 1, dim, n_rep, thr, cent, ws, n_q)
+  switch (bits) {
+    case 1: TQ_LAUNCH(1); break;
+    case 2: TQ_LAUNCH(2); break;
+    case 3: TQ_LAUNCH(3); break;
+    default: TQ_LAUNCH(4); break;
+  }
+#undef TQ_LAUNCH
+  if ((rc = check_launch("tq_sparse_v_matvec_noalloc (partial)"))) return rc;
+  sparse_v_finish_kernel<<<n_q, dim, 0, st>>>(ws, splits, n_q, dim, sg, 1.0f / dim, out);
+  return check_launch("tq_sparse_v_matvec_noalloc (finish)");
+}
