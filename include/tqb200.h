@@ -218,12 +218,15 @@ int tq_flash_decode(const tq_flash_params* p);
  * non-zero word there.  Diagnostic, no reference counterpart. */
 int tq_flash_decode_last_kernel(void);
 
-/* Merge n_parts partial states (split-K chunks or ranks) laid out
- * (n_parts, n_rows[, dim]) contiguous: m* = max m_i, l* = sum l_i e^(m_i - m*),
- * acc* likewise; out = post(acc*) / l* with post = signs * bfly(.) / dim when
- * v_signs_host is given, identity when NULL.  No reference counterpart: the
- * reference runs on one device without split-K. */
-int tq_merge_partials(const float* part_m, const float* part_l, const float* part_acc,
+/* Merge n_parts partial states (split-K chunks or ranks): part i of row r is at
+ * part_m[i * m_part_stride + r], part_l[i * l_part_stride + r] and
+ * part_acc[i * acc_part_stride + r * dim ...], so the three fields may be views
+ * into one gathered buffer.  m* = max m_i, l* = sum l_i e^(m_i - m*), acc*
+ * likewise; out = post(acc*) / l* with post = signs * bfly(.) / dim when
+ * v_signs_host is given, identity when NULL; a part with l == 0 is a no-op.
+ * No reference counterpart: the reference runs on one device without split-K. */
+int tq_merge_partials(const float* part_m, int64_t m_part_stride, const float* part_l,
+                      int64_t l_part_stride, const float* part_acc, int64_t acc_part_stride,
                       int n_parts, int64_t n_rows, int dim, const float* v_signs_host,
                       void* out, int out_dtype, int64_t out_row_stride, void* stream);
 

@@ -1,0 +1,59 @@
+"""Two-GPU test of sequence-parallel decode over NCCL (skipped on a one-GPU box).
+Ranks are child processes; each attends over half of the positions and the
+merged result must equal single-GPU decode over the whole sequence."""
+
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+_CHILD = r'''
+import os, sys, math
+sys.path.insert(0, os.environ["TQ_ROOT"])
+import torch, torch.distributed as dist
+import __graft_entry__ as entry
+tq = entry.load_package()
+from turboquant_mlx_b200.distributed import sequence_parallel_decode, shard_range
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dev = torch.device("cuda", rank)
+dist.init_process_group("nccl", device_id=dev)
+g = torch.Generator().manual_seed(11)
+B, n_kv, n_rep, S, D = 2, 2, 7, 2048, 128
+kd = torch.randn((B, n_kv, S, D), generator=g).half().to(dev)
+vraw = torch.randn((B, n_kv, S, D), generator=g).half().to(dev)
+q = torch.randn((B, n_kv * n_rep, D), generator=g).half().to(dev)
+pq = tq.PolarQuantizer(D, 3, seed=43, device=dev)
+vp, vn = pq.quantize_packed(vraw)
+scale = 1 / math.sqrt(D)
+full = tq.flash_decode(q, k=dict(format="dense", data=kd),
+                       v=dict(format="polar", packed=vp, norms=vn, centroids=pq.centroids, signs=pq.signs, bits=3),
+                       attn_scale=scale, out_dtype=torch.float32)
+a, b = shard_range(S, world, rank)
+out = sequence_parallel_decode(
+    q, k=dict(format="dense", data=kd[:, :, a:b]),
+    v=dict(format="polar", packed=vp[:, :, a:b], norms=vn[:, :, a:b], centroids=pq.centroids, signs=pq.signs, bits=3),
+    attn_scale=scale, out_dtype=torch.float32)
+torch.cuda.synchronize()
+err = float((out - full).abs().max() / full.abs().max())
+print(f"rank {rank} rel err {err:.3e}")
+dist.destroy_process_group()
+sys.exit(0 if err < 1e-3 else 1)
+'''
+
+
+def test_sequence_parallel_decode_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "child.py"
+    script.write_text(_CHILD)
+    env = dict(os.environ, TQ_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29611", str(script)]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]

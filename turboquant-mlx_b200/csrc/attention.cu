@@ -394,8 +394,9 @@ flash_generic_kernel(const FlashArgs a) {
 // merge of partial states (split-K chunks or ranks)
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void merge_partials_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
-                                      const float* __restrict__ pacc, int n_parts, int64_t n_rows,
+__global__ void merge_partials_kernel(const float* __restrict__ pm, int64_t sm, const float* __restrict__ pl,
+                                      int64_t sl, const float* __restrict__ pacc, int64_t sa,
+                                      int n_parts, int64_t n_rows,
                                       int dim, int rotate, SignMask signs, int finalize, T* out,
                                       int64_t out_row_stride, int64_t rows_per_batch,
                                       int64_t out_batch_stride, float* om, float* ol, float* oacc) {
@@ -404,17 +405,17 @@ __global__ void merge_partials_kernel(const float* __restrict__ pm, const float*
   const int e = threadIdx.x;
   float m_star = -INFINITY;
   for (int i = 0; i < n_parts; ++i) {
-    const float li = pl[(int64_t)i * n_rows + row];
-    const float mi = pm[(int64_t)i * n_rows + row];
+    const float li = pl[(int64_t)i * sl + row];
+    const float mi = pm[(int64_t)i * sm + row];
     if (li > 0.f) m_star = fmaxf(m_star, mi);
   }
   float l_star = 0.f, acc = 0.f;
   for (int i = 0; i < n_parts; ++i) {
-    const float li = pl[(int64_t)i * n_rows + row];
+    const float li = pl[(int64_t)i * sl + row];
     if (!(li > 0.f)) continue;   // empty or fully masked chunk merges as a no-op
-    const float w = __expf(pm[(int64_t)i * n_rows + row] - m_star);
+    const float w = __expf(pm[(int64_t)i * sm + row] - m_star);
     l_star += li * w;
-    acc += pacc[((int64_t)i * n_rows + row) * dim + e] * w;
+    acc += pacc[(int64_t)i * sa + row * dim + e] * w;
   }
   if (!finalize) {
     oacc[row * dim + e] = acc;
@@ -443,25 +444,26 @@ __global__ void merge_partials_kernel(const float* __restrict__ pm, const float*
   out[bb * out_batch_stride + hh2 * out_row_stride + e] = from_f32<T>(res);
 }
 
-int launch_merge(const float* pm, const float* pl, const float* pacc, int n_parts, int64_t n_rows,
+int launch_merge(const float* pm, int64_t sm, const float* pl, int64_t sl, const float* pacc,
+                 int64_t sa, int n_parts, int64_t n_rows,
                  int dim, int rotate, const SignMask& signs, int finalize, void* out, int out_dtype,
                  int64_t out_row_stride, int64_t rows_per_batch, int64_t out_batch_stride,
                  float* om, float* ol, float* oacc, cudaStream_t st) {
   if (n_rows <= 0) return TQ_OK;
   const dim3 grid((unsigned)n_rows), block(dim);
   if (!finalize || out_dtype == TQ_F32)
-    merge_partials_kernel<float><<<grid, block, 0, st>>>(pm, pl, pacc, n_parts, n_rows, dim, rotate,
+    merge_partials_kernel<float><<<grid, block, 0, st>>>(pm, sm, pl, sl, pacc, sa, n_parts, n_rows, dim, rotate,
                                                          signs, finalize, (float*)out,
                                                          out_row_stride, rows_per_batch,
                                                          out_batch_stride, om, ol, oacc);
   else if (out_dtype == TQ_F16)
-    merge_partials_kernel<__half><<<grid, block, 0, st>>>(pm, pl, pacc, n_parts, n_rows, dim, rotate,
+    merge_partials_kernel<__half><<<grid, block, 0, st>>>(pm, sm, pl, sl, pacc, sa, n_parts, n_rows, dim, rotate,
                                                           signs, finalize, (__half*)out,
                                                           out_row_stride, rows_per_batch,
                                                           out_batch_stride, om, ol, oacc);
   else if (out_dtype == TQ_BF16)
     merge_partials_kernel<__nv_bfloat16><<<grid, block, 0, st>>>(
-        pm, pl, pacc, n_parts, n_rows, dim, rotate, signs, finalize, (__nv_bfloat16*)out,
+        pm, sm, pl, sl, pacc, sa, n_parts, n_rows, dim, rotate, signs, finalize, (__nv_bfloat16*)out,
         out_row_stride, rows_per_batch, out_batch_stride, om, ol, oacc);
   else
     return set_error(TQ_ERR_BAD_ARG, "unknown dtype %d", out_dtype);
@@ -633,9 +635,11 @@ extern "C" int tq_sparse_v_matvec(const float* weights, int64_t w_head_stride,
   return check_launch("tq_sparse_v_matvec (finish)");
 }
 
-extern "C" int tq_merge_partials(const float* part_m, const float* part_l, const float* part_acc,
-                                 int n_parts, int64_t n_rows, int dim, const float* v_signs_host,
-                                 void* out, int out_dtype, int64_t out_row_stride, void* stream) {
+extern "C" int tq_merge_partials(const float* part_m, int64_t m_part_stride, const float* part_l,
+                                 int64_t l_part_stride, const float* part_acc,
+                                 int64_t acc_part_stride, int n_parts, int64_t n_rows, int dim,
+                                 const float* v_signs_host, void* out, int out_dtype,
+                                 int64_t out_row_stride, void* stream) {
   TQ_REQUIRE(dim >= 32 && dim <= 256 && !(dim & (dim - 1)), TQ_ERR_BAD_DIM,
              "dim must be a power of 2 in [32, 256], got %d", dim);
   TQ_REQUIRE(n_parts > 0 && n_rows >= 0, TQ_ERR_BAD_ARG, "bad part / row count");
@@ -644,9 +648,9 @@ extern "C" int tq_merge_partials(const float* part_m, const float* part_l, const
   SignMask sg = {};
   int rc;
   if (v_signs_host && (rc = make_sign_mask(v_signs_host, dim, &sg))) return rc;
-  return launch_merge(part_m, part_l, part_acc, n_parts, n_rows, dim, v_signs_host != nullptr, sg,
-                      1, out, out_dtype, out_row_stride, n_rows, 0, nullptr, nullptr, nullptr,
-                      (cudaStream_t)stream);
+  return launch_merge(part_m, m_part_stride, part_l, l_part_stride, part_acc, acc_part_stride,
+                      n_parts, n_rows, dim, v_signs_host != nullptr, sg, 1, out, out_dtype,
+                      out_row_stride, n_rows, 0, nullptr, nullptr, nullptr, (cudaStream_t)stream);
 }
 
 // ---------------------------------------------------------------------------

@@ -248,7 +248,8 @@ extern "C" int tq_flash_decode(const tq_flash_params* p) {
   if (rc) return rc;
   if (direct) return TQ_OK;
   const int rotate = p->v_format == TQ_KV_POLAR;
-  return launch_merge(a.part_m, a.part_l, a.part_acc, plan.splits, rows, p->dim, rotate, a.v_signs,
+  return launch_merge(a.part_m, rows, a.part_l, rows, a.part_acc, rows * p->dim, plan.splits, rows, p->dim,
+                      rotate, a.v_signs,
                       p->out_mode == 0, p->out, p->out_dtype, p->out_head_stride, p->n_q_heads,
                       p->out_batch_stride, p->part_m, p->part_l, p->part_acc, st);
 }

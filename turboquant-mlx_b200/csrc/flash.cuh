@@ -71,7 +71,8 @@ int flash_mma_max_splits();
 int flash_mma_level1_parts();
 int launch_flash_mma(const FlashArgs& a, int splits, const MmaOutput& mo, cudaStream_t st);
 
-int launch_merge(const float* pm, const float* pl, const float* pacc, int n_parts, int64_t n_rows,
+int launch_merge(const float* pm, int64_t sm, const float* pl, int64_t sl, const float* pacc,
+                 int64_t sa, int n_parts, int64_t n_rows,
                  int dim, int rotate, const SignMask& signs, int finalize, void* out, int out_dtype,
                  int64_t out_row_stride, int64_t rows_per_batch, int64_t out_batch_stride,
                  float* om, float* ol, float* oacc, cudaStream_t st);

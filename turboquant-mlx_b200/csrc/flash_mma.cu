@@ -5,7 +5,7 @@
 //
 //   producer warp : streams 64-position tiles of K / V (and their norms) into a
 //                   4-stage shared-memory ring with cp.async.bulk (TMA, 1-D) and
-//                   mbarrier transaction counts; no multicast, local memory only.
+//                   mbarrier transaction counts; every copy reads this GPU's own memory into this CTA only.
 //   4 consumer warps: each owns 16 positions of a tile and keeps its own online
 //                   softmax state, so the main loop has no CTA-wide barrier.
 //       scores  : mma.sync m16n8k16 (f16 x f16 -> f32).  A = query rows (rows 0-7

@@ -226,7 +226,7 @@ def _strides3(t: torch.Tensor, batched: bool):
 
 def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerotated: bool = False,
                  mask: torch.Tensor | None = None, num_splits: int = 0, out_dtype=None,
-                 partials: bool = False):
+                 partials: bool = False, partial_out=None):
     """Split-K flash decoding for one query token per sequence.
 
     q: (B, n_q, dim).  k / v: dicts describing the stored keys / values:
@@ -239,7 +239,8 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
     strides are passed through).  mask: optional additive float mask
     broadcastable to (B, n_q, S).  Returns (B, n_q, dim) in out_dtype (default
     q.dtype), or with partials=True the merged state (m (B, n_q), l (B, n_q),
-    acc (B, n_q, dim)) before the final butterfly / normalisation.
+    acc (B, n_q, dim)) before the final butterfly / normalisation; `partial_out`
+    optionally names the three tensors to write (e.g. slices of a send buffer).
     """
     _lib.require_cuda(q)
     B, n_q, dim = q.shape
@@ -335,9 +336,13 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
     dev = q.device
     if partials:
         P.out_mode = 1
-        pm = torch.empty((B, n_q), dtype=torch.float32, device=dev)
-        pl = torch.empty((B, n_q), dtype=torch.float32, device=dev)
-        pa = torch.empty((B, n_q, dim), dtype=torch.float32, device=dev)
+        if partial_out is not None:     # contiguous float32 views (B, n_q), (B, n_q), (B, n_q, dim)
+            pm, pl, pa = partial_out
+            assert pm.is_contiguous() and pl.is_contiguous() and pa.is_contiguous()
+        else:
+            pm = torch.empty((B, n_q), dtype=torch.float32, device=dev)
+            pl = torch.empty((B, n_q), dtype=torch.float32, device=dev)
+            pa = torch.empty((B, n_q, dim), dtype=torch.float32, device=dev)
         P.part_m, P.part_l, P.part_acc = pm.data_ptr(), pl.data_ptr(), pa.data_ptr()
     else:
         P.out_mode = 0
@@ -384,13 +389,19 @@ def flash_attention_turboquant(q_rot, k_packed, k_norms, v_packed, v_norms, k_ce
 
 def merge_partials(part_m, part_l, part_acc, v_signs, out_dtype=torch.float32) -> torch.Tensor:
     """Merge (n_parts, rows) / (n_parts, rows, dim) partial states from sequence
-    chunks or ranks into the final (rows, dim) output."""
+    chunks or ranks into the final (rows, dim) output.  The three tensors may be
+    views into one gathered buffer: only the part stride (dim 0) is free."""
     _lib.require_cuda(part_m, part_l, part_acc)
     n_parts, rows, dim = part_acc.shape
-    pm, pl, pa = part_m.contiguous(), part_l.contiguous(), part_acc.contiguous()
+
+    def rows_contiguous(t, inner):
+        ok = t.stride(-1) == 1 and (t.ndim == 2 or t.stride(1) == inner)
+        return t if ok else t.contiguous()
+
+    pm, pl, pa = rows_contiguous(part_m, 1), rows_contiguous(part_l, 1), rows_contiguous(part_acc, dim)
     out = torch.empty((rows, dim), dtype=out_dtype, device=pa.device)
-    _lib.check(_lib.lib().tq_merge_partials(_lib.ptr(pm), _lib.ptr(pl), _lib.ptr(pa), n_parts, rows,
-                                            dim, _lib.host_floats(v_signs), _lib.ptr(out),
-                                            _lib.dtype_code(out_dtype), dim,
-                                            _lib.stream_ptr(pa.device)))
+    _lib.check(_lib.lib().tq_merge_partials(
+        _lib.ptr(pm), pm.stride(0), _lib.ptr(pl), pl.stride(0), _lib.ptr(pa), pa.stride(0), n_parts,
+        rows, dim, _lib.host_floats(v_signs), _lib.ptr(out), _lib.dtype_code(out_dtype), dim,
+        _lib.stream_ptr(pa.device)))
     return out
