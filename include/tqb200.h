@@ -170,7 +170,10 @@ typedef struct tq_flash_params {
   const float* k_centroids_host;
   const float* k_signs_host;
 
-  int32_t v_format, v_bits, v_group, v_reserved;
+  int32_t v_format, v_bits, v_group;
+  int32_t kv_stable;           /* 1: no K / V row or norm read by this call is written by the kernel launched
+                                  immediately before it on the stream, so the kernel may prefetch K / V while
+                                  that kernel is still finishing (programmatic dependent launch); 0: wait first */
   const void* v_data;
   int64_t v_batch_stride, v_head_stride;
   const float* v_norms;

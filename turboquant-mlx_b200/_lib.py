@@ -40,7 +40,7 @@ class FlashParams(ctypes.Structure):
         ("k_scales", c_void_p), ("k_biases", c_void_p),
         ("ks_batch_stride", c_int64), ("ks_head_stride", c_int64),
         ("k_centroids_host", POINTER(c_float)), ("k_signs_host", POINTER(c_float)),
-        ("v_format", c_int32), ("v_bits", c_int32), ("v_group", c_int32), ("v_reserved", c_int32),
+        ("v_format", c_int32), ("v_bits", c_int32), ("v_group", c_int32), ("kv_stable", c_int32),
         ("v_data", c_void_p), ("v_batch_stride", c_int64), ("v_head_stride", c_int64),
         ("v_norms", c_void_p), ("vn_batch_stride", c_int64), ("vn_head_stride", c_int64),
         ("v_scales", c_void_p), ("v_biases", c_void_p),

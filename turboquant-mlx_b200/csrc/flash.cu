@@ -101,6 +101,7 @@ static int fill_args(const tq_flash_params* p, FlashArgs* a) {
   a->v_format = p->v_format;
   a->v_bits = p->v_bits;
   a->v_group = p->v_group > 0 ? p->v_group : p->dim;
+  a->kv_stable = p->kv_stable;
   a->v_data = p->v_data;
   a->v_batch_stride = p->v_batch_stride;
   a->v_head_stride = p->v_head_stride;

@@ -25,6 +25,7 @@ struct FlashArgs {
   SignMask k_signs;
 
   int v_format, v_bits, v_group;
+  int kv_stable;
   const void* v_data;
   int64_t v_batch_stride, v_head_stride;
   const float* v_norms;

@@ -44,8 +44,7 @@ constexpr int kDenseRowBytes = 256;    // rows as in memory: one bulk copy per t
 constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units; P stays <= 2^8
-constexpr int kMaxMerge = 16;               // accumulator loads in flight per lane during a merge
-constexpr int kMaxParts = 64;               // partial states one merge call combines
+constexpr int kMaxParts = 37;               // partial states one merge call combines (all staged in shared memory)
 constexpr int kMaxGroups = 16;              // level-1 groups when there are more than kMaxParts splits
 constexpr int kCtrPerGroup = kMaxGroups + 1; // level-1 counters + the top counter
 
@@ -91,9 +90,16 @@ template <int KF, int VB> struct Layout {
   static constexpr int v_off = kn_off + KGeom<KF>::norms;
   static constexpr int vn_off = v_off + kTile * VGeom<VB>::row;
   static constexpr int stage_bytes = vn_off + kTile * 4;
-  static constexpr int total = stage0 + kStages * stage_bytes;
+  // the ring is reused by the epilogue: warp exchange, then the staged split merge
+  static constexpr int merge_bytes = (kMaxParts * 8 * kDim + kMaxParts * 16 + 8 * 64) * 4;
+  static constexpr int xch_bytes = kConsumerWarps * 34 * 32 * 4;
+  static constexpr int ring_bytes = kStages * stage_bytes;
+  static constexpr int work_bytes =
+      ring_bytes > merge_bytes ? (ring_bytes > xch_bytes ? ring_bytes : xch_bytes)
+                               : (merge_bytes > xch_bytes ? merge_bytes : xch_bytes);
+  static constexpr int total = stage0 + work_bytes;
   static_assert(stage_bytes % 16 == 0 && stage0 % 16 == 0, "stage alignment");
-  static_assert(kStages * stage_bytes >= kConsumerWarps * (8 * kDim + 16) * 4, "epilogue reuse");
+  static_assert(total <= 227 * 1024, "shared memory per CTA");
 };
 
 // ---- PTX wrappers -----------------------------------------------------------------
@@ -186,63 +192,102 @@ __device__ __forceinline__ float load_q(const void* base, int64_t idx) {
   return to_f32<T>(reinterpret_cast<const T*>(base)[idx]);
 }
 
-// Merge `count` (<= kMaxParts) partial states of one output row, one warp per row:
-// lane i owns the weights of parts i and i + 32, every lane owns 4 accumulator
-// elements.  Accumulator loads go out in batches of kMaxMerge before their first
-// use, so a merge costs about one L2 round trip per batch.
-__device__ __forceinline__ void merge_parts(const float* pm, const float* pl, const float* pacc,
-                                            int64_t n_rows, int64_t row, int first, int count,
-                                            int lane, float& m_star, float& l_star, float4& acc4) {
-  float mi[2], li[2];
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int i = lane + 32 * h;
-    li[h] = 0.f;
-    mi[h] = -INFINITY;
-    if (i < count) {
-      li[h] = __ldcg(pl + (int64_t)(first + i) * n_rows + row);
-      mi[h] = __ldcg(pm + (int64_t)(first + i) * n_rows + row);
-    }
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+
+// Merge `count` (<= kMaxParts) partial states of the n_rep rows of one (batch, kv
+// head) group.  Every dependent trip to global memory costs about a microsecond
+// here, so all partials are pulled into shared memory (the ring is free by now)
+// with cp.async in ONE round trip by all consumer threads, and the reduction runs
+// from shared memory: warp r owns row r, lane owns elements 4*lane .. 4*lane+3,
+// which is also the layout the final butterfly wants.
+// Shared layout at `stage`: acc [count][n_rep][128], then m [count][8], l [count][8], w [8][64].
+__device__ __forceinline__ bool merge_staged(uint8_t* smem_stage, uint32_t stage_addr, uint32_t bar,
+                                             uint32_t parity, int* status,
+                                             const float* pm, const float* pl, const float* pacc,
+                                             int64_t n_rows, int64_t row0, int n_rep, int first,
+                                             int count, int tid, int warp, int lane,
+                                             float& m_star, float& l_star, float4& acc4) {
+  const int acc_floats = count * n_rep * kDim;
+  float* s_acc = reinterpret_cast<float*>(smem_stage);
+  float* s_m = s_acc + acc_floats;
+  float* s_l = s_m + count * 8;
+  float* s_w = s_l + count * 8;
+  const int chunks_per_part = n_rep * (kDim / 4);          // 16-byte chunks of one part
+  // one bulk copy per part (its n_rep rows are contiguous), all in flight together
+  const uint32_t part_bytes = (uint32_t)n_rep * kDim * 4u;
+  if (tid == 0) mbar_arrive_expect_tx(bar, (uint32_t)count * part_bytes);
+  asm volatile("fence.proxy.async;" ::: "memory");
+  for (int i = tid; i < count; i += kConsumerThreads)
+    bulk_g2s(stage_addr + (uint32_t)i * part_bytes, pacc + ((int64_t)(first + i) * n_rows + row0) * kDim,
+             part_bytes, bar);
+  for (int c = tid; c < count * n_rep; c += kConsumerThreads) {
+    const int i = c / n_rep, r = c - i * n_rep;
+    cp_async4(stage_addr + (uint32_t)(acc_floats + i * 8 + r) * 4u, pm + (int64_t)(first + i) * n_rows + row0 + r);
+    cp_async4(stage_addr + (uint32_t)(acc_floats + count * 8 + i * 8 + r) * 4u,
+              pl + (int64_t)(first + i) * n_rows + row0 + r);
   }
-  float4 v[kMaxMerge];
-#pragma unroll
-  for (int i = 0; i < kMaxMerge; ++i) {
-    v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (i < count)
-      v[i] = __ldcg(reinterpret_cast<const float4*>(pacc + ((int64_t)(first + i) * n_rows + row) * kDim) + lane);
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+  const bool arrived = mbar_wait(bar, parity);
+  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+  if (!arrived) {          // bounded wait gave up: report through the status word, produce nothing
+    if (tid == 0) atomicExch(status, 3);
+    m_star = -INFINITY;
+    l_star = 0.f;
+    acc4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    return false;
   }
-  m_star = warp_max(fmaxf(li[0] > 0.f ? mi[0] : -INFINITY, li[1] > 0.f ? mi[1] : -INFINITY));
-  float w[2];
-#pragma unroll
-  for (int h = 0; h < 2; ++h) w[h] = li[h] > 0.f ? __expf(mi[h] - m_star) : 0.f;
-  l_star = warp_sum(li[0] * w[0] + li[1] * w[1]);
+  m_star = -INFINITY;
+  l_star = 0.f;
   acc4 = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int base = 0; base < count; base += kMaxMerge) {
-    if (base > 0) {
+  if (warp < n_rep) {
+    const int r = warp;
+    float mi[2], li[2];
 #pragma unroll
-      for (int i = 0; i < kMaxMerge; ++i) {
-        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (base + i < count)
-          v[i] = __ldcg(reinterpret_cast<const float4*>(pacc + ((int64_t)(first + base + i) * n_rows + row) * kDim) + lane);
-      }
+    for (int h = 0; h < 2; ++h) {
+      const int i = lane + 32 * h;
+      li[h] = i < count ? s_l[i * 8 + r] : 0.f;
+      mi[h] = i < count ? s_m[i * 8 + r] : -INFINITY;
     }
+    m_star = warp_max(fmaxf(li[0] > 0.f ? mi[0] : -INFINITY, li[1] > 0.f ? mi[1] : -INFINITY));
+    float w[2];
 #pragma unroll
-    for (int i = 0; i < kMaxMerge; ++i) {
-      const int part = base + i;                       // parts >= count carry weight 0
-      const float wi = __shfl_sync(0xffffffffu, part < 32 ? w[0] : w[1], part & 31);
-      acc4.x += v[i].x * wi; acc4.y += v[i].y * wi; acc4.z += v[i].z * wi; acc4.w += v[i].w * wi;
+    for (int h = 0; h < 2; ++h) {
+      w[h] = li[h] > 0.f ? __expf(mi[h] - m_star) : 0.f;
+      s_w[r * 64 + lane + 32 * h] = w[h];
+    }
+    l_star = warp_sum(li[0] * w[0] + li[1] * w[1]);
+    __syncwarp();
+    const float4* src = reinterpret_cast<const float4*>(s_acc) + r * (kDim / 4) + lane;
+#pragma unroll 4
+    for (int i = 0; i < count; ++i) {
+      const float wi = s_w[r * 64 + i];
+      const float4 v = src[i * chunks_per_part];
+      acc4.x += v.x * wi; acc4.y += v.y * wi; acc4.z += v.z * wi; acc4.w += v.w * wi;
     }
   }
+  return true;
 }
 
 // Optional per-CTA cycle stamps for tuning (build with -DTQ_TIMING; the stamps land
 // 2 MiB into the workspace, which must be at least 3 MiB).  Off in normal builds.
 #ifdef TQ_TIMING
+__device__ __forceinline__ long long tq_now(int slot) {
+  if (slot >= 28) {   // slots 28..31: nanoseconds on the GPU-wide timer, comparable across launches
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return (long long)t;
+  }
+  return clock64();
+}
+// one block of stamps per output address (4 consecutive launches writing 7168-byte outputs stay apart)
 #define TQ_STAMP(slot)                                                                   \
   do {                                                                                   \
     if (lane == 0 && (warp == 0 || warp == kConsumerWarps))                              \
       reinterpret_cast<long long*>(reinterpret_cast<char*>(tb.status) + (2 << 20))       \
-          [((blockIdx.x + gridDim.x * blockIdx.y) * 2 + (warp == 0 ? 0 : 1)) * 32 + (slot)] = clock64(); \
+          [(((reinterpret_cast<uintptr_t>(tb.out) / 7168) & 3) * 148 * 2 +               \
+            (blockIdx.x + gridDim.x * blockIdx.y) * 2 + (warp == 0 ? 0 : 1)) * 32 + (slot)] = tq_now(slot); \
   } while (0)
 #else
 #define TQ_STAMP(slot) do { } while (0)
@@ -264,8 +309,14 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   const int h0 = kvh * a.n_rep;
 
   TQ_STAMP(0);
+  TQ_STAMP(28);
+  // Programmatic dependent launch: let the next kernel on the stream be scheduled as
+  // soon as SMs free up; its own griddepcontrol.wait keeps it from consuming
+  // anything this grid produces before this grid has completed.
+  if (tid == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   auto full_bar = [&](int s) { return sbase + L::bars + 8 * s; };
   auto empty_bar = [&](int s) { return sbase + L::bars + 8 * (kStages + s); };
+  const uint32_t merge_bar = sbase + L::bars + 8 * (2 * kStages);   // completion of the staged-merge copies
 
   __shared__ uint16_t c16_s[32];
   if (tid == 0) {
@@ -273,6 +324,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), kConsumerWarps);
     }
+    mbar_init(merge_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (tid < 16) c16_s[tid] = tb.v_c16[tid];
@@ -297,6 +349,10 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       }
     }
   }
+  // Everything below reads the query and later writes the shared workspace: both
+  // may belong to the preceding kernel until it has completed.
+  if (warp < kConsumerWarps) asm volatile("griddepcontrol.wait;" ::: "memory");
+  TQ_STAMP(29);
   // query rows -> shared f16: row r = high part of head r, row 8 + r = residual
   if (warp < kConsumerWarps) {
     __half* qs = reinterpret_cast<__half*>(smem + L::q);
@@ -340,6 +396,9 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
 
   // =============================== producer ===============================
   if (warp == kConsumerWarps) {
+    // K / V may be fetched while the preceding kernel is still running only if the
+    // caller vouches that it does not write them (kv_stable).
+    if (!a.kv_stable) asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int i = 0; i < n_tiles; ++i) {
       const int s = i % kStages;
       const uint32_t ph = (i / kStages) & 1;
@@ -579,86 +638,92 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   }
   TQ_STAMP(20);
 
-  // ---------------- CTA epilogue: pairwise tree over the consumer warps ----------------
-  // Round by round the upper half of the live warps hands (m, l, o) to the lower
-  // half through shared memory, [slot][value][lane] so every access is conflict
-  // free; l stays a per-thread partial until the end (it is linear).
+  // ---------------- CTA epilogue: one exchange through shared memory ----------------
+  // Every warp writes its (o[32], m, l) once, [warp][value][lane] (conflict free);
+  // after one barrier each thread sums a fixed slice of the 32 accumulator values
+  // over the 12 source warps and stores its share of the split's partial state.
   asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");   // every consumer is done with the ring
+  float* xch = reinterpret_cast<float*>(smem + L::stage0);               // [warp][34][32]
   {
-    float* xch = reinterpret_cast<float*>(smem + L::stage0);             // [slot][34][32]
-    int live = kConsumerWarps;
-    while (live > 1) {
-      const int half = (live + 1) / 2;          // receivers 0 .. half-1, senders half .. live-1
-      if (warp >= half && warp < live) {
-        float* dst = xch + (warp - half) * 34 * 32 + lane;
+    float* dst = xch + warp * 34 * 32 + lane;
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+    for (int j = 0; j < 8; ++j)
 #pragma unroll
-          for (int c = 0; c < 4; ++c) dst[(j * 4 + c) * 32] = o[j][c];
-        dst[32 * 32] = m_run;
-        dst[33 * 32] = l_run;
-      }
-      asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
-      if (warp < live - half) {
-        const float* src = xch + warp * 34 * 32 + lane;
-        const float m_b = src[32 * 32], l_b = src[33 * 32];
-        const float m_new = fmaxf(m_run, m_b);
-        const float fa = m_run == -INFINITY ? 0.f : ex2(m_run - m_new);
-        const float fb = m_b == -INFINITY ? 0.f : ex2(m_b - m_new);
-        l_run = l_run * fa + l_b * fb;
-        m_run = m_new;
-        const float fa0 = __shfl_sync(0xffffffffu, fa, 8 * t), fa1 = __shfl_sync(0xffffffffu, fa, 8 * t + 4);
-        const float fb0 = __shfl_sync(0xffffffffu, fb, 8 * t), fb1 = __shfl_sync(0xffffffffu, fb, 8 * t + 4);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          o[j][0] = o[j][0] * fa0 + src[(j * 4 + 0) * 32] * fb0;
-          o[j][1] = o[j][1] * fa1 + src[(j * 4 + 1) * 32] * fb1;
-          o[j][2] = o[j][2] * fa0 + src[(j * 4 + 2) * 32] * fb0;
-          o[j][3] = o[j][3] * fa1 + src[(j * 4 + 3) * 32] * fb1;
-        }
-      }
-      asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");   // slots free for the next round
-      live = half;
-    }
+      for (int c = 0; c < 4; ++c) dst[(j * 4 + c) * 32] = o[j][c];
+    dst[32 * 32] = m_run;
+    dst[33 * 32] = l_run;
   }
-  TQ_STAMP(24);   // tree merge done
+  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+  TQ_STAMP(24);   // exchange written
   if (!ok) return;
   const int64_t n_rows = (int64_t)a.batch * a.n_q_heads;
-  if (warp == 0) {   // warp 0 now holds the CTA's state: head g in lanes 4g..4g+3, o columns = heads 2t, 2t+1
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-    const int64_t row0 = (int64_t)b * a.n_q_heads + h0;
+  const int64_t row0 = (int64_t)b * a.n_q_heads + h0;
+  {
+    // rescale factors of the 12 sources for this thread's two heads (2t, 2t+1)
+    float f0[kConsumerWarps], f1[kConsumerWarps];
+    float m0 = -INFINITY, m1 = -INFINITY;
+#pragma unroll
+    for (int sw = 0; sw < kConsumerWarps; ++sw) {
+      f0[sw] = xch[(sw * 34 + 32) * 32 + 8 * t];        // m of head 2t   (any lane with g == 2t)
+      f1[sw] = xch[(sw * 34 + 32) * 32 + 8 * t + 4];    // m of head 2t+1
+      m0 = fmaxf(m0, f0[sw]);
+      m1 = fmaxf(m1, f1[sw]);
+    }
+#pragma unroll
+    for (int sw = 0; sw < kConsumerWarps; ++sw) {
+      f0[sw] = f0[sw] == -INFINITY ? 0.f : ex2(f0[sw] - m0);
+      f1[sw] = f1[sw] == -INFINITY ? 0.f : ex2(f1[sw] - m1);
+    }
     float* acc0 = a.part_acc + ((int64_t)split * n_rows + row0) * kDim;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int e = 16 * g + 2 * j;
-      if (2 * t < a.n_rep) {
-        acc0[(2 * t) * kDim + e] = o[j][0] * tb.v_post;
-        acc0[(2 * t) * kDim + e + 1] = o[j][2] * tb.v_post;
-      }
-      if (2 * t + 1 < a.n_rep) {
-        acc0[(2 * t + 1) * kDim + e] = o[j][1] * tb.v_post;
-        acc0[(2 * t + 1) * kDim + e + 1] = o[j][3] * tb.v_post;
+    for (int kk = 0; kk < 3; ++kk) {
+      const int k = warp + kConsumerWarps * kk;          // accumulator value index j * 4 + c
+      if (k < 32) {
+        const int j = k >> 2, c = k & 3;
+        float v = 0.f;
+#pragma unroll
+        for (int sw = 0; sw < kConsumerWarps; ++sw)
+          v += xch[(sw * 34 + k) * 32 + lane] * ((c & 1) ? f1[sw] : f0[sw]);
+        const int head = 2 * t + (c & 1);
+        if (head < a.n_rep) acc0[head * kDim + 16 * g + 2 * j + (c >> 1)] = v * tb.v_post;
       }
     }
-    if (t == 0 && g < a.n_rep) {
-      a.part_m[(int64_t)split * n_rows + row0 + g] = m_run == -INFINITY ? -INFINITY : m_run * 0.6931471805599453f;
-      a.part_l[(int64_t)split * n_rows + row0 + g] = l_run;
+    if (warp == kConsumerWarps - 1) {
+      // l and m of head g: this lane's own head needs its own factors
+      float mg = -INFINITY;
+#pragma unroll
+      for (int sw = 0; sw < kConsumerWarps; ++sw) mg = fmaxf(mg, xch[(sw * 34 + 32) * 32 + lane]);
+      float lg = 0.f;
+#pragma unroll
+      for (int sw = 0; sw < kConsumerWarps; ++sw) {
+        const float ms = xch[(sw * 34 + 32) * 32 + lane];
+        lg += xch[(sw * 34 + 33) * 32 + lane] * (ms == -INFINITY ? 0.f : ex2(ms - mg));
+      }
+      lg += __shfl_xor_sync(0xffffffffu, lg, 1);
+      lg += __shfl_xor_sync(0xffffffffu, lg, 2);
+      if (t == 0 && g < a.n_rep) {
+        a.part_m[(int64_t)split * n_rows + row0 + g] = mg == -INFINITY ? -INFINITY : mg * 0.6931471805599453f;
+        a.part_l[(int64_t)split * n_rows + row0 + g] = lg;
+      }
     }
   }
   TQ_STAMP(21);   // partial written
-  // ---------------- two-level merge, no waiting anywhere ----------------
-  // Every CTA publishes its partial and bumps the counter of its group of `group`
-  // splits; the CTA that completes a group merges it into a level-1 partial and
-  // bumps the top counter; the CTA that completes the last group merges the
-  // level-1 partials, applies butterfly * signs / dim / l and writes the output.
-  // Counters are reset by whoever completes them, so they are zero between calls.
+  TQ_STAMP(30);
+  // ---------------- merge across splits, no waiting anywhere ----------------
+  // Every CTA publishes its partial and bumps a counter; the CTA that completes
+  // the count owns the merge and resets the counter, so counters are zero between
+  // calls.  Up to kMaxParts splits are merged in one step; beyond that the splits
+  // are merged in groups first (level 1) and the group results after (level 2).
   __shared__ int flag_s;
   int* ctr = tb.counters + (b * a.n_kv_heads + kvh) * kCtrPerGroup;
   const float* src_m = a.part_m;
   const float* src_l = a.part_l;
   const float* src_acc = a.part_acc;
   int n_final = tb.splits;
+  uint8_t* stage_ptr = smem + L::stage0;
+  const uint32_t stage_addr = sbase + L::stage0;
+  float m_star, l_star;
+  float4 acc4;
   if (tb.n_groups > 1) {
     const int gi = split / tb.group;
     const int gsize = min(tb.group, tb.splits - gi * tb.group);
@@ -672,11 +737,11 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
     if (!flag_s) return;
     __threadfence();
-    for (int r = warp; r < a.n_rep; r += kConsumerWarps) {
-      const int64_t row = (int64_t)b * a.n_q_heads + h0 + r;
-      float m_star, l_star;
-      float4 acc4;
-      merge_parts(a.part_m, a.part_l, a.part_acc, n_rows, row, gi * tb.group, gsize, lane, m_star, l_star, acc4);
+    if (!merge_staged(stage_ptr, stage_addr, merge_bar, 0, tb.status, a.part_m, a.part_l, a.part_acc, n_rows,
+                      row0, a.n_rep, gi * tb.group, gsize, tid, warp, lane, m_star, l_star, acc4))
+      return;
+    if (warp < a.n_rep) {
+      const int64_t row = row0 + warp;
       reinterpret_cast<float4*>(tb.l1_acc + ((int64_t)gi * n_rows + row) * kDim)[lane] = acc4;
       if (lane == 0) {
         tb.l1_m[(int64_t)gi * n_rows + row] = m_star;
@@ -690,6 +755,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
     TQ_STAMP(22);   // level-1 merge done
   }
   __threadfence();
+  TQ_STAMP(19);   // release fence done
   asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
   const int n_arrivals = tb.n_groups > 1 ? tb.n_groups : tb.splits;
   if (tid == 0) {
@@ -698,34 +764,39 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
     if (flag_s) ctr[0] = 0;
   }
   asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+  TQ_STAMP(25);   // counter bumped, result known
   if (!flag_s) return;
   __threadfence();
-  for (int r = warp; r < a.n_rep; r += kConsumerWarps) {
-    const int64_t row = (int64_t)b * a.n_q_heads + h0 + r;
-    float m_star, l_star;
-    float4 acc4;
-    merge_parts(src_m, src_l, src_acc, n_rows, row, 0, n_final, lane, m_star, l_star, acc4);
+  TQ_STAMP(26);   // acquire fence done
+  if (!merge_staged(stage_ptr, stage_addr, merge_bar, tb.n_groups > 1 ? 1 : 0, tb.status, src_m, src_l, src_acc,
+                    n_rows, row0, a.n_rep, 0, n_final, tid, warp, lane, m_star, l_star, acc4))
+    return;
+  TQ_STAMP(27);   // staged merge done
+  if (warp < a.n_rep) {
+    const int r = warp;
+    const int64_t row = row0 + r;
     if (tb.out_mode == 1) {
       reinterpret_cast<float4*>(tb.oacc + row * kDim)[lane] = acc4;
       if (lane == 0) {
         tb.om[row] = m_star;
         tb.ol[row] = l_star;
       }
-      continue;
-    }
-    float v[4] = {acc4.x, acc4.y, acc4.z, acc4.w};
-    warp_butterfly<4>(v, lane);
-    const float inv = l_star > 0.f ? (1.0f / kDim) / l_star : 0.f;
-    const int64_t ooff = b * tb.out_batch_stride + (int64_t)(h0 + r) * tb.out_head_stride + lane * 4;
+    } else {
+      float v[4] = {acc4.x, acc4.y, acc4.z, acc4.w};
+      warp_butterfly<4>(v, lane);
+      const float inv = l_star > 0.f ? (1.0f / kDim) / l_star : 0.f;
+      const int64_t ooff = b * tb.out_batch_stride + (int64_t)(h0 + r) * tb.out_head_stride + lane * 4;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float res = v[j] * sign_at(a.v_signs, lane * 4 + j) * inv;
-      if (tb.out_dtype == TQ_F32) reinterpret_cast<float*>(tb.out)[ooff + j] = res;
-      else if (tb.out_dtype == TQ_F16) reinterpret_cast<__half*>(tb.out)[ooff + j] = __float2half_rn(res);
-      else reinterpret_cast<__nv_bfloat16*>(tb.out)[ooff + j] = __float2bfloat16_rn(res);
+      for (int j = 0; j < 4; ++j) {
+        const float res = v[j] * sign_at(a.v_signs, lane * 4 + j) * inv;
+        if (tb.out_dtype == TQ_F32) reinterpret_cast<float*>(tb.out)[ooff + j] = res;
+        else if (tb.out_dtype == TQ_F16) reinterpret_cast<__half*>(tb.out)[ooff + j] = __float2half_rn(res);
+        else reinterpret_cast<__nv_bfloat16*>(tb.out)[ooff + j] = __float2bfloat16_rn(res);
+      }
     }
   }
   TQ_STAMP(23);   // final merge done
+  TQ_STAMP(31);
 }
 
 // ---- host side: scaled f16 codebooks --------------------------------------------------
@@ -795,8 +866,18 @@ static int launch_variant(const FlashArgs& a, const MmaTables& tb, int splits, c
     if (e != cudaSuccess) return set_error(TQ_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     attr_done[dev] = true;
   }
-  const dim3 grid(splits, a.n_kv_heads, a.batch);
-  flash_mma_kernel<KF, VB><<<grid, kThreads, L::total, st>>>(a, tb);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(splits, a.n_kv_heads, a.batch);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = L::total;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;   // may start while its predecessor drains
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, flash_mma_kernel<KF, VB>, a, tb);
+  if (e != cudaSuccess) return set_error(TQ_ERR_LAUNCH, "tq_flash_decode (mma): %s", cudaGetErrorString(e));
   return check_launch("tq_flash_decode (mma)");
 }
 

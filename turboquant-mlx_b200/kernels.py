@@ -226,7 +226,7 @@ def _strides3(t: torch.Tensor, batched: bool):
 
 def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerotated: bool = False,
                  mask: torch.Tensor | None = None, num_splits: int = 0, out_dtype=None,
-                 partials: bool = False, partial_out=None):
+                 partials: bool = False, partial_out=None, kv_stable: bool = False, out=None):
     """Split-K flash decoding for one query token per sequence.
 
     q: (B, n_q, dim).  k / v: dicts describing the stored keys / values:
@@ -241,6 +241,9 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
     q.dtype), or with partials=True the merged state (m (B, n_q), l (B, n_q),
     acc (B, n_q, dim)) before the final butterfly / normalisation; `partial_out`
     optionally names the three tensors to write (e.g. slices of a send buffer).
+    `out` optionally names the (B, n_q, dim) tensor to write.  kv_stable=True promises that the kernel launched just before this call on the
+    stream does not write any K / V row this call reads (e.g. the new token was
+    appended earlier), which lets the kernel prefetch K / V while that kernel drains.
     """
     _lib.require_cuda(q)
     B, n_q, dim = q.shape
@@ -319,6 +322,7 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
         raise ValueError(f"n_q_heads ({n_q}) must equal n_kv_heads ({n_kv}) * n_rep")
     P.n_kv_heads, P.seq_len = n_kv, S
     P.attn_scale, P.num_splits = float(attn_scale), int(num_splits)
+    P.kv_stable = int(kv_stable)
 
     if mask is not None:
         m = mask.to(torch.float32)
@@ -346,7 +350,10 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
         P.part_m, P.part_l, P.part_acc = pm.data_ptr(), pl.data_ptr(), pa.data_ptr()
     else:
         P.out_mode = 0
-        out = torch.empty((B, n_q, dim), dtype=out_dtype or q.dtype, device=dev)
+        if out is None:
+            out = torch.empty((B, n_q, dim), dtype=out_dtype or q.dtype, device=dev)
+        elif tuple(out.shape) != (B, n_q, dim) or out.stride(-1) != 1:
+            raise ValueError(f"out must be ({B}, {n_q}, {dim}) with a contiguous last dimension")
         P.out, P.out_dtype = out.data_ptr(), _lib.dtype_code(out.dtype)
         P.out_batch_stride, P.out_head_stride = out.stride(0), out.stride(1)
     P.stream = torch.cuda.current_stream(dev).cuda_stream

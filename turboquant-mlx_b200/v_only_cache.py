@@ -102,7 +102,8 @@ class VOnlyTurboQuantCache:
         return self._k_cache.offset
 
 
-def v_only_attention(queries, cache: VOnlyTurboQuantCache, attn_scale: float, mask=None):
+def v_only_attention(queries, cache: VOnlyTurboQuantCache, attn_scale: float, mask=None,
+                     kv_stable: bool = False, out=None):
     """Decode attention for a fused V-only cache: queries (B, n_q, 1, dim),
     dense K and packed V read once per KV head -> (B, n_q, 1, dim)."""
     total = cache.offset
@@ -116,6 +117,7 @@ def v_only_attention(queries, cache: VOnlyTurboQuantCache, attn_scale: float, ma
         if mask.dtype == torch.bool:
             mask = torch.where(mask, 0.0, float("-inf"))
         m3 = _mask_3d(mask, queries.shape[0], queries.shape[1], total)
-    out = flash_decode(queries[:, :, 0, :], k=k, v=v, attn_scale=attn_scale, mask=m3,
-                       out_dtype=queries.dtype)
-    return out.unsqueeze(2)
+    res = flash_decode(queries[:, :, 0, :], k=k, v=v, attn_scale=attn_scale, mask=m3,
+                       out_dtype=queries.dtype, kv_stable=kv_stable,
+                       out=None if out is None else out[:, :, 0, :])
+    return res.unsqueeze(2)
