@@ -5,9 +5,16 @@
 // five stages through warp shuffles.  All float32 steps that feed the index
 // compare use explicit round-to-nearest intrinsics (no FMA contraction) so the
 // packed words are bit-identical to a sequential float32 evaluation.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace tq {
+
+int try_launch_quantize_fast(const void* x, int x_dtype, int64_t n_outer, int64_t n_inner,
+                             int64_t x_outer_stride, int dim, int bits, const SignMask& signs,
+                             const Table16& thr, uint32_t* packed, int64_t packed_outer_stride,
+                             float* norms, int64_t norms_outer_stride, cudaStream_t st);
 
 constexpr int kWarpsPerBlock = 8;
 
@@ -275,6 +282,13 @@ extern "C" int tq_quantize(const void* x, int x_dtype, int64_t n_outer, int64_t 
   a.n_thr = (1 << bits) - 1;
   make_raw_thresholds(boundaries_host, a.n_thr, dim, &a.thr);
   cudaStream_t st = (cudaStream_t)stream;
+  if (x_dtype < TQ_F32 || x_dtype > TQ_BF16) return set_error(TQ_ERR_BAD_ARG, "unknown dtype %d", x_dtype);
+  static const bool force_general = getenv("TQ_FORCE_GENERIC") != nullptr;   // debugging aid
+  if (!force_general) {   // large contiguous dim-128 batches: thread-per-vector kernel
+    rc = try_launch_quantize_fast(x, x_dtype, n_outer, n_inner, x_outer_stride, dim, bits, a.signs, a.thr,
+                                  packed, packed_outer_stride, norms, norms_outer_stride, st);
+    if (rc != TQ_ERR_UNSUPPORTED) return rc;
+  }
   switch (x_dtype) {
     case TQ_F32: return launch_quantize<float>(a, dim, bits, st);
     case TQ_F16: return launch_quantize<__half>(a, dim, bits, st);
