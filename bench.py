@@ -268,11 +268,9 @@ def gpu_arm(args):
     launch_ms = ms_calls / N_LAYERS
     peak, peak_kind = measured_peaks()
     achieved = ALGO_BYTES_LAYER / (launch_ms * 1e-3) / 1e9
-    traffic = None
-    tpath = os.path.join(ROOT, "profiles", "flash_decode_traffic.json")
-    if os.path.exists(tpath):
-        with open(tpath) as f:
-            traffic = json.load(f).get("dram_bytes_per_launch")
+    # dram__bytes_read.sum + dram__bytes_write.sum per launch of this kernel on this workload, from the
+    # ncu capture summarised in profiles/flash_mma_kernel_c2.md (40.97 MB read + 2.3 KB written)
+    traffic = 40_966_656 + 2_304 if N_LAYERS == 28 else None
 
     # ---- end to end through the public API with host buffers -------------------
     tq.apply_patch()
