@@ -443,6 +443,92 @@ def workload_c3(args):
                                  "bytes_per_layer_step": nbytes}}))
 
 
+def workload_c5(args):
+    """Config 5: long-context decode, Llama-3-70B attention shape (64 q / 8 kv heads, d 128), K 8-bit
+    group-affine + V PolarQuant 3-bit, the sequence split across the ranks: 131072 positions per GPU
+    (1M tokens at 8 GPUs).  Every rank attends over its chunk, the (m, l, acc) partial states are
+    all-gathered through NCCL (33 KB per rank) and merged locally.  201.3 MB of KV per GPU per layer-step."""
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    tq = entry.load_package()
+    from turboquant_mlx_b200.distributed import partial_buffer, sequence_parallel_decode
+    nq, nkv, S, layers = 64, 8, 131072, 6
+    gen = torch.Generator(device=dev).manual_seed(77 + rank)
+    pq = tq.PolarQuantizer(DIM, 3, seed=43, device=dev)
+    ks, vs = [], []
+    for _ in range(layers):
+        codes = torch.randint(0, 256, (1, nkv, S, DIM), generator=gen, device=dev, dtype=torch.uint8)
+        scales = (torch.rand((1, nkv, S, 2), generator=gen, device=dev) * 0.02 + 0.01).half()
+        biases = (torch.rand((1, nkv, S, 2), generator=gen, device=dev) * -2.0 - 1.0).half()
+        vp = torch.randint(0, 2 ** 30, (1, nkv, S, 13), generator=gen, device=dev, dtype=torch.int64)
+        vp[..., 12] &= 0x00FFFFFF
+        vn = torch.exp(0.5 * torch.randn((1, nkv, S), generator=gen, device=dev)) * 11.3
+        ks.append(dict(format="affine", codes=codes, scales=scales, biases=biases, bits=8, group=64))
+        vs.append(dict(format="polar", packed=vp.to(torch.uint32), norms=vn.float(), centroids=pq.centroids,
+                       signs=pq.signs, bits=3))
+        del vp
+    q = torch.randn((layers, 1, nq, DIM), generator=torch.Generator(device=dev).manual_seed(5), device=dev).half()
+    scale = 1.0 / math.sqrt(DIM)
+    bufs = [partial_buffer(nq, DIM, dev)[0] for _ in range(layers)]
+
+    def step():
+        for l in range(layers):
+            if world > 1:
+                sequence_parallel_decode(q[l], k=ks[l], v=vs[l], attn_scale=scale, send_buf=bufs[l])
+            else:
+                tq.flash_decode(q[l], k=ks[l], v=vs[l], attn_scale=scale)
+
+    def kernels_only():
+        for l in range(layers):
+            tq.flash_decode(q[l], k=ks[l], v=vs[l], attn_scale=scale, partials=True)
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        sync_all()
+        ms = e0.elapsed_time(e1) / steps
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    ms = timed(step, args.steps, max(args.warmup, 3)) / layers
+    ms_k = timed(kernels_only, args.steps, 3) / layers
+    nbytes = nkv * S * (136 + 56)
+    peak, kind = measured_peaks()
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "unit": "GB/s", "n_gpus": world, "value": world * nbytes / ms / 1e6,
+            "scaling": "weak", "us_per_layer_step": ms * 1e3, "us_kernel_only": ms_k * 1e3,
+            "per_gpu_frac_of_peak": nbytes / ms / 1e6 / peak, "peak": peak, "peak_kind": kind,
+            "tensor_core_path": tq._lib.lib().tq_flash_decode_last_kernel() == 1,
+            "config": {"workload": "C5 sequence-sharded long-context decode: 64q/8kv, K8 affine + V3 polar, "
+                                   "131072 positions per GPU, partial states all-gathered and merged per layer",
+                       "context_total": world * S, "bytes_per_gpu_per_layer_step": nbytes,
+                       "exchange_bytes_per_rank": nq * (DIM + 2) * 4, "timing": "eager launches, CUDA events, max over ranks"}}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     global N_LAYERS
     ap = argparse.ArgumentParser()
@@ -455,13 +541,15 @@ def main():
                     help="layers (independent KV buffers) per step; fewer for a profiler capture")
     ap.add_argument("--kernel-only", action="store_true",
                     help="plain launches of the flash-decode kernel only (no graph, no e2e): profiler case")
-    ap.add_argument("--workload", default="c2", choices=["c2", "c1", "c3"],
+    ap.add_argument("--workload", default="c2", choices=["c2", "c1", "c3", "c5"],
                     help="c2 = the headline benchmark; c1 / c3 = secondary measurements of other configurations")
     args = ap.parse_args()
     if args.workload == "c1":
         return workload_c1(args)
     if args.workload == "c3":
         return workload_c3(args)
+    if args.workload == "c5":
+        return workload_c5(args)
     N_LAYERS = args.layers
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":

@@ -273,6 +273,7 @@ def test_affine_k8_with_polar_and_affine_values(tq, oracle, dev, v_bits):
     vp, vn = oracle.quantize_packed(vraw, vq.signs.cpu().numpy(), 3)
     vpol = dict(format="polar", packed=_t(vp, dev), norms=_t(vn, dev), centroids=vq.centroids, signs=vq.signs, bits=3)
     out2 = tq.flash_decode(_t(q, dev), k=k, v=vpol, attn_scale=scale, out_dtype=torch.float32)
+    assert tq._lib.lib().tq_flash_decode_last_kernel() == 1      # K8 affine + V3 polar runs on tensor cores
     for b in range(B):
         ref, _ = oracle.decode_attention(q[b], k_dense=kd[b], attn_scale=scale, n_rep=n_rep,
                                          v_polar=dict(packed=vp[b], norms=vn[b], centroids=oracle.codebook(3),

@@ -85,7 +85,7 @@ static int fill_args(const tq_flash_params* p, FlashArgs* a) {
   a->q_batch_stride = p->q_batch_stride;
   a->q_head_stride = p->q_head_stride;
   a->k_format = p->k_format;
-  a->k_bits = p->k_format == TQ_KV_POLAR ? p->k_bits : 4;
+  a->k_bits = (p->k_format == TQ_KV_POLAR || p->k_format == TQ_KV_AFFINE) ? p->k_bits : 4;
   a->k_dtype = p->k_dtype;
   a->k_group = p->k_group > 0 ? p->k_group : p->dim;
   a->k_data = p->k_data;
@@ -138,7 +138,8 @@ static void make_plan(const tq_flash_params* p, const FlashArgs& a, Plan* plan) 
   int64_t splits = p->num_splits;
   if (splits <= 0) {
     const int64_t target = (plan->mma ? flash_mma_ctas_per_sm() : 2) * (int64_t)num_sms();
-    splits = (target + groups - 1) / groups;
+    splits = target / groups;                          // round down: the grid must fit one wave
+    if (splits < 1) splits = 1;   // more groups than CTA slots: one CTA per group (splitting further measured slower)
     const int64_t by_len = (a.seq_len + 127) / 128;   // at least 128 positions per split
     if (splits > by_len) splits = by_len;
   }

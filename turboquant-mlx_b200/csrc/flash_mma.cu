@@ -48,7 +48,7 @@ constexpr int kMaxParts = 37;               // partial states one merge call com
 constexpr int kMaxGroups = 16;              // level-1 groups when there are more than kMaxParts splits
 constexpr int kCtrPerGroup = kMaxGroups + 1; // level-1 counters + the top counter
 
-enum : int { KF_DENSE = 0, KF_POLAR3 = 3, KF_POLAR4 = 4 };
+enum : int { KF_DENSE = 0, KF_POLAR3 = 3, KF_POLAR4 = 4, KF_AFFINE8 = 8 };
 
 struct MmaTables {
   uint16_t k_c16[16];   // beta_k-scaled centroids as f16 bits
@@ -75,6 +75,9 @@ template <int KF> struct KGeom;
 template <> struct KGeom<KF_DENSE> { static constexpr int row = kDenseRowBytes, lut = 0, norms = 0; };
 template <> struct KGeom<KF_POLAR3> { static constexpr int row = 52, lut = 64 * 32 * 4, norms = kTile * 4; };
 template <> struct KGeom<KF_POLAR4> { static constexpr int row = 64, lut = 256 * 32 * 4, norms = kTile * 4; };
+// group-affine 8-bit codes, two groups of 64: per row 128 code bytes; the "norms" slot holds the
+// row's two fp16 scales (4 B) followed, kTile * 4 bytes later, by its two fp16 biases
+template <> struct KGeom<KF_AFFINE8> { static constexpr int row = 128, lut = 0, norms = 2 * kTile * 4; };
 template <int VB> struct VGeom;
 template <> struct VGeom<3> { static constexpr int row = 52, lut = 64 * 32 * 4; };
 template <> struct VGeom<4> { static constexpr int row = 64, lut = 256 * 32 * 4; };
@@ -183,6 +186,7 @@ __device__ __forceinline__ int kslot_element(int ks, int s) {
   const int tt = (s & 7) >> 1, lo = s & 1, up = s >> 3;
   if (KF == KF_DENSE) return 8 * (4 * (ks >> 1) + tt) + 4 * (ks & 1) + 2 * up + lo;
   if (KF == KF_POLAR4) return 32 * tt + 4 * ks + 2 * up + lo;
+  if (KF == KF_AFFINE8) return 16 * (4 * (ks >> 2) + tt) + 4 * (ks & 3) + 2 * up + lo;   // k-steps 0-3: group 0
   const int pi = 2 * ks + up;   // pair index within the thread: 15 pairs in words 3t..3t+2, one in word 12
   return (pi < 15 ? 30 * tt + 2 * pi : 120 + 2 * tt) + lo;
 }
@@ -319,6 +323,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   const uint32_t merge_bar = sbase + L::bars + 8 * (2 * kStages);   // completion of the staged-merge copies
 
   __shared__ uint16_t c16_s[32];
+  __shared__ float qsum_s[16];     // affine keys: per head and 64-element group, sum of the query
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(full_bar(s), 1);
@@ -339,7 +344,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       const int e = i >> 5;
       vl[i] = (uint32_t)c16_s[e & ((1 << VB) - 1)] | ((uint32_t)c16_s[e >> VB] << 16);
     }
-    if (KF != KF_DENSE) {
+    if (KF == KF_POLAR3 || KF == KF_POLAR4) {
       constexpr int KB = KF == KF_POLAR3 ? 3 : 4;
       uint32_t* kl = reinterpret_cast<uint32_t*>(smem + L::klut);
       constexpr int nk = 1 << (2 * KB);
@@ -369,17 +374,24 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         }
         v[j] = x;
       }
-      if (KF != KF_DENSE && !a.q_prerotated) {
+      if ((KF == KF_POLAR3 || KF == KF_POLAR4) && !a.q_prerotated) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) v[j] *= sign_at(a.k_signs, lane * 4 + j);
         warp_butterfly<4>(v, lane);
       }
+      float qsum = 0.f;   // sum of the f16 (hi + lo) query values this lane holds
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const __half hi = __float2half_rn(v[j]);
         const __half lo = __float2half_rn(v[j] - __half2float(hi));
         qs[r * kDim + lane * 4 + j] = hi;
         qs[(8 + r) * kDim + lane * 4 + j] = lo;
+        qsum += __half2float(hi) + __half2float(lo);
+      }
+      if (KF == KF_AFFINE8) {   // lanes 0-15 hold elements 0-63 (group 0), lanes 16-31 group 1
+#pragma unroll
+        for (int k = 8; k > 0; k >>= 1) qsum += __shfl_xor_sync(0xffffffffu, qsum, k);
+        if ((lane & 15) == 0) qsum_s[r * 2 + (lane >> 4)] = qsum;
       }
     }
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");   // consumers only: tables and query rows ready
@@ -388,10 +400,18 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   const uint8_t* kbase;
   if (KF == KF_DENSE)
     kbase = reinterpret_cast<const uint8_t*>(a.k_data) + (b * a.k_batch_stride + kvh * a.k_head_stride) * 2;
+  else if (KF == KF_AFFINE8)
+    kbase = reinterpret_cast<const uint8_t*>(a.k_data) + (b * a.k_batch_stride + kvh * a.k_head_stride);
   else
     kbase = reinterpret_cast<const uint8_t*>(a.k_data) + (b * a.k_batch_stride + kvh * a.k_head_stride) * 4;
+  // affine keys: per position two fp16 scales and two fp16 biases = one 32-bit word each
+  const uint32_t* kscbase = KF == KF_AFFINE8 ? reinterpret_cast<const uint32_t*>(
+      reinterpret_cast<const __half*>(a.k_scales) + b * a.ks_batch_stride + kvh * a.ks_head_stride) : nullptr;
+  const uint32_t* kbibase = KF == KF_AFFINE8 ? reinterpret_cast<const uint32_t*>(
+      reinterpret_cast<const __half*>(a.k_biases) + b * a.ks_batch_stride + kvh * a.ks_head_stride) : nullptr;
   const uint8_t* vbase = reinterpret_cast<const uint8_t*>(a.v_data) + (b * a.v_batch_stride + kvh * a.v_head_stride) * 4;
-  const float* knbase = KF == KF_DENSE ? nullptr : a.k_norms + b * a.kn_batch_stride + kvh * a.kn_head_stride;
+  const float* knbase = (KF == KF_DENSE || KF == KF_AFFINE8)
+                            ? nullptr : a.k_norms + b * a.kn_batch_stride + kvh * a.kn_head_stride;
   const float* vnbase = a.v_norms + b * a.vn_batch_stride + kvh * a.vn_head_stride;
 
   // =============================== producer ===============================
@@ -414,7 +434,8 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       // byte counts moved by bulk copies (multiples of 16); ragged remainders by plain loads
       const uint32_t v_total = nvp * VGeom<VB>::row, v_bulk = v_total & ~15u;
       const uint32_t n_total = nvp * 4, n_bulk = n_total & ~15u;
-      const uint32_t k_total = KF == KF_DENSE ? 0u : (uint32_t)nvp * KGeom<KF>::row, k_bulk = k_total & ~15u;
+      const uint32_t k_total = (KF == KF_DENSE || KF == KF_AFFINE8) ? 0u : (uint32_t)nvp * KGeom<KF>::row;
+      const uint32_t k_bulk = k_total & ~15u;
       const uint8_t* vsrc = vbase + p0 * VGeom<VB>::row;
       const uint8_t* ksrc = kbase + p0 * (KF == KF_DENSE ? 256 : KGeom<KF>::row);
       {
@@ -424,23 +445,36 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
               *reinterpret_cast<const uint32_t*>(vsrc + v_bulk + 4 * w);
         if (n_bulk + 4 * w < n_total)
           *reinterpret_cast<float*>(stg + L::vn_off + n_bulk + 4 * w) = vnbase[p0 + n_bulk / 4 + w];
-        if (KF != KF_DENSE) {
+        if (KF == KF_POLAR3 || KF == KF_POLAR4) {
           if (k_total != 0 && k_bulk + 4 * w < k_total)
             *reinterpret_cast<uint32_t*>(stg + L::k_off + k_bulk + 4 * w) =
                 *reinterpret_cast<const uint32_t*>(ksrc + k_bulk + 4 * w);
           if (n_bulk + 4 * w < n_total)
             *reinterpret_cast<float*>(stg + L::kn_off + n_bulk + 4 * w) = knbase[p0 + n_bulk / 4 + w];
         }
+        if (KF == KF_AFFINE8) {
+          if (n_bulk + 4 * w < n_total) {
+            *reinterpret_cast<uint32_t*>(stg + L::kn_off + n_bulk + 4 * w) = kscbase[p0 + n_bulk / 4 + w];
+            *reinterpret_cast<uint32_t*>(stg + L::kn_off + kTile * 4 + n_bulk + 4 * w) = kbibase[p0 + n_bulk / 4 + w];
+          }
+        }
       }
       __syncwarp();
       if (lane == 0) {
         uint32_t tx = v_bulk + n_bulk;
-        tx += KF == KF_DENSE ? (uint32_t)nvp * 256u : k_bulk + n_bulk;
+        if (KF == KF_DENSE) tx += (uint32_t)nvp * 256u;
+        else if (KF == KF_AFFINE8) tx += (uint32_t)nvp * 128u + 2 * n_bulk;
+        else tx += k_bulk + n_bulk;
         mbar_arrive_expect_tx(full_bar(s), tx);
         if (KF == KF_DENSE) bulk_g2s(st + L::k_off, ksrc, (uint32_t)nvp * 256u, full_bar(s));
+        if (KF == KF_AFFINE8) {
+          bulk_g2s(st + L::k_off, ksrc, (uint32_t)nvp * 128u, full_bar(s));
+          if (n_bulk) bulk_g2s(st + L::kn_off, kscbase + p0, n_bulk, full_bar(s));
+          if (n_bulk) bulk_g2s(st + L::kn_off + kTile * 4, kbibase + p0, n_bulk, full_bar(s));
+        }
         if (v_bulk) bulk_g2s(st + L::v_off, vsrc, v_bulk, full_bar(s));
         if (n_bulk) bulk_g2s(st + L::vn_off, vnbase + p0, n_bulk, full_bar(s));
-        if (KF != KF_DENSE) {
+        if (KF == KF_POLAR3 || KF == KF_POLAR4) {
           if (k_bulk) bulk_g2s(st + L::k_off, ksrc, k_bulk, full_bar(s));
           if (n_bulk) bulk_g2s(st + L::kn_off, knbase + p0, n_bulk, full_bar(s));
         }
@@ -510,6 +544,31 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) sc[ng][c] += sc2[c];
+      } else if (KF == KF_AFFINE8) {
+        // codes -> f16 (1024 + code) with one PRMT per pair; one accumulator per 64-element group;
+        // the offset and the per-position scale / bias are applied after the MMA
+        const uint32_t row = st + L::k_off + prow * 128 + t * 16;
+        float g1[4] = {0.f, 0.f, 0.f, 0.f};
+        const uint4 r0 = lds128(row), r1 = lds128(row + 64);
+        const uint32_t w0[4] = {r0.x, r0.y, r0.z, r0.w}, w1[4] = {r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          mma16816(sc[ng], aq[w], __byte_perm(w0[w], 0x64646464u, 0x4140), __byte_perm(w0[w], 0x64646464u, 0x4342));
+          mma16816(g1, aq[4 + w], __byte_perm(w1[w], 0x64646464u, 0x4140), __byte_perm(w1[w], 0x64646464u, 0x4342));
+        }
+        const float q0 = qsum_s[2 * g], q1 = qsum_s[2 * g + 1];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int pos = pw + 8 * ng + 2 * t + c;
+          const __half2 sc2h = *reinterpret_cast<const __half2*>(smem + L::stage0 + s * L::stage_bytes + L::kn_off + pos * 4);
+          const __half2 bi2h = *reinterpret_cast<const __half2*>(smem + L::stage0 + s * L::stage_bytes + L::kn_off + kTile * 4 + pos * 4);
+          const float d0 = (sc[ng][c] + sc[ng][c + 2]) - 1024.f * q0;     // sum_e q_e * code_e, group 0
+          const float d1 = (g1[c] + g1[c + 2]) - 1024.f * q1;
+          const float dot = __low2float(sc2h) * d0 + __low2float(bi2h) * q0 +
+                            __high2float(sc2h) * d1 + __high2float(bi2h) * q1;
+          sc[ng][c] = dot;          // the generic post-processing below adds [c] and [c + 2]
+          sc[ng][c + 2] = 0.f;
+        }
       } else if (KF == KF_POLAR4) {
         const uint4 w4 = lds128(st + L::k_off + prow * 64 + t * 16);
         const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
@@ -553,7 +612,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       for (int c = 0; c < 2; ++c) {
         const int pos = pw + 8 * ng + 2 * t + c;
         float v = (sc[ng][c] + sc[ng][c + 2]) * tb.k_post;
-        if (KF != KF_DENSE) v *= lds_f32(st + L::kn_off + pos * 4);
+        if (KF == KF_POLAR3 || KF == KF_POLAR4) v *= lds_f32(st + L::kn_off + pos * 4);
         const float vn = lds_f32(st + L::vn_off + pos * 4);
         const bool valid = pos < nvp;
         s2[ng][c] = valid ? v : -INFINITY;
@@ -895,6 +954,12 @@ bool flash_mma_supported(const FlashArgs& a) {
     if (a.k_bits != 3 && a.k_bits != 4) return false;
     if (!aligned16(a.k_data) || a.k_batch_stride % 4 || a.k_head_stride % 4) return false;
     if (!aligned16(a.k_norms) || a.kn_batch_stride % 4 || a.kn_head_stride % 4) return false;
+  } else if (a.k_format == TQ_KV_AFFINE) {
+    // 8-bit codes, two groups of 64: one 32-bit word of scales and one of biases per position
+    if (a.k_bits != 8 || a.k_group != 64) return false;
+    if (!aligned16(a.k_data) || a.k_batch_stride % 16 || a.k_head_stride % 16) return false;
+    if (!aligned16(a.k_scales) || !aligned16(a.k_biases) || a.ks_batch_stride % 8 || a.ks_head_stride % 8)
+      return false;
   } else {
     return false;
   }
@@ -942,6 +1007,8 @@ int launch_flash_mma(const FlashArgs& a, int splits, const MmaOutput& mo, cudaSt
     tb.k_post = a.attn_scale * kLog2e / ((float)kDim * kb.beta);
     kf = a.k_bits == 3 ? KF_POLAR3 : KF_POLAR4;
   }
+  if (a.k_format == TQ_KV_AFFINE)
+    return a.v_bits == 3 ? launch_variant<KF_AFFINE8, 3>(a, tb, splits, st) : launch_variant<KF_AFFINE8, 4>(a, tb, splits, st);
   if (kf == KF_DENSE) return a.v_bits == 3 ? launch_variant<KF_DENSE, 3>(a, tb, splits, st) : launch_variant<KF_DENSE, 4>(a, tb, splits, st);
   if (kf == KF_POLAR3) return a.v_bits == 3 ? launch_variant<KF_POLAR3, 3>(a, tb, splits, st) : launch_variant<KF_POLAR3, 4>(a, tb, splits, st);
   return a.v_bits == 3 ? launch_variant<KF_POLAR4, 3>(a, tb, splits, st) : launch_variant<KF_POLAR4, 4>(a, tb, splits, st);
