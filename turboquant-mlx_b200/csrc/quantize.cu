@@ -16,6 +16,11 @@ int try_launch_quantize_fast(const void* x, int x_dtype, int64_t n_outer, int64_
                              const Table16& thr, uint32_t* packed, int64_t packed_outer_stride,
                              float* norms, int64_t norms_outer_stride, cudaStream_t st);
 
+int try_launch_dequantize_fast(const uint32_t* packed, int64_t packed_outer_stride, const float* norms,
+                               int64_t norms_outer_stride, int64_t n_outer, int64_t n_inner, int dim,
+                               int bits, const Table16& cs, float s, const SignMask& signs, void* out,
+                               int out_dtype, int64_t out_outer_stride, cudaStream_t st);
+
 constexpr int kWarpsPerBlock = 8;
 
 struct QuantArgs {
@@ -325,6 +330,12 @@ extern "C" int tq_dequantize(const uint32_t* packed, int64_t packed_outer_stride
     a.cs.v[i] = cs;
   }
   cudaStream_t st = (cudaStream_t)stream;
+  static const bool force_general = getenv("TQ_FORCE_GENERIC") != nullptr;   // debugging aid
+  if (!force_general) {   // large contiguous dim-128 batches: split-per-vector kernel
+    rc = try_launch_dequantize_fast(packed, packed_outer_stride, norms, norms_outer_stride, n_outer, n_inner,
+                                    dim, bits, a.cs, a.s, a.signs, out, out_dtype, out_outer_stride, st);
+    if (rc != TQ_ERR_UNSUPPORTED) return rc;
+  }
   switch (out_dtype) {
     case TQ_F32: return launch_dequantize<float>(a, dim, bits, st);
     case TQ_F16: return launch_dequantize<__half>(a, dim, bits, st);
