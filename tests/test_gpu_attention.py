@@ -332,3 +332,25 @@ def test_tensor_core_path_is_taken_and_accurate(tq, oracle, dev):
     ws = tq._lib.workspace(16, dev, tag=f"flash{n_kv}")
     hdr = L.tq_flash_decode_header_bytes(1, n_kv)
     assert int(ws[:hdr].view(torch.int32).abs().sum()) == 0   # no bounded wait gave up, counters back at zero
+
+
+def test_prepared_calls_match_direct_calls(tq, golden, dev):
+    """FlashDecodePlan / MergePlan (arguments marshalled once) give the same result as the direct
+    calls, also when run repeatedly and with kv_stable / out set."""
+    g = golden
+    scale = 1.0 / math.sqrt(128)
+    q = _t(g["att_q"], dev).unsqueeze(0)
+    k, v = _golden_dense_case(tq, golden, dev)
+    want = tq.flash_decode(q, k=k, v=v, attn_scale=scale, out_dtype=torch.float32)
+    out = torch.empty_like(want)
+    plan = tq.FlashDecodePlan(q, k=k, v=v, attn_scale=scale, out=out, kv_stable=True)
+    for _ in range(3):
+        res = plan.run()
+    assert res.data_ptr() == out.data_ptr()
+    assert _rel(out[0].cpu().numpy(), want[0].cpu().numpy()) < 1e-6
+    m, l, acc = tq.flash_decode(q, k=k, v=v, attn_scale=scale, partials=True)
+    pm, pl, pa = torch.stack([m[0], m[0]]), torch.stack([l[0], l[0]]), torch.stack([acc[0], acc[0]])
+    merged = torch.empty((14, 128), dtype=torch.float32, device=dev)
+    mp = tq.MergePlan(pm, pl, pa, v["signs"], merged)
+    mp.run()
+    assert _rel(merged.cpu().numpy(), want[0].cpu().numpy()) < 1e-5   # two identical parts merge to the same result

@@ -20,6 +20,8 @@ from .kernels import (
     flash_attention_turboquant,
     flash_decode,
     merge_partials,
+    FlashDecodePlan,
+    MergePlan,
 )
 from .fused_attention import turboquant_attention
 from .packing import pack_indices, unpack_indices, packed_dim

@@ -41,19 +41,22 @@ def partial_views(buf: torch.Tensor, rows: int, dim: int):
     return m, l, acc
 
 
-def gather_partials(send: torch.Tensor, group=None) -> torch.Tensor:
+def gather_partials(send: torch.Tensor, group=None, recv: torch.Tensor | None = None) -> torch.Tensor:
     """all_gather of one rank's packed partial state (rows * (dim + 2),) ->
-    (world, rows * (dim + 2)).  Works on CUDA tensors (NCCL) and CPU tensors (gloo)."""
+    (world, rows * (dim + 2)).  Works on CUDA tensors (NCCL) and CPU tensors (gloo).
+    `recv` optionally names a persistent receive buffer."""
     world = dist.get_world_size(group)
     if send.ndim != 1:
         raise ValueError(f"expected a flat partial buffer, got shape {tuple(send.shape)}")
-    recv = torch.empty((world, send.numel()), dtype=send.dtype, device=send.device)
+    if recv is None:
+        recv = torch.empty((world, send.numel()), dtype=send.dtype, device=send.device)
     dist.all_gather_into_tensor(recv.view(-1), send.contiguous(), group=group)
     return recv
 
 
 def sequence_parallel_decode(q, *, k, v, attn_scale: float, group=None, out_dtype=None,
-                             q_prerotated: bool = False, mask=None, send_buf=None) -> torch.Tensor:
+                             q_prerotated: bool = False, mask=None, send_buf=None,
+                             recv_buf=None) -> torch.Tensor:
     """Decode attention with the sequence split across the ranks of `group`.
 
     q (B, n_q, dim) is replicated; `k` / `v` describe this rank's chunk of
@@ -71,7 +74,7 @@ def sequence_parallel_decode(q, *, k, v, attn_scale: float, group=None, out_dtyp
         kernels.flash_decode(q, k=k, v=v, attn_scale=attn_scale, q_prerotated=q_prerotated, mask=mask,
                              partials=True,
                              partial_out=(m.view(B, n_q), l.view(B, n_q), acc.view(B, n_q, dim)))
-    recv = gather_partials(send_buf, group)
+    recv = gather_partials(send_buf, group, recv_buf)
     gm, gl, gacc = partial_views(recv, rows, dim)
     signs = v["signs"] if (v is not None and v.get("format") == "polar") else None
     out = kernels.merge_partials(gm, gl, gacc, signs, out_dtype or q.dtype)

@@ -23,7 +23,7 @@ __all__ = [
     "fused_quantize", "dequant_fp16", "packed_dequantize", "packed_fused_qk_scores",
     "prerotate_query", "prerot_fused_qk_scores", "prerot_packed_dequantize",
     "sparse_v_matvec", "count_active_positions", "flash_attention_turboquant",
-    "flash_decode", "merge_partials",
+    "flash_decode", "merge_partials", "FlashDecodePlan", "MergePlan",
 ]
 
 
@@ -226,7 +226,8 @@ def _strides3(t: torch.Tensor, batched: bool):
 
 def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerotated: bool = False,
                  mask: torch.Tensor | None = None, num_splits: int = 0, out_dtype=None,
-                 partials: bool = False, partial_out=None, kv_stable: bool = False, out=None):
+                 partials: bool = False, partial_out=None, kv_stable: bool = False, out=None,
+                 _prepare_only: bool = False):
     """Split-K flash decoding for one query token per sequence.
 
     q: (B, n_q, dim).  k / v: dicts describing the stored keys / values:
@@ -364,9 +365,32 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
     ws = _lib.workspace(need, dev, tag=f"flash{B * n_kv}")   # counters: one layout per batch * n_kv
     if ws is not None:
         P.workspace, P.workspace_bytes = ws.data_ptr(), ws.numel()
+    result = (pm, pl, pa) if partials else out
+    if _prepare_only:
+        keep += [q, ws, result]
+        return P, keep, result, dev
     _lib.check(L.tq_flash_decode(ctypes.byref(P)))
     del keep
-    return (pm, pl, pa) if partials else out
+    return result
+
+
+class FlashDecodePlan:
+    """A flash_decode call with its arguments marshalled once.  The tensors named
+    at construction (q, K/V storage, outputs) are read / written in place on every
+    `run()`, which costs a single C call: use it in decode loops where the host
+    time per layer matters.  Same keyword arguments as `flash_decode`."""
+
+    def __init__(self, q, **kwargs):
+        self._P, self._keep, self.result, self._dev = flash_decode(q, _prepare_only=True, **kwargs)
+        self._fn = _lib.lib().tq_flash_decode
+        self._ref = ctypes.byref(self._P)
+
+    def run(self):
+        self._P.stream = torch.cuda.current_stream(self._dev).cuda_stream
+        rc = self._fn(self._ref)
+        if rc:
+            _lib.check(rc)
+        return self.result
 
 
 def flash_attention_turboquant(q_rot, k_packed, k_norms, v_packed, v_norms, k_centroids,
@@ -412,3 +436,26 @@ def merge_partials(part_m, part_l, part_acc, v_signs, out_dtype=torch.float32) -
         rows, dim, _lib.host_floats(v_signs), _lib.ptr(out), _lib.dtype_code(out_dtype), dim,
         _lib.stream_ptr(pa.device)))
     return out
+
+
+class MergePlan:
+    """`merge_partials` with its arguments marshalled once (see FlashDecodePlan)."""
+
+    def __init__(self, part_m, part_l, part_acc, v_signs, out):
+        _lib.require_cuda(part_m, part_l, part_acc, out)
+        n_parts, rows, dim = part_acc.shape
+        assert part_m.stride(-1) == 1 and part_l.stride(-1) == 1 and part_acc.stride(-1) == 1
+        assert part_acc.stride(1) == dim and out.is_contiguous()
+        self._keep = (part_m, part_l, part_acc, out, _lib.host_floats(v_signs))
+        self._args = (_lib.ptr(part_m), part_m.stride(0), _lib.ptr(part_l), part_l.stride(0),
+                      _lib.ptr(part_acc), part_acc.stride(0), n_parts, rows, dim, self._keep[4],
+                      _lib.ptr(out), _lib.dtype_code(out.dtype), dim)
+        self._fn = _lib.lib().tq_merge_partials
+        self._dev = out.device
+        self.result = out
+
+    def run(self):
+        rc = self._fn(*self._args, _lib.stream_ptr(self._dev))
+        if rc:
+            _lib.check(rc)
+        return self.result
