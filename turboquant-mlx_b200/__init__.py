@@ -32,5 +32,6 @@ from .rotation import (
     random_diagonal_sign,
 )
 from .base import KVCache, scaled_dot_product_attention
+from .mixed_cache import MixedQuantKVCache
 
 __version__ = "0.3.0"

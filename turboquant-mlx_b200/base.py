@@ -64,6 +64,12 @@ class KVCache:
             self.keys, self.values = v
             self.offset = self.keys.shape[2]
 
+    def to_quantized(self, group_size: int = 64, bits: int = 8, v_bits: int | None = None):
+        """Group-affine quantized copy of this cache (keys at `bits`, values at `v_bits`)."""
+        from .mixed_cache import MixedQuantKVCache
+        return MixedQuantKVCache.from_kvcache(self, k_bits=bits, v_bits=bits if v_bits is None else v_bits,
+                                              group_size=group_size)
+
     def make_mask(self, N, return_array: bool = False, window_size=None):
         if N == 1:
             return None

@@ -1,0 +1,160 @@
+"""Mixed-precision group-affine KV cache: keys at `k_bits` (8), values at `v_bits`
+(4 or 8), group size 64.
+
+This is the cache the reference's README recommends (`MixedQuantKVCache.from_kvcache(
+cache, k_bits=8, v_bits=4)` of its mlx-lm fork, README.md:28-47) and the format
+`KVCache.to_quantized` produces in hybrid_cache.py:57-63.  Neither implementation
+is part of the reference tree, so the number format is this library's own (see
+affine.py).  Usage follows the README: prefill into a plain `KVCache`, convert once,
+then decode; the attention hook recognises the cache by its `bits` attribute and
+runs the quantized decode kernel on the stored codes (no dequantized copy)."""
+
+from __future__ import annotations
+
+import torch
+
+from .affine import affine_dequantize, affine_quantize
+from .kernels import flash_decode
+
+
+class MixedQuantKVCache:
+    step = 256
+
+    def __init__(self, k_bits: int = 8, v_bits: int = 4, group_size: int = 64):
+        if k_bits != 8:
+            raise ValueError(f"keys are stored at 8 bits, got k_bits={k_bits}")
+        if v_bits not in (4, 8):
+            raise ValueError(f"values are stored at 4 or 8 bits, got v_bits={v_bits}")
+        self.k_bits, self.v_bits, self.group_size = k_bits, v_bits, group_size
+        self.bits = k_bits                 # what an attention router looks at
+        self.offset = 0
+        self.k_codes = self.k_scales = self.k_biases = None
+        self.v_codes = self.v_scales = self.v_biases = None
+        self._dtype = torch.float16
+
+    # ---- construction ---------------------------------------------------------
+    @classmethod
+    def from_kvcache(cls, cache, k_bits: int = 8, v_bits: int = 4, group_size: int = 64):
+        """Quantize the contents of a plain KVCache (after prefill)."""
+        obj = cls(k_bits, v_bits, group_size)
+        if cache.keys is not None and cache.offset > 0:
+            obj.update_and_fetch(cache.keys[..., :cache.offset, :], cache.values[..., :cache.offset, :])
+        return obj
+
+    def _ensure(self, B, H, n_new, dk, dv, device):
+        need = self.offset + n_new
+        cur = 0 if self.k_codes is None else self.k_codes.shape[2]
+        if need <= cur:
+            return
+        n = max(((need + self.step - 1) // self.step) * self.step, 2 * cur)
+        g = self.group_size
+        vw = dv if self.v_bits == 8 else dv // 2
+
+        def grow(old, width, dtype):
+            new = torch.zeros((B, H, n, width), dtype=dtype, device=device)
+            if old is not None and self.offset:
+                new[:, :, :self.offset] = old[:, :, :self.offset]
+            return new
+
+        self.k_codes = grow(self.k_codes, dk, torch.uint8)
+        self.k_scales = grow(self.k_scales, dk // g, torch.float16)
+        self.k_biases = grow(self.k_biases, dk // g, torch.float16)
+        self.v_codes = grow(self.v_codes, vw, torch.uint8)
+        self.v_scales = grow(self.v_scales, dv // g, torch.float16)
+        self.v_biases = grow(self.v_biases, dv // g, torch.float16)
+
+    def update_and_fetch(self, keys, values):
+        """Quantize and append; returns shape-only placeholders (attention reads the codes)."""
+        B, H, S, dk = keys.shape
+        dv = values.shape[3]
+        self._dtype = keys.dtype
+        self._ensure(B, H, S, dk, dv, keys.device)
+        p = self.offset
+        kc, ks, kb = affine_quantize(keys, self.group_size, self.k_bits)
+        vc, vs, vb = affine_quantize(values, self.group_size, self.v_bits)
+        self.k_codes[:, :, p:p + S], self.k_scales[:, :, p:p + S], self.k_biases[:, :, p:p + S] = kc, ks, kb
+        self.v_codes[:, :, p:p + S], self.v_scales[:, :, p:p + S], self.v_biases[:, :, p:p + S] = vc, vs, vb
+        self.offset = p + S
+        zk = torch.zeros((1,), dtype=keys.dtype, device=keys.device).expand(B, H, self.offset, dk)
+        zv = torch.zeros((1,), dtype=values.dtype, device=values.device).expand(B, H, self.offset, dv)
+        return zk, zv
+
+    # ---- attention --------------------------------------------------------------
+    def descriptors(self):
+        t = self.offset
+        k = dict(format="affine", codes=self.k_codes[:, :, :t], scales=self.k_scales[:, :, :t],
+                 biases=self.k_biases[:, :, :t], bits=self.k_bits, group=self.group_size)
+        v = dict(format="affine", codes=self.v_codes[:, :, :t], scales=self.v_scales[:, :, :t],
+                 biases=self.v_biases[:, :, :t], bits=self.v_bits, group=self.group_size)
+        return k, v
+
+    def dequantized(self, dtype=None):
+        dtype = dtype or self._dtype
+        t = self.offset
+        k = affine_dequantize(self.k_codes[:, :, :t], self.k_scales[:, :, :t], self.k_biases[:, :, :t],
+                              self.group_size, self.k_bits, dtype)
+        v = affine_dequantize(self.v_codes[:, :, :t], self.v_scales[:, :, :t], self.v_biases[:, :, :t],
+                              self.group_size, self.v_bits, dtype)
+        return k, v
+
+    def quantized_attention(self, queries, scale, mask=None):
+        """queries (B, n_q, L, dim) -> (B, n_q, L, dim).  L == 1 runs the quantized
+        decode kernel; longer steps attend over the dequantized tensors."""
+        if queries.shape[2] == 1:
+            k, v = self.descriptors()
+            m3 = None
+            if mask is not None and not isinstance(mask, str):
+                from .fused_attention import _mask_3d
+                if mask.dtype == torch.bool:
+                    mask = torch.where(mask, 0.0, float("-inf"))
+                m3 = _mask_3d(mask, queries.shape[0], queries.shape[1], self.offset)
+            out = flash_decode(queries[:, :, 0, :], k=k, v=v, attn_scale=scale, mask=m3, out_dtype=queries.dtype)
+            return out.unsqueeze(2)
+        from .base import _dense_sdpa
+        k, v = self.dequantized(queries.dtype)
+        return _dense_sdpa(queries, k, v, scale, mask)
+
+    # ---- cache protocol ------------------------------------------------------------
+    @property
+    def nbytes(self):
+        if self.k_codes is None:
+            return 0
+        B, H = self.k_codes.shape[:2]
+        per_row = sum(t.shape[3] * t.element_size() for t in
+                      (self.k_codes, self.k_scales, self.k_biases, self.v_codes, self.v_scales, self.v_biases))
+        return B * H * self.offset * per_row
+
+    @property
+    def state(self):
+        if self.k_codes is None:
+            return []
+        t = self.offset
+        return [x[:, :, :t] for x in (self.k_codes, self.k_scales, self.k_biases,
+                                      self.v_codes, self.v_scales, self.v_biases)]
+
+    @property
+    def meta_state(self):
+        return f"MixedQuant,{self.offset},{self.k_bits},{self.v_bits},{self.group_size}"
+
+    def make_mask(self, N, return_array: bool = False, window_size=None):
+        from .base import create_causal_mask
+        if N == 1:
+            return None
+        if return_array or (window_size is not None and N > window_size):
+            dev = self.k_codes.device if self.k_codes is not None else None
+            return create_causal_mask(N, offset=self.offset, window_size=window_size, device=dev)
+        return "causal"
+
+    def empty(self):
+        return self.k_codes is None
+
+    def is_trimmable(self):
+        return True
+
+    def trim(self, n):
+        n = min(self.offset, n)
+        self.offset -= n
+        return n
+
+    def size(self):
+        return self.offset
