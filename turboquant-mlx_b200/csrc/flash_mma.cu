@@ -786,16 +786,18 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   if (tb.n_groups > 1) {
     const int gi = split / tb.group;
     const int gsize = min(tb.group, tb.splits - gi * tb.group);
-    __threadfence();
+    // barrier, then one thread fences and bumps the counter (fence cumulativity makes the whole
+    // CTA's stores visible before the atomic, and the merged data visible after it)
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
     if (tid == 0) {
+      __threadfence();
       const int prev = atomicAdd(ctr + 1 + gi, 1);
       flag_s = prev == gsize - 1;
       if (flag_s) ctr[1 + gi] = 0;
+      __threadfence();
     }
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
     if (!flag_s) return;
-    __threadfence();
     if (!merge_staged(stage_ptr, stage_addr, merge_bar, 0, tb.status, a.part_m, a.part_l, a.part_acc, n_rows,
                       row0, a.n_rep, gi * tb.group, gsize, tid, warp, lane, m_star, l_star, acc4))
       return;
@@ -813,20 +815,20 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
     n_final = tb.n_groups;
     TQ_STAMP(22);   // level-1 merge done
   }
-  __threadfence();
-  TQ_STAMP(19);   // release fence done
   asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
   const int n_arrivals = tb.n_groups > 1 ? tb.n_groups : tb.splits;
   if (tid == 0) {
+    __threadfence();
+    TQ_STAMP(19);   // release fence done
     const int prev = atomicAdd(ctr, 1);
     flag_s = prev == n_arrivals - 1;
     if (flag_s) ctr[0] = 0;
+    __threadfence();
   }
   asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
   TQ_STAMP(25);   // counter bumped, result known
   if (!flag_s) return;
-  __threadfence();
-  TQ_STAMP(26);   // acquire fence done
+  TQ_STAMP(26);
   if (!merge_staged(stage_ptr, stage_addr, merge_bar, tb.n_groups > 1 ? 1 : 0, tb.status, src_m, src_l, src_acc,
                     n_rows, row0, a.n_rep, 0, n_final, tid, warp, lane, m_star, l_star, acc4))
     return;
