@@ -137,7 +137,8 @@ static void make_plan(const tq_flash_params* p, const FlashArgs& a, Plan* plan) 
   const int64_t max_splits = (a.seq_len + mult - 1) / mult;
   int64_t splits = p->num_splits;
   if (splits <= 0) {
-    const int64_t target = (plan->mma ? flash_mma_ctas_per_sm() : 2) * (int64_t)num_sms();
+    static const char* target_env = getenv("TQ_FLASH_TARGET_CTAS");           // tuning aid
+    const int64_t target = target_env ? atoi(target_env) : (plan->mma ? flash_mma_ctas_per_sm() : 2) * (int64_t)num_sms();
     splits = target / groups;                          // round down: the grid must fit one wave
     if (splits < 1) splits = 1;   // more groups than CTA slots: one CTA per group (splitting further measured slower)
     const int64_t by_len = (a.seq_len + 127) / 128;   // at least 128 positions per split

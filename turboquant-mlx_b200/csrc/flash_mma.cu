@@ -200,6 +200,29 @@ __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
 
+// Optional per-CTA cycle stamps for tuning (build with -DTQ_TIMING; the stamps land
+// 2 MiB into the workspace, which must be at least 3 MiB).  Off in normal builds.
+#ifdef TQ_TIMING
+__device__ __forceinline__ long long tq_now(int slot) {
+  if (slot >= 28) {   // slots 28..31: nanoseconds on the GPU-wide timer, comparable across launches
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return (long long)t;
+  }
+  return clock64();
+}
+// one block of stamps per output address (4 consecutive launches writing 7168-byte outputs stay apart)
+#define TQ_STAMP(slot)                                                                   \
+  do {                                                                                   \
+    if (lane == 0 && (warp == 0 || warp == kConsumerWarps))                              \
+      reinterpret_cast<long long*>(reinterpret_cast<char*>(tb.status) + (2 << 20))       \
+          [(((reinterpret_cast<uintptr_t>(tb.out) / 7168) & 3) * 148 * 2 +               \
+            (blockIdx.x + gridDim.x * blockIdx.y) * 2 + (warp == 0 ? 0 : 1)) * 32 + (slot)] = tq_now(slot); \
+  } while (0)
+#else
+#define TQ_STAMP(slot) do { } while (0)
+#endif
+
 // Merge `count` (<= kMaxParts) partial states of the n_rep rows of one (batch, kv
 // head) group.  Every dependent trip to global memory costs about a microsecond
 // here, so all partials are pulled into shared memory (the ring is free by now)
@@ -207,7 +230,7 @@ __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
 // from shared memory: warp r owns row r, lane owns elements 4*lane .. 4*lane+3,
 // which is also the layout the final butterfly wants.
 // Shared layout at `stage`: acc [count][n_rep][128], then m [count][8], l [count][8], w [8][64].
-__device__ __forceinline__ bool merge_staged(uint8_t* smem_stage, uint32_t stage_addr, uint32_t bar,
+__device__ __forceinline__ bool merge_staged(const MmaTables& tb, uint8_t* smem_stage, uint32_t stage_addr, uint32_t bar,
                                              uint32_t parity, int* status,
                                              const float* pm, const float* pl, const float* pacc,
                                              int64_t n_rows, int64_t row0, int n_rep, int first,
@@ -235,6 +258,7 @@ __device__ __forceinline__ bool merge_staged(uint8_t* smem_stage, uint32_t stage
   asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
   const bool arrived = mbar_wait(bar, parity);
   asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+  TQ_STAMP(16);   // partial states staged
   if (!arrived) {          // bounded wait gave up: report through the status word, produce nothing
     if (tid == 0) atomicExch(status, 3);
     m_star = -INFINITY;
@@ -273,29 +297,6 @@ __device__ __forceinline__ bool merge_staged(uint8_t* smem_stage, uint32_t stage
   }
   return true;
 }
-
-// Optional per-CTA cycle stamps for tuning (build with -DTQ_TIMING; the stamps land
-// 2 MiB into the workspace, which must be at least 3 MiB).  Off in normal builds.
-#ifdef TQ_TIMING
-__device__ __forceinline__ long long tq_now(int slot) {
-  if (slot >= 28) {   // slots 28..31: nanoseconds on the GPU-wide timer, comparable across launches
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return (long long)t;
-  }
-  return clock64();
-}
-// one block of stamps per output address (4 consecutive launches writing 7168-byte outputs stay apart)
-#define TQ_STAMP(slot)                                                                   \
-  do {                                                                                   \
-    if (lane == 0 && (warp == 0 || warp == kConsumerWarps))                              \
-      reinterpret_cast<long long*>(reinterpret_cast<char*>(tb.status) + (2 << 20))       \
-          [(((reinterpret_cast<uintptr_t>(tb.out) / 7168) & 3) * 148 * 2 +               \
-            (blockIdx.x + gridDim.x * blockIdx.y) * 2 + (warp == 0 ? 0 : 1)) * 32 + (slot)] = tq_now(slot); \
-  } while (0)
-#else
-#define TQ_STAMP(slot) do { } while (0)
-#endif
 
 // ---- the kernel ---------------------------------------------------------------------
 template <int KF, int VB>
@@ -356,10 +357,46 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   }
   // Everything below reads the query and later writes the shared workspace: both
   // may belong to the preceding kernel until it has completed.
-  if (warp < kConsumerWarps) asm volatile("griddepcontrol.wait;" ::: "memory");
-  TQ_STAMP(29);
-  // query rows -> shared f16: row r = high part of head r, row 8 + r = residual
   if (warp < kConsumerWarps) {
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");   // consumers only: tables ready
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  }
+  TQ_STAMP(29);
+  TQ_STAMP(18);
+  // The query is staged in MMA fragment order when no rotation is needed and its
+  // element pairs are naturally aligned; otherwise row by row (rotated in the warp).
+  const int q_esize = a.q_dtype == TQ_F32 ? 4 : 2;
+  const bool q_direct = ((KF != KF_POLAR3 && KF != KF_POLAR4) || a.q_prerotated) &&
+                        reinterpret_cast<uintptr_t>(a.q) % (2 * q_esize) == 0 &&
+                        a.q_batch_stride % 2 == 0 && a.q_head_stride % 2 == 0;
+  if (warp < kConsumerWarps && q_direct) {
+    // staged in fragment order [k-step][lane][4 registers]: every element pair is fetched once per
+    // CTA, split into f16 high part + residual, and read back with one conflict-free 16-byte load
+    uint32_t* qf = reinterpret_cast<uint32_t*>(smem + L::q);
+#pragma unroll
+    for (int task = tid; task < 512; task += kConsumerThreads) {
+      const int ln = task & 31, up = (task >> 5) & 1, ks = task >> 6;
+      const int gg = ln >> 2, tt = ln & 3;
+      float2 v = make_float2(0.f, 0.f);
+      if (gg < a.n_rep) {
+        const int64_t off = b * a.q_batch_stride + (int64_t)(h0 + gg) * a.q_head_stride +
+                            kslot_element<KF>(ks, 2 * tt + 8 * up);
+        if (a.q_dtype == TQ_F32) v = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(a.q) + off);
+        else if (a.q_dtype == TQ_F16)
+          v = __half22float2(*reinterpret_cast<const __half2*>(reinterpret_cast<const __half*>(a.q) + off));
+        else
+          v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const __nv_bfloat16*>(a.q) + off));
+      }
+      const __half2 hi = __floats2half2_rn(v.x, v.y);
+      const float2 hf = __half22float2(hi);
+      const __half2 lo = __floats2half2_rn(v.x - hf.x, v.y - hf.y);
+      qf[(ks * 32 + ln) * 4 + 2 * up] = *reinterpret_cast<const uint32_t*>(&hi);
+      qf[(ks * 32 + ln) * 4 + 2 * up + 1] = *reinterpret_cast<const uint32_t*>(&lo);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");   // consumers only: query fragments ready
+  }
+  // query rows -> shared f16: row r = high part of head r, row 8 + r = residual
+  if (warp < kConsumerWarps && !q_direct) {
     __half* qs = reinterpret_cast<__half*>(smem + L::q);
     for (int r = warp; r < 8; r += kConsumerWarps) {
       float v[4];
@@ -394,8 +431,9 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         if ((lane & 15) == 0) qsum_s[r * 2 + (lane >> 4)] = qsum;
       }
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");   // consumers only: tables and query rows ready
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");   // consumers only: query rows ready
   }
+  TQ_STAMP(17);
 
   const uint8_t* kbase;
   if (KF == KF_DENSE)
@@ -487,7 +525,29 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   // =============================== consumers ===============================
   // query fragments in the k-slot order of this key format
   uint32_t aq[8][4];
-  {
+  float qsum0 = 0.f, qsum1 = 0.f;   // affine keys: sums of head g's query over elements 0-63 / 64-127
+  if (q_direct) {
+    const uint4* qf = reinterpret_cast<const uint4*>(smem + L::q);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const uint4 f = qf[ks * 32 + lane];
+      aq[ks][0] = f.x; aq[ks][1] = f.y; aq[ks][2] = f.z; aq[ks][3] = f.w;
+      if (KF == KF_AFFINE8) {
+        const float2 a0 = __half22float2(*reinterpret_cast<const __half2*>(&f.x));
+        const float2 a1 = __half22float2(*reinterpret_cast<const __half2*>(&f.y));
+        const float2 a2 = __half22float2(*reinterpret_cast<const __half2*>(&f.z));
+        const float2 a3 = __half22float2(*reinterpret_cast<const __half2*>(&f.w));
+        const float sum = ((a0.x + a1.x) + (a0.y + a1.y)) + ((a2.x + a3.x) + (a2.y + a3.y));
+        if (ks < 4) qsum0 += sum; else qsum1 += sum;
+      }
+    }
+    if (KF == KF_AFFINE8) {
+      qsum0 += __shfl_xor_sync(0xffffffffu, qsum0, 1);
+      qsum0 += __shfl_xor_sync(0xffffffffu, qsum0, 2);
+      qsum1 += __shfl_xor_sync(0xffffffffu, qsum1, 1);
+      qsum1 += __shfl_xor_sync(0xffffffffu, qsum1, 2);
+    }
+  } else {
     const __half* qs = reinterpret_cast<const __half*>(smem + L::q);
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
@@ -497,6 +557,10 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       aq[ks][1] = *reinterpret_cast<const uint32_t*>(qs + (g + 8) * kDim + e_lo);
       aq[ks][2] = *reinterpret_cast<const uint32_t*>(qs + g * kDim + e_hi);
       aq[ks][3] = *reinterpret_cast<const uint32_t*>(qs + (g + 8) * kDim + e_hi);
+    }
+    if (KF == KF_AFFINE8) {
+      qsum0 = qsum_s[2 * g];
+      qsum1 = qsum_s[2 * g + 1];
     }
   }
   // V side: this thread's 16 elements are 16g .. 16g+15 (8 pairs)
@@ -556,7 +620,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
           mma16816(sc[ng], aq[w], __byte_perm(w0[w], 0x64646464u, 0x4140), __byte_perm(w0[w], 0x64646464u, 0x4342));
           mma16816(g1, aq[4 + w], __byte_perm(w1[w], 0x64646464u, 0x4140), __byte_perm(w1[w], 0x64646464u, 0x4342));
         }
-        const float q0 = qsum_s[2 * g], q1 = qsum_s[2 * g + 1];
+        const float q0 = qsum0, q1 = qsum1;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           const int pos = pw + 8 * ng + 2 * t + c;
@@ -798,7 +862,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
     }
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
     if (!flag_s) return;
-    if (!merge_staged(stage_ptr, stage_addr, merge_bar, 0, tb.status, a.part_m, a.part_l, a.part_acc, n_rows,
+    if (!merge_staged(tb, stage_ptr, stage_addr, merge_bar, 0, tb.status, a.part_m, a.part_l, a.part_acc, n_rows,
                       row0, a.n_rep, gi * tb.group, gsize, tid, warp, lane, m_star, l_star, acc4))
       return;
     if (warp < a.n_rep) {
@@ -829,7 +893,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   TQ_STAMP(25);   // counter bumped, result known
   if (!flag_s) return;
   TQ_STAMP(26);
-  if (!merge_staged(stage_ptr, stage_addr, merge_bar, tb.n_groups > 1 ? 1 : 0, tb.status, src_m, src_l, src_acc,
+  if (!merge_staged(tb, stage_ptr, stage_addr, merge_bar, tb.n_groups > 1 ? 1 : 0, tb.status, src_m, src_l, src_acc,
                     n_rows, row0, a.n_rep, 0, n_final, tid, warp, lane, m_star, l_star, acc4))
     return;
   TQ_STAMP(27);   // staged merge done
