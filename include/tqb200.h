@@ -246,6 +246,24 @@ int tq_affine_dequantize(const uint8_t* codes, const void* scales_f16, const voi
                          int64_t n_rows, int dim, int group, int bits, void* out, int out_dtype,
                          void* stream);
 
+/* Prefill attention over dense 16-bit tensors: out = softmax(scale * Q K^T [+ causal mask]) V
+ * for Q (batch, n_q_heads, seq_q, 128), K / V (batch, n_kv_heads, seq_k, 128), all
+ * of one dtype (TQ_F16 or TQ_BF16), strides in elements (multiples of 8), 16-byte
+ * aligned bases.  With causal != 0 query row i sees keys 0 .. i + (seq_k - seq_q)
+ * (seq_k >= seq_q).  Replaces the array-library SDPA the reference falls through to
+ * for every call that is not a single-token decode (turboquant_mlx/patch.py:37) on
+ * the keys / values returned by update_and_fetch (cache.py:100-150,
+ * v_only_cache.py:46-60).  Runs on the tcgen05 tensor cores (accumulators in tensor
+ * memory, operands by TMA).  `status` is one zero-initialised device int: a kernel
+ * whose bounded wait gives up writes a non-zero code there and returns. */
+int tq_prefill_sdpa(const void* q, const void* k, const void* v, void* out, int dtype, int batch,
+                    int n_q_heads, int n_kv_heads, int64_t seq_q, int64_t seq_k, int dim,
+                    int64_t q_batch_stride, int64_t q_head_stride, int64_t q_row_stride,
+                    int64_t k_batch_stride, int64_t k_head_stride, int64_t k_row_stride,
+                    int64_t v_batch_stride, int64_t v_head_stride, int64_t v_row_stride,
+                    int64_t o_batch_stride, int64_t o_head_stride, int64_t o_row_stride,
+                    float attn_scale, int causal, int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -331,6 +331,33 @@ def softmax(x, axis=-1):
     return (e / e.sum(axis=axis, keepdims=True)).astype(F32)
 
 
+def prefill_sdpa(q, k, v, scale, causal=True):
+    """Dense attention of a multi-token step: the call the reference leaves to its
+    array library (patch.py:37, `mx.fast.scaled_dot_product_attention(queries, keys,
+    values, scale=scale, mask=mask)`), restated from the published definition
+    softmax(scale * Q K^T + mask) V.  q (B, n_q, L, D), k / v (B, n_kv, S, D); query
+    head h reads kv head h // (n_q // n_kv); with `causal` query row i sees keys
+    0 .. i + (S - L), which is what create_causal_mask(L, offset=S - L) masks
+    (cache.py:328).  float64 accumulation, float32 result."""
+    q = np.asarray(q, dtype=np.float64)
+    k = np.asarray(k, dtype=np.float64)
+    v = np.asarray(v, dtype=np.float64)
+    B, n_q, L, D = q.shape
+    n_kv, S = k.shape[1], k.shape[2]
+    rep = n_q // n_kv
+    out = np.empty((B, n_q, L, D), dtype=F32)
+    allowed = None
+    if causal:
+        allowed = np.arange(S)[None, :] <= (np.arange(L)[:, None] + (S - L))
+    for b in range(B):
+        for h in range(n_q):
+            s = (q[b, h] @ k[b, h // rep].T) * scale
+            if allowed is not None:
+                s = np.where(allowed, s, -np.inf)
+            out[b, h] = softmax(s, axis=-1).astype(np.float64) @ v[b, h // rep]
+    return out
+
+
 def flash_attention_turboquant(q_rot, k_packed, k_norms, v_packed, v_norms,
                                k_centroids, v_centroids, v_signs, dim, bits,
                                attn_scale, block_size=16, n_rep=1, v_bits=None):

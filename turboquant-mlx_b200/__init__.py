@@ -22,6 +22,7 @@ from .kernels import (
     merge_partials,
     FlashDecodePlan,
     MergePlan,
+    prefill_attention,
 )
 from .fused_attention import turboquant_attention
 from .packing import pack_indices, unpack_indices, packed_dim
@@ -34,4 +35,4 @@ from .rotation import (
 from .base import KVCache, scaled_dot_product_attention
 from .mixed_cache import MixedQuantKVCache
 
-__version__ = "0.3.0"
+__version__ = "0.4.0"

@@ -90,6 +90,8 @@ _SIGNATURES = {
                                    c_void_p, c_void_p, c_void_p]),
     "tq_affine_dequantize": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,
                                      c_void_p, c_int, c_void_p]),
+    "tq_prefill_sdpa": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                c_int64, c_int64, c_int] + [c_int64] * 12 + [c_float, c_int, c_void_p, c_void_p]),
 }
 
 

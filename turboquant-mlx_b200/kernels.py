@@ -24,6 +24,7 @@ __all__ = [
     "prerotate_query", "prerot_fused_qk_scores", "prerot_packed_dequantize",
     "sparse_v_matvec", "count_active_positions", "flash_attention_turboquant",
     "flash_decode", "merge_partials", "FlashDecodePlan", "MergePlan",
+    "prefill_attention", "prefill_supported", "prefill_status",
 ]
 
 
@@ -459,3 +460,75 @@ class MergePlan:
         if rc:
             _lib.check(rc)
         return self.result
+
+
+# ---------------------------------------------------------------------------
+# prefill attention (dense 16-bit Q, K, V on the tcgen05 tensor cores)
+# ---------------------------------------------------------------------------
+def prefill_supported(queries, keys, values, mask) -> bool:
+    """True when tq_prefill_sdpa covers the call: CUDA f16 / bf16 tensors of one
+    dtype, head_dim 128, no mask or the "causal" mask, rows of 128 contiguous
+    elements and strides that are multiples of 8 elements."""
+    if not (queries.is_cuda and keys.is_cuda and values.is_cuda):
+        return False
+    if queries.dtype not in (torch.float16, torch.bfloat16):
+        return False
+    if keys.dtype != queries.dtype or values.dtype != queries.dtype:
+        return False
+    if queries.ndim != 4 or keys.ndim != 4 or values.ndim != 4:
+        return False
+    if queries.shape[-1] != 128 or keys.shape[-1] != 128 or values.shape[-1] != 128:
+        return False
+    if not (mask is None or (isinstance(mask, str) and mask == "causal")):
+        return False
+    if mask is not None and keys.shape[2] < queries.shape[2]:
+        return False
+    if keys.shape[2] != values.shape[2] or queries.shape[1] % keys.shape[1]:
+        return False
+    for t in (queries, keys, values):
+        if t.stride(-1) != 1 or any(st % 8 for st in t.stride()[:-1]) or t.data_ptr() % 16:
+            return False
+    return True
+
+
+def prefill_attention(queries: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, scale: float,
+                      causal: bool = True, out: torch.Tensor | None = None) -> torch.Tensor:
+    """softmax(scale * Q K^T [+ causal]) V for (B, n_q, L, 128) queries and
+    (B, n_kv, S, 128) keys / values of one 16-bit dtype (GQA without replication).
+    The call the reference leaves to its array library for every step that is not
+    a single-token decode (turboquant_mlx/patch.py:37)."""
+    _lib.require_cuda(queries, keys, values)
+    if queries.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("prefill_attention takes float16 or bfloat16 tensors")
+    if keys.dtype != queries.dtype or values.dtype != queries.dtype:
+        raise ValueError("queries, keys and values must share one dtype")
+    B, n_q, L, D = queries.shape
+    Bk, n_kv, S, Dk = keys.shape
+    if D != 128 or Dk != 128 or values.shape[-1] != 128:
+        raise ValueError(f"prefill_attention supports head_dim 128, got {D}")
+    if n_q % n_kv:
+        raise ValueError(f"n_q_heads ({n_q}) must equal n_kv_heads ({n_kv}) * n_rep ({n_q // max(n_kv, 1)})")
+    if values.shape[:3] != keys.shape[:3] or Bk != B:
+        raise ValueError("keys and values must have the same (batch, heads, length)")
+
+    def usable(t):
+        ok = t.stride(-1) == 1 and not any(st % 8 for st in t.stride()[:-1]) and t.data_ptr() % 16 == 0
+        return t if ok else t.contiguous()
+
+    q, k, v = usable(queries), usable(keys), usable(values)
+    if out is None:
+        out = torch.empty((B, n_q, L, D), dtype=q.dtype, device=q.device)
+    status = _lib.workspace(16, q.device, tag="prefill")
+    _lib.check(_lib.lib().tq_prefill_sdpa(
+        _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.dtype_code(q.dtype), B, n_q, n_kv, L, S, D,
+        q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+        v.stride(0), v.stride(1), v.stride(2), out.stride(0), out.stride(1), out.stride(2),
+        float(scale), 1 if causal else 0, _lib.ptr(status), _lib.stream_ptr(q.device)))
+    return out
+
+
+def prefill_status(device) -> int:
+    """Status word of the prefill kernel on this device and stream (synchronises):
+    0 unless a bounded wait inside the kernel gave up."""
+    status = _lib.workspace(16, device, tag="prefill")
+    return int(status[:4].view(torch.int32).item())

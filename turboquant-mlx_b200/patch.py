@@ -14,6 +14,15 @@ _patched = False
 _replaced: list = []   # (module, attribute) pairs that now point at _patched_sdpa
 
 
+def _prefill_sdpa(queries, keys, values, scale, mask):
+    """Multi-token attention over dense keys / values: the tensor-core prefill
+    kernel when it covers the call, the library attention otherwise."""
+    from .kernels import prefill_attention, prefill_supported
+    if queries.shape[2] > 1 and prefill_supported(queries, keys, values, mask):
+        return prefill_attention(queries, keys, values, scale, causal=mask is not None)
+    return _base._dense_sdpa(queries, keys, values, scale, mask)
+
+
 def _patched_sdpa(queries, keys, values, cache, scale, mask, sinks=None):
     """Fused TurboQuant decode, affine-quantized decode, or the original attention."""
     from .cache import TurboQuantKVCache
@@ -28,15 +37,17 @@ def _patched_sdpa(queries, keys, values, cache, scale, mask, sinks=None):
         # multi-token step on a fused cache: the placeholders returned by
         # update_and_fetch hold no data, so attend over the dequantized storage
         k, v = cache.dequantized(queries.dtype)
-        return _base._dense_sdpa(queries, k, v, scale, mask)
+        return _prefill_sdpa(queries, k, v, scale, mask)
     if isinstance(cache, VOnlyTurboQuantCache) and cache.fused and cache.offset > 0:
         if is_decode:
             from .v_only_cache import v_only_attention
             return v_only_attention(queries, cache, scale, mask)
         _, v = cache._v_tq.dequantized(queries.dtype)
-        return _base._dense_sdpa(queries, keys, v, scale, mask)
+        return _prefill_sdpa(queries, keys, v, scale, mask)
     if hasattr(cache, "bits") and getattr(cache, "bits", None) is not None and hasattr(cache, "quantized_attention"):
         return cache.quantized_attention(queries, scale, mask)
+    if not is_decode and sinks is None and _original_sdpa in (None, _base._dense_sdpa_entry):
+        return _prefill_sdpa(queries, keys, values, scale, mask)       # dense cache, prompt step
     return (_original_sdpa or _base._dense_sdpa_entry)(queries, keys, values, cache, scale, mask, sinks=sinks)
 
 
