@@ -444,6 +444,56 @@ def workload_c3(args):
                                  "bytes_per_layer_step": nbytes}}))
 
 
+def workload_c4_prefill(args):
+    """Config 4's prompt step, attention only: Qwen2.5-7B attention shape (28 q / 4 kv heads, d 128),
+    one 32768-token causal prefill of one layer through tq_prefill_sdpa (tcgen05 tiles); FLOPs counted
+    as 4 * S^2 * d * n_q / 2.  The library attention of the installed torch is timed beside it."""
+    import torch
+    import torch.nn.functional as F
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    tq = entry.load_package()
+    nq, nkv, S = 28, 4, args.ctx or 32768
+    gen = torch.Generator(device=dev).manual_seed(13)
+    dtype = torch.bfloat16
+    q = torch.randn((1, nq, S, DIM), generator=gen, device=dev).to(dtype)
+    k = torch.randn((1, nkv, S, DIM), generator=gen, device=dev).to(dtype)
+    v = torch.randn((1, nkv, S, DIM), generator=gen, device=dev).to(dtype)
+    out = torch.empty_like(q)
+    scale = 1.0 / math.sqrt(DIM)
+
+    def timed(fn, iters, warmup=3):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    with ClockSampler(0) as clk:
+        ms = timed(lambda: tq.prefill_attention(q, k, v, scale, causal=True, out=out), args.steps)
+    status = tq.kernels.prefill_status(dev)
+    ms_lib = timed(lambda: F.scaled_dot_product_attention(q, k, v, is_causal=True, scale=scale, enable_gqa=True),
+                   max(2, args.steps // 2))
+    flops = 4.0 * S * S * DIM * nq / 2
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(
+        os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+    peak = peaks.get("bf16_tflops_sustained", 1400.0) if ms * args.steps > 1000 else peaks.get("bf16_tflops", 1590.0)
+    print(json.dumps({"metric": "prefill-attn TFLOP/s", "unit": "TFLOP/s", "n_gpus": 1, "value": flops / ms / 1e9,
+                      "ms_per_layer": ms, "kernel_status": status, "dtype": "bf16",
+                      "roofline": {"bound": "tensor", "achieved": flops / ms / 1e9, "peak": peak, "unit": "TFLOP/s",
+                                   "frac": flops / ms / 1e9 / peak, "traffic": None,
+                                   "peak_kind": "measured" if peaks else "fallback"},
+                      "library_sdpa": {"ms_per_layer": ms_lib, "tflops": flops / ms_lib / 1e9},
+                      "clocks": clk.summary(),
+                      "config": {"workload": f"C4 prompt step, attention of one layer: 28q/4kv, d 128, S={S} causal, bf16",
+                                 "flops_per_layer": flops}}))
+
+
 def workload_c5(args):
     """Config 5: long-context decode, Llama-3-70B attention shape (64 q / 8 kv heads, d 128), K 8-bit
     group-affine + V PolarQuant 3-bit, the sequence split across the ranks: 131072 positions per GPU
@@ -558,7 +608,8 @@ def main():
                     help="layers (independent KV buffers) per step; fewer for a profiler capture")
     ap.add_argument("--kernel-only", action="store_true",
                     help="plain launches of the flash-decode kernel only (no graph, no e2e): profiler case")
-    ap.add_argument("--workload", default="c2", choices=["c2", "c1", "c3", "c5"],
+    ap.add_argument("--ctx", type=int, default=0, help="c4p: prompt length (default 32768)")
+    ap.add_argument("--workload", default="c2", choices=["c2", "c1", "c3", "c5", "c4p"],
                     help="c2 = the headline benchmark; c1 / c3 = secondary measurements of other configurations")
     args = ap.parse_args()
     if args.workload == "c1":
@@ -567,6 +618,8 @@ def main():
         return workload_c3(args)
     if args.workload == "c5":
         return workload_c5(args)
+    if args.workload == "c4p":
+        return workload_c4_prefill(args)
     N_LAYERS = args.layers
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":

@@ -29,22 +29,27 @@ namespace {
 constexpr int kD = 128;          // head_dim
 constexpr int kBM = 128;         // queries per CTA
 constexpr int kBN = 128;         // keys per tile
-constexpr int kStages = 2;
-constexpr int kSoftmaxThreads = 128;
+constexpr int kKStages = 3;      // K tiles run two ahead of the scores that need them
+constexpr int kVStages = 2;
+constexpr int kSoftmaxThreads = 256;             // two threads per query row: 64 score columns each
 constexpr int kThreads = kSoftmaxThreads + 64;   // + TMA warp + MMA warp
+constexpr int kProducerWarp = kSoftmaxThreads / 32, kMmaWarp = kProducerWarp + 1;
 constexpr uint32_t kTileBytes = kBM * kD * 2;    // 32 KiB: one 128 x 128 16-bit tile
 constexpr uint32_t kHalfBytes = kTileBytes / 2;  // one 128-row x 64-element swizzle block
 constexpr uint32_t kSpin = 1u << 20;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescale = 8.0f;                 // log2 units: P stays <= 2^8
-constexpr uint32_t kTmemCols = 256;              // S: columns 0-127, O: columns 128-255
+// Tensor memory (512 columns x 128 lanes): two score buffers, the output accumulator and two
+// P buffers (16-bit pairs, 64 columns for 128 keys).
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColS = 0, kColO = 256, kColP = 384;
 
 struct Smem {                    // offsets from the 1024-byte aligned base
   static constexpr uint32_t q = 0;
-  static constexpr uint32_t p = q + kTileBytes;
-  static constexpr uint32_t k0 = p + kTileBytes;                 // stage s: k0 + s * 2 * kTileBytes
-  static constexpr uint32_t v0 = k0 + kTileBytes;
-  static constexpr uint32_t bars = k0 + kStages * 2 * kTileBytes;
+  static constexpr uint32_t k0 = q + kTileBytes;                   // K stage s: k0 + s * kTileBytes
+  static constexpr uint32_t v0 = k0 + kKStages * kTileBytes;       // V stage s: v0 + s * kTileBytes
+  static constexpr uint32_t xch = v0 + kVStages * kTileBytes;      // row maxima / sums: [2 buffers][2 halves][128]
+  static constexpr uint32_t bars = xch + 2 * 2 * kBM * 4;
   static constexpr uint32_t tmem_slot = bars + 16 * 8;
   static constexpr uint32_t total = tmem_slot + 16;
 };
@@ -107,6 +112,16 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// A operand from tensor memory (row i in lane i, 16-bit elements packed two per column)
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -148,7 +163,8 @@ __device__ __forceinline__ uint32_t pack16(float a, float b, bool bf16) {
 }
 
 // Barrier slots (8 bytes each) inside Smem::bars.
-enum : int { B_Q = 0, B_KV_FULL = 1, B_KV_EMPTY = 3, B_S_FULL = 5, B_P_FULL = 6, B_PV_DONE = 7 };
+enum : int { B_Q = 0, B_K_FULL = 1, B_K_EMPTY = 4, B_V_FULL = 7, B_V_EMPTY = 9, B_S_FULL = 11, B_P_FULL = 13,
+             B_PV_DONE = 14 };
 
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -170,16 +186,21 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 
   if (tid == 0) {
     mbar_init(bar(B_Q), 1);
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(bar(B_KV_FULL + s), 1);
-      mbar_init(bar(B_KV_EMPTY + s), 1);
+    for (int s = 0; s < kKStages; ++s) {
+      mbar_init(bar(B_K_FULL + s), 1);
+      mbar_init(bar(B_K_EMPTY + s), 1);
+    }
+    for (int s = 0; s < kVStages; ++s) {
+      mbar_init(bar(B_V_FULL + s), 1);
+      mbar_init(bar(B_V_EMPTY + s), 1);
     }
     mbar_init(bar(B_S_FULL), 1);
+    mbar_init(bar(B_S_FULL + 1), 1);
     mbar_init(bar(B_P_FULL), kSoftmaxThreads);
     mbar_init(bar(B_PV_DONE), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 5) {   // this warp owns the tensor-memory allocation
+  if (warp == kMmaWarp) {   // this warp owns the tensor-memory allocation
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + Smem::tmem_slot),
                  "r"(kTmemCols)
                  : "memory");
@@ -189,34 +210,51 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(smem + Smem::tmem_slot);
-  const uint32_t tmem_s = tmem, tmem_o = tmem + kBN;
+  const uint32_t tmem_o = tmem + kColO;
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       mbar_expect_tx(bar(B_Q), kTileBytes);
       tma_load_4d(sbase + Smem::q, &map_q, 0, q0, head, batch, bar(B_Q));
       tma_load_4d(sbase + Smem::q + kHalfBytes, &map_q, 64, q0, head, batch, bar(B_Q));
+      auto load_k = [&](int j) {
+        const int s = j % kKStages;
+        if (j >= kKStages && !wait(bar(B_K_EMPTY + s), ((j / kKStages) - 1) & 1)) return false;
+        const uint32_t dst = sbase + Smem::k0 + s * kTileBytes;
+        mbar_expect_tx(bar(B_K_FULL + s), kTileBytes);
+        tma_load_4d(dst, &map_k, 0, j * kBN, kv_head, batch, bar(B_K_FULL + s));
+        tma_load_4d(dst + kHalfBytes, &map_k, 64, j * kBN, kv_head, batch, bar(B_K_FULL + s));
+        return true;
+      };
+      auto load_v = [&](int j) {
+        const int s = j % kVStages;
+        if (j >= kVStages && !wait(bar(B_V_EMPTY + s), ((j / kVStages) - 1) & 1)) return false;
+        const uint32_t dst = sbase + Smem::v0 + s * kTileBytes;
+        mbar_expect_tx(bar(B_V_FULL + s), kTileBytes);
+        tma_load_4d(dst, &map_v, 0, j * kBN, kv_head, batch, bar(B_V_FULL + s));
+        tma_load_4d(dst + kHalfBytes, &map_v, 64, j * kBN, kv_head, batch, bar(B_V_FULL + s));
+        return true;
+      };
+      // K runs ahead of V: the scores of tile j + 1 are computed while tile j is in the softmax
+      int jk = 0, jv = 0;
       bool ok = true;
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j % kStages;
-        if (j >= kStages && !wait(bar(B_KV_EMPTY + s), ((j / kStages) - 1) & 1)) {
-          atomicExch(a.status, 11);
-          ok = false;
-          break;
+      while (ok && (jk < n_tiles || jv < n_tiles)) {
+        if (jk < n_tiles && jk <= jv + 1) {
+          ok = load_k(jk);
+          if (ok) ++jk;
+        } else {
+          ok = load_v(jv);
+          if (ok) ++jv;
         }
-        const uint32_t kdst = sbase + Smem::k0 + s * 2 * kTileBytes, vdst = sbase + Smem::v0 + s * 2 * kTileBytes;
-        mbar_expect_tx(bar(B_KV_FULL + s), 2 * kTileBytes);
-        tma_load_4d(kdst, &map_k, 0, j * kBN, kv_head, batch, bar(B_KV_FULL + s));
-        tma_load_4d(kdst + kHalfBytes, &map_k, 64, j * kBN, kv_head, batch, bar(B_KV_FULL + s));
-        tma_load_4d(vdst, &map_v, 0, j * kBN, kv_head, batch, bar(B_KV_FULL + s));
-        tma_load_4d(vdst + kHalfBytes, &map_v, 64, j * kBN, kv_head, batch, bar(B_KV_FULL + s));
       }
+      if (!ok) atomicExch(a.status, 11);
       // drain: every copy this thread issued has landed before the CTA may exit
       mbar_wait(bar(B_Q), 0, nullptr);
-      for (int j = max(0, n_tiles - kStages); j < n_tiles; ++j) mbar_wait(bar(B_KV_FULL + j % kStages), (j / kStages) & 1, nullptr);
+      for (int j = max(0, jk - kKStages); j < jk; ++j) mbar_wait(bar(B_K_FULL + j % kKStages), (j / kKStages) & 1, nullptr);
+      for (int j = max(0, jv - kVStages); j < jv; ++j) mbar_wait(bar(B_V_FULL + j % kVStages), (j / kVStages) & 1, nullptr);
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
       const uint32_t fmt = a.bf16 ? 1u : 0u;
@@ -225,69 +263,105 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                                 ((uint32_t)(kBM >> 4) << 24);
       const uint32_t idesc_pv = idesc_qk | (1u << 16);
       bool ok = wait(bar(B_Q), 0);
-      if (!ok) atomicExch(a.status, 12);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j % kStages;
-        if (!wait(bar(B_KV_FULL + s), (j / kStages) & 1)) {
-          atomicExch(a.status, 13);
-          ok = false;
-          break;
-        }
+      int fail = ok ? 0 : 12;
+      auto issue_qk = [&](int j) {     // S[j & 1] = Q K_j^T
+        const int s = j % kKStages;
+        if (!wait(bar(B_K_FULL + s), (j / kKStages) & 1)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t kbase = sbase + Smem::k0 + s * 2 * kTileBytes, vbase = sbase + Smem::v0 + s * 2 * kTileBytes;
+        const uint32_t kbase = sbase + Smem::k0 + s * kTileBytes;
 #pragma unroll
         for (int kk = 0; kk < kD / 16; ++kk) {
           const uint32_t o = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
-          umma_f16(tmem_s, smem_desc(sbase + Smem::q + o, 16), smem_desc(kbase + o, 16), idesc_qk, kk > 0);
+          umma_f16(tmem + kColS + (j & 1) * kBN, smem_desc(sbase + Smem::q + o, 16), smem_desc(kbase + o, 16), idesc_qk,
+                   kk > 0);
         }
-        umma_commit(bar(B_S_FULL));
-        if (!wait(bar(B_P_FULL), j & 1)) {
-          atomicExch(a.status, 14);
+        umma_commit(bar(B_K_EMPTY + s));
+        umma_commit(bar(B_S_FULL + (j & 1)));
+        return true;
+      };
+      if (ok && !issue_qk(0)) {
+        ok = false;
+        fail = 13;
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        // the scores of the next tile are produced while this one is in the softmax: S[(j + 1) & 1] was
+        // last read for tile j - 1, whose P_FULL has been seen
+        if (j + 1 < n_tiles && !issue_qk(j + 1)) {
           ok = false;
+          fail = 13;
+          break;
+        }
+        const int s = j % kVStages;
+        if (!wait(bar(B_V_FULL + s), (j / kVStages) & 1) || !wait(bar(B_P_FULL), j & 1)) {
+          ok = false;
+          fail = 14;
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t vbase = sbase + Smem::v0 + s * kTileBytes;
+        const uint32_t p_tmem = tmem + kColP + (j & 1) * (kBN / 2);
 #pragma unroll
-        for (int kk = 0; kk < kBN / 16; ++kk) {
-          const uint32_t o = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
-          umma_f16(tmem_o, smem_desc(sbase + Smem::p + o, 16), smem_desc(vbase + kk * 2048, kHalfBytes), idesc_pv,
-                   (j > 0 || kk > 0) ? 1u : 0u);
-        }
-        umma_commit(bar(B_KV_EMPTY + s));
+        for (int kk = 0; kk < kBN / 16; ++kk)    // 16 keys = 8 packed columns of P, 2 x 1024 bytes of V
+          umma_f16_ts(tmem_o, p_tmem + kk * 8, smem_desc(vbase + kk * 2048, kHalfBytes), idesc_pv,
+                      (j > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(bar(B_V_EMPTY + s));
         umma_commit(bar(B_PV_DONE));
       }
+      if (fail) atomicExch(a.status, fail);
     }
   } else {
-    // ------------------------------ softmax: one query row per thread ------------------------------
-    const int row = tid;                                   // = tensor-memory lane
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    const int kmax = a.causal ? q0 + row + off : a.seq_k - 1;    // last key this row may see
+    // ---------------- softmax: two threads per query row, 64 score columns each ----------------
+    const int half = warp >> 2;                            // which 64 columns
+    const int row = (warp & 3) * 32 + lane;                // = tensor-memory lane
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    float* xch = reinterpret_cast<float*>(smem + Smem::xch);    // [buffer][half][row]
+    const int kmax = a.causal ? q0 + row + off : a.seq_k - 1;   // last key this row may see
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
-      if (!__all_sync(0xffffffffu, wait(bar(B_S_FULL), j & 1))) {   // warp-uniform: aligned tcgen05 ops follow
+      const int b = j & 1;
+      if (ok && !__all_sync(0xffffffffu, wait(bar(B_S_FULL + b), (j >> 1) & 1))) {   // warp-uniform: aligned tcgen05 ops follow
         if (lane == 0) atomicExch(a.status, 15);
+        ok = false;
+      }
+      // every softmax thread takes part in the exchange barrier below, failed or not; the barrier
+      // also tells every thread whether any warp has failed, so that all leave the loop together
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int kbase = j * kBN + half * 64;
+      const bool need_mask = (j * kBN + kBN - 1 > (a.causal ? q0 + off : a.seq_k - 1)) || (j * kBN + kBN > a.seq_k);
+      const int klim = min(kmax, a.seq_k - 1) - kbase;     // own columns <= klim are visible
+      float mt = -INFINITY;
+      uint32_t sraw[2][32];
+      if (ok) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) tmem_ld32(tmem + kColS + b * kBN + lane_base + half * 64 + c * 32, sraw[c]);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float x = __uint_as_float(sraw[c][i]) * a.scale_log2;
+            if (need_mask && c * 32 + i > klim) x = -INFINITY;
+            sraw[c][i] = __float_as_uint(x);
+            mt = fmaxf(mt, x);
+          }
+      }
+      // the two halves of a row agree on its maximum through shared memory
+      xch[(b * 2 + half) * kBM + row] = mt;
+      uint32_t all_ok;
+      asm volatile(
+          "{\n\t.reg .pred p, q;\n\t"
+          "setp.ne.u32 q, %1, 0;\n\t"
+          "bar.red.and.pred p, 1, %2, q;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(all_ok)
+          : "r"((uint32_t)ok), "n"(kSoftmaxThreads)
+          : "memory");
+      mt = fmaxf(mt, xch[(b * 2 + (half ^ 1)) * kBM + row]);
+      if (!all_ok) {
         ok = false;
         break;
       }
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int kbase = j * kBN;
-      const bool need_mask = (kbase + kBN - 1 > (a.causal ? q0 + off : a.seq_k - 1)) || (kbase + kBN > a.seq_k);
-      const int klim = min(kmax, a.seq_k - 1) - kbase;     // columns <= klim are visible
-      float mt = -INFINITY;
-      uint32_t sraw[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(tmem_s + lane_base + c * 32, sraw[c]);
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-      for (int c = 0; c < 4; ++c)
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(sraw[c][i]) * a.scale_log2;
-          if (need_mask && c * 32 + i > klim) x = -INFINITY;
-          sraw[c][i] = __float_as_uint(x);
-          mt = fmaxf(mt, x);
-        }
       // lazy rescale: the reference maximum only moves when a row maximum outgrows it by 2^8
       const bool grow = mt > m_run + kRescale;
       float alpha = 1.f;
@@ -296,48 +370,40 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         m_run = mt;
         l_run *= alpha;
       }
-      if (j > 0) {
-        // P of the previous tile is consumed and O is complete up to it
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {
+        // O must be complete up to the previous tile before it is rescaled (own 64 columns)
         if (!__all_sync(0xffffffffu, wait(bar(B_PV_DONE), (j - 1) & 1))) {
           if (lane == 0) atomicExch(a.status, 16);
-          ok = false;
-          break;
+          ok = false;      // reported to the other warps at the next barrier; this warp stops producing P
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (__any_sync(0xffffffffu, grow)) {
+        if (ok) {
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2; ++c) {
             uint32_t ov[32];
-            tmem_ld32(tmem_o + lane_base + c * 32, ov);
+            tmem_ld32(tmem_o + lane_base + half * 64 + c * 32, ov);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
             for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-            tmem_st32(tmem_o + lane_base + c * 32, ov);
+            tmem_st32(tmem_o + lane_base + half * 64 + c * 32, ov);
           }
-          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
       }
+      if (!ok) continue;
       const float m_use = m_run == -INFINITY ? 0.f : m_run;
-      uint8_t* prow = smem + Smem::p + row * 128;
+      uint32_t pk[32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {           // 8 keys = one 16-byte chunk
-          float pv[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            pv[i] = ex2(__uint_as_float(sraw[c][ch * 8 + i]) - m_use);
-            l_run += pv[i];
-          }
-          uint4 w;
-          w.x = pack16(pv[0], pv[1], a.bf16);
-          w.y = pack16(pv[2], pv[3], a.bf16);
-          w.z = pack16(pv[4], pv[5], a.bf16);
-          w.w = pack16(pv[6], pv[7], a.bf16);
-          const int chunk = c * 4 + ch;            // 16 chunks per row: 8 per 64-key block
-          *reinterpret_cast<uint4*>(prow + (chunk >> 3) * kHalfBytes + (((chunk & 7) ^ (row & 7)) << 4)) = w;
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = ex2(__uint_as_float(sraw[c][2 * i]) - m_use);
+          const float p1 = ex2(__uint_as_float(sraw[c][2 * i + 1]) - m_use);
+          l_run += p0 + p1;
+          pk[c * 16 + i] = pack16(p0, p1, a.bf16);
         }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P visible to the tensor core's reads
+      // P[b] columns [32 * half, 32 * half + 32): keys 64 * half .. 64 * half + 63 of this row
+      tmem_st32(tmem + kColP + b * (kBN / 2) + lane_base + half * 32, pk);
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       mbar_arrive(bar(B_P_FULL));
     }
@@ -348,15 +414,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       }
     }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    // row sums of the two halves (second use of the exchange area: every thread is past its last tile's barrier)
+    asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
+    xch[half * kBM + row] = l_run;
+    asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
+    const float l_row = l_run + xch[(half ^ 1) * kBM + row];
     if (ok) {
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
       const bool live = q0 + row < a.seq_q;
-      uint8_t* orow = reinterpret_cast<uint8_t*>(a.out) +
+      uint8_t* orow = reinterpret_cast<uint8_t*>(a.out) + half * 128 +
                       2 * (batch * a.o_batch_stride + head * a.o_head_stride + (int64_t)(q0 + row) * a.o_row_stride);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t ov[32];
-        tmem_ld32(tmem_o + lane_base + c * 32, ov);
+        tmem_ld32(tmem_o + lane_base + half * 64 + c * 32, ov);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (live) {
 #pragma unroll
@@ -374,7 +445,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
   }
