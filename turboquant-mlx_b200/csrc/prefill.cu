@@ -164,7 +164,7 @@ __device__ __forceinline__ uint32_t pack16(float a, float b, bool bf16) {
 
 // Barrier slots (8 bytes each) inside Smem::bars.
 enum : int { B_Q = 0, B_K_FULL = 1, B_K_EMPTY = 4, B_V_FULL = 7, B_V_EMPTY = 9, B_S_FULL = 11, B_P_FULL = 13,
-             B_PV_DONE = 14 };
+             B_PV_DONE = 15 };
 
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -197,6 +197,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     mbar_init(bar(B_S_FULL), 1);
     mbar_init(bar(B_S_FULL + 1), 1);
     mbar_init(bar(B_P_FULL), kSoftmaxThreads);
+    mbar_init(bar(B_P_FULL + 1), kSoftmaxThreads);
     mbar_init(bar(B_PV_DONE), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -292,7 +293,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           break;
         }
         const int s = j % kVStages;
-        if (!wait(bar(B_V_FULL + s), (j / kVStages) & 1) || !wait(bar(B_P_FULL), j & 1)) {
+        if (!wait(bar(B_V_FULL + s), (j / kVStages) & 1) || !wait(bar(B_P_FULL + (j & 1)), (j >> 1) & 1)) {
           ok = false;
           fail = 14;
           break;
@@ -331,31 +332,37 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       const bool need_mask = (j * kBN + kBN - 1 > (a.causal ? q0 + off : a.seq_k - 1)) || (j * kBN + kBN > a.seq_k);
       const int klim = min(kmax, a.seq_k - 1) - kbase;     // own columns <= klim are visible
       float mt = -INFINITY;
-      uint32_t sraw[2][32];
+      uint32_t sraw[2][32];                                // raw scores; scaled inside the exponential's FMA
       if (ok) {
 #pragma unroll
         for (int c = 0; c < 2; ++c) tmem_ld32(tmem + kColS + b * kBN + lane_base + half * 64 + c * 32, sraw[c]);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (need_mask) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i > klim) sraw[c][i] = 0xff800000u;   // -inf
+        }
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four independent chains
 #pragma unroll
         for (int c = 0; c < 2; ++c)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float x = __uint_as_float(sraw[c][i]) * a.scale_log2;
-            if (need_mask && c * 32 + i > klim) x = -INFINITY;
-            sraw[c][i] = __float_as_uint(x);
-            mt = fmaxf(mt, x);
-          }
+          for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sraw[c][i]));
+        mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * a.scale_log2;    // scale > 0: order preserved
       }
-      // the two halves of a row agree on its maximum through shared memory
+      // the two halves of a row agree on its maximum through shared memory; only the two warps that
+      // share rows synchronise (barrier 1 + quarter), so the four pairs drift apart and their
+      // exponential and load phases overlap
       xch[(b * 2 + half) * kBM + row] = mt;
       uint32_t all_ok;
       asm volatile(
           "{\n\t.reg .pred p, q;\n\t"
           "setp.ne.u32 q, %1, 0;\n\t"
-          "bar.red.and.pred p, 1, %2, q;\n\t"
+          "bar.red.and.pred p, %2, 64, q;\n\t"
           "selp.u32 %0, 1, 0, p;\n\t}"
           : "=r"(all_ok)
-          : "r"((uint32_t)ok), "n"(kSoftmaxThreads)
+          : "r"((uint32_t)ok), "r"(1 + (warp & 3))
           : "memory");
       mt = fmaxf(mt, xch[(b * 2 + (half ^ 1)) * kBM + row]);
       if (!all_ok) {
@@ -390,22 +397,24 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
       }
       if (!ok) continue;
-      const float m_use = m_run == -INFINITY ? 0.f : m_run;
+      const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
       uint32_t pk[32];
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float p0 = ex2(__uint_as_float(sraw[c][2 * i]) - m_use);
-          const float p1 = ex2(__uint_as_float(sraw[c][2 * i + 1]) - m_use);
-          l_run += p0 + p1;
+          const float p0 = ex2(fmaf(__uint_as_float(sraw[c][2 * i]), a.scale_log2, neg_m));
+          const float p1 = ex2(fmaf(__uint_as_float(sraw[c][2 * i + 1]), a.scale_log2, neg_m));
+          ls[i & 3] += p0 + p1;
           pk[c * 16 + i] = pack16(p0, p1, a.bf16);
         }
+      l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       // P[b] columns [32 * half, 32 * half + 32): keys 64 * half .. 64 * half + 63 of this row
       tmem_st32(tmem + kColP + b * (kBN / 2) + lane_base + half * 32, pk);
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(bar(B_P_FULL));
+      mbar_arrive(bar(B_P_FULL + b));
     }
     if (ok && n_tiles > 0) {
       if (!__all_sync(0xffffffffu, wait(bar(B_PV_DONE), (n_tiles - 1) & 1))) {
@@ -415,9 +424,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     // row sums of the two halves (second use of the exchange area: every thread is past its last tile's barrier)
-    asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
+    asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");
     xch[half * kBM + row] = l_run;
-    asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
+    asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");
     const float l_row = l_run + xch[(half ^ 1) * kBM + row];
     if (ok) {
       const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
@@ -510,6 +519,7 @@ extern "C" int tq_prefill_sdpa(const void* q, const void* k, const void* v, void
   TQ_REQUIRE(n_q_heads % n_kv_heads == 0, TQ_ERR_HEAD_MISMATCH, "n_q_heads (%d) must equal n_kv_heads (%d) * n_rep",
              n_q_heads, n_kv_heads);
   TQ_REQUIRE(!causal || seq_k >= seq_q, TQ_ERR_BAD_ARG, "causal attention needs seq_k >= seq_q");
+  TQ_REQUIRE(attn_scale > 0.f, TQ_ERR_BAD_ARG, "attn_scale must be positive, got %g", (double)attn_scale);
   TQ_REQUIRE(seq_k < (1ll << 31) - 256 && seq_q < (1ll << 31) - 256 && batch <= 65535 && n_q_heads <= 65535,
              TQ_ERR_BAD_ARG, "shape out of range");
   const int64_t strides[] = {q_batch_stride, q_head_stride, q_row_stride, k_batch_stride, k_head_stride, k_row_stride,
