@@ -31,7 +31,8 @@ constexpr int kBM = 128;         // queries per CTA
 constexpr int kBN = 128;         // keys per tile
 constexpr int kKStages = 3;      // K tiles run two ahead of the scores that need them
 constexpr int kVStages = 2;
-constexpr int kSoftmaxThreads = 256;             // two threads per query row: 64 score columns each
+constexpr int kParts = 4;                        // threads per query row: 32 score columns each
+constexpr int kSoftmaxThreads = kParts * 128;
 constexpr int kThreads = kSoftmaxThreads + 64;   // + TMA warp + MMA warp
 constexpr int kProducerWarp = kSoftmaxThreads / 32, kMmaWarp = kProducerWarp + 1;
 constexpr uint32_t kTileBytes = kBM * kD * 2;    // 32 KiB: one 128 x 128 16-bit tile
@@ -48,8 +49,8 @@ struct Smem {                    // offsets from the 1024-byte aligned base
   static constexpr uint32_t q = 0;
   static constexpr uint32_t k0 = q + kTileBytes;                   // K stage s: k0 + s * kTileBytes
   static constexpr uint32_t v0 = k0 + kKStages * kTileBytes;       // V stage s: v0 + s * kTileBytes
-  static constexpr uint32_t xch = v0 + kVStages * kTileBytes;      // row maxima / sums: [2 buffers][2 halves][128]
-  static constexpr uint32_t bars = xch + 2 * 2 * kBM * 4;
+  static constexpr uint32_t xch = v0 + kVStages * kTileBytes;      // row maxima / sums: [2 buffers][kParts][128]
+  static constexpr uint32_t bars = xch + 2 * kParts * kBM * 4;
   static constexpr uint32_t tmem_slot = bars + 16 * 8;
   static constexpr uint32_t total = tmem_slot + 16;
 };
@@ -146,6 +147,14 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32
         "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
         "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
         "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
       : "memory");
 }
 __device__ __forceinline__ float ex2(float x) {
@@ -311,11 +320,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       if (fail) atomicExch(a.status, fail);
     }
   } else {
-    // ---------------- softmax: two threads per query row, 64 score columns each ----------------
-    const int half = warp >> 2;                            // which 64 columns
+    // ---------------- softmax: kParts threads per query row, 32 score columns each ----------------
+    const int part = warp >> 2;                            // which 32 columns
     const int row = (warp & 3) * 32 + lane;                // = tensor-memory lane
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    float* xch = reinterpret_cast<float*>(smem + Smem::xch);    // [buffer][half][row]
+    const uint32_t bar_id = 1 + (warp & 3);                // the kParts warps that share rows synchronise
+    float* xch = reinterpret_cast<float*>(smem + Smem::xch);    // [buffer][part][row]
     const int kmax = a.causal ? q0 + row + off : a.seq_k - 1;   // last key this row may see
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
@@ -325,46 +335,41 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (lane == 0) atomicExch(a.status, 15);
         ok = false;
       }
-      // every softmax thread takes part in the exchange barrier below, failed or not; the barrier
-      // also tells every thread whether any warp has failed, so that all leave the loop together
+      // every thread of the row group takes part in the exchange barrier below, failed or not; the
+      // barrier also tells every thread whether any warp has failed, so that all leave together
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int kbase = j * kBN + half * 64;
+      const int kbase = j * kBN + part * 32;
       const bool need_mask = (j * kBN + kBN - 1 > (a.causal ? q0 + off : a.seq_k - 1)) || (j * kBN + kBN > a.seq_k);
       const int klim = min(kmax, a.seq_k - 1) - kbase;     // own columns <= klim are visible
       float mt = -INFINITY;
-      uint32_t sraw[2][32];                                // raw scores; scaled inside the exponential's FMA
+      uint32_t sraw[32];                                   // raw scores; scaled inside the exponential's FMA
       if (ok) {
-#pragma unroll
-        for (int c = 0; c < 2; ++c) tmem_ld32(tmem + kColS + b * kBN + lane_base + half * 64 + c * 32, sraw[c]);
+        tmem_ld32(tmem + kColS + b * kBN + lane_base + part * 32, sraw);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (need_mask) {
 #pragma unroll
-          for (int c = 0; c < 2; ++c)
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (c * 32 + i > klim) sraw[c][i] = 0xff800000u;   // -inf
+          for (int i = 0; i < 32; ++i)
+            if (i > klim) sraw[i] = 0xff800000u;   // -inf
         }
         float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four independent chains
 #pragma unroll
-        for (int c = 0; c < 2; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sraw[c][i]));
+        for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sraw[i]));
         mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * a.scale_log2;    // scale > 0: order preserved
       }
-      // the two halves of a row agree on its maximum through shared memory; only the two warps that
-      // share rows synchronise (barrier 1 + quarter), so the four pairs drift apart and their
-      // exponential and load phases overlap
-      xch[(b * 2 + half) * kBM + row] = mt;
+      // the threads of a row agree on its maximum through shared memory; only the warps that share
+      // rows synchronise, so the four row groups drift apart and their phases overlap
+      xch[(b * kParts + part) * kBM + row] = mt;
       uint32_t all_ok;
       asm volatile(
           "{\n\t.reg .pred p, q;\n\t"
           "setp.ne.u32 q, %1, 0;\n\t"
-          "bar.red.and.pred p, %2, 64, q;\n\t"
+          "bar.red.and.pred p, %2, %3, q;\n\t"
           "selp.u32 %0, 1, 0, p;\n\t}"
           : "=r"(all_ok)
-          : "r"((uint32_t)ok), "r"(1 + (warp & 3))
+          : "r"((uint32_t)ok), "r"(bar_id), "n"(kParts * 32)
           : "memory");
-      mt = fmaxf(mt, xch[(b * 2 + (half ^ 1)) * kBM + row]);
+#pragma unroll
+      for (int pp = 0; pp < kParts; ++pp) mt = fmaxf(mt, xch[(b * kParts + pp) * kBM + row]);
       if (!all_ok) {
         ok = false;
         break;
@@ -378,40 +383,35 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         l_run *= alpha;
       }
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
-        // O must be complete up to the previous tile before it is rescaled (own 64 columns)
+        // O must be complete up to the previous tile before it is rescaled (own 32 columns)
         if (!__all_sync(0xffffffffu, wait(bar(B_PV_DONE), (j - 1) & 1))) {
           if (lane == 0) atomicExch(a.status, 16);
           ok = false;      // reported to the other warps at the next barrier; this warp stops producing P
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
+          uint32_t ov[32];
+          tmem_ld32(tmem_o + lane_base + part * 32, ov);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            uint32_t ov[32];
-            tmem_ld32(tmem_o + lane_base + half * 64 + c * 32, ov);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-            tmem_st32(tmem_o + lane_base + half * 64 + c * 32, ov);
-          }
+          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+          tmem_st32(tmem_o + lane_base + part * 32, ov);
         }
       }
       if (!ok) continue;
       const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
-      uint32_t pk[32];
+      uint32_t pk[16];
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 2; ++c)
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float p0 = ex2(fmaf(__uint_as_float(sraw[c][2 * i]), a.scale_log2, neg_m));
-          const float p1 = ex2(fmaf(__uint_as_float(sraw[c][2 * i + 1]), a.scale_log2, neg_m));
-          ls[i & 3] += p0 + p1;
-          pk[c * 16 + i] = pack16(p0, p1, a.bf16);
-        }
+      for (int i = 0; i < 16; ++i) {
+        const float p0 = ex2(fmaf(__uint_as_float(sraw[2 * i]), a.scale_log2, neg_m));
+        const float p1 = ex2(fmaf(__uint_as_float(sraw[2 * i + 1]), a.scale_log2, neg_m));
+        ls[i & 3] += p0 + p1;
+        pk[i] = pack16(p0, p1, a.bf16);
+      }
       l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-      // P[b] columns [32 * half, 32 * half + 32): keys 64 * half .. 64 * half + 63 of this row
-      tmem_st32(tmem + kColP + b * (kBN / 2) + lane_base + half * 32, pk);
+      // P[b] columns [16 * part, 16 * part + 16): keys 32 * part .. 32 * part + 31 of this row
+      tmem_st16(tmem + kColP + b * (kBN / 2) + lane_base + part * 16, pk);
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       mbar_arrive(bar(B_P_FULL + b));
@@ -423,31 +423,30 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       }
     }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    // row sums of the two halves (second use of the exchange area: every thread is past its last tile's barrier)
-    asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");
-    xch[half * kBM + row] = l_run;
-    asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");
-    const float l_row = l_run + xch[(half ^ 1) * kBM + row];
+    // row sums of the parts (second use of the exchange area: every thread of the group is past its last tile)
+    asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "n"(kParts * 32) : "memory");
+    xch[part * kBM + row] = l_run;
+    asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "n"(kParts * 32) : "memory");
+    float l_row = 0.f;
+#pragma unroll
+    for (int pp = 0; pp < kParts; ++pp) l_row += xch[pp * kBM + row];
     if (ok) {
       const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
       const bool live = q0 + row < a.seq_q;
-      uint8_t* orow = reinterpret_cast<uint8_t*>(a.out) + half * 128 +
+      uint8_t* orow = reinterpret_cast<uint8_t*>(a.out) + part * 64 +
                       2 * (batch * a.o_batch_stride + head * a.o_head_stride + (int64_t)(q0 + row) * a.o_row_stride);
+      uint32_t ov[32];
+      tmem_ld32(tmem_o + lane_base + part * 32, ov);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (live) {
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t ov[32];
-        tmem_ld32(tmem_o + lane_base + half * 64 + c * 32, ov);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (live) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint4 w;
-            w.x = pack16(__uint_as_float(ov[8 * i]) * inv, __uint_as_float(ov[8 * i + 1]) * inv, a.bf16);
-            w.y = pack16(__uint_as_float(ov[8 * i + 2]) * inv, __uint_as_float(ov[8 * i + 3]) * inv, a.bf16);
-            w.z = pack16(__uint_as_float(ov[8 * i + 4]) * inv, __uint_as_float(ov[8 * i + 5]) * inv, a.bf16);
-            w.w = pack16(__uint_as_float(ov[8 * i + 6]) * inv, __uint_as_float(ov[8 * i + 7]) * inv, a.bf16);
-            *reinterpret_cast<uint4*>(orow + c * 64 + i * 16) = w;
-          }
+        for (int i = 0; i < 4; ++i) {
+          uint4 w;
+          w.x = pack16(__uint_as_float(ov[8 * i]) * inv, __uint_as_float(ov[8 * i + 1]) * inv, a.bf16);
+          w.y = pack16(__uint_as_float(ov[8 * i + 2]) * inv, __uint_as_float(ov[8 * i + 3]) * inv, a.bf16);
+          w.z = pack16(__uint_as_float(ov[8 * i + 4]) * inv, __uint_as_float(ov[8 * i + 5]) * inv, a.bf16);
+          w.w = pack16(__uint_as_float(ov[8 * i + 6]) * inv, __uint_as_float(ov[8 * i + 7]) * inv, a.bf16);
+          *reinterpret_cast<uint4*>(orow + i * 16) = w;
         }
       }
     }
