@@ -8,13 +8,20 @@
 //   * Q, K and V tiles arrive by TMA (cp.async.bulk.tensor, 128-byte swizzle)
 //     into shared memory; K / V tiles of 128 keys run through a 2-stage ring.
 //   * S = Q K^T and O += P V are tcgen05.mma (cta_group::1, kind::f16, M = N =
-//     128, K = 16 per instruction) issued by one thread; S and O live in tensor
-//     memory (128 lanes x 128 fp32 columns each).  V is consumed as stored
-//     (keys x head_dim, head_dim contiguous) through an MN-major descriptor.
-//   * Four warps own one query row per thread: tcgen05.ld the scores, online
-//     softmax in the log2 domain with a lazy rescale of O (tcgen05.ld/st only
-//     when a row maximum grows by more than 2^8), P back to shared memory in
-//     the K-major swizzled layout the second MMA reads.
+//     128, K = 16 per instruction) issued by one thread.  Three score buffers
+//     and O live in tensor memory (128 lanes x 128 fp32 columns each); P goes
+//     over the upper half of its scores as packed 16-bit pairs and is the A
+//     operand of the second product straight from tensor memory.  V is consumed
+//     as stored (keys x head_dim, head_dim contiguous) through an MN-major
+//     descriptor.
+//   * Two groups of four warps (one thread per query row each) take the K/V tiles
+//     in turn, group 0 the even ones and group 1 the odd ones: tcgen05.ld the
+//     scores, online softmax in the log2 domain, tcgen05.st of P.  The running
+//     row maximum travels from tile to tile through a shared-memory mailbox; a
+//     group's exponentials (special-function unit) run while the other group
+//     loads, masks and reduces its scores, and the tensor core works meanwhile
+//     on the products of the surrounding tiles.  O is rescaled lazily (only when
+//     a row maximum grows by more than 2^8) by the group that sees the growth.
 //   * Every wait is bounded; a wait that gives up sets the status word, the CTA
 //     drains its copies, frees its tensor memory and returns.
 #include <cuda.h>
@@ -29,10 +36,11 @@ namespace {
 constexpr int kD = 128;          // head_dim
 constexpr int kBM = 128;         // queries per CTA
 constexpr int kBN = 128;         // keys per tile
-constexpr int kKStages = 3;      // K tiles run two ahead of the scores that need them
+constexpr int kKStages = 3;      // K tiles run three ahead of the softmax
 constexpr int kVStages = 2;
-constexpr int kParts = 4;                        // threads per query row: 32 score columns each
-constexpr int kSoftmaxThreads = kParts * 128;
+constexpr int kSBufs = 3;        // score buffers in tensor memory: tile j uses buffer j % 3
+constexpr int kGroupThreads = 128;               // one softmax group: one thread per query row
+constexpr int kSoftmaxThreads = 2 * kGroupThreads;
 constexpr int kThreads = kSoftmaxThreads + 64;   // + TMA warp + MMA warp
 constexpr int kProducerWarp = kSoftmaxThreads / 32, kMmaWarp = kProducerWarp + 1;
 constexpr uint32_t kTileBytes = kBM * kD * 2;    // 32 KiB: one 128 x 128 16-bit tile
@@ -40,18 +48,18 @@ constexpr uint32_t kHalfBytes = kTileBytes / 2;  // one 128-row x 64-element swi
 constexpr uint32_t kSpin = 1u << 20;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescale = 8.0f;                 // log2 units: P stays <= 2^8
-// Tensor memory (512 columns x 128 lanes): two score buffers, the output accumulator and two
-// P buffers (16-bit pairs, 64 columns for 128 keys).
+// Tensor memory (512 columns x 128 lanes): scores of tile j at columns 128 (j % 3); its P (16-bit
+// pairs, 64 columns for 128 keys) goes over columns 64..127 of the same buffer; O at 384.
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColS = 0, kColO = 256, kColP = 384;
+constexpr uint32_t kColS = 0, kColO = 384, kColPinS = 64;
 
 struct Smem {                    // offsets from the 1024-byte aligned base
   static constexpr uint32_t q = 0;
   static constexpr uint32_t k0 = q + kTileBytes;                   // K stage s: k0 + s * kTileBytes
   static constexpr uint32_t v0 = k0 + kKStages * kTileBytes;       // V stage s: v0 + s * kTileBytes
-  static constexpr uint32_t xch = v0 + kVStages * kTileBytes;      // row maxima / sums: [2 buffers][kParts][128]
-  static constexpr uint32_t bars = xch + 2 * kParts * kBM * 4;
-  static constexpr uint32_t tmem_slot = bars + 16 * 8;
+  static constexpr uint32_t mbox = v0 + kVStages * kTileBytes;     // running row maxima [2][128], then final (m, l) [2][2][128]
+  static constexpr uint32_t bars = mbox + 6 * kBM * 4;
+  static constexpr uint32_t tmem_slot = bars + 32 * 8;
   static constexpr uint32_t total = tmem_slot + 16;
 };
 constexpr uint32_t kSmemBytes = Smem::total + 1024;   // slack for the alignment
@@ -149,6 +157,15 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32
         "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
@@ -172,8 +189,8 @@ __device__ __forceinline__ uint32_t pack16(float a, float b, bool bf16) {
 }
 
 // Barrier slots (8 bytes each) inside Smem::bars.
-enum : int { B_Q = 0, B_K_FULL = 1, B_K_EMPTY = 4, B_V_FULL = 7, B_V_EMPTY = 9, B_S_FULL = 11, B_P_FULL = 13,
-             B_PV_DONE = 15 };
+enum : int { B_Q = 0, B_K_FULL = 1, B_K_EMPTY = 4, B_V_FULL = 7, B_V_EMPTY = 9, B_S_FULL = 11, B_P_FULL = 14,
+             B_PV_DONE = 17 /* 2: by tile parity */, B_ALL_DONE = 19, B_MBOX = 20 /* 8: [row group][tile parity] */ };
 
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -203,11 +220,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       mbar_init(bar(B_V_FULL + s), 1);
       mbar_init(bar(B_V_EMPTY + s), 1);
     }
-    mbar_init(bar(B_S_FULL), 1);
-    mbar_init(bar(B_S_FULL + 1), 1);
-    mbar_init(bar(B_P_FULL), kSoftmaxThreads);
-    mbar_init(bar(B_P_FULL + 1), kSoftmaxThreads);
+    for (int i = 0; i < kSBufs; ++i) {
+      mbar_init(bar(B_S_FULL + i), 1);
+      mbar_init(bar(B_P_FULL + i), kGroupThreads);
+    }
     mbar_init(bar(B_PV_DONE), 1);
+    mbar_init(bar(B_PV_DONE + 1), 1);
+    mbar_init(bar(B_ALL_DONE), 1);
+    for (int i = 0; i < 8; ++i) mbar_init(bar(B_MBOX + i), 32);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == kMmaWarp) {   // this warp owns the tensor-memory allocation
@@ -246,11 +266,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         tma_load_4d(dst + kHalfBytes, &map_v, 64, j * kBN, kv_head, batch, bar(B_V_FULL + s));
         return true;
       };
-      // K runs ahead of V: the scores of tile j + 1 are computed while tile j is in the softmax
+      // K runs ahead of V: the scores are computed up to three tiles ahead of the softmax
       int jk = 0, jv = 0;
       bool ok = true;
       while (ok && (jk < n_tiles || jv < n_tiles)) {
-        if (jk < n_tiles && jk <= jv + 1) {
+        if (jk < n_tiles && jk <= jv + 2) {
           ok = load_k(jk);
           if (ok) ++jk;
         } else {
@@ -274,179 +294,219 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       const uint32_t idesc_pv = idesc_qk | (1u << 16);
       bool ok = wait(bar(B_Q), 0);
       int fail = ok ? 0 : 12;
-      auto issue_qk = [&](int j) {     // S[j & 1] = Q K_j^T
+      // descriptors are built once; inside the loops only the 16-byte-unit address field moves
+      uint64_t q_desc[kD / 16];
+#pragma unroll
+      for (int kk = 0; kk < kD / 16; ++kk)
+        q_desc[kk] = smem_desc(sbase + Smem::q + (kk >> 2) * kHalfBytes + (kk & 3) * 32, 16);
+      const uint64_t k_desc0 = smem_desc(sbase + Smem::k0, 16), v_desc0 = smem_desc(sbase + Smem::v0, kHalfBytes);
+      auto issue_qk = [&](int j) {     // S[j % 3] = Q K_j^T
         const int s = j % kKStages;
         if (!wait(bar(B_K_FULL + s), (j / kKStages) & 1)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t kbase = sbase + Smem::k0 + s * kTileBytes;
+        const uint64_t kd = k_desc0 + (uint64_t)(s * (kTileBytes >> 4));
+        const uint32_t d_tmem = tmem + kColS + (j % kSBufs) * kBN;
 #pragma unroll
-        for (int kk = 0; kk < kD / 16; ++kk) {
-          const uint32_t o = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
-          umma_f16(tmem + kColS + (j & 1) * kBN, smem_desc(sbase + Smem::q + o, 16), smem_desc(kbase + o, 16), idesc_qk,
-                   kk > 0);
-        }
+        for (int kk = 0; kk < kD / 16; ++kk)
+          umma_f16(d_tmem, q_desc[kk], kd + (uint64_t)(((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4), idesc_qk, kk > 0);
         umma_commit(bar(B_K_EMPTY + s));
-        umma_commit(bar(B_S_FULL + (j & 1)));
+        umma_commit(bar(B_S_FULL + j % kSBufs));
         return true;
       };
-      if (ok && !issue_qk(0)) {
-        ok = false;
-        fail = 13;
-      }
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        // the scores of the next tile are produced while this one is in the softmax: S[(j + 1) & 1] was
-        // last read for tile j - 1, whose P_FULL has been seen
-        if (j + 1 < n_tiles && !issue_qk(j + 1)) {
+      for (int j = 0; j < kSBufs && j < n_tiles && ok; ++j)
+        if (!issue_qk(j)) {
           ok = false;
           fail = 13;
-          break;
         }
+      for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j % kVStages;
-        if (!wait(bar(B_V_FULL + s), (j / kVStages) & 1) || !wait(bar(B_P_FULL + (j & 1)), (j >> 1) & 1)) {
+        if (!wait(bar(B_V_FULL + s), (j / kVStages) & 1) || !wait(bar(B_P_FULL + j % kSBufs), (j / kSBufs) & 1)) {
           ok = false;
           fail = 14;
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t vbase = sbase + Smem::v0 + s * kTileBytes;
-        const uint32_t p_tmem = tmem + kColP + (j & 1) * (kBN / 2);
+        const uint64_t vd = v_desc0 + (uint64_t)(s * (kTileBytes >> 4));
+        const uint32_t p_tmem = tmem + kColS + (j % kSBufs) * kBN + kColPinS;
 #pragma unroll
         for (int kk = 0; kk < kBN / 16; ++kk)    // 16 keys = 8 packed columns of P, 2 x 1024 bytes of V
-          umma_f16_ts(tmem_o, p_tmem + kk * 8, smem_desc(vbase + kk * 2048, kHalfBytes), idesc_pv,
+          umma_f16_ts(tmem_o, p_tmem + kk * 8, vd + (uint64_t)(kk * (2048 >> 4)), idesc_pv,
                       (j > 0 || kk > 0) ? 1u : 0u);
         umma_commit(bar(B_V_EMPTY + s));
-        umma_commit(bar(B_PV_DONE));
+        umma_commit(bar(B_PV_DONE + (j & 1)));
+        // the scores three tiles on go over this tile's buffer: the tensor core runs its work in
+        // issue order, so they follow the product that has just read P from it
+        if (j + kSBufs < n_tiles && !issue_qk(j + kSBufs)) {
+          ok = false;
+          fail = 13;
+          break;
+        }
       }
+      umma_commit(bar(B_ALL_DONE));
       if (fail) atomicExch(a.status, fail);
     }
   } else {
-    // ---------------- softmax: kParts threads per query row, 32 score columns each ----------------
-    const int part = warp >> 2;                            // which 32 columns
-    const int row = (warp & 3) * 32 + lane;                // = tensor-memory lane
-    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t bar_id = 1 + (warp & 3);                // the kParts warps that share rows synchronise
-    float* xch = reinterpret_cast<float*>(smem + Smem::xch);    // [buffer][part][row]
-    const int kmax = a.causal ? q0 + row + off : a.seq_k - 1;   // last key this row may see
-    float m_run = -INFINITY, l_run = 0.f;
+    // ---------------- softmax: group `who` takes the tiles j = who, who + 2, ...; one row per thread ----------------
+    const int who = warp >> 2, rg = warp & 3;
+    const int row = rg * 32 + lane;                        // = tensor-memory lane
+    const uint32_t lane_base = (uint32_t)(rg * 32) << 16;
+    float* mbox = reinterpret_cast<float*>(smem + Smem::mbox);    // [tile parity][row]
+    float* fin = mbox + 2 * kBM;                                  // [m | l][who][row]
+    const int kmax = a.causal ? q0 + row + off : a.seq_k - 1;     // last key this row may see
+    float m_mine = -INFINITY, l_mine = 0.f;                       // l_mine is relative to m_mine
     bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const int b = j & 1;
-      if (ok && !__all_sync(0xffffffffu, wait(bar(B_S_FULL + b), (j >> 1) & 1))) {   // warp-uniform: aligned tcgen05 ops follow
-        if (lane == 0) atomicExch(a.status, 15);
-        ok = false;
-      }
-      // every thread of the row group takes part in the exchange barrier below, failed or not; the
-      // barrier also tells every thread whether any warp has failed, so that all leave together
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int kbase = j * kBN + part * 32;
+    // the 64 scores of one half row: load, mask what the row may not see
+    auto load_half = [&](int j, int h, uint32_t (&v)[2][32]) {
+      const uint32_t src = tmem + kColS + (j % kSBufs) * kBN + lane_base + h * 64;
+      tmem_ld32(src, v[0]);
+      tmem_ld32(src + 32, v[1]);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       const bool need_mask = (j * kBN + kBN - 1 > (a.causal ? q0 + off : a.seq_k - 1)) || (j * kBN + kBN > a.seq_k);
-      const int klim = min(kmax, a.seq_k - 1) - kbase;     // own columns <= klim are visible
-      float mt = -INFINITY;
-      uint32_t sraw[32];                                   // raw scores; scaled inside the exponential's FMA
-      if (ok) {
-        tmem_ld32(tmem + kColS + b * kBN + lane_base + part * 32, sraw);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (need_mask) {
+      if (need_mask) {
+        const int klim = min(kmax, a.seq_k - 1) - (j * kBN + h * 64);     // columns <= klim are visible
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (i > klim) sraw[i] = 0xff800000u;   // -inf
-        }
-        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four independent chains
-#pragma unroll
-        for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sraw[i]));
-        mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * a.scale_log2;    // scale > 0: order preserved
+            if (c * 32 + i > klim) v[c][i] = 0xff800000u;   // -inf
       }
-      // the threads of a row agree on its maximum through shared memory; only the warps that share
-      // rows synchronise, so the four row groups drift apart and their phases overlap
-      xch[(b * kParts + part) * kBM + row] = mt;
-      uint32_t all_ok;
-      asm volatile(
-          "{\n\t.reg .pred p, q;\n\t"
-          "setp.ne.u32 q, %1, 0;\n\t"
-          "bar.red.and.pred p, %2, %3, q;\n\t"
-          "selp.u32 %0, 1, 0, p;\n\t}"
-          : "=r"(all_ok)
-          : "r"((uint32_t)ok), "r"(bar_id), "n"(kParts * 32)
-          : "memory");
+    };
+    auto half_max = [&](const uint32_t (&v)[2][32]) {
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four independent chains
 #pragma unroll
-      for (int pp = 0; pp < kParts; ++pp) mt = fmaxf(mt, xch[(b * kParts + pp) * kBM + row]);
-      if (!all_ok) {
+      for (int c = 0; c < 2; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(v[c][i]));
+      return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+    };
+    // exponentials of a half row -> 32 packed columns of P at `dst`; returns their sum
+    auto half_exp = [&](const uint32_t (&v)[2][32], float neg_m, uint32_t dst) {
+      uint32_t pk[32];
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < 2; ++c)
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = ex2(fmaf(__uint_as_float(v[c][2 * i]), a.scale_log2, neg_m));
+          const float p1 = ex2(fmaf(__uint_as_float(v[c][2 * i + 1]), a.scale_log2, neg_m));
+          ls[i & 3] += p0 + p1;
+          pk[c * 16 + i] = pack16(p0, p1, a.bf16);
+        }
+      tmem_st32(dst, pk);
+      return (ls[0] + ls[1]) + (ls[2] + ls[3]);
+    };
+    for (int j = who; j < n_tiles && ok; j += 2) {
+      if (!__all_sync(0xffffffffu, wait(bar(B_S_FULL + j % kSBufs), (j / kSBufs) & 1))) {   // warp-uniform: aligned tcgen05 ops follow
+        if (lane == 0) atomicExch(a.status, 15);
         ok = false;
         break;
       }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // pass 1: the row maximum (the lower half is read again for its exponentials; the upper half stays)
+      uint32_t sv[2][32];
+      load_half(j, 0, sv);
+      float mraw = half_max(sv);
+      load_half(j, 1, sv);
+      mraw = fmaxf(mraw, half_max(sv));
+      const float mt = mraw * a.scale_log2;              // scale > 0: order preserved
+      // the running maximum after the previous tile comes from the other group
+      if (j > 0) {
+        if (!__all_sync(0xffffffffu, wait(bar(B_MBOX + rg * 2 + ((j - 1) & 1)), ((j - 1) >> 1) & 1))) {
+          if (lane == 0) atomicExch(a.status, 18);
+          ok = false;
+          break;
+        }
+        const float m_prev = mbox[((j - 1) & 1) * kBM + row];
+        if (m_prev != m_mine) {
+          l_mine *= m_mine == -INFINITY ? 0.f : ex2(m_mine - m_prev);
+          m_mine = m_prev;
+        }
+      }
       // lazy rescale: the reference maximum only moves when a row maximum outgrows it by 2^8
-      const bool grow = mt > m_run + kRescale;
+      const bool grow = mt > m_mine + kRescale;
       float alpha = 1.f;
       if (grow) {
-        alpha = m_run == -INFINITY ? 0.f : ex2(m_run - mt);
-        m_run = mt;
-        l_run *= alpha;
+        alpha = m_mine == -INFINITY ? 0.f : ex2(m_mine - mt);
+        m_mine = mt;
+        l_mine *= alpha;
       }
+      // publish before touching O: the other group only scales its P with it, and its product is
+      // issued after this tile's, which waits for the arrival at the end of this iteration
+      mbox[(j & 1) * kBM + row] = m_mine;
+      mbar_arrive(bar(B_MBOX + rg * 2 + (j & 1)));
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
-        // O must be complete up to the previous tile before it is rescaled (own 32 columns)
-        if (!__all_sync(0xffffffffu, wait(bar(B_PV_DONE), (j - 1) & 1))) {
+        // O must be complete up to the previous tile before it is rescaled
+        if (!__all_sync(0xffffffffu, wait(bar(B_PV_DONE + ((j - 1) & 1)), ((j - 1) >> 1) & 1))) {
           if (lane == 0) atomicExch(a.status, 16);
-          ok = false;      // reported to the other warps at the next barrier; this warp stops producing P
+          ok = false;
+          break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok) {
-          uint32_t ov[32];
-          tmem_ld32(tmem_o + lane_base + part * 32, ov);
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {      // rare path: kept small in registers
+          uint32_t ov[16];
+          tmem_ld16(tmem_o + lane_base + c * 16, ov);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-          tmem_st32(tmem_o + lane_base + part * 32, ov);
+          for (int i = 0; i < 16; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+          tmem_st16(tmem_o + lane_base + c * 16, ov);
         }
       }
-      if (!ok) continue;
-      const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
-      uint32_t pk[16];
-      float ls[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float p0 = ex2(fmaf(__uint_as_float(sraw[2 * i]), a.scale_log2, neg_m));
-        const float p1 = ex2(fmaf(__uint_as_float(sraw[2 * i + 1]), a.scale_log2, neg_m));
-        ls[i & 3] += p0 + p1;
-        pk[i] = pack16(p0, p1, a.bf16);
+      if (j == 1) {
+        // start half a period behind group 0, so that one group's exponentials run while the other
+        // loads and reduces scores
+        if (!__all_sync(0xffffffffu, wait(bar(B_P_FULL), 0))) {
+          if (lane == 0) atomicExch(a.status, 19);
+          ok = false;
+          break;
+        }
       }
-      l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-      // P[b] columns [16 * part, 16 * part + 16): keys 32 * part .. 32 * part + 31 of this row
-      tmem_st16(tmem + kColP + b * (kBN / 2) + lane_base + part * 16, pk);
+      // pass 2: P over columns 64..127 of the scores (both halves of which are in registers or consumed by now)
+      const float neg_m = m_mine == -INFINITY ? 0.f : -m_mine;
+      const uint32_t p_dst = tmem + kColS + (j % kSBufs) * kBN + lane_base + kColPinS;
+      l_mine += half_exp(sv, neg_m, p_dst + 32);          // keys 64..127 -> packed columns 32..63
+      load_half(j, 0, sv);
+      l_mine += half_exp(sv, neg_m, p_dst);               // keys 0..63 -> packed columns 0..31
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(bar(B_P_FULL + b));
+      mbar_arrive(bar(B_P_FULL + j % kSBufs));
     }
     if (ok && n_tiles > 0) {
-      if (!__all_sync(0xffffffffu, wait(bar(B_PV_DONE), (n_tiles - 1) & 1))) {
+      if (!__all_sync(0xffffffffu, wait(bar(B_ALL_DONE), 0))) {
         if (lane == 0) atomicExch(a.status, 17);
         ok = false;
       }
     }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    // row sums of the parts (second use of the exchange area: every thread of the group is past its last tile)
-    asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "n"(kParts * 32) : "memory");
-    xch[part * kBM + row] = l_run;
-    asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "n"(kParts * 32) : "memory");
-    float l_row = 0.f;
-#pragma unroll
-    for (int pp = 0; pp < kParts; ++pp) l_row += xch[pp * kBM + row];
-    if (ok) {
+    // the two groups combine their row sums (each relative to its own last maximum); group 0 writes
+    // output columns 0..63, group 1 columns 64..127
+    fin[who * kBM + row] = m_mine;
+    fin[(2 + who) * kBM + row] = l_mine;
+    asm volatile("bar.sync %0, 64;" ::"r"(1 + rg) : "memory");
+    const float m_oth = fin[(who ^ 1) * kBM + row], l_oth = fin[(2 + (who ^ 1)) * kBM + row];
+    const float m_fin = fmaxf(m_mine, m_oth);
+    const float l_row = (m_mine == -INFINITY ? 0.f : l_mine * ex2(m_mine - m_fin)) +
+                        (m_oth == -INFINITY ? 0.f : l_oth * ex2(m_oth - m_fin));
+    if (ok && n_tiles > 0) {
       const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
       const bool live = q0 + row < a.seq_q;
-      uint8_t* orow = reinterpret_cast<uint8_t*>(a.out) + part * 64 +
+      uint8_t* orow = reinterpret_cast<uint8_t*>(a.out) + who * 128 +
                       2 * (batch * a.o_batch_stride + head * a.o_head_stride + (int64_t)(q0 + row) * a.o_row_stride);
-      uint32_t ov[32];
-      tmem_ld32(tmem_o + lane_base + part * 32, ov);
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      if (live) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint4 w;
-          w.x = pack16(__uint_as_float(ov[8 * i]) * inv, __uint_as_float(ov[8 * i + 1]) * inv, a.bf16);
-          w.y = pack16(__uint_as_float(ov[8 * i + 2]) * inv, __uint_as_float(ov[8 * i + 3]) * inv, a.bf16);
-          w.z = pack16(__uint_as_float(ov[8 * i + 4]) * inv, __uint_as_float(ov[8 * i + 5]) * inv, a.bf16);
-          w.w = pack16(__uint_as_float(ov[8 * i + 6]) * inv, __uint_as_float(ov[8 * i + 7]) * inv, a.bf16);
-          *reinterpret_cast<uint4*>(orow + i * 16) = w;
+      for (int c = 0; c < 2; ++c) {
+        uint32_t ov[32];
+        tmem_ld32(tmem_o + lane_base + who * 64 + c * 32, ov);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (live) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 w;
+            w.x = pack16(__uint_as_float(ov[8 * i]) * inv, __uint_as_float(ov[8 * i + 1]) * inv, a.bf16);
+            w.y = pack16(__uint_as_float(ov[8 * i + 2]) * inv, __uint_as_float(ov[8 * i + 3]) * inv, a.bf16);
+            w.z = pack16(__uint_as_float(ov[8 * i + 4]) * inv, __uint_as_float(ov[8 * i + 5]) * inv, a.bf16);
+            w.w = pack16(__uint_as_float(ov[8 * i + 6]) * inv, __uint_as_float(ov[8 * i + 7]) * inv, a.bf16);
+            *reinterpret_cast<uint4*>(orow + c * 64 + i * 16) = w;
+          }
         }
       }
     }
