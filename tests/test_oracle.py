@@ -208,6 +208,31 @@ def test_affine_roundtrip(oracle):
     assert (code == 0).all() and (oracle.affine_dequantize(code, sc, bi, 64, 8) == 0).all()
 
 
+def test_prefill_sdpa_definition(oracle):
+    """The dense prompt-step attention: causal rows see keys 0 .. i + (S - L), query head h reads
+    kv head h // n_rep, a single visible key returns that key's value row, and the last query row of
+    a causal call equals a one-token decode over all keys."""
+    rng = np.random.default_rng(21)
+    B, n_q, n_kv, L, S, D = 2, 4, 2, 5, 9, 16
+    q = rng.standard_normal((B, n_q, L, D)).astype(np.float32)
+    k = rng.standard_normal((B, n_kv, S, D)).astype(np.float32)
+    v = rng.standard_normal((B, n_kv, S, D)).astype(np.float32)
+    scale = 0.3
+    out = oracle.prefill_sdpa(q, k, v, scale, causal=True)
+    for b in range(B):
+        for h in range(n_q):
+            for i in range(L):
+                vis = i + (S - L) + 1
+                s_ = (k[b, h // 2, :vis].astype(np.float64) @ q[b, h, i].astype(np.float64)) * scale
+                w = np.exp(s_ - s_.max())
+                ref = (w / w.sum()) @ v[b, h // 2, :vis].astype(np.float64)
+                assert np.allclose(out[b, h, i], ref, rtol=1e-5, atol=1e-6)
+    one = oracle.prefill_sdpa(q[:, :, :1], k[:, :, :1], v[:, :, :1], scale, causal=True)
+    assert np.allclose(one[:, :, 0], np.repeat(v[:, :, 0], 2, axis=1), atol=1e-6)
+    full = oracle.prefill_sdpa(q[:, :, -1:], k, v, scale, causal=False)
+    assert np.allclose(full[:, :, 0], out[:, :, -1], rtol=1e-5, atol=1e-6)
+
+
 def test_golden_fixtures_match_oracle(oracle, golden):
     g = golden
     assert np.array_equal(oracle.signs_from_seed(128, 42), g["signs_42"])
