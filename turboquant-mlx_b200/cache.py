@@ -38,6 +38,20 @@ _DTYPE_MAP = {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": t
 _DTYPE_NAME = {v: k for k, v in _DTYPE_MAP.items()}
 
 
+_ZEROS: dict = {}
+
+
+def _zero(dtype, device) -> torch.Tensor:
+    """One zero element per (dtype, device), made once: placeholders are stride-0 views of it, so
+    handing them out launches nothing."""
+    key = (dtype, str(device))
+    z = _ZEROS.get(key)
+    if z is None:
+        z = torch.zeros((1,), dtype=dtype, device=device)
+        _ZEROS[key] = z
+    return z
+
+
 class TurboQuantKVCache:
     """TurboQuant KV cache, drop-in for a plain KVCache."""
 
@@ -164,8 +178,8 @@ class TurboQuantKVCache:
         if self.fused:
             # attention reads the packed storage directly; hand back shape-only
             # placeholders (stride-0 views, no memory)
-            zk = torch.zeros((1,), dtype=keys.dtype, device=keys.device).expand(B, H, total, k_dim)
-            zv = torch.zeros((1,), dtype=values.dtype, device=values.device).expand(B, H, total, v_dim)
+            zk = _zero(keys.dtype, keys.device).expand(B, H, total, k_dim)
+            zv = _zero(values.dtype, values.device).expand(B, H, total, v_dim)
             return zk, zv
 
         incremental = S <= 4 and self._v_deq_buf is not None and self._deq_offset == prev
@@ -193,7 +207,7 @@ class TurboQuantKVCache:
         v_out = self._v_deq_buf[..., :total, :]
         if self.v_only:
             # K is handled by the caller; the K return is a placeholder
-            zk = torch.zeros((1,), dtype=keys.dtype, device=keys.device).expand(B, H, total, k_dim)
+            zk = _zero(keys.dtype, keys.device).expand(B, H, total, k_dim)
             return zk, v_out
         return self._k_deq_buf[..., :total, :], v_out
 
