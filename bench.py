@@ -494,6 +494,55 @@ def workload_c4_prefill(args):
                                  "flops_per_layer": flops}}))
 
 
+def workload_c4(args):
+    """Config 4 end to end: random-init Qwen2.5-7B architecture (28 layers, hidden 3584, 28 q / 4 kv heads,
+    d 128, vocab 152064, bf16 weights ~N(0, 0.02)), a prompt of uniform-random token ids prefilled into plain
+    bf16 caches (prompt attention through tq_prefill_sdpa), conversion to the K8 / V4 group-64 cache, then greedy
+    decode steps through the hooked attention.  MLP width, RoPE base and norm eps are assumed (printed)."""
+    import torch
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    tq = entry.load_package()
+    from turboquant_mlx_b200.qwen2 import Qwen2Config, Qwen2Model
+    cfg = Qwen2Config()
+    if args.layers != 28:
+        cfg.n_layers = args.layers
+    S, n_new = args.ctx or 32768, max(2, args.steps if args.steps != 50 else 256)
+    model = Qwen2Model(cfg, dev, torch.bfloat16, seed=0)
+    prompt = torch.randint(0, cfg.vocab, (1, S), generator=torch.Generator().manual_seed(1)).to(dev)
+    tq.apply_patch()
+    try:
+        caches = [tq.KVCache() for _ in range(cfg.n_layers)]
+        torch.cuda.synchronize()
+        e0, e1, e2, e3 = (torch.cuda.Event(enable_timing=True) for _ in range(4))
+        e0.record()
+        logits = model.forward(prompt, caches)
+        e1.record()
+        caches = [tq.MixedQuantKVCache.from_kvcache(c, k_bits=8, v_bits=4, group_size=64) for c in caches]
+        tok = logits[:, -1].argmax(-1, keepdim=True)
+        e2.record()
+        toks = [tok]
+        with ClockSampler(0) as clk:
+            for _ in range(n_new - 1):
+                tok = model.forward(tok, caches)[:, -1].argmax(-1, keepdim=True)
+                toks.append(tok)
+            e3.record()
+            torch.cuda.synchronize()
+        prefill_status = tq.kernels.prefill_status(dev)
+    finally:
+        tq.remove_patch()
+    t_prefill, t_convert, t_decode = e0.elapsed_time(e1), e1.elapsed_time(e2), e2.elapsed_time(e3)
+    kv_bytes_per_token = cfg.n_layers * cfg.n_kv_heads * (S + n_new // 2) * (136 + 72)
+    print(json.dumps({"metric": "K8/V4 end-to-end decode tok/s", "unit": "tok/s", "n_gpus": 1,
+                      "value": (n_new - 1) / (t_decode / 1e3), "decode_ms_per_token": t_decode / (n_new - 1),
+                      "prefill_ms": t_prefill, "prefill_tok_per_s": S / (t_prefill / 1e3), "convert_ms": t_convert,
+                      "prefill_kernel_status": prefill_status, "tokens": [int(t) for t in torch.cat(toks, 1)[0, :8]],
+                      "kv_GBs_during_decode": kv_bytes_per_token / (t_decode / (n_new - 1)) / 1e6,
+                      "cache_bytes": sum(c.nbytes for c in caches), "params": model.n_params(), "dtype": "bf16",
+                      "data": "synthetic", "clocks": clk.summary(),
+                      "config": {"workload": f"C4: prompt {S}, {n_new} greedy tokens, K8/V4 group 64", **cfg.describe()}}))
+
+
 def workload_c5(args):
     """Config 5: long-context decode, Llama-3-70B attention shape (64 q / 8 kv heads, d 128), K 8-bit
     group-affine + V PolarQuant 3-bit, the sequence split across the ranks: 131072 positions per GPU
@@ -609,7 +658,7 @@ def main():
     ap.add_argument("--kernel-only", action="store_true",
                     help="plain launches of the flash-decode kernel only (no graph, no e2e): profiler case")
     ap.add_argument("--ctx", type=int, default=0, help="c4p: prompt length (default 32768)")
-    ap.add_argument("--workload", default="c2", choices=["c2", "c1", "c3", "c5", "c4p"],
+    ap.add_argument("--workload", default="c2", choices=["c2", "c1", "c3", "c5", "c4p", "c4"],
                     help="c2 = the headline benchmark; c1 / c3 = secondary measurements of other configurations")
     args = ap.parse_args()
     if args.workload == "c1":
@@ -620,6 +669,8 @@ def main():
         return workload_c5(args)
     if args.workload == "c4p":
         return workload_c4_prefill(args)
+    if args.workload == "c4":
+        return workload_c4(args)
     N_LAYERS = args.layers
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":

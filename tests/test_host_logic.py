@@ -82,3 +82,23 @@ def test_meta_state_format(tq):
     assert v.empty() and v.is_trimmable() and tq.TurboQuantKVCache().empty()
     with pytest.raises(ValueError, match="Expected 2"):
         c.state = [torch.zeros(1)] * 3
+
+
+def test_qwen2_module_cache_consistency():
+    """The random-init decoder that drives the caches: prompt + one decode step through a plain
+    cache gives the logits of the full sequence's last position (CPU, library attention)."""
+    import torch
+    import __graft_entry__ as entry
+    tq = entry.load_package()
+    from turboquant_mlx_b200.qwen2 import Qwen2Config, Qwen2Model
+    cfg = Qwen2Config(n_layers=2, hidden=64, n_q_heads=4, n_kv_heads=2, head_dim=16, ffn=96, vocab=50,
+                      init_std=0.2)
+    model = Qwen2Model(cfg, "cpu", torch.float32, seed=1)
+    toks = torch.randint(0, cfg.vocab, (2, 9), generator=torch.Generator().manual_seed(0))
+    full = model.forward(toks, [tq.KVCache() for _ in range(cfg.n_layers)], last_only=False)
+    caches = [tq.KVCache() for _ in range(cfg.n_layers)]
+    model.forward(toks[:, :8], caches)
+    step = model.forward(toks[:, 8:], caches)
+    assert caches[0].offset == 9
+    assert torch.allclose(step[:, 0], full[:, -1], atol=1e-4, rtol=1e-4)
+    assert model.n_params() == sum(t.numel() for lw in model.layers for t in lw.values()) + 2 * cfg.vocab * cfg.hidden

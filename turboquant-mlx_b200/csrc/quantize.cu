@@ -42,6 +42,10 @@ quantize_warp_kernel(const QuantArgs a) {
   constexpr int VPW = vals_per_word(BITS);
   constexpr int PDIM = packed_words(DIM, BITS);
   __shared__ uint8_t idx_s[kWarpsPerBlock][DIM];
+  // A kernel launched behind this one with programmatic stream serialization (the decode
+  // attention after a cache append) may be scheduled now; it waits for this grid's completion
+  // before it reads anything written here.
+  if (threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
