@@ -262,6 +262,8 @@ def test_affine_k8_with_polar_and_affine_values(tq, oracle, dev, v_bits):
     out = tq.flash_decode(_t(q, dev), k=k, v=v, attn_scale=scale, out_dtype=torch.float32)
     kd = oracle.affine_dequantize(kc, ks, kb, G, 8)
     vd = oracle.affine_dequantize(vc, vs, vb, G, v_bits)
+    # K8 / V4 (group 64) runs on the tensor-core kernel, 8-bit values on the general one
+    assert tq._lib.lib().tq_flash_decode_last_kernel() == (1 if v_bits == 4 else 0)
     for b in range(B):
         kv = np.arange(n_kv * n_rep) // n_rep
         sc = np.einsum("hpe,he->hp", kd[b][kv].astype(np.float64), q[b].astype(np.float64)) * scale
@@ -279,6 +281,37 @@ def test_affine_k8_with_polar_and_affine_values(tq, oracle, dev, v_bits):
                                          v_polar=dict(packed=vp[b], norms=vn[b], centroids=oracle.codebook(3),
                                                       signs=vq.signs.cpu().numpy(), bits=3))
         assert _rel(out2[b].cpu().numpy(), ref) < ATT_TOL
+
+
+@pytest.mark.parametrize("k_format", ["affine", "dense"])
+@pytest.mark.parametrize("S,n_rep", [(4100, 7), (40004, 2)])   # row strides stay 16-byte multiples
+def test_affine_v4_tensor_core_path(tq, oracle, dev, k_format, S, n_rep):
+    """4-bit group-affine values on the tensor-core kernel: values with a large common offset and
+    per-row spread (so that bias and scale terms both matter), ragged lengths, many splits
+    (two merge levels at 40000 positions), fp16 output."""
+    rng = np.random.default_rng(S)
+    n_kv, D, G = 2, 128, 64
+    kraw = rng.standard_normal((1, n_kv, S, D)).astype(np.float16)
+    vraw = (3.0 + rng.standard_normal((1, n_kv, S, D)) * rng.lognormal(0, 0.7, (1, n_kv, S, 1))).astype(np.float16)
+    q = (1.5 * rng.standard_normal((1, n_kv * n_rep, D))).astype(np.float16)
+    from turboquant_mlx_b200 import affine
+    gvc, gvs, gvb = affine.affine_quantize(_t(vraw, dev), G, 4)
+    vd = oracle.affine_dequantize(gvc.cpu().numpy(), gvs.cpu().numpy(), gvb.cpu().numpy(), G, 4)
+    v = dict(format="affine", codes=gvc, scales=gvs, biases=gvb, bits=4, group=G)
+    if k_format == "affine":
+        gkc, gks, gkb = affine.affine_quantize(_t(kraw, dev), G, 8)
+        k = dict(format="affine", codes=gkc, scales=gks, biases=gkb, bits=8, group=G)
+        kd = oracle.affine_dequantize(gkc.cpu().numpy(), gks.cpu().numpy(), gkb.cpu().numpy(), G, 8)
+    else:
+        k = dict(format="dense", data=_t(kraw, dev))
+        kd = kraw.astype(np.float32)
+    scale = 1.0 / math.sqrt(D)
+    out = tq.flash_decode(_t(q, dev), k=k, v=v, attn_scale=scale, out_dtype=torch.float16)
+    assert tq._lib.lib().tq_flash_decode_last_kernel() == 1
+    kv = np.arange(n_kv * n_rep) // n_rep
+    sc = np.einsum("hpe,he->hp", kd[0][kv].astype(np.float64), q[0].astype(np.float64)) * scale
+    ref = np.einsum("hp,hpe->he", oracle.softmax(sc).astype(np.float64), vd[0][kv].astype(np.float64))
+    assert _rel(out[0].float().cpu().numpy(), ref) < ATT_TOL
 
 
 def test_tensor_core_path_is_taken_and_accurate(tq, oracle, dev):

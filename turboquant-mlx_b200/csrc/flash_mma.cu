@@ -81,6 +81,9 @@ template <> struct KGeom<KF_AFFINE8> { static constexpr int row = 128, lut = 0, 
 template <int VB> struct VGeom;
 template <> struct VGeom<3> { static constexpr int row = 52, lut = 64 * 32 * 4; };
 template <> struct VGeom<4> { static constexpr int row = 64, lut = 256 * 32 * 4; };
+// VB == 40: group-affine 4-bit values (two codes per byte, low nibble first: the same bit layout as the
+// packed 4-bit rows), groups of 64 elements, one fp16 scale and bias per group and position.
+template <> struct VGeom<40> { static constexpr int row = 64, lut = 256 * 32 * 4; };
 
 template <int KF, int VB> struct Layout {
   static constexpr int bars = 0;                         // 2 * kStages * 8 bytes
@@ -92,10 +95,11 @@ template <int KF, int VB> struct Layout {
   static constexpr int kn_off = kTile * KGeom<KF>::row;
   static constexpr int v_off = kn_off + KGeom<KF>::norms;
   static constexpr int vn_off = v_off + kTile * VGeom<VB>::row;
-  static constexpr int stage_bytes = vn_off + kTile * 4;
+  static constexpr int stage_bytes = vn_off + kTile * (VB == 40 ? 8 : 4);   // norms, or scale + bias words
   // the ring is reused by the epilogue: warp exchange, then the staged split merge
   static constexpr int merge_bytes = (kMaxParts * 8 * kDim + kMaxParts * 16 + 8 * 64) * 4;
-  static constexpr int xch_bytes = kConsumerWarps * 34 * 32 * 4;
+  static constexpr int xch_rows = VB == 40 ? 36 : 34;   // 32 accumulator values, m, l [, two bias sums]
+  static constexpr int xch_bytes = kConsumerWarps * xch_rows * 32 * 4;
   static constexpr int ring_bytes = kStages * stage_bytes;
   static constexpr int work_bytes =
       ring_bytes > merge_bytes ? (ring_bytes > xch_bytes ? ring_bytes : xch_bytes)
@@ -173,6 +177,10 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
   return v;
 }
 __device__ __forceinline__ float lds_f32(uint32_t addr) { return __uint_as_float(lds32(addr)); }
+__device__ __forceinline__ uint32_t hmul2_bits(uint32_t a, uint32_t b) {
+  const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
 __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
@@ -340,10 +348,11 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   if (warp < kConsumerWarps) {
     constexpr int kCT = kConsumerThreads;
     uint32_t* vl = reinterpret_cast<uint32_t*>(smem + L::vlut);
-    constexpr int nv = 1 << (2 * VB);
+    constexpr int VBITS = VB == 40 ? 4 : VB;
+    constexpr int nv = 1 << (2 * VBITS);
     for (int i = tid; i < nv * 32; i += kCT) {
       const int e = i >> 5;
-      vl[i] = (uint32_t)c16_s[e & ((1 << VB) - 1)] | ((uint32_t)c16_s[e >> VB] << 16);
+      vl[i] = (uint32_t)c16_s[e & ((1 << VBITS) - 1)] | ((uint32_t)c16_s[e >> VBITS] << 16);
     }
     if (KF == KF_POLAR3 || KF == KF_POLAR4) {
       constexpr int KB = KF == KF_POLAR3 ? 3 : 4;
@@ -447,10 +456,18 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       reinterpret_cast<const __half*>(a.k_scales) + b * a.ks_batch_stride + kvh * a.ks_head_stride) : nullptr;
   const uint32_t* kbibase = KF == KF_AFFINE8 ? reinterpret_cast<const uint32_t*>(
       reinterpret_cast<const __half*>(a.k_biases) + b * a.ks_batch_stride + kvh * a.ks_head_stride) : nullptr;
-  const uint8_t* vbase = reinterpret_cast<const uint8_t*>(a.v_data) + (b * a.v_batch_stride + kvh * a.v_head_stride) * 4;
+  constexpr bool VAFF = VB == 40;
+  // packed values: strides in 32-bit words; affine codes: strides in bytes
+  const uint8_t* vbase = reinterpret_cast<const uint8_t*>(a.v_data) +
+                         (b * a.v_batch_stride + kvh * a.v_head_stride) * (VAFF ? 1 : 4);
   const float* knbase = (KF == KF_DENSE || KF == KF_AFFINE8)
                             ? nullptr : a.k_norms + b * a.kn_batch_stride + kvh * a.kn_head_stride;
-  const float* vnbase = a.v_norms + b * a.vn_batch_stride + kvh * a.vn_head_stride;
+  const float* vnbase = VAFF ? nullptr : a.v_norms + b * a.vn_batch_stride + kvh * a.vn_head_stride;
+  // affine values: per position two fp16 scales and two fp16 biases = one 32-bit word each
+  const uint32_t* vscbase = VAFF ? reinterpret_cast<const uint32_t*>(
+      reinterpret_cast<const __half*>(a.v_scales) + b * a.vs_batch_stride + kvh * a.vs_head_stride) : nullptr;
+  const uint32_t* vbibase = VAFF ? reinterpret_cast<const uint32_t*>(
+      reinterpret_cast<const __half*>(a.v_biases) + b * a.vs_batch_stride + kvh * a.vs_head_stride) : nullptr;
 
   // =============================== producer ===============================
   if (warp == kConsumerWarps) {
@@ -481,8 +498,14 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         if (v_bulk + 4 * w < v_total)
           *reinterpret_cast<uint32_t*>(stg + L::v_off + v_bulk + 4 * w) =
               *reinterpret_cast<const uint32_t*>(vsrc + v_bulk + 4 * w);
-        if (n_bulk + 4 * w < n_total)
-          *reinterpret_cast<float*>(stg + L::vn_off + n_bulk + 4 * w) = vnbase[p0 + n_bulk / 4 + w];
+        if (n_bulk + 4 * w < n_total) {
+          if (VAFF) {
+            *reinterpret_cast<uint32_t*>(stg + L::vn_off + n_bulk + 4 * w) = vscbase[p0 + n_bulk / 4 + w];
+            *reinterpret_cast<uint32_t*>(stg + L::vn_off + kTile * 4 + n_bulk + 4 * w) = vbibase[p0 + n_bulk / 4 + w];
+          } else {
+            *reinterpret_cast<float*>(stg + L::vn_off + n_bulk + 4 * w) = vnbase[p0 + n_bulk / 4 + w];
+          }
+        }
         if (KF == KF_POLAR3 || KF == KF_POLAR4) {
           if (k_total != 0 && k_bulk + 4 * w < k_total)
             *reinterpret_cast<uint32_t*>(stg + L::k_off + k_bulk + 4 * w) =
@@ -499,7 +522,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       }
       __syncwarp();
       if (lane == 0) {
-        uint32_t tx = v_bulk + n_bulk;
+        uint32_t tx = v_bulk + (VAFF ? 2 * n_bulk : n_bulk);
         if (KF == KF_DENSE) tx += (uint32_t)nvp * 256u;
         else if (KF == KF_AFFINE8) tx += (uint32_t)nvp * 128u + 2 * n_bulk;
         else tx += k_bulk + n_bulk;
@@ -511,7 +534,12 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
           if (n_bulk) bulk_g2s(st + L::kn_off + kTile * 4, kbibase + p0, n_bulk, full_bar(s));
         }
         if (v_bulk) bulk_g2s(st + L::v_off, vsrc, v_bulk, full_bar(s));
-        if (n_bulk) bulk_g2s(st + L::vn_off, vnbase + p0, n_bulk, full_bar(s));
+        if (VAFF) {
+          if (n_bulk) bulk_g2s(st + L::vn_off, vscbase + p0, n_bulk, full_bar(s));
+          if (n_bulk) bulk_g2s(st + L::vn_off + kTile * 4, vbibase + p0, n_bulk, full_bar(s));
+        } else if (n_bulk) {
+          bulk_g2s(st + L::vn_off, vnbase + p0, n_bulk, full_bar(s));
+        }
         if (KF == KF_POLAR3 || KF == KF_POLAR4) {
           if (k_bulk) bulk_g2s(st + L::k_off, ksrc, k_bulk, full_bar(s));
           if (n_bulk) bulk_g2s(st + L::kn_off, knbase + p0, n_bulk, full_bar(s));
@@ -574,6 +602,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
 #pragma unroll
   for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
   float m_run = -INFINITY, l_run = 0.f;
+  float bias_run[2] = {0.f, 0.f};   // affine values: sum of weight x bias per element group (head g, this lane's positions)
   const int pw = 16 * warp;   // first position of this warp inside a tile
   bool ok = true;
   TQ_STAMP(1);   // consumer: set-up done
@@ -668,7 +697,10 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
 
     // ---------------- softmax (log2 domain) ----------------
     // this thread: head g, positions pw + 8*ng + 2t + c
-    float s2[2][2], s2v[2][2];
+    // s2v: score + log2 of the value row's norm (packed values), so that the f16 weights stay <= 2^8
+    // for any norm; affine values carry their scale on the other operand and use the plain score
+    float s2[2][2], s2v[2][2], vbias[2][2][2];
+    uint32_t vscw[2][2];                       // affine values: (scale group 0, scale group 1) of the position
     float m_tile = -INFINITY;
 #pragma unroll
     for (int ng = 0; ng < 2; ++ng)
@@ -677,10 +709,19 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         const int pos = pw + 8 * ng + 2 * t + c;
         float v = (sc[ng][c] + sc[ng][c + 2]) * tb.k_post;
         if (KF == KF_POLAR3 || KF == KF_POLAR4) v *= lds_f32(st + L::kn_off + pos * 4);
-        const float vn = lds_f32(st + L::vn_off + pos * 4);
         const bool valid = pos < nvp;
         s2[ng][c] = valid ? v : -INFINITY;
-        s2v[ng][c] = valid ? v + lg2(fmaxf(vn, 1e-26f)) : -INFINITY;
+        if (VAFF) {
+          vscw[ng][c] = valid ? lds32(st + L::vn_off + pos * 4) : 0u;   // stale words past the end must not reach the MMA
+          const uint32_t bw = lds32(st + L::vn_off + kTile * 4 + pos * 4);
+          const __half2 vbi = *reinterpret_cast<const __half2*>(&bw);
+          vbias[ng][c][0] = valid ? __low2float(vbi) : 0.f;
+          vbias[ng][c][1] = valid ? __high2float(vbi) : 0.f;
+          s2v[ng][c] = s2[ng][c];
+        } else {
+          const float vn = lds_f32(st + L::vn_off + pos * 4);
+          s2v[ng][c] = valid ? v + lg2(fmaxf(vn, 1e-26f)) : -INFINITY;
+        }
         m_tile = fmaxf(m_tile, s2v[ng][c]);
       }
     m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 1));
@@ -690,6 +731,10 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       const float alpha = need ? (m_run == -INFINITY ? 0.f : ex2(m_run - m_tile)) : 1.f;
       if (need) m_run = m_tile;
       l_run *= alpha;
+      if (VAFF) {
+        bias_run[0] *= alpha;
+        bias_run[1] *= alpha;
+      }
       const float al0 = __shfl_sync(0xffffffffu, alpha, 8 * t);        // head 2t lives in lanes 8t..8t+3
       const float al1 = __shfl_sync(0xffffffffu, alpha, 8 * t + 4);    // head 2t + 1
 #pragma unroll
@@ -704,10 +749,20 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         pv[ng][c] = ex2(s2v[ng][c] - m_use);
-        l_run += ex2(s2[ng][c] - m_use);
+        if (VAFF) {
+          l_run += pv[ng][c];
+          bias_run[0] += pv[ng][c] * vbias[ng][c][0];     // the bias of a group reaches all of its elements alike
+          bias_run[1] += pv[ng][c] * vbias[ng][c][1];
+        } else {
+          l_run += ex2(s2[ng][c] - m_use);
+        }
       }
     const uint32_t pb0 = pack_h2(pv[0][0], pv[0][1]);   // k = 2t, 2t+1      (positions pw + 2t ..)
     const uint32_t pb1 = pack_h2(pv[1][0], pv[1][1]);   // k = 2t+8, 2t+9    (positions pw + 8 + 2t ..)
+    // affine values: this lane's 16 elements lie in group g / 4; its scales for the two position pairs
+    const uint32_t grp_sel = (g >> 2) ? 0x7632u : 0x5410u;
+    const uint32_t vs0 = VAFF ? __byte_perm(vscw[0][0], vscw[0][1], grp_sel) : 0u;
+    const uint32_t vs1 = VAFF ? __byte_perm(vscw[1][0], vscw[1][1], grp_sel) : 0u;
 
     // ---------------- values ----------------
     // positions handled by this thread as MMA k: pw + 2t, +1 and pw + 8 + 2t, +1
@@ -753,6 +808,12 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       af[1] = __byte_perm(lv[0], lv[1], 0x7632);   // element 16g+2j+1, positions 2t, 2t+1
       af[2] = __byte_perm(lv[2], lv[3], 0x5410);   // element 16g+2j,   positions 2t+8, 2t+9
       af[3] = __byte_perm(lv[2], lv[3], 0x7632);
+      if (VAFF) {   // code (exact in f16) x scale of (position, group)
+        af[0] = hmul2_bits(af[0], vs0);
+        af[1] = hmul2_bits(af[1], vs0);
+        af[2] = hmul2_bits(af[2], vs1);
+        af[3] = hmul2_bits(af[3], vs1);
+      }
       mma16816(o[j], af, pb0, pb1);
     }
     __syncwarp();
@@ -766,15 +827,25 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   // after one barrier each thread sums a fixed slice of the 32 accumulator values
   // over the 12 source warps and stores its share of the split's partial state.
   asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");   // every consumer is done with the ring
-  float* xch = reinterpret_cast<float*>(smem + L::stage0);               // [warp][34][32]
+  float* xch = reinterpret_cast<float*>(smem + L::stage0);               // [warp][xch_rows][32]
   {
-    float* dst = xch + warp * 34 * 32 + lane;
+    constexpr int R = L::xch_rows;
+    float* dst = xch + warp * R * 32 + lane;
 #pragma unroll
     for (int j = 0; j < 8; ++j)
 #pragma unroll
       for (int c = 0; c < 4; ++c) dst[(j * 4 + c) * 32] = o[j][c];
     dst[32 * 32] = m_run;
     dst[33 * 32] = l_run;
+    if (VAFF) {   // bias sums of head g, both element groups, summed over the four lanes of the head
+#pragma unroll
+      for (int gi = 0; gi < 2; ++gi) {
+        float bsum = bias_run[gi];
+        bsum += __shfl_xor_sync(0xffffffffu, bsum, 1);
+        bsum += __shfl_xor_sync(0xffffffffu, bsum, 2);
+        dst[(34 + gi) * 32] = bsum;
+      }
+    }
   }
   asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
   TQ_STAMP(24);   // exchange written
@@ -782,13 +853,14 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   const int64_t n_rows = (int64_t)a.batch * a.n_q_heads;
   const int64_t row0 = (int64_t)b * a.n_q_heads + h0;
   {
+    constexpr int R = L::xch_rows;
     // rescale factors of the 12 sources for this thread's two heads (2t, 2t+1)
     float f0[kConsumerWarps], f1[kConsumerWarps];
     float m0 = -INFINITY, m1 = -INFINITY;
 #pragma unroll
     for (int sw = 0; sw < kConsumerWarps; ++sw) {
-      f0[sw] = xch[(sw * 34 + 32) * 32 + 8 * t];        // m of head 2t   (any lane with g == 2t)
-      f1[sw] = xch[(sw * 34 + 32) * 32 + 8 * t + 4];    // m of head 2t+1
+      f0[sw] = xch[(sw * R + 32) * 32 + 8 * t];        // m of head 2t   (any lane with g == 2t)
+      f1[sw] = xch[(sw * R + 32) * 32 + 8 * t + 4];    // m of head 2t+1
       m0 = fmaxf(m0, f0[sw]);
       m1 = fmaxf(m1, f1[sw]);
     }
@@ -796,6 +868,15 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
     for (int sw = 0; sw < kConsumerWarps; ++sw) {
       f0[sw] = f0[sw] == -INFINITY ? 0.f : ex2(f0[sw] - m0);
       f1[sw] = f1[sw] == -INFINITY ? 0.f : ex2(f1[sw] - m1);
+    }
+    // affine values: weighted bias of this lane's element group (g / 4) for its two heads
+    float bias0 = 0.f, bias1 = 0.f;
+    if (VAFF) {
+#pragma unroll
+      for (int sw = 0; sw < kConsumerWarps; ++sw) {
+        bias0 += xch[(sw * R + 34 + (g >> 2)) * 32 + 8 * t] * f0[sw];
+        bias1 += xch[(sw * R + 34 + (g >> 2)) * 32 + 8 * t + 4] * f1[sw];
+      }
     }
     float* acc0 = a.part_acc + ((int64_t)split * n_rows + row0) * kDim;
 #pragma unroll
@@ -806,21 +887,22 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         float v = 0.f;
 #pragma unroll
         for (int sw = 0; sw < kConsumerWarps; ++sw)
-          v += xch[(sw * 34 + k) * 32 + lane] * ((c & 1) ? f1[sw] : f0[sw]);
+          v += xch[(sw * R + k) * 32 + lane] * ((c & 1) ? f1[sw] : f0[sw]);
         const int head = 2 * t + (c & 1);
-        if (head < a.n_rep) acc0[head * kDim + 16 * g + 2 * j + (c >> 1)] = v * tb.v_post;
+        if (head < a.n_rep)
+          acc0[head * kDim + 16 * g + 2 * j + (c >> 1)] = v * tb.v_post + (VAFF ? ((c & 1) ? bias1 : bias0) : 0.f);
       }
     }
     if (warp == kConsumerWarps - 1) {
       // l and m of head g: this lane's own head needs its own factors
       float mg = -INFINITY;
 #pragma unroll
-      for (int sw = 0; sw < kConsumerWarps; ++sw) mg = fmaxf(mg, xch[(sw * 34 + 32) * 32 + lane]);
+      for (int sw = 0; sw < kConsumerWarps; ++sw) mg = fmaxf(mg, xch[(sw * R + 32) * 32 + lane]);
       float lg = 0.f;
 #pragma unroll
       for (int sw = 0; sw < kConsumerWarps; ++sw) {
-        const float ms = xch[(sw * 34 + 32) * 32 + lane];
-        lg += xch[(sw * 34 + 33) * 32 + lane] * (ms == -INFINITY ? 0.f : ex2(ms - mg));
+        const float ms = xch[(sw * R + 32) * 32 + lane];
+        lg += xch[(sw * R + 33) * 32 + lane] * (ms == -INFINITY ? 0.f : ex2(ms - mg));
       }
       lg += __shfl_xor_sync(0xffffffffu, lg, 1);
       lg += __shfl_xor_sync(0xffffffffu, lg, 2);
@@ -908,12 +990,12 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       }
     } else {
       float v[4] = {acc4.x, acc4.y, acc4.z, acc4.w};
-      warp_butterfly<4>(v, lane);
-      const float inv = l_star > 0.f ? (1.0f / kDim) / l_star : 0.f;
+      if (!VAFF) warp_butterfly<4>(v, lane);      // packed values are summed in the rotated domain
+      const float inv = l_star > 0.f ? (VAFF ? 1.0f : 1.0f / kDim) / l_star : 0.f;
       const int64_t ooff = b * tb.out_batch_stride + (int64_t)(h0 + r) * tb.out_head_stride + lane * 4;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float res = v[j] * sign_at(a.v_signs, lane * 4 + j) * inv;
+        const float res = v[j] * (VAFF ? 1.0f : sign_at(a.v_signs, lane * 4 + j)) * inv;
         if (tb.out_dtype == TQ_F32) reinterpret_cast<float*>(tb.out)[ooff + j] = res;
         else if (tb.out_dtype == TQ_F16) reinterpret_cast<__half*>(tb.out)[ooff + j] = __float2half_rn(res);
         else reinterpret_cast<__nv_bfloat16*>(tb.out)[ooff + j] = __float2bfloat16_rn(res);
@@ -1010,9 +1092,20 @@ static int launch_variant(const FlashArgs& a, const MmaTables& tb, int splits, c
 
 bool flash_mma_supported(const FlashArgs& a) {
   if (a.dim != kDim || a.n_rep > 8 || a.mask != nullptr) return false;
-  if (a.v_format != TQ_KV_POLAR || (a.v_bits != 3 && a.v_bits != 4)) return false;
-  if (!aligned16(a.v_data) || a.v_batch_stride % 4 || a.v_head_stride % 4) return false;
-  if (!aligned16(a.v_norms) || a.vn_batch_stride % 4 || a.vn_head_stride % 4) return false;
+  if (a.v_format == TQ_KV_POLAR) {
+    if (a.v_bits != 3 && a.v_bits != 4) return false;
+    if (!aligned16(a.v_data) || a.v_batch_stride % 4 || a.v_head_stride % 4) return false;
+    if (!aligned16(a.v_norms) || a.vn_batch_stride % 4 || a.vn_head_stride % 4) return false;
+  } else if (a.v_format == TQ_KV_AFFINE) {
+    // 4-bit codes, two groups of 64, with fp16 or 8-bit affine keys (the K8 / V4 configuration)
+    if (a.v_bits != 4 || a.v_group != 64) return false;
+    if (a.k_format == TQ_KV_POLAR) return false;
+    if (!aligned16(a.v_data) || a.v_batch_stride % 16 || a.v_head_stride % 16) return false;
+    if (!aligned16(a.v_scales) || !aligned16(a.v_biases) || a.vs_batch_stride % 8 || a.vs_head_stride % 8)
+      return false;
+  } else {
+    return false;
+  }
   if (a.k_format == TQ_KV_DENSE) {
     if (a.k_dtype != TQ_F16) return false;
     if (!aligned16(a.k_data) || a.k_batch_stride % 8 || a.k_head_stride % 8) return false;
@@ -1060,10 +1153,16 @@ int launch_flash_mma(const FlashArgs& a, int splits, const MmaOutput& mo, cudaSt
   tb.om = mo.om;
   tb.ol = mo.ol;
   tb.oacc = mo.oacc;
-  ScaledBook vb;
-  scale_codebook(a.v_cent.v, 1 << a.v_bits, &vb);
-  memcpy(tb.v_c16, vb.c16, sizeof(tb.v_c16));
-  tb.v_post = 1.0f / vb.beta;
+  const bool v_affine = a.v_format == TQ_KV_AFFINE;
+  if (v_affine) {
+    for (int i = 0; i < 16; ++i) tb.v_c16[i] = (uint16_t)(i == 0 ? 0 : __half_as_ushort(__float2half_rn((float)i)));
+    tb.v_post = 1.0f;
+  } else {
+    ScaledBook vb;
+    scale_codebook(a.v_cent.v, 1 << a.v_bits, &vb);
+    memcpy(tb.v_c16, vb.c16, sizeof(tb.v_c16));
+    tb.v_post = 1.0f / vb.beta;
+  }
   tb.k_post = a.attn_scale * kLog2e;
   int kf = KF_DENSE;
   if (a.k_format == TQ_KV_POLAR) {
@@ -1073,6 +1172,9 @@ int launch_flash_mma(const FlashArgs& a, int splits, const MmaOutput& mo, cudaSt
     tb.k_post = a.attn_scale * kLog2e / ((float)kDim * kb.beta);
     kf = a.k_bits == 3 ? KF_POLAR3 : KF_POLAR4;
   }
+  if (v_affine)
+    return a.k_format == TQ_KV_AFFINE ? launch_variant<KF_AFFINE8, 40>(a, tb, splits, st)
+                                      : launch_variant<KF_DENSE, 40>(a, tb, splits, st);
   if (a.k_format == TQ_KV_AFFINE)
     return a.v_bits == 3 ? launch_variant<KF_AFFINE8, 3>(a, tb, splits, st) : launch_variant<KF_AFFINE8, 4>(a, tb, splits, st);
   if (kf == KF_DENSE) return a.v_bits == 3 ? launch_variant<KF_DENSE, 3>(a, tb, splits, st) : launch_variant<KF_DENSE, 4>(a, tb, splits, st);

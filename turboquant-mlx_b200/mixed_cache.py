@@ -14,6 +14,7 @@ from __future__ import annotations
 import torch
 
 from .affine import affine_dequantize, affine_quantize
+from .cache import _zero
 from .kernels import flash_decode
 
 
@@ -75,8 +76,8 @@ class MixedQuantKVCache:
         self.k_codes[:, :, p:p + S], self.k_scales[:, :, p:p + S], self.k_biases[:, :, p:p + S] = kc, ks, kb
         self.v_codes[:, :, p:p + S], self.v_scales[:, :, p:p + S], self.v_biases[:, :, p:p + S] = vc, vs, vb
         self.offset = p + S
-        zk = torch.zeros((1,), dtype=keys.dtype, device=keys.device).expand(B, H, self.offset, dk)
-        zv = torch.zeros((1,), dtype=values.dtype, device=values.device).expand(B, H, self.offset, dv)
+        zk = _zero(keys.dtype, keys.device).expand(B, H, self.offset, dk)
+        zv = _zero(values.dtype, values.device).expand(B, H, self.offset, dv)
         return zk, zv
 
     # ---- attention --------------------------------------------------------------
