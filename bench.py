@@ -590,10 +590,23 @@ def workload_c5(args):
                                         partial_out=(m.view(1, nq), lsum.view(1, nq), acc.view(1, nq, DIM))))
         gm, gl, gacc = partial_views(recvs[l], rows, DIM)
         merges.append(tq.MergePlan(gm, gl, gacc, pq.signs, outs[l]))
+    p2p = world > 1 and args.exchange == "p2p"
+    if p2p:
+        # one exchange object for all layers (two alternating slots), one merge call per slot
+        from turboquant_mlx_b200.distributed import PeerExchange
+        ex = PeerExchange(rows * (DIM + 2), dev)
+        slot_merges = []
+        for slot in range(2):
+            gm, gl, gacc = partial_views(ex.data[slot], rows, DIM)
+            slot_merges.append([tq.MergePlan(gm, gl, gacc, pq.signs, outs[l]) for l in range(layers)])
 
     def step():
         for l in range(layers):
             plans[l].run()
+            if p2p:
+                ex.exchange(sends[l])
+                slot_merges[ex.epoch & 1][l].run()
+                continue
             if world > 1:
                 dist.all_gather_into_tensor(recvs[l].view(-1), sends[l])
             else:
@@ -627,8 +640,17 @@ def workload_c5(args):
         return ms
 
     ms = timed(step, args.steps, max(args.warmup, 3)) / layers
+    if p2p:
+        ex.check()
+        # the same step through the NCCL all-gather, for the record and as a cross-check of the result
+        ref = [o.clone() for o in outs]
+        p2p = False
+        ms_nccl = timed(step, args.steps, 3) / layers
+        p2p = True
+        err = max(float((a.float() - b.float()).abs().max()) for a, b in zip(outs, ref))
     ms_k = timed(kernels_only, args.steps, 3) / layers
-    mode = "eager launches through prepared calls"
+    mode = ("peer-to-peer stores + flags (tq_peer_push / tq_peer_wait)" if p2p else "NCCL all_gather") + \
+        ", eager launches through prepared calls"
     nbytes = nkv * S * (136 + 56)
     peak, kind = measured_peaks()
     if rank == 0:
@@ -637,6 +659,7 @@ def workload_c5(args):
             "scaling": "weak", "us_per_layer_step": ms * 1e3, "us_kernel_only": ms_k * 1e3,
             "per_gpu_frac_of_peak": nbytes / ms / 1e6 / peak, "peak": peak, "peak_kind": kind,
             "tensor_core_path": tq._lib.lib().tq_flash_decode_last_kernel() == 1,
+            **({"us_per_layer_step_nccl": ms_nccl * 1e3, "max_abs_diff_vs_nccl_path": err} if p2p else {}),
             "config": {"workload": "C5 sequence-sharded long-context decode: 64q/8kv, K8 affine + V3 polar, "
                                    "131072 positions per GPU, partial states all-gathered and merged per layer",
                        "context_total": world * S, "bytes_per_gpu_per_layer_step": nbytes,
@@ -658,6 +681,8 @@ def main():
     ap.add_argument("--kernel-only", action="store_true",
                     help="plain launches of the flash-decode kernel only (no graph, no e2e): profiler case")
     ap.add_argument("--ctx", type=int, default=0, help="c4p: prompt length (default 32768)")
+    ap.add_argument("--exchange", default="nccl", choices=["nccl", "p2p"],
+                    help="c5: how the partial states travel between the ranks")
     ap.add_argument("--workload", default="c2", choices=["c2", "c1", "c3", "c5", "c4p", "c4"],
                     help="c2 = the headline benchmark; c1 / c3 = secondary measurements of other configurations")
     args = ap.parse_args()

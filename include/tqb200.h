@@ -264,6 +264,20 @@ int tq_prefill_sdpa(const void* q, const void* k, const void* v, void* out, int 
                     int64_t o_batch_stride, int64_t o_head_stride, int64_t o_row_stride,
                     float attn_scale, int causal, int* status, void* stream);
 
+/* Peer-to-peer exchange of a block between the GPUs of one node (sequence-sharded
+ * decode: the per-rank (m, l, acc) partial states that tq_merge_partials combines).
+ * tq_peer_push copies `nbytes` from `src` to peer_dst[p] for every p (pointers into the
+ * peers' memory as mapped in this process, each the start of the slot that belongs to
+ * the calling rank; one of them is the rank's own buffer) and then stores `epoch` to
+ * peer_flags[p] with release semantics at system scope.  tq_peer_wait returns, in
+ * stream order, once each of the n_ranks 32-bit words at `flags` (this rank's own
+ * flag array) has reached `epoch`; its wait is bounded, and when it gives up it writes
+ * 21 + the missing rank to *status.  The host arrays are read during the call only.
+ * No reference counterpart: the reference runs on one device. */
+int tq_peer_push(const void* src, int64_t nbytes, void* const* peer_dst, void* const* peer_flags,
+                 int n_peers, uint32_t epoch, void* stream);
+int tq_peer_wait(const void* flags, int n_ranks, uint32_t epoch, int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

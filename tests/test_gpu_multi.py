@@ -1,4 +1,4 @@
-"""Two-GPU test of sequence-parallel decode over NCCL (skipped on a one-GPU box).
+"""Two-GPU test of sequence-parallel decode, over NCCL and over peer-to-peer stores (skipped on a one-GPU box).
 Ranks are child processes; each attends over half of the positions and the
 merged result must equal single-GPU decode over the whole sequence."""
 
@@ -42,8 +42,21 @@ out = sequence_parallel_decode(
 torch.cuda.synchronize()
 err = float((out - full).abs().max() / full.abs().max())
 print(f"rank {rank} rel err {err:.3e}")
+# the same exchange through peer-to-peer stores and flags, several rounds (both slots, growing epochs)
+from turboquant_mlx_b200.distributed import PeerExchange
+ex = PeerExchange(B * n_kv * n_rep * (D + 2), dev)
+err2 = 0.0
+for it in range(5):
+    out2 = sequence_parallel_decode(
+        q, k=dict(format="dense", data=kd[:, :, a:b]),
+        v=dict(format="polar", packed=vp[:, :, a:b], norms=vn[:, :, a:b], centroids=pq.centroids, signs=pq.signs, bits=3),
+        attn_scale=scale, out_dtype=torch.float32, exchange=ex)
+    err2 = max(err2, float((out2 - full).abs().max() / full.abs().max()))
+ex.check()
+print(f"rank {rank} peer exchange rel err {err2:.3e}")
+dist.barrier()
 dist.destroy_process_group()
-sys.exit(0 if err < 1e-3 else 1)
+sys.exit(0 if err < 1e-3 and err2 < 1e-3 else 1)
 '''
 
 
@@ -52,7 +65,7 @@ def test_sequence_parallel_decode_two_gpus(tmp_path):
         pytest.skip("needs two GPUs")
     script = tmp_path / "child.py"
     script.write_text(_CHILD)
-    env = dict(os.environ, TQ_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, TQ_ROOT=ROOT, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
            "--master-addr", "127.0.0.1", "--master-port", "29611", str(script)]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)

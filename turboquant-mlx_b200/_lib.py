@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
+from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint32, c_void_p
 
 import torch
 
@@ -90,6 +90,8 @@ _SIGNATURES = {
                                    c_void_p, c_void_p, c_void_p]),
     "tq_affine_dequantize": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,
                                      c_void_p, c_int, c_void_p]),
+    "tq_peer_push": (c_int, [c_void_p, c_int64, POINTER(c_void_p), POINTER(c_void_p), c_int, c_uint32, c_void_p]),
+    "tq_peer_wait": (c_int, [c_void_p, c_int, c_uint32, c_void_p, c_void_p]),
     "tq_prefill_sdpa": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                 c_int64, c_int64, c_int] + [c_int64] * 12 + [c_float, c_int, c_void_p, c_void_p]),
 }

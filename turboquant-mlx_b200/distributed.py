@@ -12,10 +12,13 @@ the merge.  The reference has no multi-device code; this module is new.
 
 from __future__ import annotations
 
+import ctypes
+import os
+
 import torch
 import torch.distributed as dist
 
-from . import kernels
+from . import _lib, kernels
 
 
 def shard_range(n_items: int, world: int, rank: int):
@@ -54,14 +57,76 @@ def gather_partials(send: torch.Tensor, group=None, recv: torch.Tensor | None = 
     return recv
 
 
+class PeerExchange:
+    """All-gather of one flat float32 block per rank through peer-to-peer stores over
+    NVLink instead of a library collective: `tq_peer_push` writes this rank's block into
+    every rank's receive slot and raises a flag there, `tq_peer_wait` lets the stream
+    continue once all ranks' flags show the current epoch.  The buffers are torch
+    symmetric memory (one allocation per rank, mapped into every process of the group);
+    two slots alternate so that a rank that is one exchange ahead never overwrites a
+    block that is still being merged.  All ranks must call `exchange` the same number
+    of times.  Multicast mappings are not used (and switched off before the rendezvous)."""
+
+    def __init__(self, n_floats: int, device, group=None):
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm
+        if n_floats % 4:
+            raise ValueError("the block must be a multiple of 4 floats (16 bytes)")
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.n = n_floats
+        self.device = torch.device(device)
+        self.data = symm.empty((2, self.world, n_floats), dtype=torch.float32, device=self.device)
+        self.flags = symm.empty((2, 64), dtype=torch.int32, device=self.device)
+        self.data.zero_()
+        self.flags.zero_()
+        self._hd = symm.rendezvous(self.data, self.group)
+        self._hf = symm.rendezvous(self.flags, self.group)
+        self.status = torch.zeros((4,), dtype=torch.int32, device=self.device)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)          # every rank's buffers are zeroed before anyone pushes
+        self.epoch = 0
+        vp = ctypes.c_void_p
+        self._dst, self._flg = [], []
+        for slot in range(2):
+            d = (vp * self.world)(*[int(self._hd.buffer_ptrs[p]) + (slot * self.world + self.rank) * n_floats * 4
+                                    for p in range(self.world)])
+            f = (vp * self.world)(*[int(self._hf.buffer_ptrs[p]) + (slot * 64 + self.rank) * 4
+                                    for p in range(self.world)])
+            self._dst.append(d)
+            self._flg.append(f)
+
+    def exchange(self, send: torch.Tensor) -> torch.Tensor:
+        """Push `send` (n_floats,) to all ranks; returns the (world, n_floats) block of this
+        exchange, valid in stream order.  Nothing here synchronises with the host."""
+        if send.numel() != self.n or send.dtype != torch.float32 or not send.is_contiguous():
+            raise ValueError("send must be a contiguous float32 tensor of the size given at construction")
+        self.epoch += 1
+        slot = self.epoch & 1
+        lib, stream = _lib.lib(), _lib.stream_ptr(self.device)
+        _lib.check(lib.tq_peer_push(_lib.ptr(send), self.n * 4, self._dst[slot], self._flg[slot], self.world,
+                                    self.epoch, stream))
+        _lib.check(lib.tq_peer_wait(_lib.ptr(self.flags[slot]), self.world, self.epoch, _lib.ptr(self.status), stream))
+        return self.data[slot]
+
+    def check(self) -> None:
+        """Synchronises; raises if a bounded wait gave up (a rank never pushed)."""
+        code = int(self.status[0].item())
+        if code:
+            raise RuntimeError(f"peer exchange: no block from rank {code - 21} within the wait limit")
+
+
 def sequence_parallel_decode(q, *, k, v, attn_scale: float, group=None, out_dtype=None,
                              q_prerotated: bool = False, mask=None, send_buf=None,
-                             recv_buf=None) -> torch.Tensor:
+                             recv_buf=None, exchange: "PeerExchange | None" = None) -> torch.Tensor:
     """Decode attention with the sequence split across the ranks of `group`.
 
     q (B, n_q, dim) is replicated; `k` / `v` describe this rank's chunk of
     positions (formats as in `kernels.flash_decode`).  Returns (B, n_q, dim) on
-    every rank.  A rank whose chunk is empty passes k = v = None."""
+    every rank.  A rank whose chunk is empty passes k = v = None.  With `exchange`
+    (a PeerExchange sized rows * (dim + 2) floats) the partial states travel by peer
+    stores instead of the all_gather."""
     B, n_q, dim = q.shape
     rows = B * n_q
     dev = q.device
@@ -74,7 +139,7 @@ def sequence_parallel_decode(q, *, k, v, attn_scale: float, group=None, out_dtyp
         kernels.flash_decode(q, k=k, v=v, attn_scale=attn_scale, q_prerotated=q_prerotated, mask=mask,
                              partials=True,
                              partial_out=(m.view(B, n_q), l.view(B, n_q), acc.view(B, n_q, dim)))
-    recv = gather_partials(send_buf, group, recv_buf)
+    recv = exchange.exchange(send_buf) if exchange is not None else gather_partials(send_buf, group, recv_buf)
     gm, gl, gacc = partial_views(recv, rows, dim)
     signs = v["signs"] if (v is not None and v.get("format") == "polar") else None
     out = kernels.merge_partials(gm, gl, gacc, signs, out_dtype or q.dtype)
