@@ -595,6 +595,7 @@ def workload_c5(args):
         # one exchange object for all layers (two alternating slots), one merge call per slot
         from turboquant_mlx_b200.distributed import PeerExchange
         ex = PeerExchange(rows * (DIM + 2), dev)
+        ex_status = tq._lib.ptr(ex.status)
         slot_merges = []
         for slot in range(2):
             gm, gl, gacc = partial_views(ex.data[slot], rows, DIM)
@@ -604,8 +605,8 @@ def workload_c5(args):
         for l in range(layers):
             plans[l].run()
             if p2p:
-                ex.exchange(sends[l])
-                slot_merges[ex.epoch & 1][l].run()
+                _, flags_ptr, epoch = ex.push(sends[l])
+                slot_merges[epoch & 1][l].run_after_peers(flags_ptr, world, epoch, ex_status)
                 continue
             if world > 1:
                 dist.all_gather_into_tensor(recvs[l].view(-1), sends[l])

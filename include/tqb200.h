@@ -277,6 +277,13 @@ int tq_prefill_sdpa(const void* q, const void* k, const void* v, void* out, int 
 int tq_peer_push(const void* src, int64_t nbytes, void* const* peer_dst, void* const* peer_flags,
                  int n_peers, uint32_t epoch, void* stream);
 int tq_peer_wait(const void* flags, int n_ranks, uint32_t epoch, int* status, void* stream);
+/* tq_merge_partials whose kernel first performs tq_peer_wait's bounded wait (one launch
+ * instead of two): the parts were pushed by the peers with tq_peer_push. */
+int tq_merge_partials_after_peers(const void* flags, int n_ranks, uint32_t epoch, int* status,
+                                  const float* part_m, int64_t m_part_stride, const float* part_l,
+                                  int64_t l_part_stride, const float* part_acc, int64_t acc_part_stride,
+                                  int n_parts, int64_t n_rows, int dim, const float* v_signs_host,
+                                  void* out, int out_dtype, int64_t out_row_stride, void* stream);
 
 #ifdef __cplusplus
 }

@@ -52,6 +52,22 @@ for it in range(5):
         v=dict(format="polar", packed=vp[:, :, a:b], norms=vn[:, :, a:b], centroids=pq.centroids, signs=pq.signs, bits=3),
         attn_scale=scale, out_dtype=torch.float32, exchange=ex)
     err2 = max(err2, float((out2 - full).abs().max() / full.abs().max()))
+# push + merge gated inside the merge kernel (one launch less)
+from turboquant_mlx_b200.distributed import partial_buffer, partial_views
+rows = B * n_kv * n_rep
+send = partial_buffer(rows, D, dev)[0]
+m_, l_, acc_ = partial_views(send, rows, D)
+tq.flash_decode(q, k=dict(format="dense", data=kd[:, :, a:b]),
+                v=dict(format="polar", packed=vp[:, :, a:b], norms=vn[:, :, a:b], centroids=pq.centroids,
+                       signs=pq.signs, bits=3),
+                attn_scale=scale, partials=True,
+                partial_out=(m_.view(B, -1), l_.view(B, -1), acc_.view(B, -1, D)))
+out3 = torch.empty((rows, D), dtype=torch.float32, device=dev)
+for it in range(4):
+    block, flags_ptr, epoch = ex.push(send)
+    gm, gl, gacc = partial_views(block, rows, D)
+    tq.MergePlan(gm, gl, gacc, pq.signs, out3).run_after_peers(flags_ptr, world, epoch, tq._lib.ptr(ex.status))
+    err2 = max(err2, float((out3.view(B, -1, D) - full).abs().max() / full.abs().max()))
 ex.check()
 print(f"rank {rank} peer exchange rel err {err2:.3e}")
 dist.barrier()

@@ -90,6 +90,8 @@ _SIGNATURES = {
                                    c_void_p, c_void_p, c_void_p]),
     "tq_affine_dequantize": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,
                                      c_void_p, c_int, c_void_p]),
+    "tq_merge_partials_after_peers": (c_int, [c_void_p, c_int, c_uint32, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int,
+                                  c_int64, c_int, _FP, c_void_p, c_int, c_int64, c_void_p]),
     "tq_peer_push": (c_int, [c_void_p, c_int64, POINTER(c_void_p), POINTER(c_void_p), c_int, c_uint32, c_void_p]),
     "tq_peer_wait": (c_int, [c_void_p, c_int, c_uint32, c_void_p, c_void_p]),
     "tq_prefill_sdpa": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,

@@ -399,23 +399,64 @@ __global__ void merge_partials_kernel(const float* __restrict__ pm, int64_t sm, 
                                       int n_parts, int64_t n_rows,
                                       int dim, int rotate, SignMask signs, int finalize, T* out,
                                       int64_t out_row_stride, int64_t rows_per_batch,
-                                      int64_t out_batch_stride, float* om, float* ol, float* oacc) {
+                                      int64_t out_batch_stride, float* om, float* ol, float* oacc,
+                                      const PeerGate gate) {
   __shared__ float sh[256];
   const int64_t row = blockIdx.x;
   const int e = threadIdx.x;
-  float m_star = -INFINITY;
-  for (int i = 0; i < n_parts; ++i) {
-    const float li = pl[(int64_t)i * sl + row];
-    const float mi = pm[(int64_t)i * sm + row];
-    if (li > 0.f) m_star = fmaxf(m_star, mi);
+  // a decode kernel launched behind this merge with programmatic stream serialization may set up
+  // now; it waits for this grid's completion before it reads the query or touches its workspace
+  if (e == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (gate.flags != nullptr) {
+    // parts pushed by peer GPUs: one thread per rank waits (bounded) for that rank's flag
+    if (e < gate.n) {
+      bool seen = false;
+      for (uint32_t it = 0; it < (1u << 21) && !seen; ++it) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(gate.flags + e) : "memory");
+        seen = (int32_t)(v - gate.epoch) >= 0;
+        if (!seen) __nanosleep(50);
+      }
+      if (!seen) atomicExch(gate.status, 21 + e);
+    }
+    __syncthreads();
   }
+  float m_star = -INFINITY;
   float l_star = 0.f, acc = 0.f;
-  for (int i = 0; i < n_parts; ++i) {
-    const float li = pl[(int64_t)i * sl + row];
-    if (!(li > 0.f)) continue;   // empty or fully masked chunk merges as a no-op
-    const float w = __expf(pm[(int64_t)i * sm + row] - m_star);
-    l_star += li * w;
-    acc += pacc[(int64_t)i * sa + row * dim + e] * w;
+  if (n_parts <= 16) {
+    // few parts (ranks of a node, a handful of chunks): every load is issued before the first use,
+    // so the kernel pays one trip to memory instead of one per part
+    float mi[16], li[16], ai[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const bool on = i < n_parts;
+      li[i] = on ? pl[(int64_t)i * sl + row] : 0.f;
+      mi[i] = on ? pm[(int64_t)i * sm + row] : -INFINITY;
+      ai[i] = on ? pacc[(int64_t)i * sa + row * dim + e] : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (li[i] > 0.f) m_star = fmaxf(m_star, mi[i]);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      if (!(li[i] > 0.f)) continue;   // empty or fully masked chunk merges as a no-op
+      const float w = __expf(mi[i] - m_star);
+      l_star += li[i] * w;
+      acc += ai[i] * w;
+    }
+  } else {
+    for (int i = 0; i < n_parts; ++i) {
+      const float li = pl[(int64_t)i * sl + row];
+      const float mi = pm[(int64_t)i * sm + row];
+      if (li > 0.f) m_star = fmaxf(m_star, mi);
+    }
+    for (int i = 0; i < n_parts; ++i) {
+      const float li = pl[(int64_t)i * sl + row];
+      if (!(li > 0.f)) continue;   // empty or fully masked chunk merges as a no-op
+      const float w = __expf(pm[(int64_t)i * sm + row] - m_star);
+      l_star += li * w;
+      acc += pacc[(int64_t)i * sa + row * dim + e] * w;
+    }
   }
   if (!finalize) {
     oacc[row * dim + e] = acc;
@@ -448,23 +489,25 @@ int launch_merge(const float* pm, int64_t sm, const float* pl, int64_t sl, const
                  int64_t sa, int n_parts, int64_t n_rows,
                  int dim, int rotate, const SignMask& signs, int finalize, void* out, int out_dtype,
                  int64_t out_row_stride, int64_t rows_per_batch, int64_t out_batch_stride,
-                 float* om, float* ol, float* oacc, cudaStream_t st) {
+                 float* om, float* ol, float* oacc, cudaStream_t st, const PeerGate* gate_in) {
   if (n_rows <= 0) return TQ_OK;
+  PeerGate gate = {nullptr, 0, 0u, nullptr};
+  if (gate_in) gate = *gate_in;
   const dim3 grid((unsigned)n_rows), block(dim);
   if (!finalize || out_dtype == TQ_F32)
     merge_partials_kernel<float><<<grid, block, 0, st>>>(pm, sm, pl, sl, pacc, sa, n_parts, n_rows, dim, rotate,
                                                          signs, finalize, (float*)out,
                                                          out_row_stride, rows_per_batch,
-                                                         out_batch_stride, om, ol, oacc);
+                                                         out_batch_stride, om, ol, oacc, gate);
   else if (out_dtype == TQ_F16)
     merge_partials_kernel<__half><<<grid, block, 0, st>>>(pm, sm, pl, sl, pacc, sa, n_parts, n_rows, dim, rotate,
                                                           signs, finalize, (__half*)out,
                                                           out_row_stride, rows_per_batch,
-                                                          out_batch_stride, om, ol, oacc);
+                                                          out_batch_stride, om, ol, oacc, gate);
   else if (out_dtype == TQ_BF16)
     merge_partials_kernel<__nv_bfloat16><<<grid, block, 0, st>>>(
         pm, sm, pl, sl, pacc, sa, n_parts, n_rows, dim, rotate, signs, finalize, (__nv_bfloat16*)out,
-        out_row_stride, rows_per_batch, out_batch_stride, om, ol, oacc);
+        out_row_stride, rows_per_batch, out_batch_stride, om, ol, oacc, gate);
   else
     return set_error(TQ_ERR_BAD_ARG, "unknown dtype %d", out_dtype);
   return check_launch("tq_merge_partials");
@@ -651,6 +694,27 @@ extern "C" int tq_merge_partials(const float* part_m, int64_t m_part_stride, con
   return launch_merge(part_m, m_part_stride, part_l, l_part_stride, part_acc, acc_part_stride,
                       n_parts, n_rows, dim, v_signs_host != nullptr, sg, 1, out, out_dtype,
                       out_row_stride, n_rows, 0, nullptr, nullptr, nullptr, (cudaStream_t)stream);
+}
+
+extern "C" int tq_merge_partials_after_peers(const void* flags, int n_ranks, uint32_t epoch, int* status,
+                                             const float* part_m, int64_t m_part_stride, const float* part_l,
+                                             int64_t l_part_stride, const float* part_acc,
+                                             int64_t acc_part_stride, int n_parts, int64_t n_rows, int dim,
+                                             const float* v_signs_host, void* out, int out_dtype,
+                                             int64_t out_row_stride, void* stream) {
+  TQ_REQUIRE(dim >= 32 && dim <= 256 && !(dim & (dim - 1)), TQ_ERR_BAD_DIM,
+             "dim must be a power of 2 in [32, 256], got %d", dim);
+  TQ_REQUIRE(n_parts > 0 && n_rows >= 0, TQ_ERR_BAD_ARG, "bad part / row count");
+  TQ_REQUIRE(flags && status && n_ranks >= 1 && n_ranks <= dim, TQ_ERR_BAD_ARG, "bad flag array");
+  if (n_rows == 0) return TQ_OK;
+  TQ_REQUIRE(part_m && part_l && part_acc && out, TQ_ERR_BAD_ARG, "NULL tensor pointer");
+  SignMask sg = {};
+  int rc;
+  if (v_signs_host && (rc = make_sign_mask(v_signs_host, dim, &sg))) return rc;
+  const PeerGate gate = {static_cast<const uint32_t*>(flags), n_ranks, epoch, status};
+  return launch_merge(part_m, m_part_stride, part_l, l_part_stride, part_acc, acc_part_stride,
+                      n_parts, n_rows, dim, v_signs_host != nullptr, sg, 1, out, out_dtype,
+                      out_row_stride, n_rows, 0, nullptr, nullptr, nullptr, (cudaStream_t)stream, &gate);
 }
 
 // ---------------------------------------------------------------------------

@@ -72,10 +72,19 @@ int flash_mma_max_splits();
 int flash_mma_level1_parts();
 int launch_flash_mma(const FlashArgs& a, int splits, const MmaOutput& mo, cudaStream_t st);
 
+// Optional gate of a merge: wait (bounded) until `n` flag words have reached `epoch` (the parts
+// were pushed by peer GPUs, see exchange.cu); flags == nullptr: no wait.
+struct PeerGate {
+  const uint32_t* flags;
+  int n;
+  uint32_t epoch;
+  int* status;
+};
+
 int launch_merge(const float* pm, int64_t sm, const float* pl, int64_t sl, const float* pacc,
                  int64_t sa, int n_parts, int64_t n_rows,
                  int dim, int rotate, const SignMask& signs, int finalize, void* out, int out_dtype,
                  int64_t out_row_stride, int64_t rows_per_batch, int64_t out_batch_stride,
-                 float* om, float* ol, float* oacc, cudaStream_t st);
+                 float* om, float* ol, float* oacc, cudaStream_t st, const PeerGate* gate = nullptr);
 
 }  // namespace tq

@@ -110,6 +110,15 @@ class PeerExchange:
         _lib.check(lib.tq_peer_wait(_lib.ptr(self.flags[slot]), self.world, self.epoch, _lib.ptr(self.status), stream))
         return self.data[slot]
 
+    def push(self, send: torch.Tensor):
+        """First half of `exchange`: push only.  Returns (block view, flags pointer, epoch) for a
+        merge that waits inside its own kernel (`MergePlan.run_after_peers`)."""
+        self.epoch += 1
+        slot = self.epoch & 1
+        _lib.check(_lib.lib().tq_peer_push(_lib.ptr(send), self.n * 4, self._dst[slot], self._flg[slot], self.world,
+                                           self.epoch, _lib.stream_ptr(self.device)))
+        return self.data[slot], _lib.ptr(self.flags[slot]), self.epoch
+
     def check(self) -> None:
         """Synchronises; raises if a bounded wait gave up (a rank never pushed)."""
         code = int(self.status[0].item())

@@ -461,6 +461,14 @@ class MergePlan:
             _lib.check(rc)
         return self.result
 
+    def run_after_peers(self, flags_ptr, n_ranks: int, epoch: int, status_ptr):
+        """The same merge, gated inside the kernel on the peers' flags (see PeerExchange)."""
+        rc = _lib.lib().tq_merge_partials_after_peers(flags_ptr, n_ranks, epoch, status_ptr, *self._args,
+                                                      _lib.stream_ptr(self._dev))
+        if rc:
+            _lib.check(rc)
+        return self.result
+
 
 # ---------------------------------------------------------------------------
 # prefill attention (dense 16-bit Q, K, V on the tcgen05 tensor cores)
