@@ -546,8 +546,9 @@ def workload_c4(args):
 def workload_c5(args):
     """Config 5: long-context decode, Llama-3-70B attention shape (64 q / 8 kv heads, d 128), K 8-bit
     group-affine + V PolarQuant 3-bit, the sequence split across the ranks: 131072 positions per GPU
-    (1M tokens at 8 GPUs).  Every rank attends over its chunk, the (m, l, acc) partial states are
-    all-gathered through NCCL (33 KB per rank) and merged locally.  201.3 MB of KV per GPU per layer-step."""
+    (1M tokens at 8 GPUs).  Every rank attends over its chunk, the (m, l, acc) partial states (33 KB per rank)
+    reach every rank by peer-to-peer stores over NVLink (--exchange p2p, default; the NCCL all-gather is timed
+    beside it) and are merged locally.  201.3 MB of KV per GPU per layer-step."""
     import torch
     import torch.distributed as dist
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -682,7 +683,7 @@ def main():
     ap.add_argument("--kernel-only", action="store_true",
                     help="plain launches of the flash-decode kernel only (no graph, no e2e): profiler case")
     ap.add_argument("--ctx", type=int, default=0, help="c4p: prompt length (default 32768)")
-    ap.add_argument("--exchange", default="nccl", choices=["nccl", "p2p"],
+    ap.add_argument("--exchange", default="p2p", choices=["nccl", "p2p"],
                     help="c5: how the partial states travel between the ranks")
     ap.add_argument("--workload", default="c2", choices=["c2", "c1", "c3", "c5", "c4p", "c4"],
                     help="c2 = the headline benchmark; c1 / c3 = secondary measurements of other configurations")
