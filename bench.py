@@ -595,7 +595,15 @@ def workload_c5(args):
     if p2p:
         # one exchange object for all layers (two alternating slots), one merge call per slot
         from turboquant_mlx_b200.distributed import PeerExchange
-        ex = PeerExchange(rows * (DIM + 2), dev)
+        ex, note = None, ""
+        try:
+            ex = PeerExchange(rows * (DIM + 2), dev)
+        except Exception as exc:      # symmetric memory not available here: every rank falls back together
+            note = f"peer exchange unavailable ({type(exc).__name__}), NCCL all-gather used"
+        agreed = torch.tensor([1 if ex is not None else 0], device=dev)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+        p2p = bool(agreed.item())
+    if p2p:
         ex_status = tq._lib.ptr(ex.status)
         slot_merges = []
         for slot in range(2):
