@@ -591,7 +591,7 @@ def workload_c5(args):
                                         partial_out=(m.view(1, nq), lsum.view(1, nq), acc.view(1, nq, DIM))))
         gm, gl, gacc = partial_views(recvs[l], rows, DIM)
         merges.append(tq.MergePlan(gm, gl, gacc, pq.signs, outs[l]))
-    p2p = world > 1 and args.exchange == "p2p"
+    p2p = world > 1 and args.exchange in ("p2p", "fused")
     if p2p:
         # one exchange object for all layers (two alternating slots), one merge call per slot
         from turboquant_mlx_b200.distributed import PeerExchange
@@ -603,15 +603,32 @@ def workload_c5(args):
         agreed = torch.tensor([1 if ex is not None else 0], device=dev)
         dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
         p2p = bool(agreed.item())
+    fused = p2p and args.exchange == "fused" and world <= 8
     if p2p:
         ex_status = tq._lib.ptr(ex.status)
         slot_merges = []
         for slot in range(2):
             gm, gl, gacc = partial_views(ex.data[slot], rows, DIM)
             slot_merges.append([tq.MergePlan(gm, gl, gacc, pq.signs, outs[l]) for l in range(layers)])
+    if fused:
+        # the decode kernel's final step stores the merged state into every rank's slot itself
+        slot_plans = []
+        for slot in range(2):
+            tg = ex.targets(slot, rows, DIM)
+            slot_plans.append([])
+            for l in range(layers):
+                m, lsum, acc = partial_views(sends[l], rows, DIM)
+                slot_plans[slot].append(tq.FlashDecodePlan(
+                    q[l], k=ks[l], v=vs[l], attn_scale=scale, partials=True, peers=tg,
+                    partial_out=(m.view(1, nq), lsum.view(1, nq), acc.view(1, nq, DIM))))
 
     def step():
         for l in range(layers):
+            if fused:
+                slot, _, flags_ptr, want = ex.next_fused(nkv)
+                slot_plans[slot][l].run()
+                slot_merges[slot][l].run_after_peers(flags_ptr, world, want, ex_status)
+                continue
             plans[l].run()
             if p2p:
                 _, flags_ptr, epoch = ex.push(sends[l])
@@ -654,12 +671,13 @@ def workload_c5(args):
         ex.check()
         # the same step through the NCCL all-gather, for the record and as a cross-check of the result
         ref = [o.clone() for o in outs]
-        p2p = False
+        was_fused, p2p, fused = fused, False, False
         ms_nccl = timed(step, args.steps, 3) / layers
-        p2p = True
+        p2p, fused = True, was_fused
         err = max(float((a.float() - b.float()).abs().max()) for a, b in zip(outs, ref))
     ms_k = timed(kernels_only, args.steps, 3) / layers
-    mode = ("peer-to-peer stores + flags (tq_peer_push / tq_peer_wait)" if p2p else "NCCL all_gather") + \
+    mode = ("peer stores from the decode kernel's final step + gated merge" if fused else
+            "peer-to-peer stores + flags (tq_peer_push, gated merge)" if p2p else "NCCL all_gather") + \
         ", eager launches through prepared calls"
     nbytes = nkv * S * (136 + 56)
     peak, kind = measured_peaks()
@@ -691,7 +709,7 @@ def main():
     ap.add_argument("--kernel-only", action="store_true",
                     help="plain launches of the flash-decode kernel only (no graph, no e2e): profiler case")
     ap.add_argument("--ctx", type=int, default=0, help="c4p: prompt length (default 32768)")
-    ap.add_argument("--exchange", default="p2p", choices=["nccl", "p2p"],
+    ap.add_argument("--exchange", default="fused", choices=["nccl", "p2p", "fused"],
                     help="c5: how the partial states travel between the ranks")
     ap.add_argument("--workload", default="c2", choices=["c2", "c1", "c3", "c5", "c4p", "c4"],
                     help="c2 = the headline benchmark; c1 / c3 = secondary measurements of other configurations")

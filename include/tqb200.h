@@ -200,6 +200,18 @@ typedef struct tq_flash_params {
   float* part_l;               /* mode 1: (batch * n_q_heads) */
   float* part_acc;             /* mode 1: (batch * n_q_heads, dim), before the butterfly */
   void* stream;
+  /* mode 1, optional (n_peers 0: off; tensor-core path only): the CTA that completes a (batch, kv head)
+   * group also stores its rows of the merged state into each peer_m / peer_l / peer_acc [p] (same row
+   * layout as part_*; pointers into other GPUs' memory as mapped in this process, or this GPU's own)
+   * and then adds 1 to *peer_counter[p] with release semantics at system scope: after
+   * batch * n_kv_heads additions all rows are in place (sequence-sharded decode: the push of
+   * tq_peer_push done by the decode kernel itself).  No reference counterpart. */
+  int32_t n_peers;             /* 0 .. 8 */
+  int32_t peer_reserved;
+  float* peer_m[8];
+  float* peer_l[8];
+  float* peer_acc[8];
+  uint32_t* peer_counter[8];
 } tq_flash_params;
 
 /* Workspace contract: 16-byte aligned, at least tq_flash_decode_workspace_bytes()

@@ -69,6 +69,21 @@ for it in range(4):
     tq.MergePlan(gm, gl, gacc, pq.signs, out3).run_after_peers(flags_ptr, world, epoch, tq._lib.ptr(ex.status))
     err2 = max(err2, float((out3.view(B, -1, D) - full).abs().max() / full.abs().max()))
 ex.check()
+# the push done by the decode kernel's own final step (peer stores + counters), merge gated as above
+ex2 = PeerExchange(rows * (D + 2), dev)
+for it in range(4):
+    slot, block, flags_ptr, want = ex2.next_fused(B * n_kv)
+    tq.flash_decode(q, k=dict(format="dense", data=kd[:, :, a:b]),
+                    v=dict(format="polar", packed=vp[:, :, a:b], norms=vn[:, :, a:b], centroids=pq.centroids,
+                           signs=pq.signs, bits=3),
+                    attn_scale=scale, partials=True, peers=ex2.targets(slot, rows, D),
+                    partial_out=(m_.view(B, -1), l_.view(B, -1), acc_.view(B, -1, D)))
+    assert tq._lib.lib().tq_flash_decode_last_kernel() == 1
+    gm, gl, gacc = partial_views(block, rows, D)
+    out4 = torch.empty((rows, D), dtype=torch.float32, device=dev)
+    tq.MergePlan(gm, gl, gacc, pq.signs, out4).run_after_peers(flags_ptr, world, want, tq._lib.ptr(ex2.status))
+    err2 = max(err2, float((out4.view(B, -1, D) - full).abs().max() / full.abs().max()))
+ex2.check()
 print(f"rank {rank} peer exchange rel err {err2:.3e}")
 dist.barrier()
 dist.destroy_process_group()

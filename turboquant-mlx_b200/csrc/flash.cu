@@ -27,6 +27,12 @@ static int validate(const tq_flash_params* p) {
              "n_q_heads (%d) must equal n_kv_heads (%d) * n_rep", p->n_q_heads, p->n_kv_heads);
   TQ_REQUIRE(p->seq_len > 0, TQ_ERR_BAD_ARG, "seq_len must be positive, got %lld",
              (long long)p->seq_len);
+  TQ_REQUIRE(p->n_peers >= 0 && p->n_peers <= 8, TQ_ERR_BAD_ARG, "n_peers must be 0..8, got %d", p->n_peers);
+  TQ_REQUIRE(p->n_peers == 0 || p->out_mode == 1, TQ_ERR_BAD_ARG, "peer targets need out_mode 1");
+  for (int i = 0; i < p->n_peers; ++i)
+    TQ_REQUIRE(p->peer_m[i] && p->peer_l[i] && p->peer_acc[i] && p->peer_counter[i] &&
+                   (reinterpret_cast<uintptr_t>(p->peer_acc[i]) & 15) == 0,
+               TQ_ERR_BAD_ARG, "peer %d: NULL or misaligned target", i);
   TQ_REQUIRE(p->q_dtype >= TQ_F32 && p->q_dtype <= TQ_BF16, TQ_ERR_BAD_ARG, "bad q_dtype");
   switch (p->k_format) {
     case TQ_KV_POLAR:
@@ -245,8 +251,16 @@ extern "C" int tq_flash_decode(const tq_flash_params* p) {
     mo.l1_m = l1_m;
     mo.l1_l = l1_l;
     mo.l1_acc = l1_acc;
+    mo.n_peers = p->out_mode == 1 ? p->n_peers : 0;
+    for (int i = 0; i < 8; ++i) {
+      mo.peer_m[i] = p->peer_m[i];
+      mo.peer_l[i] = p->peer_l[i];
+      mo.peer_acc[i] = p->peer_acc[i];
+      mo.peer_counter[i] = p->peer_counter[i];
+    }
     return launch_flash_mma(a, plan.splits, mo, st);
   }
+  TQ_REQUIRE(p->n_peers == 0, TQ_ERR_UNSUPPORTED, "peer targets need the tensor-core decode path");
   rc = launch_flash_generic(a, plan.splits, st);
   if (rc) return rc;
   if (direct) return TQ_OK;

@@ -66,6 +66,11 @@ struct MmaOutput {       // where the tensor-core kernel's fused merge writes
   float* l1_m;           // level-1 partials: flash_mma_level1_parts() x rows [x dim]
   float* l1_l;
   float* l1_acc;
+  int n_peers;           // out_mode 1: peers that also receive the merged state (0: none)
+  float* peer_m[8];
+  float* peer_l[8];
+  float* peer_acc[8];
+  uint32_t* peer_counter[8];
 };
 int64_t flash_mma_header_bytes(int batch, int n_kv_heads);
 int flash_mma_max_splits();

@@ -69,6 +69,11 @@ struct MmaTables {
   float* om;            // merged partial outputs (out_mode 1)
   float* ol;
   float* oacc;
+  int n_peers;          // out_mode 1: the merged state also goes to these peers (other GPUs' memory)
+  float* peer_m[8];
+  float* peer_l[8];
+  float* peer_acc[8];
+  uint32_t* peer_counter[8];
 };
 
 template <int KF> struct KGeom;
@@ -988,6 +993,16 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         tb.om[row] = m_star;
         tb.ol[row] = l_star;
       }
+#pragma unroll
+      for (int p = 0; p < 8; ++p) {               // plain peer stores over NVLink (static indices: no local copy)
+        if (p < tb.n_peers) {
+          reinterpret_cast<float4*>(tb.peer_acc[p] + row * kDim)[lane] = acc4;
+          if (lane == 0) {
+            tb.peer_m[p][row] = m_star;
+            tb.peer_l[p][row] = l_star;
+          }
+        }
+      }
     } else {
       float v[4] = {acc4.x, acc4.y, acc4.z, acc4.w};
       if (!VAFF) warp_butterfly<4>(v, lane);      // packed values are summed in the rotated domain
@@ -1000,6 +1015,17 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         else if (tb.out_dtype == TQ_F16) reinterpret_cast<__half*>(tb.out)[ooff + j] = __float2half_rn(res);
         else reinterpret_cast<__nv_bfloat16*>(tb.out)[ooff + j] = __float2bfloat16_rn(res);
       }
+    }
+  }
+  if (tb.out_mode == 1 && tb.n_peers > 0) {
+    // every row of this (batch, kv head) group is on its way: one thread fences at system scope (the
+    // barrier makes the other threads' stores precede it) and tells each peer
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+    if (tid == 0) {
+      __threadfence_system();
+#pragma unroll
+      for (int p = 0; p < 8; ++p)
+        if (p < tb.n_peers) atomicAdd_system(tb.peer_counter[p], 1u);
     }
   }
   TQ_STAMP(23);   // final merge done
@@ -1153,6 +1179,13 @@ int launch_flash_mma(const FlashArgs& a, int splits, const MmaOutput& mo, cudaSt
   tb.om = mo.om;
   tb.ol = mo.ol;
   tb.oacc = mo.oacc;
+  tb.n_peers = mo.n_peers;
+  for (int i = 0; i < 8; ++i) {
+    tb.peer_m[i] = mo.peer_m[i];
+    tb.peer_l[i] = mo.peer_l[i];
+    tb.peer_acc[i] = mo.peer_acc[i];
+    tb.peer_counter[i] = mo.peer_counter[i];
+  }
   const bool v_affine = a.v_format == TQ_KV_AFFINE;
   if (v_affine) {
     for (int i = 0; i < 16; ++i) tb.v_c16[i] = (uint16_t)(i == 0 ? 0 : __half_as_ushort(__float2half_rn((float)i)));

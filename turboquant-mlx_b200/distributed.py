@@ -87,6 +87,7 @@ class PeerExchange:
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)          # every rank's buffers are zeroed before anyone pushes
         self.epoch = 0
+        self._slot_uses = [0, 0]
         vp = ctypes.c_void_p
         self._dst, self._flg = [], []
         for slot in range(2):
@@ -118,6 +119,27 @@ class PeerExchange:
         _lib.check(_lib.lib().tq_peer_push(_lib.ptr(send), self.n * 4, self._dst[slot], self._flg[slot], self.world,
                                            self.epoch, _lib.stream_ptr(self.device)))
         return self.data[slot], _lib.ptr(self.flags[slot]), self.epoch
+
+    # ---- push done by the decode kernel itself -------------------------------------------------
+    def targets(self, slot: int, rows: int, dim: int) -> dict:
+        """Peer addresses of this rank's block in `slot` for `flash_decode(..., peers=...)`: the block
+        is laid out [m (rows) | l (rows) | acc (rows * dim)] as in `partial_buffer`.  The decode
+        kernel adds 1 to every rank's flag word per (batch, kv head) group it completes, so an
+        exchange object must be used either this way or through `push` / `exchange`, not both."""
+        if rows * (dim + 2) != self.n:
+            raise ValueError("rows * (dim + 2) must equal the block size given at construction")
+        base = [int(self._hd.buffer_ptrs[p]) + (slot * self.world + self.rank) * self.n * 4 for p in range(self.world)]
+        return dict(m=base, l=[b + rows * 4 for b in base], acc=[b + 2 * rows * 4 for b in base],
+                    counter=[int(self._hf.buffer_ptrs[p]) + (slot * 64 + self.rank) * 4 for p in range(self.world)])
+
+    def next_fused(self, groups: int):
+        """Bookkeeping of one exchange whose push is done by the decode kernel: returns (slot, block
+        view, flags pointer, counter value to wait for).  `groups` = batch * n_kv_heads additions
+        arrive from every rank per exchange."""
+        self.epoch += 1
+        slot = self.epoch & 1
+        self._slot_uses[slot] += 1
+        return slot, self.data[slot], _lib.ptr(self.flags[slot]), self._slot_uses[slot] * groups
 
     def check(self) -> None:
         """Synchronises; raises if a bounded wait gave up (a rank never pushed)."""

@@ -227,7 +227,7 @@ def _strides3(t: torch.Tensor, batched: bool):
 
 def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerotated: bool = False,
                  mask: torch.Tensor | None = None, num_splits: int = 0, out_dtype=None,
-                 partials: bool = False, partial_out=None, kv_stable: bool = False, out=None,
+                 partials: bool = False, partial_out=None, kv_stable: bool = False, out=None, peers=None,
                  _prepare_only: bool = False):
     """Split-K flash decoding for one query token per sequence.
 
@@ -243,7 +243,9 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
     q.dtype), or with partials=True the merged state (m (B, n_q), l (B, n_q),
     acc (B, n_q, dim)) before the final butterfly / normalisation; `partial_out`
     optionally names the three tensors to write (e.g. slices of a send buffer).
-    `out` optionally names the (B, n_q, dim) tensor to write.  kv_stable=True promises that the kernel launched just before this call on the
+    `out` optionally names the (B, n_q, dim) tensor to write.  `peers` (partials only, see
+    distributed.PeerExchange.targets) makes the kernel also store the merged state into the
+    given peer buffers and bump their counters.  kv_stable=True promises that the kernel launched just before this call on the
     stream does not write any K / V row this call reads (e.g. the new token was
     appended earlier), which lets the kernel prefetch K / V while that kernel drains.
     """
@@ -350,6 +352,14 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
             pl = torch.empty((B, n_q), dtype=torch.float32, device=dev)
             pa = torch.empty((B, n_q, dim), dtype=torch.float32, device=dev)
         P.part_m, P.part_l, P.part_acc = pm.data_ptr(), pl.data_ptr(), pa.data_ptr()
+        if peers is not None:           # the merged state also goes to these (peer GPU) addresses
+            n_peers = len(peers["acc"])
+            if not (1 <= n_peers <= 8) or any(len(peers[key]) != n_peers for key in ("m", "l", "counter")):
+                raise ValueError("peers: 1..8 entries in each of m, l, acc, counter")
+            P.n_peers = n_peers
+            for i in range(n_peers):
+                P.peer_m[i], P.peer_l[i] = int(peers["m"][i]), int(peers["l"][i])
+                P.peer_acc[i], P.peer_counter[i] = int(peers["acc"][i]), int(peers["counter"][i])
     else:
         P.out_mode = 0
         if out is None:
