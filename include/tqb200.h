@@ -254,6 +254,11 @@ int tq_merge_partials(const float* part_m, int64_t m_part_stride, const float* p
  * byte, low nibble first. */
 int tq_affine_quantize(const void* x, int x_dtype, int64_t n_rows, int dim, int group, int bits,
                        uint8_t* codes, void* scales_f16, void* biases_f16, void* stream);
+/* The same with row strides (elements of x; bytes of codes; halfs of scales / biases), so that the
+ * rows of one decode step go straight into their places in a pre-sized cache. */
+int tq_affine_quantize_rows(const void* x, int x_dtype, int64_t n_rows, int dim, int group, int bits,
+                            int64_t x_row_stride, uint8_t* codes, int64_t codes_row_stride,
+                            void* scales_f16, void* biases_f16, int64_t sb_row_stride, void* stream);
 int tq_affine_dequantize(const uint8_t* codes, const void* scales_f16, const void* biases_f16,
                          int64_t n_rows, int dim, int group, int bits, void* out, int out_dtype,
                          void* stream);

@@ -196,3 +196,25 @@ def test_adaptive_cache_layout(tq):
     assert len(caches) == 12
     assert all(isinstance(c, KVCache) for c in caches[:2] + caches[-2:])
     assert all(isinstance(c, tq.TurboQuantKVCache) for c in caches[2:-2])
+
+
+def test_mixed_cache_single_step_append_matches_bulk(tq, dev):
+    """One-token appends go straight into the storage rows (strided quantize); the stored codes,
+    scales and biases must equal those of a bulk append of the same rows."""
+    g = torch.Generator(device=dev).manual_seed(4)
+    B, H, D = 2, 3, 128
+    k = torch.randn((B, H, 7, D), generator=g, device=dev).half()
+    v = (torch.randn((B, H, 7, D), generator=g, device=dev) * 2 + 1).half()
+    bulk = tq.MixedQuantKVCache(8, 4, 64)
+    bulk.update_and_fetch(k, v)
+    step = tq.MixedQuantKVCache(8, 4, 64)
+    step.update_and_fetch(k[:, :, :3], v[:, :, :3])
+    for i in range(3, 7):
+        # the layout a model produces: (B, 1, H, D) transposed to (B, H, 1, D)
+        ki = k[:, :, i:i + 1].transpose(1, 2).contiguous().transpose(1, 2)
+        vi = v[:, :, i:i + 1].transpose(1, 2).contiguous().transpose(1, 2)
+        zk, zv = step.update_and_fetch(ki, vi)
+        assert zk.shape == (B, H, i + 1, D) and zv.shape == (B, H, i + 1, D)
+    assert step.offset == bulk.offset == 7
+    for name in ("k_codes", "k_scales", "k_biases", "v_codes", "v_scales", "v_biases"):
+        assert torch.equal(getattr(step, name)[:, :, :7], getattr(bulk, name)[:, :, :7]), name

@@ -32,6 +32,23 @@ def affine_quantize(x: torch.Tensor, group: int = 64, bits: int = 8):
             biases.reshape(*lead, dim // group))
 
 
+def affine_quantize_rows_into(x: torch.Tensor, codes: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor,
+                              group: int, bits: int) -> bool:
+    """Quantize the rows of x (n, dim) straight into codes / scales / biases (n, width), views whose
+    rows may be far apart (one decode step's rows inside a pre-sized cache).  Returns False, writing
+    nothing, when a view does not have unit-stride rows at one uniform row distance."""
+    for t in (x, codes, scales, biases):
+        if t.ndim != 2 or t.stride(1) != 1:
+            return False
+    if scales.stride(0) != biases.stride(0) or not x.is_cuda:
+        return False
+    n, dim = x.shape
+    _lib.check(_lib.lib().tq_affine_quantize_rows(
+        _lib.ptr(x), _lib.dtype_code(x.dtype), n, dim, group, bits, x.stride(0), _lib.ptr(codes), codes.stride(0),
+        _lib.ptr(scales), _lib.ptr(biases), scales.stride(0), _lib.stream_ptr(x.device)))
+    return True
+
+
 def affine_dequantize(codes, scales, biases, group: int = 64, bits: int = 8,
                       dtype=torch.float16) -> torch.Tensor:
     _lib.require_cuda(codes, scales, biases)

@@ -9,14 +9,17 @@ template <typename T, int EPG>
 __global__ void __launch_bounds__(256)
 affine_quantize_kernel(const T* __restrict__ x, int64_t n_groups, int bits,
                        uint8_t* __restrict__ codes, __half* __restrict__ scales,
-                       __half* __restrict__ biases) {
+                       __half* __restrict__ biases, int gpr /* groups per row */, int64_t x_row_stride,
+                       int64_t codes_row_stride /* bytes */, int64_t sb_row_stride) {
   constexpr int GROUP = EPG * 32;
   const int lane = threadIdx.x & 31;
   const int64_t warp_global = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   const int64_t warp_stride = (int64_t)gridDim.x * 8;
   const float qmax = (float)((1 << bits) - 1);
   for (int64_t g = warp_global; g < n_groups; g += warp_stride) {
-    const T* src = x + g * GROUP + lane * EPG;
+    const int64_t row = g / gpr;
+    const int gi = (int)(g - row * gpr);
+    const T* src = x + row * x_row_stride + gi * GROUP + lane * EPG;
     float v[EPG];
     float lo = INFINITY, hi = -INFINITY;
 #pragma unroll
@@ -40,11 +43,11 @@ affine_quantize_kernel(const T* __restrict__ x, int64_t n_groups, int bits,
       code[j] = (int)fminf(fmaxf(c, 0.f), qmax);
     }
     if (bits == 8) {
-      uint8_t* dst = codes + g * GROUP + lane * EPG;
+      uint8_t* dst = codes + row * codes_row_stride + gi * GROUP + lane * EPG;
 #pragma unroll
       for (int j = 0; j < EPG; ++j) dst[j] = (uint8_t)code[j];
     } else {  // 4-bit: two codes per byte, low nibble first
-      uint8_t* dst = codes + (g * GROUP + lane * EPG) / 2;
+      uint8_t* dst = codes + row * codes_row_stride + (gi * GROUP + lane * EPG) / 2;
       if (EPG == 1) {
         const int other = __shfl_xor_sync(0xffffffffu, code[0], 1);
         if ((lane & 1) == 0) dst[0] = (uint8_t)(code[0] | (other << 4));
@@ -54,8 +57,8 @@ affine_quantize_kernel(const T* __restrict__ x, int64_t n_groups, int bits,
       }
     }
     if (lane == 0) {
-      scales[g] = sc_h;
-      biases[g] = bi_h;
+      scales[row * sb_row_stride + gi] = sc_h;
+      biases[row * sb_row_stride + gi] = bi_h;
     }
   }
 }
@@ -75,15 +78,15 @@ __global__ void affine_dequantize_kernel(const uint8_t* __restrict__ codes,
 
 template <typename T>
 static int launch_affine_q(const void* x, int64_t n_groups, int group, int bits, uint8_t* codes,
-                           void* sc, void* bi, cudaStream_t st) {
+                           void* sc, void* bi, int gpr, int64_t xs, int64_t cs, int64_t ss, cudaStream_t st) {
   int64_t blocks = (n_groups + 7) / 8;
   const int64_t cap = (int64_t)num_sms() * 8;
   const int grid = (int)(blocks > cap ? cap : blocks);
   const T* xt = reinterpret_cast<const T*>(x);
   switch (group) {
-    case 32: affine_quantize_kernel<T, 1><<<grid, 256, 0, st>>>(xt, n_groups, bits, codes, (__half*)sc, (__half*)bi); break;
-    case 64: affine_quantize_kernel<T, 2><<<grid, 256, 0, st>>>(xt, n_groups, bits, codes, (__half*)sc, (__half*)bi); break;
-    default: affine_quantize_kernel<T, 4><<<grid, 256, 0, st>>>(xt, n_groups, bits, codes, (__half*)sc, (__half*)bi); break;
+    case 32: affine_quantize_kernel<T, 1><<<grid, 256, 0, st>>>(xt, n_groups, bits, codes, (__half*)sc, (__half*)bi, gpr, xs, cs, ss); break;
+    case 64: affine_quantize_kernel<T, 2><<<grid, 256, 0, st>>>(xt, n_groups, bits, codes, (__half*)sc, (__half*)bi, gpr, xs, cs, ss); break;
+    default: affine_quantize_kernel<T, 4><<<grid, 256, 0, st>>>(xt, n_groups, bits, codes, (__half*)sc, (__half*)bi, gpr, xs, cs, ss); break;
   }
   return check_launch("tq_affine_quantize");
 }
@@ -100,21 +103,39 @@ static int affine_check(int dim, int group, int bits) {
   return TQ_OK;
 }
 
+extern "C" int tq_affine_quantize_rows(const void* x, int x_dtype, int64_t n_rows, int dim, int group,
+                                       int bits, int64_t x_row_stride, uint8_t* codes, int64_t codes_row_stride,
+                                       void* scales_f16, void* biases_f16, int64_t sb_row_stride, void* stream) {
+  int rc = affine_check(dim, group, bits);
+  if (rc) return rc;
+  if (n_rows <= 0) return TQ_OK;
+  TQ_REQUIRE(x && codes && scales_f16 && biases_f16, TQ_ERR_BAD_ARG, "NULL tensor pointer");
+  const int gpr = dim / group;
+  TQ_REQUIRE(x_row_stride >= dim && codes_row_stride >= (bits == 8 ? dim : dim / 2) && sb_row_stride >= gpr,
+             TQ_ERR_BAD_ARG, "row strides shorter than a row");
+  const int64_t n_groups = n_rows * gpr;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (x_dtype) {
+    case TQ_F32:
+      return launch_affine_q<float>(x, n_groups, group, bits, codes, scales_f16, biases_f16, gpr, x_row_stride,
+                                    codes_row_stride, sb_row_stride, st);
+    case TQ_F16:
+      return launch_affine_q<__half>(x, n_groups, group, bits, codes, scales_f16, biases_f16, gpr, x_row_stride,
+                                     codes_row_stride, sb_row_stride, st);
+    case TQ_BF16:
+      return launch_affine_q<__nv_bfloat16>(x, n_groups, group, bits, codes, scales_f16, biases_f16, gpr,
+                                            x_row_stride, codes_row_stride, sb_row_stride, st);
+    default: return set_error(TQ_ERR_BAD_ARG, "unknown dtype %d", x_dtype);
+  }
+}
+
 extern "C" int tq_affine_quantize(const void* x, int x_dtype, int64_t n_rows, int dim, int group,
                                   int bits, uint8_t* codes, void* scales_f16, void* biases_f16,
                                   void* stream) {
   int rc = affine_check(dim, group, bits);
   if (rc) return rc;
-  if (n_rows <= 0) return TQ_OK;
-  TQ_REQUIRE(x && codes && scales_f16 && biases_f16, TQ_ERR_BAD_ARG, "NULL tensor pointer");
-  const int64_t n_groups = n_rows * (dim / group);
-  cudaStream_t st = (cudaStream_t)stream;
-  switch (x_dtype) {
-    case TQ_F32: return launch_affine_q<float>(x, n_groups, group, bits, codes, scales_f16, biases_f16, st);
-    case TQ_F16: return launch_affine_q<__half>(x, n_groups, group, bits, codes, scales_f16, biases_f16, st);
-    case TQ_BF16: return launch_affine_q<__nv_bfloat16>(x, n_groups, group, bits, codes, scales_f16, biases_f16, st);
-    default: return set_error(TQ_ERR_BAD_ARG, "unknown dtype %d", x_dtype);
-  }
+  return tq_affine_quantize_rows(x, x_dtype, n_rows, dim, group, bits, dim, codes, bits == 8 ? dim : dim / 2,
+                                 scales_f16, biases_f16, dim / group, stream);
 }
 
 extern "C" int tq_affine_dequantize(const uint8_t* codes, const void* scales_f16,

@@ -18,6 +18,11 @@ from .cache import _zero
 from .kernels import flash_decode
 
 
+def H_stride_zero(rows_view) -> bool:
+    """A (B * H, W) row view whose rows coincide (broadcast input): not a valid source."""
+    return rows_view.shape[0] > 1 and rows_view.stride(0) == 0
+
+
 class MixedQuantKVCache:
     step = 256
 
@@ -71,6 +76,10 @@ class MixedQuantKVCache:
         self._dtype = keys.dtype
         self._ensure(B, H, S, dk, dv, keys.device)
         p = self.offset
+        if S == 1 and self._append_one(keys, values, p):
+            self.offset = p + 1
+            return (_zero(keys.dtype, keys.device).expand(B, H, self.offset, dk),
+                    _zero(values.dtype, values.device).expand(B, H, self.offset, dv))
         kc, ks, kb = affine_quantize(keys, self.group_size, self.k_bits)
         vc, vs, vb = affine_quantize(values, self.group_size, self.v_bits)
         self.k_codes[:, :, p:p + S], self.k_scales[:, :, p:p + S], self.k_biases[:, :, p:p + S] = kc, ks, kb
@@ -79,6 +88,28 @@ class MixedQuantKVCache:
         zk = _zero(keys.dtype, keys.device).expand(B, H, self.offset, dk)
         zv = _zero(values.dtype, values.device).expand(B, H, self.offset, dv)
         return zk, zv
+
+    def _append_one(self, keys, values, p) -> bool:
+        """One decode step: the (batch, head) rows are quantized straight into position p of the
+        storage (two launches, no intermediate tensors).  False when a view is not row-uniform."""
+        from .affine import affine_quantize_rows_into
+
+        def rows(t):            # (B, H, 1 or n, W) at position -> (B * H, W) view, or None
+            v = t[:, :, 0] if t.shape[2] == 1 else t[:, :, p]
+            B, H, W = v.shape
+            if v.stride(2) != 1 or (B > 1 and v.stride(0) != H * v.stride(1)):
+                return None
+            return v.as_strided((B * H, W), (v.stride(1), 1))
+
+        views = [rows(keys), rows(self.k_codes), rows(self.k_scales), rows(self.k_biases),
+                 rows(values), rows(self.v_codes), rows(self.v_scales), rows(self.v_biases)]
+        if any(v is None for v in views):
+            return False
+        kx, kc, ks, kb, vx, vc, vs, vb = views
+        if H_stride_zero(kx) or H_stride_zero(vx):
+            return False
+        return (affine_quantize_rows_into(kx, kc, ks, kb, self.group_size, self.k_bits) and
+                affine_quantize_rows_into(vx, vc, vs, vb, self.group_size, self.v_bits))
 
     # ---- attention --------------------------------------------------------------
     def descriptors(self):

@@ -34,14 +34,25 @@ class Qwen2Config:
         return dict(self.__dict__)
 
 
-def rope(x: torch.Tensor, pos: torch.Tensor, theta: float) -> torch.Tensor:
-    """Rotary embedding, half-split layout: x (B, H, L, D), pos (L,)."""
-    half = x.shape[-1] // 2
-    freqs = 1.0 / (theta ** (torch.arange(half, device=x.device, dtype=torch.float32) / half))
+def rope_tables(pos: torch.Tensor, head_dim: int, theta: float, dtype):
+    """(cos, sin) of shape (1, 1, L, head_dim / 2) for the positions `pos` (L,): computed once per
+    forward pass and shared by all layers."""
+    half = head_dim // 2
+    freqs = 1.0 / (theta ** (torch.arange(half, device=pos.device, dtype=torch.float32) / half))
     ang = pos[:, None].float() * freqs[None]
-    cos, sin = ang.cos()[None, None].to(x.dtype), ang.sin()[None, None].to(x.dtype)
+    return ang.cos()[None, None].to(dtype), ang.sin()[None, None].to(dtype)
+
+
+def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotary embedding, half-split layout: x (B, H, L, D)."""
+    half = x.shape[-1] // 2
     x1, x2 = x[..., :half], x[..., half:]
     return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1)
+
+
+def rope(x: torch.Tensor, pos: torch.Tensor, theta: float) -> torch.Tensor:
+    cos, sin = rope_tables(pos, x.shape[-1], theta, x.dtype)
+    return apply_rope(x, cos, sin)
 
 
 class Qwen2Model:
@@ -73,10 +84,11 @@ class Qwen2Model:
         pos = torch.arange(caches[0].offset, caches[0].offset + L, device=x.device)
         mask = caches[0].make_mask(L)
         scale = 1.0 / math.sqrt(D)
+        cos, sin = rope_tables(pos, D, cfg.rope_theta, x.dtype)
         for lw, cache in zip(self.layers, caches):
             h = F.rms_norm(x, (cfg.hidden,), eps=cfg.rms_eps)
-            q = rope((h @ lw["wq"]).view(B, L, cfg.n_q_heads, D).transpose(1, 2), pos, cfg.rope_theta)
-            k = rope((h @ lw["wk"]).view(B, L, cfg.n_kv_heads, D).transpose(1, 2), pos, cfg.rope_theta)
+            q = apply_rope((h @ lw["wq"]).view(B, L, cfg.n_q_heads, D).transpose(1, 2), cos, sin)
+            k = apply_rope((h @ lw["wk"]).view(B, L, cfg.n_kv_heads, D).transpose(1, 2), cos, sin)
             v = (h @ lw["wv"]).view(B, L, cfg.n_kv_heads, D).transpose(1, 2)
             keys, values = cache.update_and_fetch(k, v)
             att = base.scaled_dot_product_attention(q, keys, values, cache, scale, mask)
