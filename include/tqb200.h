@@ -72,6 +72,17 @@ int tq_quantize(const void* x, int x_dtype, int64_t n_outer, int64_t n_inner,
                 uint32_t* packed, int64_t packed_outer_stride,
                 float* norms, int64_t norms_outer_stride, void* stream);
 
+/* tq_quantize plus, in the same launch, a strided copy of `copy_rows` rows of `copy_row_bytes`
+ * bytes (16-byte multiples): the cache append of one step when the keys are stored as they are and
+ * the values are PolarQuant-packed (v_only_cache.py:46-60: `KVCache.update_and_fetch` for K, then
+ * quantize-on-insert for V).  One launch instead of two in front of every decode attention. */
+int tq_quantize_append(const void* x, int x_dtype, int64_t n_outer, int64_t n_inner,
+                       int64_t x_outer_stride, int dim, int bits, const float* signs_host,
+                       const float* boundaries_host, uint32_t* packed, int64_t packed_outer_stride,
+                       float* norms, int64_t norms_outer_stride, const void* copy_src, void* copy_dst,
+                       int64_t copy_rows, int64_t copy_row_bytes, int64_t copy_src_stride_bytes,
+                       int64_t copy_dst_stride_bytes, void* stream);
+
 /* ---- dequantize ----------------------------------------------------------
  * Replaces dequant_fp16 (metal.py:199-232) and packed_dequantize
  * (kernels.py:123-155): unpack, centroid * s, raw butterfly, * s * signs *

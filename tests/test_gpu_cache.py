@@ -218,3 +218,34 @@ def test_mixed_cache_single_step_append_matches_bulk(tq, dev):
     assert step.offset == bulk.offset == 7
     for name in ("k_codes", "k_scales", "k_biases", "v_codes", "v_scales", "v_biases"):
         assert torch.equal(getattr(step, name)[:, :, :7], getattr(bulk, name)[:, :, :7]), name
+
+
+def test_v_only_fused_append_matches_two_step_append(tq, dev):
+    """Decode-step appends of the fused V-only cache take one launch (K copy + V quantize); the stored
+    keys, packed values and norms must equal those of the plain two-step path."""
+    g = torch.Generator(device=dev).manual_seed(8)
+    B, H, D, n0 = 2, 4, 128, 37
+    k0 = torch.randn((B, H, n0, D), generator=g, device=dev).half()
+    v0 = torch.randn((B, H, n0, D), generator=g, device=dev).half()
+    fast = tq.VOnlyTurboQuantCache(bits=3, seed=5, fused=True)
+    fast.reserve(B, H, 512, D, D, torch.float16, dev)
+    slow = tq.VOnlyTurboQuantCache(bits=3, seed=5, fused=True)         # grows on demand: never takes the one-launch path
+    fast.update_and_fetch(k0, v0)
+    slow.update_and_fetch(k0, v0)
+    took_fast = 0
+    for s in (1, 1, 2, 1):
+        k = torch.randn((B, H, s, D), generator=g, device=dev).half()
+        v = torch.randn((B, H, s, D), generator=g, device=dev).half()
+        took_fast += fast._append_fused(k, v) is not None
+        slow._k_cache.update_and_fetch(k, v)
+        slow._v_tq.update_and_fetch(k, v)
+    n = n0 + 5
+    assert took_fast == 4 and fast.offset == slow.offset == n and fast._v_tq.offset == n
+    assert torch.equal(fast._k_cache.keys[:, :, :n], slow._k_cache.keys[:, :, :n])
+    assert torch.equal(fast._v_tq.v_packed[:, :, :n], slow._v_tq.v_packed[:, :, :n])
+    assert torch.equal(fast._v_tq.v_norms[:, :, :n], slow._v_tq.v_norms[:, :, :n])
+    # the public call takes the same path and hands back the key view plus a value placeholder
+    k = torch.randn((B, H, 1, D), generator=g, device=dev).half()
+    keys, vals = fast.update_and_fetch(k, k)
+    assert keys.shape == (B, H, n + 1, D) and vals.shape == (B, H, n + 1, D)
+    assert torch.equal(keys[:, :, n], k[:, :, 0])

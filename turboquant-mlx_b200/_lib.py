@@ -67,6 +67,9 @@ _SIGNATURES = {
     "tq_last_error_string": (c_char_p, []),
     "tq_quantize": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, _FP, _FP,
                             c_void_p, c_int64, c_void_p, c_int64, c_void_p]),
+    "tq_quantize_append": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, _FP, _FP,
+                                   c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64,
+                                   c_int64, c_int64, c_void_p]),
     "tq_dequantize": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int, c_int,
                               _FP, _FP, c_void_p, c_int, c_int64, c_void_p]),
     "tq_prerotate_query": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, _FP, c_void_p, c_void_p]),

@@ -33,6 +33,11 @@ struct QuantArgs {
   SignMask signs;
   Table16 thr;   // thresholds on the raw butterfly output
   int n_thr;
+  // optional row copy done by extra blocks of the same launch (the dense K rows of a cache append)
+  int q_blocks;              // blocks that quantize; blocks beyond copy (0: no copy job)
+  const uint4* cp_src;
+  uint4* cp_dst;
+  int64_t cp_rows, cp_row16, cp_src_stride16, cp_dst_stride16;   // 16-byte units
 };
 
 template <typename T, int EPL, int BITS>
@@ -49,8 +54,18 @@ quantize_warp_kernel(const QuantArgs a) {
 
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
+  const int q_blocks = a.q_blocks > 0 ? a.q_blocks : (int)gridDim.x;
+  if ((int)blockIdx.x >= q_blocks) {      // copy blocks: rows of 16-byte chunks, strided on both sides
+    const int64_t total = a.cp_rows * a.cp_row16;
+    const int64_t step = (int64_t)(gridDim.x - q_blocks) * blockDim.x;
+    for (int64_t i = (int64_t)(blockIdx.x - q_blocks) * blockDim.x + threadIdx.x; i < total; i += step) {
+      const int64_t r = i / a.cp_row16, c = i - r * a.cp_row16;
+      a.cp_dst[r * a.cp_dst_stride16 + c] = a.cp_src[r * a.cp_src_stride16 + c];
+    }
+    return;
+  }
   const int64_t warp_global = (int64_t)blockIdx.x * kWarpsPerBlock + warp;
-  const int64_t warp_stride = (int64_t)gridDim.x * kWarpsPerBlock;
+  const int64_t warp_stride = (int64_t)q_blocks * kWarpsPerBlock;
 
   uint32_t sbit[EPL];
 #pragma unroll
@@ -206,9 +221,16 @@ static int grid_for(int64_t n_vecs) {
 }
 
 template <typename T, int EPL>
-static int launch_quantize_bits(const QuantArgs& a, int bits, cudaStream_t st) {
-  const int grid = grid_for(a.n_vecs);
+static int launch_quantize_bits(const QuantArgs& a_in, int bits, cudaStream_t st) {
+  QuantArgs a = a_in;
+  int grid = grid_for(a.n_vecs);
   const int block = kWarpsPerBlock * 32;
+  if (a.cp_rows > 0) {       // add copy blocks: 256 chunks of 16 bytes per block, at most 64 blocks
+    a.q_blocks = grid;
+    const int64_t chunks = a.cp_rows * a.cp_row16;
+    int64_t cb = (chunks + block - 1) / block;
+    grid += (int)(cb > 64 ? 64 : cb);
+  }
   switch (bits) {
     case 1: quantize_warp_kernel<T, EPL, 1><<<grid, block, 0, st>>>(a); break;
     case 2: quantize_warp_kernel<T, EPL, 2><<<grid, block, 0, st>>>(a); break;
@@ -266,11 +288,19 @@ static int launch_hadamard(const HadamardArgs& a, int dim, cudaStream_t st) {
 
 using namespace tq;
 
-extern "C" int tq_quantize(const void* x, int x_dtype, int64_t n_outer, int64_t n_inner,
-                           int64_t x_outer_stride, int dim, int bits, const float* signs_host,
-                           const float* boundaries_host, uint32_t* packed,
-                           int64_t packed_outer_stride, float* norms, int64_t norms_outer_stride,
-                           void* stream) {
+namespace {
+struct RowCopy {
+  const void* src;
+  void* dst;
+  int64_t rows, row_bytes, src_stride_bytes, dst_stride_bytes;
+};
+}  // namespace
+
+static int quantize_impl(const void* x, int x_dtype, int64_t n_outer, int64_t n_inner,
+                         int64_t x_outer_stride, int dim, int bits, const float* signs_host,
+                         const float* boundaries_host, uint32_t* packed,
+                         int64_t packed_outer_stride, float* norms, int64_t norms_outer_stride,
+                         const RowCopy* copy, void* stream) {
   int rc = check_dim_bits(dim, bits, 256);
   if (rc) return rc;
   TQ_REQUIRE(n_outer >= 0 && n_inner >= 0, TQ_ERR_BAD_ARG, "negative vector count");
@@ -278,6 +308,18 @@ extern "C" int tq_quantize(const void* x, int x_dtype, int64_t n_outer, int64_t 
   if (n_outer * n_inner == 0) return TQ_OK;
   TQ_REQUIRE(x && packed && norms, TQ_ERR_BAD_ARG, "NULL tensor pointer");
   QuantArgs a;
+  a.q_blocks = 0;
+  a.cp_src = nullptr;
+  a.cp_dst = nullptr;
+  a.cp_rows = a.cp_row16 = a.cp_src_stride16 = a.cp_dst_stride16 = 0;
+  if (copy) {
+    a.cp_src = static_cast<const uint4*>(copy->src);
+    a.cp_dst = static_cast<uint4*>(copy->dst);
+    a.cp_rows = copy->rows;
+    a.cp_row16 = copy->row_bytes / 16;
+    a.cp_src_stride16 = copy->src_stride_bytes / 16;
+    a.cp_dst_stride16 = copy->dst_stride_bytes / 16;
+  }
   a.x = x;
   a.n_vecs = n_outer * n_inner;
   a.n_inner = n_inner;
@@ -293,7 +335,7 @@ extern "C" int tq_quantize(const void* x, int x_dtype, int64_t n_outer, int64_t 
   cudaStream_t st = (cudaStream_t)stream;
   if (x_dtype < TQ_F32 || x_dtype > TQ_BF16) return set_error(TQ_ERR_BAD_ARG, "unknown dtype %d", x_dtype);
   static const bool force_general = getenv("TQ_FORCE_GENERIC") != nullptr;   // debugging aid
-  if (!force_general) {   // large contiguous dim-128 batches: thread-per-vector kernel
+  if (!force_general && !copy) {   // large contiguous dim-128 batches: thread-per-vector kernel
     rc = try_launch_quantize_fast(x, x_dtype, n_outer, n_inner, x_outer_stride, dim, bits, a.signs, a.thr,
                                   packed, packed_outer_stride, norms, norms_outer_stride, st);
     if (rc != TQ_ERR_UNSUPPORTED) return rc;
@@ -304,6 +346,32 @@ extern "C" int tq_quantize(const void* x, int x_dtype, int64_t n_outer, int64_t 
     case TQ_BF16: return launch_quantize<__nv_bfloat16>(a, dim, bits, st);
     default: return set_error(TQ_ERR_BAD_ARG, "unknown dtype %d", x_dtype);
   }
+}
+
+extern "C" int tq_quantize(const void* x, int x_dtype, int64_t n_outer, int64_t n_inner,
+                           int64_t x_outer_stride, int dim, int bits, const float* signs_host,
+                           const float* boundaries_host, uint32_t* packed,
+                           int64_t packed_outer_stride, float* norms, int64_t norms_outer_stride,
+                           void* stream) {
+  return quantize_impl(x, x_dtype, n_outer, n_inner, x_outer_stride, dim, bits, signs_host, boundaries_host,
+                       packed, packed_outer_stride, norms, norms_outer_stride, nullptr, stream);
+}
+
+extern "C" int tq_quantize_append(const void* x, int x_dtype, int64_t n_outer, int64_t n_inner,
+                                  int64_t x_outer_stride, int dim, int bits, const float* signs_host,
+                                  const float* boundaries_host, uint32_t* packed,
+                                  int64_t packed_outer_stride, float* norms, int64_t norms_outer_stride,
+                                  const void* copy_src, void* copy_dst, int64_t copy_rows,
+                                  int64_t copy_row_bytes, int64_t copy_src_stride_bytes,
+                                  int64_t copy_dst_stride_bytes, void* stream) {
+  TQ_REQUIRE(n_outer * n_inner > 0, TQ_ERR_BAD_ARG, "tq_quantize_append needs at least one vector");
+  TQ_REQUIRE(copy_src && copy_dst && copy_rows > 0 && copy_row_bytes > 0, TQ_ERR_BAD_ARG, "empty copy job");
+  TQ_REQUIRE(((reinterpret_cast<uintptr_t>(copy_src) | reinterpret_cast<uintptr_t>(copy_dst) |
+               (uintptr_t)copy_row_bytes | (uintptr_t)copy_src_stride_bytes | (uintptr_t)copy_dst_stride_bytes) & 15) == 0,
+             TQ_ERR_MISALIGNED, "copy rows must be 16-byte multiples at 16-byte boundaries");
+  const RowCopy rc = {copy_src, copy_dst, copy_rows, copy_row_bytes, copy_src_stride_bytes, copy_dst_stride_bytes};
+  return quantize_impl(x, x_dtype, n_outer, n_inner, x_outer_stride, dim, bits, signs_host, boundaries_host,
+                       packed, packed_outer_stride, norms, norms_outer_stride, &rc, stream);
 }
 
 extern "C" int tq_dequantize(const uint32_t* packed, int64_t packed_outer_stride,

@@ -56,6 +56,30 @@ def quantize_into(x: torch.Tensor, signs, boundaries, dim: int, bits: int,
         p_ptr, packed_out.stride(0), n_ptr, norms_out.stride(0), _lib.stream_ptr(x.device)))
 
 
+def quantize_append(x: torch.Tensor, signs, boundaries, dim: int, bits: int, packed_out: torch.Tensor,
+                    norms_out: torch.Tensor, row_offset: int, copy_src: torch.Tensor, copy_dst: torch.Tensor) -> None:
+    """`quantize_into` plus, in the same launch, the row copy copy_src (rows, n) -> copy_dst (rows, n)
+    (views with unit-stride rows at uniform row distances whose byte sizes are multiples of 16):
+    one step's cache append for dense keys + packed values."""
+    _check_bits(bits)
+    _lib.require_cuda(x, packed_out, norms_out, copy_src, copy_dst)
+    n_outer, n_inner, d = x.shape
+    assert d == dim and x.is_contiguous()
+    assert packed_out.stride(-1) == 1 and packed_out.stride(-2) == packed_out.shape[-1]
+    assert copy_src.shape == copy_dst.shape and copy_src.dtype == copy_dst.dtype and copy_src.ndim == 2
+    assert copy_src.stride(1) == 1 and copy_dst.stride(1) == 1
+    es = copy_src.element_size()
+    pd = packed_out.shape[-1]
+    p_ptr = ctypes.c_void_p(packed_out.data_ptr() + row_offset * pd * 4)
+    n_ptr = ctypes.c_void_p(norms_out.data_ptr() + row_offset * 4)
+    _lib.check(_lib.lib().tq_quantize_append(
+        _lib.ptr(x), _lib.dtype_code(x.dtype), n_outer, n_inner, n_inner * dim, dim, bits,
+        _lib.host_floats(signs), _lib.host_floats(boundaries),
+        p_ptr, packed_out.stride(0), n_ptr, norms_out.stride(0),
+        _lib.ptr(copy_src), _lib.ptr(copy_dst), copy_src.shape[0], copy_src.shape[1] * es,
+        copy_src.stride(0) * es, copy_dst.stride(0) * es, _lib.stream_ptr(x.device)))
+
+
 def fused_quantize(vectors: torch.Tensor, signs, boundaries, dim: int, bits: int):
     """Raw vectors (n_vecs, dim) fp16/bf16/fp32 -> (packed (n_vecs, packed_dim)
     uint32, norms (n_vecs,) float32) in one kernel."""

@@ -40,8 +40,43 @@ class VOnlyTurboQuantCache:
             kc.keys = new_k
             kc.values = torch.zeros((B, H, n_positions, 0), dtype=dtype, device=new_k.device)
 
+    def _append_fused(self, keys, values):
+        """Decode-step append in one launch (`tq_quantize_append`): the K rows are copied and the V
+        rows quantized by the same kernel.  Only when nothing has to grow and every view is
+        row-uniform and 16-byte friendly; returns None otherwise."""
+        kc, tq = self._k_cache, self._v_tq
+        B, H, S, Dk = keys.shape
+        if not (self.fused and keys.is_cuda and S <= 4 and kc.keys is not None and tq.v_packed is not None):
+            return None
+        prev = kc.offset
+        if prev != tq.offset or prev + S > kc.keys.shape[2] or prev + S > tq.v_packed.shape[2]:
+            return None
+        if kc.keys.dtype != keys.dtype or kc.keys.shape[:2] != (B, H) or kc.keys.shape[3] != Dk:
+            return None
+        Dv = values.shape[3]
+        if tq._v_q is None or tq._v_q.dim != Dv or not values.is_contiguous() or not keys.is_contiguous():
+            return None
+        es = keys.element_size()
+        if (S * Dk * es) % 16 or (kc.keys.shape[2] * Dk * es) % 16 or (prev * Dk * es) % 16 or keys.data_ptr() % 16:
+            return None
+        src = keys.view(B * H, S * Dk)
+        dst = kc.keys.view(B * H, kc.keys.shape[2] * Dk)[:, prev * Dk:(prev + S) * Dk]
+        from .kernels import quantize_append
+        q = tq._v_q
+        tq._dtype = keys.dtype
+        quantize_append(values.view(B * H, S, Dv), q.signs, q.boundaries, Dv, q.bits,
+                        tq.v_packed.view(B * H, tq.v_packed.shape[2], tq.v_packed.shape[3]),
+                        tq.v_norms.view(B * H, tq.v_norms.shape[2]), prev, src, dst)
+        kc.offset = prev + S
+        tq.offset = prev + S
+        from .cache import _zero
+        return kc.keys[..., :kc.offset, :], _zero(values.dtype, values.device).expand(B, H, kc.offset, Dv)
+
     def update_and_fetch(self, keys, values):
         """Store K as is, compress V, return (K, V_dequant)."""
+        fused = self._append_fused(keys, values)
+        if fused is not None:
+            return fused
         k_out, _ = self._k_cache.update_and_fetch(keys, values)
         if self._no_v_buffer and not self.fused:
             # quantize, then re-dequantize everything from packed storage each call
