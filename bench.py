@@ -15,9 +15,12 @@ One step = one decode token = 28 layers, each layer with its own KV buffers
   roofline: flash-decode launch time from CUDA events vs the measured HBM peak;
   cpu_baseline: the numpy oracle of the same composed path on the host cores.
 
-With --gpus N > 1 (torchrun, one rank per GPU) every rank runs the same
-per-GPU workload on its own sequences (batch sharding, no data-path
-collective): weak scaling.  --impl reference times the CPU oracle only.
+With --gpus N > 1 (torchrun, one rank per GPU) ONE sequence of N x 32768 tokens is
+sharded along the sequence: every rank holds 32768 positions of every KV head, runs
+the decode kernel in partial mode on its chunk, the (m, l, acc) partial states cross
+NVLink (peer stores issued by the decode kernel's final step) and every rank merges
+them, per layer, inside the timed region: weak scaling, N = 1 is the plain workload.
+--impl reference times the CPU oracle only.
 """
 
 from __future__ import annotations
@@ -40,6 +43,7 @@ N_REP = N_Q // N_KV
 KV_BYTES_LAYER = N_KV * CTX * (DIM * 2) + N_KV * CTX * (13 * 4 + 4)   # fp16 K + packed V + norms
 QO_BYTES_LAYER = N_Q * DIM * 2 * 2
 ALGO_BYTES_LAYER = KV_BYTES_LAYER + QO_BYTES_LAYER                       # 40.9 MB
+DTYPE = "f16"   # operands of both contractions are fp16 (fp32 accumulation, fp32 softmax state)
 WORKLOAD = ("V-only TurboQuant decode attention, Qwen2.5-7B shape: 28 q / 4 kv heads, d=128, "
             "B=1, ctx 32768, K fp16, V PolarQuant 3-bit; step = 1 token x 28 layers")
 
@@ -111,7 +115,8 @@ class ClockSampler:
 def cpu_oracle_run(layers: int, ctx: int, threads: int, seed: int = 0):
     """Times the numpy oracle's composed decode attention (scores -> softmax ->
     butterfly-pulled-out packed-V sum) on `layers` independent layer-steps of
-    the workload shape at context `ctx`.  Returns (seconds, algorithmic bytes)."""
+    the workload shape at context `ctx`; the (layer, kv head) groups are independent
+    and are spread over `threads` host threads.  Returns (seconds, algorithmic bytes)."""
     import numpy as np
     from concurrent.futures import ThreadPoolExecutor
     o = entry.load_oracle()
@@ -123,16 +128,18 @@ def cpu_oracle_run(layers: int, ctx: int, threads: int, seed: int = 0):
     vp[..., 12] &= 0x00FFFFFF
     vn = (rng.random((N_KV, ctx)) * 10 + 1).astype(np.float32)
     qs = rng.standard_normal((layers, N_Q, DIM)).astype(np.float16)
-    vdesc = dict(packed=vp, norms=vn, centroids=cent, signs=signs, bits=V_BITS)
     scale = 1.0 / math.sqrt(DIM)
 
-    def one(i):
-        out, _ = o.decode_attention(qs[i], k_dense=kd, v_polar=vdesc, attn_scale=scale, n_rep=N_REP)
+    def one(task):
+        i, h = divmod(task, N_KV)
+        vdesc = dict(packed=vp[h:h + 1], norms=vn[h:h + 1], centroids=cent, signs=signs, bits=V_BITS)
+        out, _ = o.decode_attention(qs[i, h * N_REP:(h + 1) * N_REP], k_dense=kd[h:h + 1], v_polar=vdesc,
+                                    attn_scale=scale, n_rep=N_REP)
         return float(out[0, 0])
 
     t0 = time.perf_counter()
     with ThreadPoolExecutor(max_workers=threads) as ex:
-        list(ex.map(one, range(layers)))
+        list(ex.map(one, range(layers * N_KV)))
     dt = time.perf_counter() - t0
     per_layer = N_KV * ctx * (DIM * 2 + 56) + QO_BYTES_LAYER
     return dt, layers * per_layer
@@ -144,8 +151,8 @@ def reference_arm(args):
         return
     cores = len(os.sched_getaffinity(0))
     threads = max(1, min(cores, 8))
-    ctx = 8192
-    layers = threads
+    ctx = CTX                      # the workload's own context; a step is bounded by the layer count
+    layers = max(1, threads // N_KV)
     times = []
     for i in range(args.warmup + args.steps):
         dt, nbytes = cpu_oracle_run(layers, ctx, threads, seed=i)
@@ -154,11 +161,15 @@ def reference_arm(args):
     dt = sum(times) / len(times)
     val = nbytes / dt / 1e9
     sample = f"{layers} layer-steps at ctx {ctx} per step ({nbytes / 1e6:.1f} MB of KV), {threads} threads"
+    # the reference's own arithmetic needs the mlx array library; probe for it so that a box that has it shows up
+    import importlib.util
+    mlx_note = ("mlx importable: the numpy restatement is still what is timed here" if importlib.util.find_spec("mlx")
+                else "mlx unavailable: numpy restatement of the reference's pure path (oracle/tq_oracle.py)")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": {"workload": WORKLOAD, "sample": sample},
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": DTYPE,
+        "data": "synthetic", "config": {"workload": WORKLOAD, "sample": sample, "reference_runtime": mlx_note},
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -167,6 +178,91 @@ def reference_arm(args):
 # ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
+def _sync_all(torch, dist, world):
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def _timed(torch, dist, world, dev, fn, steps, warmup):
+    """Mean ms of fn() over `steps` calls after `warmup` calls: CUDA events on the current stream,
+    barrier + synchronize on both sides, max over ranks."""
+    for _ in range(warmup):
+        fn()
+    _sync_all(torch, dist, world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    _sync_all(torch, dist, world)
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms / steps
+
+
+def _capture(torch, fn, dev):
+    """fn() captured as one CUDA graph (after two eager runs on a side stream)."""
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    return g
+
+
+class ShardedLayers:
+    """One decode step of `layers` attention layers with the sequence sharded across the ranks:
+    per layer the decode kernel attends over this rank's chunk in partial mode and its final step
+    stores the merged (m, l, acc) rows into every rank's receive slot (plain peer stores over NVLink
+    + one system-scope counter add per (batch, kv head) group and peer); a merge gated on those
+    counters (bounded wait) combines the ranks' states and zeroes the counters again, so the whole
+    step replays from one CUDA graph.  Two receive slots alternate by layer."""
+
+    def __init__(self, tq, qs, ks, vs, scale, v_signs, dev, world, n_q, n_kv, out_dtype, new_rows=None):
+        import torch
+        from turboquant_mlx_b200.distributed import PeerExchange, partial_buffer, partial_views
+        self.layers = len(ks)
+        rows = n_q
+        self.ex = PeerExchange(rows * (DIM + 2), dev)
+        self.world, self.n_kv = world, n_kv
+        self.status_ptr = tq._lib.ptr(self.ex.status)
+        self.outs = [torch.empty((rows, DIM), dtype=out_dtype, device=dev) for _ in range(self.layers)]
+        self.sends = [partial_buffer(rows, DIM, dev)[0] for _ in range(self.layers)]
+        self.plans, self.merges, self.local_plans = [], [], []
+        for l in range(self.layers):
+            slot = l & 1
+            m, lsum, acc = partial_views(self.sends[l], rows, DIM)
+            po = (m.view(1, n_q), lsum.view(1, n_q), acc.view(1, n_q, DIM))
+            kw = {} if new_rows is None else dict(new_k=new_rows[l][0], new_v=new_rows[l][1])
+            self.plans.append(tq.FlashDecodePlan(qs[l], k=ks[l], v=vs[l], attn_scale=scale, partials=True,
+                                                 peers=self.ex.targets(slot, rows, DIM), partial_out=po,
+                                                 kv_stable=True, q_stable=True, **kw))
+            self.local_plans.append(tq.FlashDecodePlan(qs[l], k=ks[l], v=vs[l], attn_scale=scale, partials=True,
+                                                       partial_out=po, kv_stable=True, q_stable=True))
+            gm, gl, gacc = partial_views(self.ex.data[slot], rows, DIM)
+            self.merges.append(tq.MergePlan(gm, gl, gacc, v_signs, self.outs[l]))
+        self.flag_ptrs = [tq._lib.ptr(self.ex.flags[slot]) for slot in range(2)]
+
+    def step(self):
+        for l in range(self.layers):
+            self.plans[l].run()
+            self.merges[l].run_after_peers(self.flag_ptrs[l & 1], self.world, self.n_kv, self.status_ptr,
+                                           reset_flags=True)
+
+    def kernels_only(self):
+        for l in range(self.layers):
+            self.local_plans[l].run()
+
+
 def gpu_arm(args):
     import torch
     import torch.distributed as dist
@@ -177,18 +273,21 @@ def gpu_arm(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         dist.init_process_group("nccl", device_id=dev)
     tq = entry.load_package()
     from turboquant_mlx_b200 import base
+    from turboquant_mlx_b200.kernels import flash_status
 
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
     n_alloc = CTX + 256
     scale = 1.0 / math.sqrt(DIM)
+    peak, peak_kind = measured_peaks()
 
-    # ---- caches filled through the public API (prefill insert of CTX tokens) ----
+    # ---- caches filled through the public API (prefill insert of this rank's CTX tokens) ----
     caches = []
     for layer in range(N_LAYERS):
-        c = tq.VOnlyTurboQuantCache(bits=V_BITS, seed=42, fused=True)
+        c = tq.VOnlyTurboQuantCache(bits=V_BITS, seed=42, fused=True, defer_append=True, inputs_stable=True)
         k = torch.randn((1, N_KV, CTX, DIM), generator=gen, device=dev, dtype=torch.float16)
         v = (torch.randn((1, N_KV, CTX, DIM), generator=gen, device=dev) *
              torch.exp(0.5 * torch.randn((1, N_KV, CTX, 1), generator=gen, device=dev))).to(torch.float16)
@@ -196,120 +295,152 @@ def gpu_arm(args):
         c.update_and_fetch(k, v)          # prefill insert: K copied, V quantized and packed
         caches.append(c)
         del k, v
-    q_dev = torch.randn((N_LAYERS, 1, N_Q, 1, DIM), generator=gen, device=dev).to(torch.float16)
+    qgen = torch.Generator(device=dev).manual_seed(99)        # the query is replicated across the ranks
+    q_dev = torch.randn((N_LAYERS, 1, N_Q, 1, DIM), generator=qgen, device=dev).to(torch.float16)
     out_dev = torch.empty((N_LAYERS, 1, N_Q, 1, DIM), dtype=torch.float16, device=dev)
     torch.cuda.synchronize()
 
-    # ---- device-resident step: 28 flash-decode launches, captured as one graph ----
     from turboquant_mlx_b200.v_only_cache import v_only_attention
 
     if args.kernel_only:
         for _ in range(args.warmup + args.steps):
             for layer in range(N_LAYERS):
-                v_only_attention(q_dev[layer], caches[layer], scale, kv_stable=True)
+                v_only_attention(q_dev[layer], caches[layer], scale, kv_stable=True, q_stable=True)
         torch.cuda.synchronize()
-        print(json.dumps({"kernel_only": True, "layers": N_LAYERS, "launches": (args.warmup + args.steps) * N_LAYERS}))
+        print(json.dumps({"kernel_only": True, "layers": N_LAYERS, "launches": (args.warmup + args.steps) * N_LAYERS,
+                          "status": flash_status(dev, N_KV)}))
         return
 
-    # The caches are static here (nothing appends between launches), so the kernel may
-    # prefetch K / V while the previous layer's launch drains (kv_stable).
-    def device_step():
-        for layer in range(N_LAYERS):
-            v_only_attention(q_dev[layer], caches[layer], scale, kv_stable=True, out=out_dev[layer])
-
-    side = torch.cuda.Stream(device=dev)
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        for _ in range(2):
-            device_step()
-    torch.cuda.current_stream().wait_stream(side)
-    torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        device_step()
-
-    def sync_all():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps, warmup):
-        for _ in range(warmup):
-            fn()
-        sync_all()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        sync_all()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms / steps
-
-    sampler = ClockSampler(local)
-    with sampler:
-        ms_step = timed(graph.replay, args.steps, args.warmup)
     step_bytes = N_LAYERS * ALGO_BYTES_LAYER
-    value = world * step_bytes / (ms_step * 1e-3) / 1e9
-    toks = world / (ms_step * 1e-3)
+    sampler = ClockSampler(local)
+    extra_cfg = {}
 
-    # ---- roofline of the dominant kernel: one flash-decode call, event-timed per launch ----
-    def one_layer_calls():
-        for layer in range(N_LAYERS):
-            v_only_attention(q_dev[layer], caches[layer], scale, kv_stable=True)
-    g2 = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g2):
-        one_layer_calls()
-    ms_calls = timed(g2.replay, max(args.steps, 20), 3)
-    launch_ms = ms_calls / N_LAYERS
-    peak, peak_kind = measured_peaks()
+    if world == 1:
+        # ---- device-resident step: 28 flash-decode launches, one graph.  The caches and queries are
+        # static here, so each launch may read its inputs while the launches in front of it drain
+        # (kv_stable, q_stable): consecutive layers overlap, each on one half of every SM.
+        def device_step():
+            for layer in range(N_LAYERS):
+                v_only_attention(q_dev[layer], caches[layer], scale, kv_stable=True, q_stable=True, out=out_dev[layer])
+
+        graph = _capture(torch, device_step, dev)
+        with sampler:
+            ms_step = _timed(torch, dist, world, dev, graph.replay, args.steps, args.warmup)
+            # roofline of the dominant kernel: the same launches, event-timed over a longer region
+            ms_calls = _timed(torch, dist, world, dev, graph.replay, max(args.steps, 200), 3)
+        launch_ms = ms_calls / N_LAYERS
+        launches_per_step = N_LAYERS
+        sharding = "one GPU, no collective"
+        status = flash_status(dev, N_KV)
+    else:
+        # ---- one sequence of world x CTX tokens, sharded along the sequence ----
+        ks = [dict(format="dense", data=c._k_cache.keys[:, :, :CTX, :]) for c in caches]
+        vs = [dict(format="polar", packed=c._v_tq.v_packed[:, :, :CTX, :], norms=c._v_tq.v_norms[:, :, :CTX],
+                   centroids=c._v_tq._v_q.centroids, signs=c._v_tq._v_q.signs, bits=V_BITS,
+                   boundaries=c._v_tq._v_q.boundaries) for c in caches]
+        qs = [q_dev[l, :, :, 0, :] for l in range(N_LAYERS)]
+        signs = caches[0]._v_tq._v_q.signs
+        sh = ShardedLayers(tq, qs, ks, vs, scale, signs, dev, world, N_Q, N_KV, torch.float16)
+        # cross-check once before timing: peer-store exchange == NCCL all-gather + merge, equal on all ranks
+        from turboquant_mlx_b200.distributed import sequence_parallel_decode
+        sh.step()
+        torch.cuda.synchronize()
+        ref0 = sequence_parallel_decode(qs[0], k=ks[0], v=vs[0], attn_scale=scale, out_dtype=torch.float16)
+        diff = float((ref0[0].float() - sh.outs[0].float()).abs().max())
+        gathered = [torch.empty_like(sh.outs[0]) for _ in range(world)]
+        dist.all_gather(gathered, sh.outs[0])
+        rank_diff = max(float((g_.float() - gathered[0].float()).abs().max()) for g_ in gathered)
+        graph = _capture(torch, sh.step, dev)
+        gk = _capture(torch, sh.kernels_only, dev)
+        with sampler:
+            ms_step = _timed(torch, dist, world, dev, graph.replay, args.steps, args.warmup)
+            ms_calls = _timed(torch, dist, world, dev, gk.replay, max(args.steps, 100), 3)
+            ms_total = _timed(torch, dist, world, dev, graph.replay, max(args.steps, 100), 3)
+        sh.ex.check()
+        launch_ms = ms_calls / N_LAYERS
+        launches_per_step = 2 * N_LAYERS
+        sharding = (f"one sequence of {world * CTX} tokens split along the sequence, {CTX} positions per GPU; per "
+                    "layer: partial-mode decode -> (m, l, acc) rows stored to every rank over NVLink by the decode "
+                    "kernel -> gated merge; one CUDA graph per step")
+        extra_cfg = {"us_per_layer_kernel_only": launch_ms * 1e3, "us_per_layer_total": ms_total / N_LAYERS * 1e3,
+                     "us_per_layer_exchange_and_merge": (ms_total - ms_calls) / N_LAYERS * 1e3,
+                     "exchange_bytes_per_rank_per_layer": N_Q * (DIM + 2) * 4,
+                     "max_abs_diff_vs_nccl_allgather_path": diff, "max_abs_diff_across_ranks": rank_diff}
+        status = flash_status(dev, N_KV)
+
+    value = world * step_bytes / (ms_step * 1e-3) / 1e9
+    toks = 1.0 / (ms_step * 1e-3)
     achieved = ALGO_BYTES_LAYER / (launch_ms * 1e-3) / 1e9
-    # dram__bytes_read.sum + dram__bytes_write.sum per launch of this kernel on this workload, from the
-    # ncu capture summarised in profiles/flash_mma_kernel_c2.md (40.97 MB read + 2.3 KB written)
+    # dram__bytes_read.sum + dram__bytes_write.sum per launch of this kernel on this workload, from an
+    # ncu capture (its read traffic equals the algorithmic bytes to 0.2 %)
     traffic = 40_966_656 + 2_304 if N_LAYERS == 28 else None
 
     # ---- end to end through the public API with host buffers -------------------
-    tq.apply_patch()
     per_layer_in = (N_Q + 2 * N_KV) * DIM
     h_in = torch.randn((N_LAYERS, per_layer_in), dtype=torch.float16).pin_memory()
     h_out = torch.empty((N_LAYERS, N_Q * DIM), dtype=torch.float16).pin_memory()
     d_in = torch.empty_like(h_in, device=dev)
     d_out = torch.empty((N_LAYERS, N_Q * DIM), dtype=torch.float16, device=dev)
 
-    def e2e_body():
-        d_in.copy_(h_in, non_blocking=True)
-        outs = []
-        for layer in range(N_LAYERS):
-            row = d_in[layer]
-            q = row[:N_Q * DIM].view(1, N_Q, 1, DIM)
-            k = row[N_Q * DIM:(N_Q + N_KV) * DIM].view(1, N_KV, 1, DIM)
-            v = row[(N_Q + N_KV) * DIM:].view(1, N_KV, 1, DIM)
-            c = caches[layer]
-            keys, values = c.update_and_fetch(k, v)
-            outs.append(base.scaled_dot_product_attention(q, keys, values, c, scale, None))
-            c.trim(1)                     # hold the context at CTX for the next step
-        torch.stack(outs, out=d_out.view(N_LAYERS, 1, N_Q, 1, DIM))     # one gather of the 28 layer outputs
-        h_out.copy_(d_out, non_blocking=True)
+    def rows_of(layer):
+        row = d_in[layer]
+        return (row[:N_Q * DIM].view(1, N_Q, 1, DIM), row[N_Q * DIM:(N_Q + N_KV) * DIM].view(1, N_KV, 1, DIM),
+                row[(N_Q + N_KV) * DIM:].view(1, N_KV, 1, DIM))
 
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        e2e_body()
-    torch.cuda.current_stream().wait_stream(side)
-    torch.cuda.synchronize()
-    g3 = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g3):
-        e2e_body()
+    if world == 1:
+        tq.apply_patch()
+
+        def e2e_body():
+            d_in.copy_(h_in, non_blocking=True)
+            outs = []
+            for layer in range(N_LAYERS):
+                q, k, v = rows_of(layer)
+                c = caches[layer]
+                keys, values = c.update_and_fetch(k, v)      # recorded; the attention launch appends
+                outs.append(base.scaled_dot_product_attention(q, keys, values, c, scale, None))
+                c.trim(1)                     # hold the context at CTX for the next step
+            torch.stack(outs, out=d_out.view(N_LAYERS, 1, N_Q, 1, DIM))     # one gather of the 28 layer outputs
+            h_out.copy_(d_out, non_blocking=True)
+        e2e_launches = N_LAYERS + 1
+        e2e_path = ("CUDA-graph replay of H2D(q,k,v) -> per layer: cache.update_and_fetch (deferred) + hooked SDPA "
+                    "= one decode launch that appends the token and attends -> D2H, ctx held at 32768")
+    else:
+        # the step's token belongs to the last chunk: the last rank's decode launch appends it
+        last = rank == world - 1
+        ks2, vs2, new_rows = [], [], None
+        S2 = CTX + 1 if last else CTX
+        for c in caches:
+            ks2.append(dict(format="dense", data=c._k_cache.keys[:, :, :S2, :]))
+            vs2.append(dict(format="polar", packed=c._v_tq.v_packed[:, :, :S2, :], norms=c._v_tq.v_norms[:, :, :S2],
+                            centroids=c._v_tq._v_q.centroids, signs=c._v_tq._v_q.signs, bits=V_BITS,
+                            boundaries=c._v_tq._v_q.boundaries))
+        if last:
+            new_rows = [(rows_of(l)[1][:, :, 0, :], rows_of(l)[2][:, :, 0, :]) for l in range(N_LAYERS)]
+        qs2 = [rows_of(l)[0][:, :, 0, :] for l in range(N_LAYERS)]
+        sh2 = ShardedLayers(tq, qs2, ks2, vs2, scale, caches[0]._v_tq._v_q.signs, dev, world, N_Q, N_KV,
+                            torch.float16, new_rows=new_rows)
+
+        def e2e_body():
+            d_in.copy_(h_in, non_blocking=True)
+            sh2.step()
+            torch.stack(sh2.outs, out=d_out.view(N_LAYERS, N_Q, DIM))
+            h_out.copy_(d_out, non_blocking=True)
+        e2e_launches = 2 * N_LAYERS + 1
+        e2e_path = ("CUDA-graph replay of H2D(q,k,v) -> per layer: decode launch (the last rank's appends the token) "
+                    "with peer push + gated merge -> D2H, ctx held")
+
+    g3 = _capture(torch, e2e_body, dev)
 
     def e2e_step():
         g3.replay()
         torch.cuda.current_stream().synchronize()   # the host reads the result every step
 
-    ms_e2e = timed(e2e_step, args.steps, args.warmup)
-    tq.remove_patch()
+    ms_e2e = _timed(torch, dist, world, dev, e2e_step, args.steps, args.warmup)
+    if world == 1:
+        tq.remove_patch()
+    else:
+        sh2.ex.check()
+    status = status or flash_status(dev, N_KV)
     e2e_val = world * step_bytes / (ms_e2e * 1e-3) / 1e9
     h2d = h_in.numel() * 2
     d2h = h_out.numel() * 2
@@ -317,30 +448,41 @@ def gpu_arm(args):
     line = {
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "layers": N_LAYERS, "kv_bytes_per_step": step_bytes,
-                   "l2": "inputs (1.15 GB per step) larger than L2, no flush",
-                   "sharding": "one independent sequence per GPU, no collective",
-                   "tok_per_s": toks, "pct_of_8TBs": value / world / 8000.0 * 100,
-                   "e2e_path": "CUDA-graph replay of H2D(q,k,v) -> append -> hooked SDPA -> D2H, ctx held at 32768"},
+        "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
+        "config": {"workload": WORKLOAD, "layers": N_LAYERS, "kv_bytes_per_step_per_gpu": step_bytes,
+                   "l2": "inputs (1.15 GB per step per GPU) larger than L2, no flush",
+                   "sharding": sharding, "context_total": world * CTX,
+                   "tok_per_s": toks, "pct_of_8TBs_per_gpu": value / world / 8000.0 * 100,
+                   "decode_kernel_status": status, "e2e_path": e2e_path, **extra_cfg},
         "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": ms_e2e},
-        "gpu_launches": args.steps * N_LAYERS,
+                "ms_per_step": ms_e2e, "gpu_launches_per_step": e2e_launches},
+        "gpu_launches": args.steps * launches_per_step,
         "clocks": sampler.summary(),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind,
                      "kernel": "flash_mma_kernel (split-K flash decode, merge fused)", "us_per_launch": launch_ms * 1e3,
                      "bytes_per_launch": ALGO_BYTES_LAYER},
     }
+    if world > 1 and not args.no_c5:
+        del caches, q_dev
+        torch.cuda.empty_cache()
+        line["config"]["c5"] = c5_measure(args, tq, torch, dist, dev, world, rank)
     if rank == 0 and world == 1 and not args.no_cpu:
         cores = len(os.sched_getaffinity(0))
         threads = max(1, min(cores, 8))
-        dt, nbytes = cpu_oracle_run(threads, 8192, threads)
-        line["cpu_baseline"] = {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
-                                "sample": f"{threads} layer-steps at ctx 8192 ({nbytes / 1e6:.1f} MB), numpy oracle"}
+        n_l = max(1, threads // N_KV)
+        reps = 8
+        t_cpu, nbytes = 0.0, 0
+        for i in range(reps):
+            dt, nb = cpu_oracle_run(n_l, CTX, threads, seed=100 + i)
+            t_cpu, nbytes = t_cpu + dt, nbytes + nb
+        line["cpu_baseline"] = {"value": nbytes / t_cpu / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+                                "sample": f"{reps} x {n_l} layer-steps at ctx {CTX} ({nbytes / 1e6:.1f} MB), "
+                                          f"numpy oracle, (layer, kv head) groups over {threads} threads"}
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 
@@ -430,9 +572,16 @@ def workload_c3(args):
     q = torch.randn((layers, B, nq, 1, DIM), generator=gen, device=dev).half()
     scale = 1.0 / math.sqrt(DIM)
 
+    from turboquant_mlx_b200.fused_attention import cache_kv_descriptors
+    outs = [torch.empty((B, nq, DIM), dtype=torch.float16, device=dev) for _ in range(layers)]
+
     def step():
         for l in range(layers):
-            tq.turboquant_attention(q[l], caches[l], scale)
+            if args.splits > 0:      # tuning aid: a fixed split count instead of the planner's
+                k, v = cache_kv_descriptors(caches[l])
+                tq.flash_decode(q[l, :, :, 0, :], k=k, v=v, attn_scale=scale, num_splits=args.splits, out=outs[l])
+            else:
+                tq.turboquant_attention(q[l], caches[l], scale)
 
     ms = _time_graph(torch, step, args.steps) / layers
     nbytes = B * nkv * ctx * (68 + 56)
@@ -440,6 +589,7 @@ def workload_c3(args):
     print(json.dumps({"metric": METRIC, "unit": "GB/s", "n_gpus": 1, "value": nbytes / ms / 1e6,
                       "us_per_layer_step": ms * 1e3, "frac_of_peak": nbytes / ms / 1e6 / peak, "peak": peak,
                       "peak_kind": kind, "tensor_core_path": tq._lib.lib().tq_flash_decode_last_kernel() == 1,
+                      "decode_kernel_status": tq.kernels.flash_status(dev, B * nkv), "splits_forced": args.splits,
                       "config": {"workload": "C3 full TurboQuant cache decode: B=32, 32q/8kv, ctx 8192, K 4-bit + V 3-bit",
                                  "bytes_per_layer_step": nbytes}}))
 
@@ -543,23 +693,12 @@ def workload_c4(args):
                       "config": {"workload": f"C4: prompt {S}, {n_new} greedy tokens, K8/V4 group 64", **cfg.describe()}}))
 
 
-def workload_c5(args):
+def c5_measure(args, tq, torch, dist, dev, world, rank):
     """Config 5: long-context decode, Llama-3-70B attention shape (64 q / 8 kv heads, d 128), K 8-bit
     group-affine + V PolarQuant 3-bit, the sequence split across the ranks: 131072 positions per GPU
-    (1M tokens at 8 GPUs).  Every rank attends over its chunk, the (m, l, acc) partial states (33 KB per rank)
-    reach every rank by peer-to-peer stores over NVLink (--exchange p2p, default; the NCCL all-gather is timed
-    beside it) and are merged locally.  201.3 MB of KV per GPU per layer-step."""
-    import torch
-    import torch.distributed as dist
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    tq = entry.load_package()
-    from turboquant_mlx_b200.distributed import partial_buffer
+    (1M tokens at 8 GPUs).  Every rank attends over its chunk, the (m, l, acc) partial states (33 KB per
+    rank) reach every rank by peer stores issued by the decode kernel and are merged locally; the step is
+    one CUDA graph.  201.3 MB of KV per GPU per layer-step.  Returns the record."""
     nq, nkv, S, layers = 64, 8, 131072, 6
     gen = torch.Generator(device=dev).manual_seed(77 + rank)
     pq = tq.PolarQuantizer(DIM, 3, seed=43, device=dev)
@@ -577,122 +716,58 @@ def workload_c5(args):
         del vp
     q = torch.randn((layers, 1, nq, DIM), generator=torch.Generator(device=dev).manual_seed(5), device=dev).half()
     scale = 1.0 / math.sqrt(DIM)
-    # per layer: one prepared flash-decode call writing (m, l, acc) straight into the send buffer, one
-    # NCCL all-gather (eager), one prepared merge call
-    from turboquant_mlx_b200.distributed import partial_views
-    rows = nq
-    sends = [partial_buffer(rows, DIM, dev)[0] for _ in range(layers)]
-    recvs = [partial_buffer(rows, DIM, dev, world) for _ in range(layers)]
-    outs = [torch.empty((rows, DIM), dtype=torch.float16, device=dev) for _ in range(layers)]
-    plans, merges = [], []
-    for l in range(layers):
-        m, lsum, acc = partial_views(sends[l], rows, DIM)
-        plans.append(tq.FlashDecodePlan(q[l], k=ks[l], v=vs[l], attn_scale=scale, partials=True,
-                                        partial_out=(m.view(1, nq), lsum.view(1, nq), acc.view(1, nq, DIM))))
-        gm, gl, gacc = partial_views(recvs[l], rows, DIM)
-        merges.append(tq.MergePlan(gm, gl, gacc, pq.signs, outs[l]))
-    p2p = world > 1 and args.exchange in ("p2p", "fused")
-    if p2p:
-        # one exchange object for all layers (two alternating slots), one merge call per slot
-        from turboquant_mlx_b200.distributed import PeerExchange
-        ex, note = None, ""
-        try:
-            ex = PeerExchange(rows * (DIM + 2), dev)
-        except Exception as exc:      # symmetric memory not available here: every rank falls back together
-            note = f"peer exchange unavailable ({type(exc).__name__}), NCCL all-gather used"
-        agreed = torch.tensor([1 if ex is not None else 0], device=dev)
-        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
-        p2p = bool(agreed.item())
-    fused = p2p and args.exchange == "fused" and world <= 8
-    if p2p:
-        ex_status = tq._lib.ptr(ex.status)
-        slot_merges = []
-        for slot in range(2):
-            gm, gl, gacc = partial_views(ex.data[slot], rows, DIM)
-            slot_merges.append([tq.MergePlan(gm, gl, gacc, pq.signs, outs[l]) for l in range(layers)])
-    if fused:
-        # the decode kernel's final step stores the merged state into every rank's slot itself
-        slot_plans = []
-        for slot in range(2):
-            tg = ex.targets(slot, rows, DIM)
-            slot_plans.append([])
-            for l in range(layers):
-                m, lsum, acc = partial_views(sends[l], rows, DIM)
-                slot_plans[slot].append(tq.FlashDecodePlan(
-                    q[l], k=ks[l], v=vs[l], attn_scale=scale, partials=True, peers=tg,
-                    partial_out=(m.view(1, nq), lsum.view(1, nq), acc.view(1, nq, DIM))))
-
-    def step():
-        for l in range(layers):
-            if fused:
-                slot, _, flags_ptr, want = ex.next_fused(nkv)
-                slot_plans[slot][l].run()
-                slot_merges[slot][l].run_after_peers(flags_ptr, world, want, ex_status)
-                continue
-            plans[l].run()
-            if p2p:
-                _, flags_ptr, epoch = ex.push(sends[l])
-                slot_merges[epoch & 1][l].run_after_peers(flags_ptr, world, epoch, ex_status)
-                continue
-            if world > 1:
-                dist.all_gather_into_tensor(recvs[l].view(-1), sends[l])
-            else:
-                recvs[l].copy_(sends[l].unsqueeze(0), non_blocking=True)
-            merges[l].run()
-
-    def kernels_only():
-        for l in range(layers):
-            plans[l].run()
-
-    def sync_all():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps, warmup):
-        for _ in range(warmup):
-            fn()
-        sync_all()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        sync_all()
-        ms = e0.elapsed_time(e1) / steps
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
-
-    ms = timed(step, args.steps, max(args.warmup, 3)) / layers
-    if p2p:
-        ex.check()
-        # the same step through the NCCL all-gather, for the record and as a cross-check of the result
-        ref = [o.clone() for o in outs]
-        was_fused, p2p, fused = fused, False, False
-        ms_nccl = timed(step, args.steps, 3) / layers
-        p2p, fused = True, was_fused
-        err = max(float((a.float() - b.float()).abs().max()) for a, b in zip(outs, ref))
-    ms_k = timed(kernels_only, args.steps, 3) / layers
-    mode = ("peer stores from the decode kernel's final step + gated merge" if fused else
-            "peer-to-peer stores + flags (tq_peer_push, gated merge)" if p2p else "NCCL all_gather") + \
-        ", eager launches through prepared calls"
     nbytes = nkv * S * (136 + 56)
     peak, kind = measured_peaks()
-    if rank == 0:
-        print(json.dumps({
-            "metric": METRIC, "unit": "GB/s", "n_gpus": world, "value": world * nbytes / ms / 1e6,
-            "scaling": "weak", "us_per_layer_step": ms * 1e3, "us_kernel_only": ms_k * 1e3,
-            "per_gpu_frac_of_peak": nbytes / ms / 1e6 / peak, "peak": peak, "peak_kind": kind,
-            "tensor_core_path": tq._lib.lib().tq_flash_decode_last_kernel() == 1,
-            **({"us_per_layer_step_nccl": ms_nccl * 1e3, "max_abs_diff_vs_nccl_path": err} if p2p else {}),
-            "config": {"workload": "C5 sequence-sharded long-context decode: 64q/8kv, K8 affine + V3 polar, "
-                                   "131072 positions per GPU, partial states all-gathered and merged per layer",
-                       "context_total": world * S, "bytes_per_gpu_per_layer_step": nbytes,
-                       "exchange_bytes_per_rank": nq * (DIM + 2) * 4, "timing": mode + ", CUDA events, max over ranks"}}))
+    rec = {"workload": "C5 sequence-sharded long-context decode: 64q/8kv, K8 affine + V3 polar, "
+                       "131072 positions per GPU", "n_gpus": world, "context_total": world * S,
+           "bytes_per_gpu_per_layer_step": nbytes, "exchange_bytes_per_rank": nq * (DIM + 2) * 4}
     if world > 1:
+        sh = ShardedLayers(tq, [q[l] for l in range(layers)], ks, vs, scale, pq.signs, dev, world, nq, nkv,
+                           torch.float16)
+        sh.step()
+        torch.cuda.synchronize()
+        from turboquant_mlx_b200.distributed import sequence_parallel_decode
+        ref0 = sequence_parallel_decode(q[0], k=ks[0], v=vs[0], attn_scale=scale, out_dtype=torch.float16)
+        rec["max_abs_diff_vs_nccl_allgather_path"] = float((ref0[0].float() - sh.outs[0].float()).abs().max())
+        g = _capture(torch, sh.step, dev)
+        gk = _capture(torch, sh.kernels_only, dev)
+        ms = _timed(torch, dist, world, dev, g.replay, max(args.steps, 50), 3) / layers
+        ms_k = _timed(torch, dist, world, dev, gk.replay, max(args.steps, 50), 3) / layers
+        sh.ex.check()
+    else:
+        outs = [torch.empty((1, nq, DIM), dtype=torch.float16, device=dev) for _ in range(layers)]
+
+        def step():
+            for l in range(layers):
+                tq.flash_decode(q[l], k=ks[l], v=vs[l], attn_scale=scale, kv_stable=True, q_stable=True, out=outs[l])
+        g = _capture(torch, step, dev)
+        ms = ms_k = _timed(torch, dist, world, dev, g.replay, max(args.steps, 50), 3) / layers
+    rec.update({"GBs_aggregate": world * nbytes / ms / 1e6, "us_per_layer_step": ms * 1e3,
+                "us_kernel_only": ms_k * 1e3, "per_gpu_frac_of_peak": nbytes / ms / 1e6 / peak, "peak": peak,
+                "peak_kind": kind, "tensor_core_path": tq._lib.lib().tq_flash_decode_last_kernel() == 1,
+                "decode_kernel_status": tq.kernels.flash_status(dev, nkv)})
+    return rec
+
+
+def workload_c5(args):
+    """Config 5 alone (see c5_measure); under torchrun the sequence is sharded across the ranks."""
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        dist.init_process_group("nccl", device_id=dev)
+    tq = entry.load_package()
+    rec = c5_measure(args, tq, torch, dist, dev, world, rank)
+    if rank == 0:
+        print(json.dumps({"metric": METRIC, "unit": "GB/s", "n_gpus": world, "value": rec["GBs_aggregate"],
+                          "scaling": "weak", "config": rec}))
+    if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 
@@ -709,8 +784,8 @@ def main():
     ap.add_argument("--kernel-only", action="store_true",
                     help="plain launches of the flash-decode kernel only (no graph, no e2e): profiler case")
     ap.add_argument("--ctx", type=int, default=0, help="c4p: prompt length (default 32768)")
-    ap.add_argument("--exchange", default="fused", choices=["nccl", "p2p", "fused"],
-                    help="c5: how the partial states travel between the ranks")
+    ap.add_argument("--no-c5", action="store_true", help="N > 1: skip the secondary config-5 record")
+    ap.add_argument("--splits", type=int, default=0, help="c3: force the split count of the decode kernel (0 = planner)")
     ap.add_argument("--workload", default="c2", choices=["c2", "c1", "c3", "c5", "c4p", "c4"],
                     help="c2 = the headline benchmark; c1 / c3 = secondary measurements of other configurations")
     args = ap.parse_args()

@@ -182,9 +182,10 @@ typedef struct tq_flash_params {
   const float* k_signs_host;
 
   int32_t v_format, v_bits, v_group;
-  int32_t kv_stable;           /* 1: no K / V row or norm read by this call is written by the kernel launched
-                                  immediately before it on the stream, so the kernel may prefetch K / V while
-                                  that kernel is still finishing (programmatic dependent launch); 0: wait first */
+  int32_t kv_stable;           /* 1: no K / V row or norm read by this call is written by a kernel that may still
+                                  be running when this call's kernel starts (the decode kernel is launched with
+                                  programmatic stream serialization: it may start while the kernels in front of
+                                  it on the stream drain), so it may fetch K / V at once; 0: wait first */
   const void* v_data;
   int64_t v_batch_stride, v_head_stride;
   const float* v_norms;
@@ -223,25 +224,45 @@ typedef struct tq_flash_params {
   float* peer_l[8];
   float* peer_acc[8];
   uint32_t* peer_counter[8];
+  /* 1: the same promise as kv_stable for the query (and new_k / new_v): with both set the kernel
+   * reads its inputs without waiting for the launches in front of it and only waits before it
+   * first writes the workspace, so consecutive decode launches overlap (each takes half of every
+   * SM).  0: wait before reading the query. */
+  int32_t q_stable;
+  /* Optional in-launch cache append (no reference counterpart; it takes the place of the
+   * quantize-on-insert launch of cache.py:131-150 / v_only_cache.py:46-60 in front of a decode
+   * step): new_k / new_v are the raw rows (batch, n_kv_heads, dim) of the step's own token.
+   * seq_len counts that token; the kernel stores / quantizes the rows into position
+   * seq_len - 1 of k_data / v_data (and the norms) and attends over them in the same launch.
+   * Tensor-core path only: packed values; keys packed, or dense fp16 with new_dtype TQ_F16.
+   * k_boundaries_host / v_boundaries_host: the 2^bits - 1 codebook boundaries. */
+  int32_t new_dtype;
+  const void* new_k;
+  const void* new_v;
+  int64_t new_k_batch_stride, new_k_head_stride, new_v_batch_stride, new_v_head_stride;
+  const float* k_boundaries_host;
+  const float* v_boundaries_host;
 } tq_flash_params;
 
 /* Workspace contract: 16-byte aligned, at least tq_flash_decode_workspace_bytes()
  * bytes.  It starts with a header of tq_flash_decode_header_bytes(batch,
- * n_kv_heads) bytes (a status block and split counters) that must be zero the
- * first time the workspace is used; every call leaves the counters at zero, so
- * a workspace can be reused by later calls with the same batch * n_kv_heads.
+ * n_kv_heads) bytes (a status block and one split counter per (batch, kv head)) that
+ * must be zero the first time the workspace is used; every call leaves the counters at
+ * zero, so a workspace can be reused by later calls with the same batch * n_kv_heads.
  * Zero the header again before reusing the memory with a different
- * batch * n_kv_heads or after any other use.  Calls that share a workspace must
- * not overlap on the GPU. */
+ * batch * n_kv_heads or after any other use.  Calls on one stream may share a
+ * workspace (the kernel orders its workspace accesses after the preceding launch);
+ * calls on different streams must not. */
 int64_t tq_flash_decode_header_bytes(int batch, int n_kv_heads);
 int64_t tq_flash_decode_workspace_bytes(const tq_flash_params* p);
 int tq_flash_decode(const tq_flash_params* p);
 /* Which kernel the calling thread's last tq_flash_decode launched: 1 = tensor-core
- * path (dim 128, n_rep <= 8, fp16 or 3/4-bit packed keys, 3/4-bit packed values,
- * 16-byte aligned rows, no mask), 0 = general float32 path, -1 = none yet.  The
- * workspace's first 16 bytes are a status header for the tensor-core path: the
- * caller zero-fills it once; a kernel whose bounded wait gives up writes a
- * non-zero word there.  Diagnostic, no reference counterpart. */
+ * path (dim 128, n_rep <= 8, no mask, 16-byte aligned rows; keys fp16, 3/4-bit packed
+ * or 8-bit group-64 affine; values 3/4-bit packed, or 4-bit group-64 affine with fp16
+ * or affine keys), 0 = general float32 path, -1 = none yet.  The workspace's first
+ * 16 bytes are a status header for the tensor-core path: the caller zero-fills it
+ * once; a kernel whose bounded wait gives up writes a non-zero word there (and its
+ * output is invalid).  Diagnostic, no reference counterpart. */
 int tq_flash_decode_last_kernel(void);
 
 /* Merge n_parts partial states (split-K chunks or ranks): part i of row r is at
@@ -299,19 +320,27 @@ int tq_prefill_sdpa(const void* q, const void* k, const void* v, void* out, int 
  * the calling rank; one of them is the rank's own buffer) and then stores `epoch` to
  * peer_flags[p] with release semantics at system scope.  tq_peer_wait returns, in
  * stream order, once each of the n_ranks 32-bit words at `flags` (this rank's own
- * flag array) has reached `epoch`; its wait is bounded, and when it gives up it writes
- * 21 + the missing rank to *status.  The host arrays are read during the call only.
+ * flag array) has reached `epoch`; its wait is bounded (tq_set_peer_wait_limit_ms), and when it gives
+ * up it writes 21 + the missing rank to *status.  The host arrays are read during the call only.
  * No reference counterpart: the reference runs on one device. */
 int tq_peer_push(const void* src, int64_t nbytes, void* const* peer_dst, void* const* peer_flags,
                  int n_peers, uint32_t epoch, void* stream);
 int tq_peer_wait(const void* flags, int n_ranks, uint32_t epoch, int* status, void* stream);
 /* tq_merge_partials whose kernel first performs tq_peer_wait's bounded wait (one launch
- * instead of two): the parts were pushed by the peers with tq_peer_push. */
-int tq_merge_partials_after_peers(const void* flags, int n_ranks, uint32_t epoch, int* status,
+ * instead of two): the parts were pushed by the peers with tq_peer_push or by the decode
+ * kernel (tq_flash_params.peer_*).  `status` points at two zero-initialised ints: word 0
+ * receives 21 + the missing rank when the wait gives up, and the merge then writes NaN
+ * instead of a partial result; word 1 is scratch.  With reset_flags != 0 the kernel sets the
+ * n_ranks flag words back to zero once all of its blocks are past the wait, so a launch with a
+ * constant `epoch` (the additions expected per exchange) can be replayed from a CUDA graph. */
+int tq_merge_partials_after_peers(void* flags, int n_ranks, uint32_t epoch, int* status, int reset_flags,
                                   const float* part_m, int64_t m_part_stride, const float* part_l,
                                   int64_t l_part_stride, const float* part_acc, int64_t acc_part_stride,
                                   int n_parts, int64_t n_rows, int dim, const float* v_signs_host,
                                   void* out, int out_dtype, int64_t out_row_stride, void* stream);
+/* Time limit of the peer waits above in milliseconds (default 2000; <= 0 only queries).
+ * Returns the previous limit.  The waits stay bounded whatever the value. */
+int tq_set_peer_wait_limit_ms(int ms);
 
 #ifdef __cplusplus
 }

@@ -52,11 +52,27 @@ def test_wait_gives_up_and_names_the_missing_rank(tq):
     L, st = tq._lib.lib(), tq._lib.stream_ptr(dev)
     flags = torch.tensor([5, 5, 4, 5], dtype=torch.int32, device=dev)      # rank 2 never reached epoch 5
     status = torch.zeros(4, dtype=torch.int32, device=dev)
-    t0 = time.perf_counter()
-    tq._lib.check(L.tq_peer_wait(tq._lib.ptr(flags), 4, 5, tq._lib.ptr(status), st))
-    torch.cuda.synchronize()
-    assert time.perf_counter() - t0 < 30.0           # bounded
-    assert int(status[0]) == 21 + 2
+    prev = L.tq_set_peer_wait_limit_ms(100)          # the default limit is seconds; keep the test short
+    assert prev == 2000 and L.tq_set_peer_wait_limit_ms(0) == 100
+    try:
+        t0 = time.perf_counter()
+        tq._lib.check(L.tq_peer_wait(tq._lib.ptr(flags), 4, 5, tq._lib.ptr(status), st))
+        torch.cuda.synchronize()
+        assert 0.05 < time.perf_counter() - t0 < 10.0    # the time limit, not an iteration count, ended it
+        assert int(status[0]) == 21 + 2
+        # a merge gated on the same incomplete flags reports the rank and hands out NaN, not a partial merge
+        status.zero_()
+        g = torch.Generator(device=dev).manual_seed(3)
+        m = torch.randn((4, 6), generator=g, device=dev)
+        l = torch.rand((4, 6), generator=g, device=dev) + 0.1
+        acc = torch.randn((4, 6, 128), generator=g, device=dev)
+        out = torch.zeros((6, 128), dtype=torch.float32, device=dev)
+        pq = tq.PolarQuantizer(128, 3, seed=43, device=dev)
+        tq.MergePlan(m, l, acc, pq.signs, out).run_after_peers(tq._lib.ptr(flags), 4, 5, tq._lib.ptr(status))
+        torch.cuda.synchronize()
+        assert int(status[0]) == 21 + 2 and bool(torch.isnan(out).all())
+    finally:
+        L.tq_set_peer_wait_limit_ms(prev)
     # the context is still usable and a later epoch that is complete passes at once
     status.zero_()
     tq._lib.check(L.tq_peer_wait(tq._lib.ptr(flags), 4, 4, tq._lib.ptr(status), st))
@@ -80,3 +96,27 @@ def test_merge_gated_on_flags_equals_plain_merge(tq):
     torch.cuda.synchronize()
     assert int(status[0]) == 0 and torch.equal(out, ref)
     assert np.isfinite(out.cpu().numpy()).all()
+
+
+def test_gated_merge_resets_its_flags_for_graph_replay(tq):
+    """reset_flags: the launch zeroes the flag words once every block is past the gate, so the same
+    call (constant expected count) can be replayed; counters pushed between replays gate each one."""
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(2)
+    parts, rows, D = 2, 28, 128
+    m = torch.randn((parts, rows), generator=g, device=dev)
+    l = torch.rand((parts, rows), generator=g, device=dev) + 0.1
+    acc = torch.randn((parts, rows, D), generator=g, device=dev)
+    pq = tq.PolarQuantizer(D, 3, seed=43, device=dev)
+    ref = tq.merge_partials(m, l, acc, pq.signs, torch.float32)
+    out = torch.empty((rows, D), dtype=torch.float32, device=dev)
+    flags = torch.zeros((parts,), dtype=torch.int32, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    plan = tq.MergePlan(m, l, acc, pq.signs, out)
+    for _ in range(3):
+        flags.add_(4)                 # what the peers' decode kernels would add (4 groups each)
+        out.zero_()
+        plan.run_after_peers(tq._lib.ptr(flags), parts, 4, tq._lib.ptr(status), reset_flags=True)
+        torch.cuda.synchronize()
+        assert int(status[0]) == 0 and int(status[1]) == 0 and torch.equal(out, ref)
+        assert int(flags.abs().sum()) == 0

@@ -56,6 +56,11 @@ class FlashParams(ctypes.Structure):
         ("n_peers", c_int32), ("peer_reserved", c_int32),
         ("peer_m", c_void_p * 8), ("peer_l", c_void_p * 8), ("peer_acc", c_void_p * 8),
         ("peer_counter", c_void_p * 8),
+        ("q_stable", c_int32), ("new_dtype", c_int32),
+        ("new_k", c_void_p), ("new_v", c_void_p),
+        ("new_k_batch_stride", c_int64), ("new_k_head_stride", c_int64),
+        ("new_v_batch_stride", c_int64), ("new_v_head_stride", c_int64),
+        ("k_boundaries_host", POINTER(c_float)), ("v_boundaries_host", POINTER(c_float)),
     ]
 
 
@@ -98,8 +103,10 @@ _SIGNATURES = {
                                         c_void_p, c_void_p, c_int64, c_void_p]),
     "tq_affine_dequantize": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,
                                      c_void_p, c_int, c_void_p]),
-    "tq_merge_partials_after_peers": (c_int, [c_void_p, c_int, c_uint32, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int,
-                                  c_int64, c_int, _FP, c_void_p, c_int, c_int64, c_void_p]),
+    "tq_merge_partials_after_peers": (c_int, [c_void_p, c_int, c_uint32, c_void_p, c_int, c_void_p, c_int64, c_void_p,
+                                              c_int64, c_void_p, c_int64, c_int, c_int64, c_int, _FP, c_void_p,
+                                              c_int, c_int64, c_void_p]),
+    "tq_set_peer_wait_limit_ms": (c_int, [c_int]),
     "tq_peer_push": (c_int, [c_void_p, c_int64, POINTER(c_void_p), POINTER(c_void_p), c_int, c_uint32, c_void_p]),
     "tq_peer_wait": (c_int, [c_void_p, c_int, c_uint32, c_void_p, c_void_p]),
     "tq_prefill_sdpa": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,

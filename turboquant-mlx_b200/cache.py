@@ -59,7 +59,14 @@ class TurboQuantKVCache:
 
     def __init__(self, bits: int = 3, seed: int = 42, fused: bool = False,
                  sparse_v_threshold: float | None = None, v_only: bool = False,
-                 k_bits: int | None = None, v_bits: int | None = None):
+                 k_bits: int | None = None, v_bits: int | None = None,
+                 defer_append: bool = False, inputs_stable: bool = False):
+        """`defer_append` / `inputs_stable` (fused caches, additions to the reference's
+        arguments): see `VOnlyTurboQuantCache` - a one-token insert is recorded and carried out
+        by the decode attention's own launch; consecutive decode launches may overlap."""
+        self.defer_append = defer_append and fused and not v_only
+        self.inputs_stable = inputs_stable
+        self._pending = None
         self.quant_bits = bits
         self.k_bits = bits if k_bits is None else k_bits
         self.v_bits = bits if v_bits is None else v_bits
@@ -151,6 +158,7 @@ class TurboQuantKVCache:
 
     def dequantized(self, dtype=None):
         """(K, V) (B, H, offset, D) dequantized from storage (K is None in v_only mode)."""
+        self.flush_pending()
         dtype = dtype or self._dtype or torch.float16
         B, H = self.v_packed.shape[0], self.v_packed.shape[1]
         total = self.offset
@@ -161,10 +169,36 @@ class TurboQuantKVCache:
         v, _ = self._full_dequant(self.v_packed, self.v_norms, self._v_q, self._v_dim, B, H, total, dtype)
         return k, v[..., :total, :]
 
+    def flush_pending(self):
+        """Materialise a deferred one-token insert with the ordinary quantize kernels."""
+        if getattr(self, "_pending", None) is None:
+            return
+        k_row, v_row = self._pending
+        self._pending = None
+        self.offset -= 1
+        defer, self.defer_append = self.defer_append, False
+        try:
+            self.update_and_fetch(k_row.unsqueeze(2), v_row.unsqueeze(2))
+        finally:
+            self.defer_append = defer
+
+    def take_pending(self):
+        rows, self._pending = getattr(self, "_pending", None), None
+        return rows
+
     def update_and_fetch(self, keys, values):
+        self.flush_pending()
         B, H, S, k_dim = keys.shape
         v_dim = values.shape[3]
         self._dtype = keys.dtype
+        if (getattr(self, "defer_append", False) and S == 1 and keys.is_cuda and self.k_packed is not None
+                and self.offset + 1 <= self.v_packed.shape[2] and k_dim == 128 and v_dim == 128
+                and self.k_packed.shape[:2] == (B, H) and keys.dtype == values.dtype
+                and self.k_bits in (3, 4) and self.v_bits in (3, 4)):
+            self._pending = (keys[:, :, 0, :], values[:, :, 0, :])
+            self.offset += 1
+            return (_zero(keys.dtype, keys.device).expand(B, H, self.offset, k_dim),
+                    _zero(values.dtype, values.device).expand(B, H, self.offset, v_dim))
         self._ensure_quantizer(k_dim, v_dim, values.device)
         self._ensure_storage(B, H, S, values.device)
         prev = self.offset
@@ -239,6 +273,7 @@ class TurboQuantKVCache:
 
     @property
     def state(self):
+        self.flush_pending()
         if self.v_packed is None and self.k_packed is None:
             return []
         parts = []
@@ -291,6 +326,7 @@ class TurboQuantKVCache:
         return True
 
     def trim(self, n):
+        self.flush_pending()
         n = min(self.offset, n)
         self.offset -= n
         self._k_deq_buf = None

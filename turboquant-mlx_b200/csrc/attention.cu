@@ -394,8 +394,8 @@ flash_generic_kernel(const FlashArgs a) {
 // merge of partial states (split-K chunks or ranks)
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void merge_partials_kernel(const float* __restrict__ pm, int64_t sm, const float* __restrict__ pl,
-                                      int64_t sl, const float* __restrict__ pacc, int64_t sa,
+__global__ void merge_partials_kernel(const float* pm, int64_t sm, const float* pl,
+                                      int64_t sl, const float* pacc, int64_t sa,
                                       int n_parts, int64_t n_rows,
                                       int dim, int rotate, SignMask signs, int finalize, T* out,
                                       int64_t out_row_stride, int64_t rows_per_batch,
@@ -407,19 +407,47 @@ __global__ void merge_partials_kernel(const float* __restrict__ pm, int64_t sm, 
   // a decode kernel launched behind this merge with programmatic stream serialization may set up
   // now; it waits for this grid's completion before it reads the query or touches its workspace
   if (e == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  bool gate_failed = false;
   if (gate.flags != nullptr) {
-    // parts pushed by peer GPUs: one thread per rank waits (bounded) for that rank's flag
+    // parts pushed by peer GPUs: one thread per rank waits for that rank's flag, bounded by a time
+    // limit on the GPU-wide nanosecond timer (and by an iteration count as a second bound)
+    __shared__ int failed_s;
+    if (e == 0) failed_s = 0;
+    __syncthreads();
     if (e < gate.n) {
       bool seen = false;
-      for (uint32_t it = 0; it < (1u << 21) && !seen; ++it) {
+      unsigned long long t0;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+      for (uint32_t it = 0; it < (1u << 28) && !seen; ++it) {
         uint32_t v;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(gate.flags + e) : "memory");
         seen = (int32_t)(v - gate.epoch) >= 0;
-        if (!seen) __nanosleep(50);
+        if (!seen) {
+          __nanosleep(50);
+          unsigned long long t1;
+          asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+          if (t1 - t0 > gate.limit_ns) break;
+        }
       }
-      if (!seen) atomicExch(gate.status, 21 + e);
+      if (!seen) {
+        atomicExch(gate.status, 21 + e);
+        failed_s = 1;
+      }
     }
     __syncthreads();
+    gate_failed = failed_s != 0;
+    if (gate.reset) {
+      // every block has to pass the gate before the flags go back to zero: the last one does it
+      if (e == 0) {
+        __threadfence();
+        const int prev = atomicAdd(gate.done, 1);
+        if (prev == (int)gridDim.x - 1) {
+          for (int i = 0; i < gate.n; ++i)
+            asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(gate.flags + i), "r"(0u) : "memory");
+          *gate.done = 0;
+        }
+      }
+    }
   }
   float m_star = -INFINITY;
   float l_star = 0.f, acc = 0.f;
@@ -430,9 +458,9 @@ __global__ void merge_partials_kernel(const float* __restrict__ pm, int64_t sm, 
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       const bool on = i < n_parts;
-      li[i] = on ? pl[(int64_t)i * sl + row] : 0.f;
-      mi[i] = on ? pm[(int64_t)i * sm + row] : -INFINITY;
-      ai[i] = on ? pacc[(int64_t)i * sa + row * dim + e] : 0.f;
+      li[i] = on ? __ldcg(pl + (int64_t)i * sl + row) : 0.f;
+      mi[i] = on ? __ldcg(pm + (int64_t)i * sm + row) : -INFINITY;
+      ai[i] = on ? __ldcg(pacc + (int64_t)i * sa + row * dim + e) : 0.f;
     }
 #pragma unroll
     for (int i = 0; i < 16; ++i)
@@ -446,16 +474,16 @@ __global__ void merge_partials_kernel(const float* __restrict__ pm, int64_t sm, 
     }
   } else {
     for (int i = 0; i < n_parts; ++i) {
-      const float li = pl[(int64_t)i * sl + row];
-      const float mi = pm[(int64_t)i * sm + row];
+      const float li = __ldcg(pl + (int64_t)i * sl + row);
+      const float mi = __ldcg(pm + (int64_t)i * sm + row);
       if (li > 0.f) m_star = fmaxf(m_star, mi);
     }
     for (int i = 0; i < n_parts; ++i) {
-      const float li = pl[(int64_t)i * sl + row];
+      const float li = __ldcg(pl + (int64_t)i * sl + row);
       if (!(li > 0.f)) continue;   // empty or fully masked chunk merges as a no-op
-      const float w = __expf(pm[(int64_t)i * sm + row] - m_star);
+      const float w = __expf(__ldcg(pm + (int64_t)i * sm + row) - m_star);
       l_star += li * w;
-      acc += pacc[(int64_t)i * sa + row * dim + e] * w;
+      acc += __ldcg(pacc + (int64_t)i * sa + row * dim + e) * w;
     }
   }
   if (!finalize) {
@@ -481,6 +509,7 @@ __global__ void merge_partials_kernel(const float* __restrict__ pm, int64_t sm, 
     res = sh[e] * sign_at(signs, e) * (1.0f / dim);
   }
   res = l_star > 0.f ? res / l_star : 0.f;
+  if (gate_failed) res = __int_as_float(0x7fc00000);   // a rank never pushed: do not hand out a partial merge
   const int64_t bb = row / rows_per_batch, hh2 = row - bb * rows_per_batch;
   out[bb * out_batch_stride + hh2 * out_row_stride + e] = from_f32<T>(res);
 }
@@ -491,7 +520,7 @@ int launch_merge(const float* pm, int64_t sm, const float* pl, int64_t sl, const
                  int64_t out_row_stride, int64_t rows_per_batch, int64_t out_batch_stride,
                  float* om, float* ol, float* oacc, cudaStream_t st, const PeerGate* gate_in) {
   if (n_rows <= 0) return TQ_OK;
-  PeerGate gate = {nullptr, 0, 0u, nullptr};
+  PeerGate gate = {nullptr, 0, 0u, nullptr, 0, nullptr, 0ull};
   if (gate_in) gate = *gate_in;
   const dim3 grid((unsigned)n_rows), block(dim);
   if (!finalize || out_dtype == TQ_F32)
@@ -648,6 +677,7 @@ extern "C" int tq_sparse_v_matvec(const float* weights, int64_t w_head_stride,
   TQ_REQUIRE(n_kv_heads > 0 && n_rep > 0 && seq_len >= 0, TQ_ERR_BAD_ARG, "bad head / seq count");
   TQ_REQUIRE(centroids_host != nullptr, TQ_ERR_BAD_ARG, "centroids pointer is NULL");
   TQ_REQUIRE(out != nullptr, TQ_ERR_BAD_ARG, "NULL output pointer");
+  TQ_REQUIRE(seq_len == 0 || (weights && v_packed && v_norms), TQ_ERR_BAD_ARG, "NULL tensor pointer");
   const int n_q = n_kv_heads * n_rep;
   const size_t need = tq_sparse_v_workspace_bytes(n_q, seq_len, dim);
   TQ_REQUIRE(workspace && workspace_bytes >= need, TQ_ERR_WORKSPACE,
@@ -696,7 +726,7 @@ extern "C" int tq_merge_partials(const float* part_m, int64_t m_part_stride, con
                       out_row_stride, n_rows, 0, nullptr, nullptr, nullptr, (cudaStream_t)stream);
 }
 
-extern "C" int tq_merge_partials_after_peers(const void* flags, int n_ranks, uint32_t epoch, int* status,
+extern "C" int tq_merge_partials_after_peers(void* flags, int n_ranks, uint32_t epoch, int* status, int reset_flags,
                                              const float* part_m, int64_t m_part_stride, const float* part_l,
                                              int64_t l_part_stride, const float* part_acc,
                                              int64_t acc_part_stride, int n_parts, int64_t n_rows, int dim,
@@ -711,7 +741,9 @@ extern "C" int tq_merge_partials_after_peers(const void* flags, int n_ranks, uin
   SignMask sg = {};
   int rc;
   if (v_signs_host && (rc = make_sign_mask(v_signs_host, dim, &sg))) return rc;
-  const PeerGate gate = {static_cast<const uint32_t*>(flags), n_ranks, epoch, status};
+  // status[0]: give-up code; status[1]: blocks past the gate (reset_flags only), zero between calls
+  const PeerGate gate = {static_cast<uint32_t*>(flags), n_ranks, epoch, status, reset_flags != 0, status + 1,
+                         peer_wait_limit_ns()};
   return launch_merge(part_m, m_part_stride, part_l, l_part_stride, part_acc, acc_part_stride,
                       n_parts, n_rows, dim, v_signs_host != nullptr, sg, 1, out, out_dtype,
                       out_row_stride, n_rows, 0, nullptr, nullptr, nullptr, (cudaStream_t)stream, &gate);
@@ -782,6 +814,7 @@ extern "C" int tq_sparse_v_matvec_noalloc(const float* weights, int64_t w_head_s
   TQ_REQUIRE(n_kv_heads > 0 && n_rep > 0 && seq_len >= 0, TQ_ERR_BAD_ARG, "bad head / seq count");
   TQ_REQUIRE(centroids_host != nullptr, TQ_ERR_BAD_ARG, "centroids pointer is NULL");
   TQ_REQUIRE(out != nullptr, TQ_ERR_BAD_ARG, "NULL output pointer");
+  TQ_REQUIRE(seq_len == 0 || (weights && v_packed && v_norms), TQ_ERR_BAD_ARG, "NULL tensor pointer");
   const int n_q = n_kv_heads * n_rep;
   const size_t need = tq_sparse_v_workspace_bytes(n_q, seq_len, dim);
   TQ_REQUIRE(need <= TQ_SPARSE_V_STATIC_BYTES, TQ_ERR_WORKSPACE,

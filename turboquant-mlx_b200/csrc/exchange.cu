@@ -6,16 +6,24 @@
 // no counterpart.
 //
 // The pushing kernel never waits; the waiting kernel only waits for pushes, so no two
-// kernels wait on one another.  The wait is bounded: when it gives up it writes a
-// status word and returns, and the merge that follows produces a wrong result that
-// the host can tell from the status.
+// kernels wait on one another.  The wait is bounded by a time limit on the GPU-wide
+// nanosecond timer (tq_set_peer_wait_limit_ms, 2 s unless changed: ordinary host skew
+// between ranks must not trip it) and by an iteration count: when it gives up it writes a
+// status word and returns; a merge gated on the same flags then writes NaN, and the host
+// reads the status at its next synchronisation point.
+#include <atomic>
+
 #include "common.cuh"
+#include "flash.cuh"
 
 namespace tq {
+
+static std::atomic<unsigned long long> g_wait_limit_ns{2000ull * 1000ull * 1000ull};
+unsigned long long peer_wait_limit_ns() { return g_wait_limit_ns.load(); }
+
 namespace {
 
 constexpr int kMaxPeers = 16;
-constexpr uint32_t kWaitSpins = 1u << 21;     // x ~50 ns sleep: gives up after roughly 0.1-0.2 s
 
 struct PushArgs {
   const uint4* src;
@@ -36,14 +44,20 @@ __global__ void __launch_bounds__(256) peer_push_kernel(const PushArgs a) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.flag[p]), "r"(a.epoch) : "memory");
 }
 
-__global__ void peer_wait_kernel(const uint32_t* flags, int n, uint32_t epoch, int* status) {
+__global__ void peer_wait_kernel(const uint32_t* flags, int n, uint32_t epoch, int* status,
+                                 unsigned long long limit_ns) {
   const int i = threadIdx.x;
   if (i >= n) return;
-  for (uint32_t it = 0; it < kWaitSpins; ++it) {
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+  for (uint32_t it = 0; it < (1u << 28); ++it) {
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + i) : "memory");
     if ((int32_t)(v - epoch) >= 0) return;
     __nanosleep(50);
+    unsigned long long t1;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+    if (t1 - t0 > limit_ns) break;
   }
   atomicExch(status, 21 + i);   // rank i never arrived
 }
@@ -80,6 +94,12 @@ extern "C" int tq_peer_wait(const void* flags, int n_ranks, uint32_t epoch, int*
   TQ_REQUIRE(n_ranks >= 1 && n_ranks <= kMaxPeers, TQ_ERR_BAD_ARG, "tq_peer_wait: 1..%d ranks, got %d", kMaxPeers,
              n_ranks);
   peer_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint32_t*>(flags), n_ranks,
-                                                                    epoch, status);
+                                                                    epoch, status, peer_wait_limit_ns());
   return check_launch("tq_peer_wait");
+}
+
+extern "C" int tq_set_peer_wait_limit_ms(int ms) {
+  const int prev = (int)(tq::g_wait_limit_ns.load() / 1000000ull);
+  if (ms > 0) tq::g_wait_limit_ns.store((unsigned long long)ms * 1000000ull);
+  return prev;
 }

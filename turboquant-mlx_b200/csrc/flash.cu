@@ -1,6 +1,5 @@
 // tq_flash_decode: argument validation, split-K planning, kernel choice, merge.
 #include <math.h>
-#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -71,9 +70,21 @@ static int validate(const tq_flash_params* p) {
   if (p->out_mode == 0)
     TQ_REQUIRE(p->out && p->out_dtype >= TQ_F32 && p->out_dtype <= TQ_BF16, TQ_ERR_BAD_ARG,
                "mode 0 needs out and a valid out_dtype");
-  else
+  else {
     TQ_REQUIRE(p->part_m && p->part_l && p->part_acc, TQ_ERR_BAD_ARG,
                "mode 1 needs part_m, part_l and part_acc");
+    TQ_REQUIRE((reinterpret_cast<uintptr_t>(p->part_acc) & 15) == 0, TQ_ERR_MISALIGNED,
+               "part_acc must be 16-byte aligned (its rows are stored as 16-byte vectors)");
+  }
+  if (p->new_k || p->new_v) {
+    TQ_REQUIRE(p->new_k && p->new_v, TQ_ERR_BAD_ARG, "new_k and new_v must be given together");
+    TQ_REQUIRE(p->new_dtype >= TQ_F32 && p->new_dtype <= TQ_BF16, TQ_ERR_BAD_ARG, "bad new_dtype");
+    TQ_REQUIRE(p->v_format == TQ_KV_POLAR && p->v_boundaries_host, TQ_ERR_UNSUPPORTED,
+               "the in-launch append needs packed values and v_boundaries_host");
+    TQ_REQUIRE(p->k_format != TQ_KV_AFFINE, TQ_ERR_UNSUPPORTED, "the in-launch append does not cover affine keys");
+    TQ_REQUIRE(p->k_format != TQ_KV_POLAR || (p->k_boundaries_host && p->k_signs_host), TQ_ERR_BAD_ARG,
+               "appending packed keys needs k_boundaries_host and k_signs_host");
+  }
   return TQ_OK;
 }
 
@@ -108,6 +119,14 @@ static int fill_args(const tq_flash_params* p, FlashArgs* a) {
   a->v_bits = p->v_bits;
   a->v_group = p->v_group > 0 ? p->v_group : p->dim;
   a->kv_stable = p->kv_stable;
+  a->q_stable = p->q_stable;
+  a->new_k = p->new_k;
+  a->new_v = p->new_v;
+  a->new_dtype = p->new_dtype;
+  a->nk_batch_stride = p->new_k_batch_stride;
+  a->nk_head_stride = p->new_k_head_stride;
+  a->nv_batch_stride = p->new_v_batch_stride;
+  a->nv_head_stride = p->new_v_head_stride;
   a->v_data = p->v_data;
   a->v_batch_stride = p->v_batch_stride;
   a->v_head_stride = p->v_head_stride;
@@ -125,32 +144,48 @@ static int fill_args(const tq_flash_params* p, FlashArgs* a) {
   int rc;
   if (p->k_format == TQ_KV_POLAR) {
     for (int i = 0; i < (1 << p->k_bits); ++i) a->k_cent.v[i] = p->k_centroids_host[i];
-    if (!p->q_prerotated && (rc = make_sign_mask(p->k_signs_host, p->dim, &a->k_signs))) return rc;
+    if ((!p->q_prerotated || p->new_k) && (rc = make_sign_mask(p->k_signs_host, p->dim, &a->k_signs))) return rc;
+    if (p->new_k) make_raw_thresholds(p->k_boundaries_host, (1 << p->k_bits) - 1, p->dim, &a->k_thr);
   }
   if (p->v_format == TQ_KV_POLAR) {
     for (int i = 0; i < (1 << p->v_bits); ++i) a->v_cent.v[i] = p->v_centroids_host[i];
     if ((rc = make_sign_mask(p->v_signs_host, p->dim, &a->v_signs))) return rc;
+    if (p->new_v) make_raw_thresholds(p->v_boundaries_host, (1 << p->v_bits) - 1, p->dim, &a->v_thr);
   }
   return TQ_OK;
 }
 
 static void make_plan(const tq_flash_params* p, const FlashArgs& a, Plan* plan) {
-  static const bool force_generic = getenv("TQ_FORCE_GENERIC") != nullptr;   // debugging aid
-  plan->mma = !force_generic && flash_mma_supported(a);
+  plan->mma = flash_mma_supported(a);
   const int mult = plan->mma ? flash_mma_chunk_multiple() : 32;
   const int rgroups = plan->mma ? 1 : (a.n_rep + 7) / 8;
   const int64_t groups = (int64_t)a.batch * a.n_kv_heads * rgroups;
   const int64_t max_splits = (a.seq_len + mult - 1) / mult;
   int64_t splits = p->num_splits;
   if (splits <= 0) {
-    static const char* target_env = getenv("TQ_FLASH_TARGET_CTAS");           // tuning aid
-    const int64_t target = target_env ? atoi(target_env) : (plan->mma ? flash_mma_ctas_per_sm() : 2) * (int64_t)num_sms();
-    splits = target / groups;                          // round down: the grid must fit one wave
-    // The CTA that merges a group outlives the others; with launch overlap the next call's CTAs land
-    // on time only if those SMs are spare.  Leaving one SM per group free pays off when it makes the
-    // chunks barely longer (measured: +1.6 % at 4 groups x 37 -> 36 splits, -6 % at 8 x 18 -> 17).
-    if (plan->mma && !target_env && (target - groups) / groups >= 32) splits = (target - groups) / groups;
-    if (splits < 1) splits = 1;   // more groups than CTA slots: one CTA per group (splitting further measured slower)
+    const int64_t sms = num_sms();
+    // Tensor-core kernel: two CTAs fit on an SM.  A call that may overlap its neighbours on the
+    // stream (kv_stable and q_stable) takes one CTA per SM, so that the next launch's CTAs run
+    // beside this one's and its prologue and epilogue hide behind their streaming; a call that
+    // runs alone fills both halves of every SM.
+    const int per_sm = plan->mma ? ((a.kv_stable && a.q_stable) ? 1 : flash_mma_ctas_per_sm()) : 2;
+    const int64_t target = per_sm * sms;
+    splits = target / groups;                          // round down: the grid fits one wave
+    if (splits < 1) {
+      // more groups than CTA slots: several waves.  Pick the split count whose CTA count comes
+      // closest to a whole number of CTAs per SM (e.g. 256 groups on 148 SMs: 4 splits = 1024
+      // CTAs = 6.9 per SM instead of 1.7), keeping at least 1024 positions per CTA.
+      splits = 1;
+      double best = 1e30;
+      for (int64_t s = 1; s <= 8 && (s == 1 || a.seq_len / s >= 1024); ++s) {
+        const double per = (double)(groups * s) / (double)sms;
+        const double waste = ceil(per) / per;
+        if (waste < best - 0.02) {
+          best = waste;
+          splits = s;
+        }
+      }
+    }
     const int64_t by_len = (a.seq_len + 127) / 128;   // at least 128 positions per split
     if (splits > by_len) splits = by_len;
   }
@@ -163,7 +198,7 @@ static void make_plan(const tq_flash_params* p, const FlashArgs& a, Plan* plan) 
   plan->splits = (int)((a.seq_len + chunk - 1) / chunk);
 }
 
-// Workspace layout: [header][m][l][acc].  The header is a
+// Workspace layout: [header][acc][m][l].  The header is a
 // 16-byte status block (word 0 is set non-zero by a kernel whose bounded wait
 // gave up) followed by one split counter per (batch, kv head); the caller
 // zero-fills the workspace once when it allocates it and the kernel leaves the
@@ -174,7 +209,7 @@ static int64_t header_bytes(const tq_flash_params* p, const Plan&) {
 static int64_t partial_bytes(const tq_flash_params* p, const Plan& plan) {
   if (!plan.mma && p->out_mode == 1 && plan.splits == 1) return 0;
   const int64_t rows = (int64_t)p->batch * p->n_q_heads;
-  const int64_t parts = plan.splits + (plan.mma ? flash_mma_level1_parts() : 0);
+  const int64_t parts = plan.splits;
   return parts * rows * (p->dim + 2) * (int64_t)sizeof(float);
 }
 static int64_t workspace_need(const tq_flash_params* p, const Plan& plan) {
@@ -221,22 +256,16 @@ extern "C" int tq_flash_decode(const tq_flash_params* p) {
              (long long)p->workspace_bytes);
   const int64_t rows = (int64_t)p->batch * p->n_q_heads;
   const bool direct = partial_bytes(p, plan) == 0;
-  float *l1_acc = nullptr, *l1_m = nullptr, *l1_l = nullptr;
   if (direct) {
     a.part_m = p->part_m;
     a.part_l = p->part_l;
     a.part_acc = p->part_acc;
   } else {
-    // [acc level 0][acc level 1][m0][l0][m1][l1]: both accumulator blocks stay 16-byte aligned
+    // [acc][m][l]: the accumulator block stays 16-byte aligned
     float* ws = (float*)((char*)p->workspace + header_bytes(p, plan));
-    const int64_t n1 = plan.mma ? flash_mma_level1_parts() : 0;
     a.part_acc = ws;
-    l1_acc = ws + (int64_t)plan.splits * rows * p->dim;
-    float* sc = l1_acc + n1 * rows * p->dim;
-    a.part_m = sc;
-    a.part_l = sc + (int64_t)plan.splits * rows;
-    l1_m = sc + 2 * (int64_t)plan.splits * rows;
-    l1_l = l1_m + n1 * rows;
+    a.part_m = ws + (int64_t)plan.splits * rows * p->dim;
+    a.part_l = a.part_m + (int64_t)plan.splits * rows;
   }
   cudaStream_t st = (cudaStream_t)p->stream;
   g_last_kernel = plan.mma ? 1 : 0;
@@ -252,9 +281,6 @@ extern "C" int tq_flash_decode(const tq_flash_params* p) {
     mo.om = p->part_m;
     mo.ol = p->part_l;
     mo.oacc = p->part_acc;
-    mo.l1_m = l1_m;
-    mo.l1_l = l1_l;
-    mo.l1_acc = l1_acc;
     mo.n_peers = p->out_mode == 1 ? p->n_peers : 0;
     for (int i = 0; i < 8; ++i) {
       mo.peer_m[i] = p->peer_m[i];
@@ -265,6 +291,9 @@ extern "C" int tq_flash_decode(const tq_flash_params* p) {
     return launch_flash_mma(a, plan.splits, mo, st);
   }
   TQ_REQUIRE(p->n_peers == 0, TQ_ERR_UNSUPPORTED, "peer targets need the tensor-core decode path");
+  TQ_REQUIRE(p->new_v == nullptr, TQ_ERR_UNSUPPORTED,
+             "the in-launch append needs the tensor-core decode path (dim 128, n_rep <= 8, no mask, fp16 or "
+             "packed keys, new_k of the keys' type)");
   rc = launch_flash_generic(a, plan.splits, st);
   if (rc) return rc;
   if (direct) return TQ_OK;

@@ -25,7 +25,8 @@ struct FlashArgs {
   SignMask k_signs;
 
   int v_format, v_bits, v_group;
-  int kv_stable;
+  int kv_stable;                   // K / V are not written by kernels that may still run when this one starts
+  int q_stable;                    // likewise the query and the rows to append
   const void* v_data;
   int64_t v_batch_stride, v_head_stride;
   const float* v_norms;
@@ -40,6 +41,15 @@ struct FlashArgs {
   const float* mask;
   int64_t mask_batch_stride, mask_head_stride;
 
+  // optional in-launch append of the step's own token (position seq_len - 1): raw rows
+  // (batch, n_kv_heads, dim); the CTA that owns the last chunk of a (batch, kv head) group
+  // stores / quantizes them into the cache before it streams that chunk
+  const void* new_k;
+  const void* new_v;
+  int new_dtype;
+  int64_t nk_batch_stride, nk_head_stride, nv_batch_stride, nv_head_stride;
+  Table16 k_thr, v_thr;            // thresholds on the raw butterfly output (make_raw_thresholds)
+
   // per-split partial state, laid out (splits, batch * n_q_heads[, dim])
   float* part_m;
   float* part_l;
@@ -48,24 +58,21 @@ struct FlashArgs {
 
 int launch_flash_generic(const FlashArgs& a, int splits, cudaStream_t st);
 
-// Tensor-core path (dim 128, polar or dense keys, polar values, no mask).
-// Returns TQ_ERR_UNSUPPORTED without launching when the arguments do not
-// qualify; the caller then takes the generic kernel.
+// Tensor-core path (dim 128, n_rep <= 8, fp16 / 3-4-bit packed / 8-bit affine keys,
+// 3-4-bit packed or 4-bit affine values, no mask).  flash_mma_supported() says whether
+// the arguments qualify; otherwise the caller takes the general kernel.
 bool flash_mma_supported(const FlashArgs& a);
 int flash_mma_chunk_multiple();
 int flash_mma_ctas_per_sm();
 struct MmaOutput {       // where the tensor-core kernel's fused merge writes
   int* status;           // workspace header word 0
-  int* counters;         // batch * n_kv_heads ints after the header, zero between calls
+  int* counters;         // one int per (batch, kv head) after the status block, zero between calls
   int out_mode, out_dtype;
   void* out;
   int64_t out_batch_stride, out_head_stride;
   float* om;
   float* ol;
   float* oacc;
-  float* l1_m;           // level-1 partials: flash_mma_level1_parts() x rows [x dim]
-  float* l1_l;
-  float* l1_acc;
   int n_peers;           // out_mode 1: peers that also receive the merged state (0: none)
   float* peer_m[8];
   float* peer_l[8];
@@ -74,17 +81,23 @@ struct MmaOutput {       // where the tensor-core kernel's fused merge writes
 };
 int64_t flash_mma_header_bytes(int batch, int n_kv_heads);
 int flash_mma_max_splits();
-int flash_mma_level1_parts();
 int launch_flash_mma(const FlashArgs& a, int splits, const MmaOutput& mo, cudaStream_t st);
 
-// Optional gate of a merge: wait (bounded) until `n` flag words have reached `epoch` (the parts
-// were pushed by peer GPUs, see exchange.cu); flags == nullptr: no wait.
+// Optional gate of a merge: wait (bounded by a time limit) until `n` flag words have reached `epoch`
+// (the parts were pushed by peer GPUs, see exchange.cu); flags == nullptr: no wait.  When the wait
+// gives up the status word is set and the merge writes NaN.  With `reset` the block that is last to
+// pass the gate sets the flags back to zero (`done` counts the blocks), so the same launch can be
+// replayed from a CUDA graph with a constant `epoch`.
 struct PeerGate {
-  const uint32_t* flags;
+  uint32_t* flags;
   int n;
   uint32_t epoch;
   int* status;
+  int reset;
+  int* done;
+  unsigned long long limit_ns;
 };
+unsigned long long peer_wait_limit_ns();
 
 int launch_merge(const float* pm, int64_t sm, const float* pl, int64_t sl, const float* pacc,
                  int64_t sa, int n_parts, int64_t n_rows,

@@ -3,23 +3,37 @@
 // One CTA = one (batch, kv head, sequence chunk).  All n_rep <= 8 query heads of
 // the group consume the same K/V bytes, so every KV byte is read once.
 //
-//   producer warp : streams 64-position tiles of K / V (and their norms) into a
-//                   4-stage shared-memory ring with cp.async.bulk (TMA, 1-D) and
-//                   mbarrier transaction counts; every copy reads this GPU's own memory into this CTA only.
-//   4 consumer warps: each owns 16 positions of a tile and keeps its own online
+// A CTA is half an SM: 6 consumer warps + 1 producer warp, at most ~112 KB of shared
+// memory, two CTAs resident per SM.  The launcher normally asks for one CTA per SM, so
+// the CTAs of the NEXT launch on the stream (programmatic dependent launch) take the
+// other half of every SM and stream their K/V while this launch is in its tail
+// (partial-state hand-over, merge); in steady state the HBM pipe and the issue slots
+// never wait for a prologue or an epilogue.
+//
+//   producer warp : streams 96-position tiles of K / V (and their norms) into a
+//                   shared-memory ring with cp.async.bulk (TMA, 1-D) and mbarrier
+//                   transaction counts; every copy reads this GPU's own memory into
+//                   this CTA only.  It also performs the optional in-launch cache
+//                   append of the step's own token before it streams the tile that
+//                   holds it.
+//   consumer warps: each owns 16 positions of a tile and keeps its own online
 //                   softmax state, so the main loop has no CTA-wide barrier.
 //       scores  : mma.sync m16n8k16 (f16 x f16 -> f32).  A = query rows (rows 0-7
 //                 the f16 high part, rows 8-15 the f16 residual, summed after the
 //                 MMA, so the query keeps ~22 bits), B = K^T built in registers:
 //                 fp16 keys come straight from shared memory; packed keys are
 //                 decoded two elements at a time through a lane-replicated pair
-//                 LUT in shared memory (conflict-free: entry * 32 + lane).
+//                 LUT in shared memory (conflict-free: entry * 32 + lane); 8-bit
+//                 affine codes become f16 (1024 + code) with one PRMT per pair.
 //       values  : out^T[e][head] += Vc^T[e][p] * P[p][head]; Vc pairs come from the
 //                 same kind of LUT, position pairs are zipped with PRMT.
 //       The V norm is folded into the softmax exponent (log2 domain) so P stays
 //       <= 2^8 in f16 whatever the norms are; l is accumulated without it.
-//   The accumulator stays in the rotated domain; (m, l, acc) per split go to the
-//   workspace and the shared merge kernel applies butterfly * signs / dim / l.
+//   epilogue      : the warps' states are combined through shared memory, the CTA's
+//                   (m, l, acc) goes to the workspace (acc in the rotated domain), and
+//                   the CTA that completes the (batch, kv head) counter merges all
+//                   splits straight from L2 into registers, applies butterfly * signs
+//                   / dim / l and writes the output.  No CTA waits for another.
 //
 // The element <-> MMA k-slot assignment is a free permutation as long as the
 // query fragments use the same one; it is chosen per key format so that each
@@ -29,24 +43,27 @@
 #include <mutex>
 
 #include "flash.cuh"
+#include "quantize_row.cuh"
 
 namespace tq {
 namespace {
 
 constexpr int kDim = 128;
-constexpr int kConsumerWarps = 12;     // 1 CTA per SM: 12 compute warps + 1 producer at ~145 registers
+constexpr int kConsumerWarps = 6;
+constexpr int kCtasPerSm = 2;
 constexpr int kTile = 16 * kConsumerWarps;   // positions per stage (16 per warp)
-constexpr int kChunkMultiple = 64;     // split boundaries: keeps every tile start 16-byte aligned
+constexpr int kChunkMultiple = 32;     // split boundaries: keeps every tile start 16-byte aligned
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;
-constexpr int kStages = 3;
+constexpr int kMaxStages = 6;
+constexpr int kSmemBudget = 112 * 1024;   // dynamic shared memory of one CTA: two CTAs + their static data fit in 228 KB
 constexpr int kDenseRowBytes = 256;    // rows as in memory: one bulk copy per tile (2-way LDS.128 conflicts accepted)
 constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units; P stays <= 2^8
-constexpr int kMaxParts = 37;               // partial states one merge call combines (all staged in shared memory)
-constexpr int kMaxGroups = 16;              // level-1 groups when there are more than kMaxParts splits
-constexpr int kCtrPerGroup = kMaxGroups + 1; // level-1 counters + the top counter
+constexpr int kMaxParts = 96;               // splits of one (batch, kv head) group
+constexpr int kMergeBatch = 20;             // 16-byte loads a merging lane keeps in flight
+constexpr int kXBatch = (kMaxParts + kConsumerWarps - 1) / kConsumerWarps;
 
 enum : int { KF_DENSE = 0, KF_POLAR3 = 3, KF_POLAR4 = 4, KF_AFFINE8 = 8 };
 
@@ -56,13 +73,8 @@ struct MmaTables {
   float k_post;         // multiplies the raw MMA score: attn_scale * log2(e) [/ (dim * beta_k)]
   float v_post;         // multiplies the accumulator when it is written: 1 / beta_v
   int* status;          // set non-zero if a bounded wait gives up
-  int* counters;        // kCtrPerGroup per (batch, kv head); zero between calls
-  int splits;           // level-0 partials per (batch, kv head)
-  int group;            // splits merged by one level-1 merge (<= kMaxParts)
-  int n_groups;         // level-1 partials per (batch, kv head) (<= kMaxGroups); 1 = single level
-  float* l1_m;          // level-1 partial state (n_groups, rows[, dim])
-  float* l1_l;
-  float* l1_acc;
+  int* counters;        // one per (batch, kv head); zero between calls
+  int splits;           // partials per (batch, kv head)
   int out_mode, out_dtype;
   void* out;
   int64_t out_batch_stride, out_head_stride;
@@ -91,7 +103,7 @@ template <> struct VGeom<4> { static constexpr int row = 64, lut = 256 * 32 * 4;
 template <> struct VGeom<40> { static constexpr int row = 64, lut = 256 * 32 * 4; };
 
 template <int KF, int VB> struct Layout {
-  static constexpr int bars = 0;                         // 2 * kStages * 8 bytes
+  static constexpr int bars = 0;                         // 2 * stages * 8 bytes (128 reserved)
   static constexpr int q = 128;                          // 16 rows x 128 halfs
   static constexpr int klut = q + 16 * kDim * 2;
   static constexpr int vlut = klut + KGeom<KF>::lut;
@@ -101,17 +113,21 @@ template <int KF, int VB> struct Layout {
   static constexpr int v_off = kn_off + KGeom<KF>::norms;
   static constexpr int vn_off = v_off + kTile * VGeom<VB>::row;
   static constexpr int stage_bytes = vn_off + kTile * (VB == 40 ? 8 : 4);   // norms, or scale + bias words
-  // the ring is reused by the epilogue: warp exchange, then the staged split merge
-  static constexpr int merge_bytes = (kMaxParts * 8 * kDim + kMaxParts * 16 + 8 * 64) * 4;
+  static constexpr int fit = (kSmemBudget - stage0) / stage_bytes;
+  static constexpr int stages = fit > kMaxStages ? kMaxStages : fit;
+  // the ring is reused by the epilogue: warp exchange, then the merge's scratch
   static constexpr int xch_rows = VB == 40 ? 36 : 34;   // 32 accumulator values, m, l [, two bias sums]
   static constexpr int xch_bytes = kConsumerWarps * xch_rows * 32 * 4;
-  static constexpr int ring_bytes = kStages * stage_bytes;
+  static constexpr int merge_bytes = (8 * kMaxParts + 16 + kConsumerWarps * 2 * kDim) * 4;
+  static constexpr int ring_bytes = stages * stage_bytes;
   static constexpr int work_bytes =
       ring_bytes > merge_bytes ? (ring_bytes > xch_bytes ? ring_bytes : xch_bytes)
                                : (merge_bytes > xch_bytes ? merge_bytes : xch_bytes);
   static constexpr int total = stage0 + work_bytes;
+  static_assert(stages >= 2, "at least two stages must fit");
+  static_assert(2 * stages * 8 <= 128, "barrier block");
   static_assert(stage_bytes % 16 == 0 && stage0 % 16 == 0, "stage alignment");
-  static_assert(total <= 227 * 1024, "shared memory per CTA");
+  static_assert(total <= kSmemBudget, "shared memory per CTA");
 };
 
 // ---- PTX wrappers -----------------------------------------------------------------
@@ -148,6 +164,12 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
       "l"(src), "r"(bytes), "r"(bar)
       : "memory");
+}
+__device__ __forceinline__ void consumer_barrier() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+}
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -208,114 +230,55 @@ template <typename T>
 __device__ __forceinline__ float load_q(const void* base, int64_t idx) {
   return to_f32<T>(reinterpret_cast<const T*>(base)[idx]);
 }
-
-__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+__device__ __forceinline__ float load_any(const void* base, int dtype, int64_t idx) {
+  return dtype == TQ_F32 ? load_q<float>(base, idx)
+         : dtype == TQ_F16 ? load_q<__half>(base, idx)
+                           : load_q<__nv_bfloat16>(base, idx);
 }
 
-// Optional per-CTA cycle stamps for tuning (build with -DTQ_TIMING; the stamps land
-// 2 MiB into the workspace, which must be at least 3 MiB).  Off in normal builds.
-#ifdef TQ_TIMING
-__device__ __forceinline__ long long tq_now(int slot) {
-  if (slot >= 28) {   // slots 28..31: nanoseconds on the GPU-wide timer, comparable across launches
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return (long long)t;
-  }
-  return clock64();
-}
-// one block of stamps per output address (4 consecutive launches writing 7168-byte outputs stay apart)
-#define TQ_STAMP(slot)                                                                   \
-  do {                                                                                   \
-    if (lane == 0 && (warp == 0 || warp == kConsumerWarps))                              \
-      reinterpret_cast<long long*>(reinterpret_cast<char*>(tb.status) + (2 << 20))       \
-          [(((reinterpret_cast<uintptr_t>(tb.out) / 7168) & 3) * 148 * 2 +               \
-            (blockIdx.x + gridDim.x * blockIdx.y) * 2 + (warp == 0 ? 0 : 1)) * 32 + (slot)] = tq_now(slot); \
-  } while (0)
-#else
-#define TQ_STAMP(slot) do { } while (0)
-#endif
-
-// Merge `count` (<= kMaxParts) partial states of the n_rep rows of one (batch, kv
-// head) group.  Every dependent trip to global memory costs about a microsecond
-// here, so all partials are pulled into shared memory (the ring is free by now)
-// with cp.async in ONE round trip by all consumer threads, and the reduction runs
-// from shared memory: warp r owns row r, lane owns elements 4*lane .. 4*lane+3,
-// which is also the layout the final butterfly wants.
-// Shared layout at `stage`: acc [count][n_rep][128], then m [count][8], l [count][8], w [8][64].
-__device__ __forceinline__ bool merge_staged(const MmaTables& tb, uint8_t* smem_stage, uint32_t stage_addr, uint32_t bar,
-                                             uint32_t parity, int* status,
-                                             const float* pm, const float* pl, const float* pacc,
-                                             int64_t n_rows, int64_t row0, int n_rep, int first,
-                                             int count, int tid, int warp, int lane,
-                                             float& m_star, float& l_star, float4& acc4) {
-  const int acc_floats = count * n_rep * kDim;
-  float* s_acc = reinterpret_cast<float*>(smem_stage);
-  float* s_m = s_acc + acc_floats;
-  float* s_l = s_m + count * 8;
-  float* s_w = s_l + count * 8;
-  const int chunks_per_part = n_rep * (kDim / 4);          // 16-byte chunks of one part
-  // one bulk copy per part (its n_rep rows are contiguous), all in flight together
-  const uint32_t part_bytes = (uint32_t)n_rep * kDim * 4u;
-  if (tid == 0) mbar_arrive_expect_tx(bar, (uint32_t)count * part_bytes);
-  asm volatile("fence.proxy.async;" ::: "memory");
-  for (int i = tid; i < count; i += kConsumerThreads)
-    bulk_g2s(stage_addr + (uint32_t)i * part_bytes, pacc + ((int64_t)(first + i) * n_rows + row0) * kDim,
-             part_bytes, bar);
-  for (int c = tid; c < count * n_rep; c += kConsumerThreads) {
-    const int i = c / n_rep, r = c - i * n_rep;
-    cp_async4(stage_addr + (uint32_t)(acc_floats + i * 8 + r) * 4u, pm + (int64_t)(first + i) * n_rows + row0 + r);
-    cp_async4(stage_addr + (uint32_t)(acc_floats + count * 8 + i * 8 + r) * 4u,
-              pl + (int64_t)(first + i) * n_rows + row0 + r);
-  }
-  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
-  const bool arrived = mbar_wait(bar, parity);
-  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
-  TQ_STAMP(16);   // partial states staged
-  if (!arrived) {          // bounded wait gave up: report through the status word, produce nothing
-    if (tid == 0) atomicExch(status, 3);
-    m_star = -INFINITY;
-    l_star = 0.f;
-    acc4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    return false;
-  }
-  m_star = -INFINITY;
-  l_star = 0.f;
-  acc4 = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (warp < n_rep) {
-    const int r = warp;
-    float mi[2], li[2];
+// One row of the merged result, held by one warp (lane = elements 4*lane .. 4*lane+3):
+// final output (butterfly * signs / dim / l) or the merged partial state, which may also
+// go to peer GPUs by plain stores.
+template <bool VAFF>
+__device__ __forceinline__ void write_row(const FlashArgs& a, const MmaTables& tb, int b, int head, int64_t row,
+                                          float4 acc4, float m_star, float l_star, int lane) {
+  if (tb.out_mode == 1) {
+    reinterpret_cast<float4*>(tb.oacc + row * kDim)[lane] = acc4;
+    if (lane == 0) {
+      tb.om[row] = m_star;
+      tb.ol[row] = l_star;
+    }
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int i = lane + 32 * h;
-      li[h] = i < count ? s_l[i * 8 + r] : 0.f;
-      mi[h] = i < count ? s_m[i * 8 + r] : -INFINITY;
+    for (int p = 0; p < 8; ++p) {               // plain peer stores over NVLink (static indices: no local copy)
+      if (p < tb.n_peers) {
+        reinterpret_cast<float4*>(tb.peer_acc[p] + row * kDim)[lane] = acc4;
+        if (lane == 0) {
+          tb.peer_m[p][row] = m_star;
+          tb.peer_l[p][row] = l_star;
+        }
+      }
     }
-    m_star = warp_max(fmaxf(li[0] > 0.f ? mi[0] : -INFINITY, li[1] > 0.f ? mi[1] : -INFINITY));
-    float w[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      w[h] = li[h] > 0.f ? __expf(mi[h] - m_star) : 0.f;
-      s_w[r * 64 + lane + 32 * h] = w[h];
-    }
-    l_star = warp_sum(li[0] * w[0] + li[1] * w[1]);
-    __syncwarp();
-    const float4* src = reinterpret_cast<const float4*>(s_acc) + r * (kDim / 4) + lane;
-#pragma unroll 4
-    for (int i = 0; i < count; ++i) {
-      const float wi = s_w[r * 64 + i];
-      const float4 v = src[i * chunks_per_part];
-      acc4.x += v.x * wi; acc4.y += v.y * wi; acc4.z += v.z * wi; acc4.w += v.w * wi;
-    }
+    return;
   }
-  return true;
+  float v[4] = {acc4.x, acc4.y, acc4.z, acc4.w};
+  if (!VAFF) warp_butterfly<4>(v, lane);      // packed values are summed in the rotated domain
+  const float inv = l_star > 0.f ? (VAFF ? 1.0f : 1.0f / kDim) / l_star : 0.f;
+  const int64_t ooff = b * tb.out_batch_stride + (int64_t)head * tb.out_head_stride + lane * 4;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float res = v[j] * (VAFF ? 1.0f : sign_at(a.v_signs, lane * 4 + j)) * inv;
+    if (tb.out_dtype == TQ_F32) reinterpret_cast<float*>(tb.out)[ooff + j] = res;
+    else if (tb.out_dtype == TQ_F16) reinterpret_cast<__half*>(tb.out)[ooff + j] = __float2half_rn(res);
+    else reinterpret_cast<__nv_bfloat16*>(tb.out)[ooff + j] = __float2bfloat16_rn(res);
+  }
 }
 
 // ---- the kernel ---------------------------------------------------------------------
 template <int KF, int VB>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   using L = Layout<KF, VB>;
+  constexpr int kStages = L::stages;
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t sbase = smem_u32(smem);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -326,24 +289,24 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   const int n_tiles = (int)((pe - pb + kTile - 1) / kTile);
   const int h0 = kvh * a.n_rep;
 
-  TQ_STAMP(0);
-  TQ_STAMP(28);
   // Programmatic dependent launch: let the next kernel on the stream be scheduled as
-  // soon as SMs free up; its own griddepcontrol.wait keeps it from consuming
+  // soon as resources free up; its own griddepcontrol.wait keeps it from consuming
   // anything this grid produces before this grid has completed.
   if (tid == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   auto full_bar = [&](int s) { return sbase + L::bars + 8 * s; };
   auto empty_bar = [&](int s) { return sbase + L::bars + 8 * (kStages + s); };
-  const uint32_t merge_bar = sbase + L::bars + 8 * (2 * kStages);   // completion of the staged-merge copies
 
   __shared__ uint16_t c16_s[32];
   __shared__ float qsum_s[16];     // affine keys: per head and 64-element group, sum of the query
+  __shared__ int abort_s;          // a bounded wait of this CTA gave up
+  __shared__ int elected_s;        // this CTA completed its group's counter
+  __shared__ uint8_t idx_s[kDim];  // producer warp: codes of the row being appended
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), kConsumerWarps);
     }
-    mbar_init(merge_bar, 1);
+    abort_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (tid < 16) c16_s[tid] = tb.v_c16[tid];
@@ -369,14 +332,13 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       }
     }
   }
-  // Everything below reads the query and later writes the shared workspace: both
-  // may belong to the preceding kernel until it has completed.
+  // The query may belong to a kernel that is still running unless the caller vouches
+  // for it (q_stable); the shared workspace is first touched after the main loop, and
+  // every consumer thread waits for the preceding grid before that.
   if (warp < kConsumerWarps) {
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");   // consumers only: tables ready
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    consumer_barrier();   // tables ready
+    if (!a.q_stable) grid_dependency_wait();
   }
-  TQ_STAMP(29);
-  TQ_STAMP(18);
   // The query is staged in MMA fragment order when no rotation is needed and its
   // element pairs are naturally aligned; otherwise row by row (rotated in the warp).
   const int q_esize = a.q_dtype == TQ_F32 ? 4 : 2;
@@ -387,7 +349,6 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
     // staged in fragment order [k-step][lane][4 registers]: every element pair is fetched once per
     // CTA, split into f16 high part + residual, and read back with one conflict-free 16-byte load
     uint32_t* qf = reinterpret_cast<uint32_t*>(smem + L::q);
-#pragma unroll
     for (int task = tid; task < 512; task += kConsumerThreads) {
       const int ln = task & 31, up = (task >> 5) & 1, ks = task >> 6;
       const int gg = ln >> 2, tt = ln & 3;
@@ -407,7 +368,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       qf[(ks * 32 + ln) * 4 + 2 * up] = *reinterpret_cast<const uint32_t*>(&hi);
       qf[(ks * 32 + ln) * 4 + 2 * up + 1] = *reinterpret_cast<const uint32_t*>(&lo);
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");   // consumers only: query fragments ready
+    consumer_barrier();   // query fragments ready
   }
   // query rows -> shared f16: row r = high part of head r, row 8 + r = residual
   if (warp < kConsumerWarps && !q_direct) {
@@ -417,12 +378,8 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         float x = 0.f;
-        if (r < a.n_rep) {
-          const int64_t off = b * a.q_batch_stride + (int64_t)(h0 + r) * a.q_head_stride + lane * 4 + j;
-          x = a.q_dtype == TQ_F32 ? load_q<float>(a.q, off)
-              : a.q_dtype == TQ_F16 ? load_q<__half>(a.q, off)
-                                    : load_q<__nv_bfloat16>(a.q, off);
-        }
+        if (r < a.n_rep)
+          x = load_any(a.q, a.q_dtype, b * a.q_batch_stride + (int64_t)(h0 + r) * a.q_head_stride + lane * 4 + j);
         v[j] = x;
       }
       if ((KF == KF_POLAR3 || KF == KF_POLAR4) && !a.q_prerotated) {
@@ -445,9 +402,8 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         if ((lane & 15) == 0) qsum_s[r * 2 + (lane >> 4)] = qsum;
       }
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");   // consumers only: query rows ready
+    consumer_barrier();   // query rows ready
   }
-  TQ_STAMP(17);
 
   const uint8_t* kbase;
   if (KF == KF_DENSE)
@@ -476,9 +432,12 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
 
   // =============================== producer ===============================
   if (warp == kConsumerWarps) {
-    // K / V may be fetched while the preceding kernel is still running only if the
-    // caller vouches that it does not write them (kv_stable).
-    if (!a.kv_stable) asm volatile("griddepcontrol.wait;" ::: "memory");
+    // The step's own token (position seq_len - 1) is appended by the CTA that owns the last chunk of
+    // the group, just before it streams the tile that holds it.
+    const bool appends = a.new_v != nullptr && split == (int)gridDim.x - 1 && KF != KF_AFFINE8 && !VAFF;
+    // K / V may be fetched while preceding kernels are still running only if the caller vouches
+    // that they do not write them (kv_stable); likewise the rows to append (q_stable).
+    if (!a.kv_stable || (appends && !a.q_stable)) grid_dependency_wait();
     for (int i = 0; i < n_tiles; ++i) {
       const int s = i % kStages;
       const uint32_t ph = (i / kStages) & 1;
@@ -486,7 +445,38 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         if (lane == 0) atomicExch(tb.status, 1);
         break;
       }
-      TQ_STAMP(1 + i);   // producer: about to issue tile i
+      if (appends && i == n_tiles - 1) {
+        const int64_t pn = a.seq_len - 1;
+        const int64_t koff = b * a.nk_batch_stride + (int64_t)kvh * a.nk_head_stride;
+        const int64_t voff = b * a.nv_batch_stride + (int64_t)kvh * a.nv_head_stride;
+        if (KF == KF_DENSE) {          // key row stored as it is (same 16-bit type as the cache)
+          if (lane < 16)
+            reinterpret_cast<uint4*>(const_cast<uint8_t*>(kbase) + pn * kDenseRowBytes)[lane] =
+                reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(a.new_k) + koff * 2)[lane];
+        } else if (KF == KF_POLAR3 || KF == KF_POLAR4) {
+          constexpr int KB = KF == KF_POLAR3 ? 3 : 4;
+          float x[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) x[j] = load_any(a.new_k, a.new_dtype, koff + lane * 4 + j);
+          quantize_row_warp<4, KB>(x, a.k_signs, a.k_thr, idx_s,
+                                   reinterpret_cast<uint32_t*>(const_cast<uint8_t*>(kbase)) + pn * (KGeom<KF>::row / 4),
+                                   const_cast<float*>(knbase) + pn, lane);
+        }
+        {
+          constexpr int VBB = VB == 40 ? 4 : VB;
+          float x[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) x[j] = load_any(a.new_v, a.new_dtype, voff + lane * 4 + j);
+          quantize_row_warp<4, VBB>(x, a.v_signs, a.v_thr, idx_s,
+                                    reinterpret_cast<uint32_t*>(const_cast<uint8_t*>(vbase)) + pn * (VGeom<VB>::row / 4),
+                                    const_cast<float*>(vnbase) + pn, lane);
+        }
+        // the rows were written through the generic proxy; the bulk copies below read them
+        // through the async proxy
+        __threadfence();
+        __syncwarp();
+        asm volatile("fence.proxy.async;" ::: "memory");
+      }
       const int64_t p0 = pb + (int64_t)i * kTile;
       const int nvp = (int)min((int64_t)kTile, pe - p0);
       const uint32_t st = sbase + L::stage0 + s * L::stage_bytes;
@@ -502,21 +492,23 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         const int w = lane;   // remainders are at most 3 words each
         if (v_bulk + 4 * w < v_total)
           *reinterpret_cast<uint32_t*>(stg + L::v_off + v_bulk + 4 * w) =
-              *reinterpret_cast<const uint32_t*>(vsrc + v_bulk + 4 * w);
+              *reinterpret_cast<const volatile uint32_t*>(vsrc + v_bulk + 4 * w);
         if (n_bulk + 4 * w < n_total) {
           if (VAFF) {
             *reinterpret_cast<uint32_t*>(stg + L::vn_off + n_bulk + 4 * w) = vscbase[p0 + n_bulk / 4 + w];
             *reinterpret_cast<uint32_t*>(stg + L::vn_off + kTile * 4 + n_bulk + 4 * w) = vbibase[p0 + n_bulk / 4 + w];
           } else {
-            *reinterpret_cast<float*>(stg + L::vn_off + n_bulk + 4 * w) = vnbase[p0 + n_bulk / 4 + w];
+            *reinterpret_cast<float*>(stg + L::vn_off + n_bulk + 4 * w) =
+                *reinterpret_cast<const volatile float*>(vnbase + p0 + n_bulk / 4 + w);
           }
         }
         if (KF == KF_POLAR3 || KF == KF_POLAR4) {
           if (k_total != 0 && k_bulk + 4 * w < k_total)
             *reinterpret_cast<uint32_t*>(stg + L::k_off + k_bulk + 4 * w) =
-                *reinterpret_cast<const uint32_t*>(ksrc + k_bulk + 4 * w);
+                *reinterpret_cast<const volatile uint32_t*>(ksrc + k_bulk + 4 * w);
           if (n_bulk + 4 * w < n_total)
-            *reinterpret_cast<float*>(stg + L::kn_off + n_bulk + 4 * w) = knbase[p0 + n_bulk / 4 + w];
+            *reinterpret_cast<float*>(stg + L::kn_off + n_bulk + 4 * w) =
+                *reinterpret_cast<const volatile float*>(knbase + p0 + n_bulk / 4 + w);
         }
         if (KF == KF_AFFINE8) {
           if (n_bulk + 4 * w < n_total) {
@@ -609,19 +601,21 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   float m_run = -INFINITY, l_run = 0.f;
   float bias_run[2] = {0.f, 0.f};   // affine values: sum of weight x bias per element group (head g, this lane's positions)
   const int pw = 16 * warp;   // first position of this warp inside a tile
-  bool ok = true;
-  TQ_STAMP(1);   // consumer: set-up done
 
   for (int i = 0; i < n_tiles; ++i) {
     const int s = i % kStages;
     if (!mbar_wait(full_bar(s), (i / kStages) & 1)) {
-      if (lane == 0) atomicExch(tb.status, 2);
-      ok = false;
+      // Bounded wait gave up: flag it for the whole CTA.  Every warp still walks through the
+      // epilogue's barriers and the split counter, so nobody is left waiting and the counters
+      // return to zero; the result is invalid and the status word says so.
+      if (lane == 0) {
+        atomicExch(tb.status, 2);
+        abort_s = 1;
+      }
       break;
     }
     const uint32_t st = sbase + L::stage0 + s * L::stage_bytes;
     const int nvp = (int)min((int64_t)kTile, pe - (pb + (int64_t)i * kTile));
-    TQ_STAMP(2 + 2 * i);   // consumer: tile i arrived
 
     // ---------------- scores ----------------
     float sc[2][4];
@@ -670,6 +664,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       } else if (KF == KF_POLAR4) {
         const uint4 w4 = lds128(st + L::k_off + prow * 64 + t * 16);
         const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
+        float sc2[4] = {0.f, 0.f, 0.f, 0.f};   // second accumulator: two independent MMA chains
 #pragma unroll
         for (int wi = 0; wi < 4; ++wi) {
           const uint32_t a0 = ((w[wi] << 7) & 0x7F80u) | lane4;
@@ -677,8 +672,10 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
           const uint32_t a2 = ((w[wi] >> 9) & 0x7F80u) | lane4;
           const uint32_t a3 = ((w[wi] >> 17) & 0x7F80u) | lane4;
           mma16816(sc[ng], aq[2 * wi], lds32(klut + a0), lds32(klut + a1));
-          mma16816(sc[ng], aq[2 * wi + 1], lds32(klut + a2), lds32(klut + a3));
+          mma16816(sc2, aq[2 * wi + 1], lds32(klut + a2), lds32(klut + a3));
         }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) sc[ng][c] += sc2[c];
       } else {
         const uint32_t row = st + L::k_off + prow * 52;
         uint32_t w[3];
@@ -694,9 +691,14 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
           bq[pi] = ((sh >= 0 ? (ww >> sh) : (ww << (-sh))) & 0x1F80u) | lane4;
         }
         bq[15] = ((w12 << 7) & 0x1F80u) | lane4;
+        float sc2[4] = {0.f, 0.f, 0.f, 0.f};   // second accumulator: two independent MMA chains
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
+        for (int ks = 0; ks < 8; ks += 2) {
           mma16816(sc[ng], aq[ks], lds32(klut + bq[2 * ks]), lds32(klut + bq[2 * ks + 1]));
+          mma16816(sc2, aq[ks + 1], lds32(klut + bq[2 * ks + 2]), lds32(klut + bq[2 * ks + 3]));
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) sc[ng][c] += sc2[c];
       }
     }
 
@@ -823,15 +825,13 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(empty_bar(s));
-    TQ_STAMP(3 + 2 * i);   // consumer: tile i done
   }
-  TQ_STAMP(20);
 
   // ---------------- CTA epilogue: one exchange through shared memory ----------------
   // Every warp writes its (o[32], m, l) once, [warp][value][lane] (conflict free);
   // after one barrier each thread sums a fixed slice of the 32 accumulator values
-  // over the 12 source warps and stores its share of the split's partial state.
-  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");   // every consumer is done with the ring
+  // over the source warps and stores its share of the split's partial state.
+  consumer_barrier();   // every consumer is done with the ring
   float* xch = reinterpret_cast<float*>(smem + L::stage0);               // [warp][xch_rows][32]
   {
     constexpr int R = L::xch_rows;
@@ -852,14 +852,15 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       }
     }
   }
-  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
-  TQ_STAMP(24);   // exchange written
-  if (!ok) return;
+  consumer_barrier();
+  // The workspace (partial states, counters) is shared with the preceding launch: from here on
+  // this grid writes it, so every consumer thread first waits for that launch to complete.
+  if (a.q_stable) grid_dependency_wait();
   const int64_t n_rows = (int64_t)a.batch * a.n_q_heads;
   const int64_t row0 = (int64_t)b * a.n_q_heads + h0;
   {
     constexpr int R = L::xch_rows;
-    // rescale factors of the 12 sources for this thread's two heads (2t, 2t+1)
+    // rescale factors of the source warps for this thread's two heads (2t, 2t+1)
     float f0[kConsumerWarps], f1[kConsumerWarps];
     float m0 = -INFINITY, m1 = -INFINITY;
 #pragma unroll
@@ -885,7 +886,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
     }
     float* acc0 = a.part_acc + ((int64_t)split * n_rows + row0) * kDim;
 #pragma unroll
-    for (int kk = 0; kk < 3; ++kk) {
+    for (int kk = 0; kk < (32 + kConsumerWarps - 1) / kConsumerWarps; ++kk) {
       const int k = warp + kConsumerWarps * kk;          // accumulator value index j * 4 + c
       if (k < 32) {
         const int j = k >> 2, c = k & 3;
@@ -917,110 +918,124 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       }
     }
   }
-  TQ_STAMP(21);   // partial written
-  TQ_STAMP(30);
   // ---------------- merge across splits, no waiting anywhere ----------------
-  // Every CTA publishes its partial and bumps a counter; the CTA that completes
-  // the count owns the merge and resets the counter, so counters are zero between
-  // calls.  Up to kMaxParts splits are merged in one step; beyond that the splits
-  // are merged in groups first (level 1) and the group results after (level 2).
-  __shared__ int flag_s;
-  int* ctr = tb.counters + (b * a.n_kv_heads + kvh) * kCtrPerGroup;
-  const float* src_m = a.part_m;
-  const float* src_l = a.part_l;
-  const float* src_acc = a.part_acc;
-  int n_final = tb.splits;
-  uint8_t* stage_ptr = smem + L::stage0;
-  const uint32_t stage_addr = sbase + L::stage0;
-  float m_star, l_star;
-  float4 acc4;
-  if (tb.n_groups > 1) {
-    const int gi = split / tb.group;
-    const int gsize = min(tb.group, tb.splits - gi * tb.group);
-    // barrier, then one thread fences and bumps the counter (fence cumulativity makes the whole
-    // CTA's stores visible before the atomic, and the merged data visible after it)
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
-    if (tid == 0) {
-      __threadfence();
-      const int prev = atomicAdd(ctr + 1 + gi, 1);
-      flag_s = prev == gsize - 1;
-      if (flag_s) ctr[1 + gi] = 0;
-      __threadfence();
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
-    if (!flag_s) return;
-    if (!merge_staged(tb, stage_ptr, stage_addr, merge_bar, 0, tb.status, a.part_m, a.part_l, a.part_acc, n_rows,
-                      row0, a.n_rep, gi * tb.group, gsize, tid, warp, lane, m_star, l_star, acc4))
-      return;
-    if (warp < a.n_rep) {
-      const int64_t row = row0 + warp;
-      reinterpret_cast<float4*>(tb.l1_acc + ((int64_t)gi * n_rows + row) * kDim)[lane] = acc4;
-      if (lane == 0) {
-        tb.l1_m[(int64_t)gi * n_rows + row] = m_star;
-        tb.l1_l[(int64_t)gi * n_rows + row] = l_star;
-      }
-    }
-    src_m = tb.l1_m;
-    src_l = tb.l1_l;
-    src_acc = tb.l1_acc;
-    n_final = tb.n_groups;
-    TQ_STAMP(22);   // level-1 merge done
-  }
-  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
-  const int n_arrivals = tb.n_groups > 1 ? tb.n_groups : tb.splits;
+  // Every CTA publishes its partial and bumps the group's counter with one release /
+  // acquire atomic (the barrier in front makes the whole CTA's stores precede it); the CTA
+  // that completes the count owns the merge and resets the counter, so counters are zero
+  // between calls.
+  const int count = tb.splits;
+  consumer_barrier();
   if (tid == 0) {
-    __threadfence();
-    TQ_STAMP(19);   // release fence done
-    const int prev = atomicAdd(ctr, 1);
-    flag_s = prev == n_arrivals - 1;
-    if (flag_s) ctr[0] = 0;
-    __threadfence();
+    int elected = 1;
+    if (count > 1) {
+      int* ctr = tb.counters + (b * a.n_kv_heads + kvh);
+      int prev;
+      asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(prev) : "l"(ctr) : "memory");
+      elected = prev == count - 1;
+      if (elected) *ctr = 0;
+    }
+    elected_s = elected;
   }
-  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
-  TQ_STAMP(25);   // counter bumped, result known
-  if (!flag_s) return;
-  TQ_STAMP(26);
-  if (!merge_staged(tb, stage_ptr, stage_addr, merge_bar, tb.n_groups > 1 ? 1 : 0, tb.status, src_m, src_l, src_acc,
-                    n_rows, row0, a.n_rep, 0, n_final, tid, warp, lane, m_star, l_star, acc4))
-    return;
-  TQ_STAMP(27);   // staged merge done
-  if (warp < a.n_rep) {
-    const int r = warp;
-    const int64_t row = row0 + r;
-    if (tb.out_mode == 1) {
-      reinterpret_cast<float4*>(tb.oacc + row * kDim)[lane] = acc4;
-      if (lane == 0) {
-        tb.om[row] = m_star;
-        tb.ol[row] = l_star;
-      }
+  consumer_barrier();
+  if (!elected_s) return;
+
+  // The merge reads every split's state straight from L2 into registers.  Shared scratch
+  // (the ring is free): weights [8][kMaxParts], m* [8], l* [8], partial rows [warp][2][128].
+  float* wgt = reinterpret_cast<float*>(smem + L::stage0);
+  float* mst = wgt + 8 * kMaxParts;
+  float* lst = mst + 8;
+  float* xrow = lst + 8;
+  for (int r = warp; r < a.n_rep; r += kConsumerWarps) {
+    // lane i (+32, +64) holds part i: m* = max over parts with l > 0, weight = e^(m - m*)
+    float mi[3], li[3];
 #pragma unroll
-      for (int p = 0; p < 8; ++p) {               // plain peer stores over NVLink (static indices: no local copy)
-        if (p < tb.n_peers) {
-          reinterpret_cast<float4*>(tb.peer_acc[p] + row * kDim)[lane] = acc4;
-          if (lane == 0) {
-            tb.peer_m[p][row] = m_star;
-            tb.peer_l[p][row] = l_star;
-          }
+    for (int s3 = 0; s3 < 3; ++s3) {
+      const int i = lane + 32 * s3;
+      const bool on = i < count;
+      li[s3] = on ? __ldcg(a.part_l + (int64_t)i * n_rows + row0 + r) : 0.f;
+      mi[s3] = on ? __ldcg(a.part_m + (int64_t)i * n_rows + row0 + r) : -INFINITY;
+    }
+    float mx = -INFINITY;
+#pragma unroll
+    for (int s3 = 0; s3 < 3; ++s3)
+      if (li[s3] > 0.f) mx = fmaxf(mx, mi[s3]);
+    mx = warp_max(mx);
+    float lsum = 0.f;
+#pragma unroll
+    for (int s3 = 0; s3 < 3; ++s3) {
+      const int i = lane + 32 * s3;
+      const float w = li[s3] > 0.f ? __expf(mi[s3] - mx) : 0.f;
+      if (i < count) wgt[r * kMaxParts + i] = w;
+      lsum += li[s3] * w;
+    }
+    lsum = warp_sum(lsum);
+    if (lane == 0) {
+      mst[r] = mx;
+      lst[r] = lsum;
+    }
+  }
+  consumer_barrier();
+  const int64_t pstride = n_rows * (kDim / 4);          // float4s between consecutive parts
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  // rows 0 .. kConsumerWarps-1: warp r owns row r, lane owns elements 4*lane .. 4*lane+3
+  float4 acc4 = zero4;
+  if (warp < a.n_rep) {
+    const float4* src = reinterpret_cast<const float4*>(a.part_acc + (row0 + warp) * kDim) + lane;
+    const float* wr = wgt + warp * kMaxParts;
+    for (int i0 = 0; i0 < count; i0 += kMergeBatch) {
+      float4 v[kMergeBatch];
+#pragma unroll
+      for (int j = 0; j < kMergeBatch; ++j)
+        v[j] = i0 + j < count ? __ldcg(src + (int64_t)(i0 + j) * pstride) : zero4;
+#pragma unroll
+      for (int j = 0; j < kMergeBatch; ++j) {
+        const float wi = i0 + j < count ? wr[i0 + j] : 0.f;
+        acc4.x += v[j].x * wi; acc4.y += v[j].y * wi; acc4.z += v[j].z * wi; acc4.w += v[j].w * wi;
+      }
+    }
+    write_row<VAFF>(a, tb, b, h0 + warp, row0 + warp, acc4, mst[warp], lst[warp], lane);
+  }
+  // rows beyond the warp count (n_rep 7, 8): every warp sums its share of the parts, the
+  // shares meet in shared memory
+  if (a.n_rep > kConsumerWarps) {
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+      const int r = kConsumerWarps + x;
+      float4 part = zero4;
+      if (r < a.n_rep) {
+        const float4* src = reinterpret_cast<const float4*>(a.part_acc + (row0 + r) * kDim) + lane;
+        const float* wr = wgt + r * kMaxParts;
+        float4 v[kXBatch];
+#pragma unroll
+        for (int j = 0; j < kXBatch; ++j) {
+          const int i = warp + kConsumerWarps * j;
+          v[j] = i < count ? __ldcg(src + (int64_t)i * pstride) : zero4;
+        }
+#pragma unroll
+        for (int j = 0; j < kXBatch; ++j) {
+          const int i = warp + kConsumerWarps * j;
+          const float wi = i < count ? wr[i] : 0.f;
+          part.x += v[j].x * wi; part.y += v[j].y * wi; part.z += v[j].z * wi; part.w += v[j].w * wi;
         }
       }
-    } else {
-      float v[4] = {acc4.x, acc4.y, acc4.z, acc4.w};
-      if (!VAFF) warp_butterfly<4>(v, lane);      // packed values are summed in the rotated domain
-      const float inv = l_star > 0.f ? (VAFF ? 1.0f : 1.0f / kDim) / l_star : 0.f;
-      const int64_t ooff = b * tb.out_batch_stride + (int64_t)(h0 + r) * tb.out_head_stride + lane * 4;
+      reinterpret_cast<float4*>(xrow + (warp * 2 + x) * kDim)[lane] = part;
+    }
+    consumer_barrier();
+    if (warp < 2 && kConsumerWarps + warp < a.n_rep) {
+      const int r = kConsumerWarps + warp;
+      float4 s4 = zero4;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float res = v[j] * (VAFF ? 1.0f : sign_at(a.v_signs, lane * 4 + j)) * inv;
-        if (tb.out_dtype == TQ_F32) reinterpret_cast<float*>(tb.out)[ooff + j] = res;
-        else if (tb.out_dtype == TQ_F16) reinterpret_cast<__half*>(tb.out)[ooff + j] = __float2half_rn(res);
-        else reinterpret_cast<__nv_bfloat16*>(tb.out)[ooff + j] = __float2bfloat16_rn(res);
+      for (int sw = 0; sw < kConsumerWarps; ++sw) {
+        const float4 p4 = reinterpret_cast<const float4*>(xrow + (sw * 2 + warp) * kDim)[lane];
+        s4.x += p4.x; s4.y += p4.y; s4.z += p4.z; s4.w += p4.w;
       }
+      write_row<VAFF>(a, tb, b, h0 + r, row0 + r, s4, mst[r], lst[r], lane);
     }
   }
   if (tb.out_mode == 1 && tb.n_peers > 0) {
     // every row of this (batch, kv head) group is on its way: one thread fences at system scope (the
     // barrier makes the other threads' stores precede it) and tells each peer
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+    consumer_barrier();
     if (tid == 0) {
       __threadfence_system();
 #pragma unroll
@@ -1028,8 +1043,6 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         if (p < tb.n_peers) atomicAdd_system(tb.peer_counter[p], 1u);
     }
   }
-  TQ_STAMP(23);   // final merge done
-  TQ_STAMP(31);
 }
 
 // ---- host side: scaled f16 codebooks --------------------------------------------------
@@ -1096,6 +1109,9 @@ static int launch_variant(const FlashArgs& a, const MmaTables& tb, int splits, c
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
     cudaError_t e = cudaFuncSetAttribute(flash_mma_kernel<KF, VB>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
+    if (e == cudaSuccess)   // two CTAs per SM need the full shared-memory carve-out
+      e = cudaFuncSetAttribute(flash_mma_kernel<KF, VB>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                               cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return set_error(TQ_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     attr_done[dev] = true;
   }
@@ -1148,17 +1164,22 @@ bool flash_mma_supported(const FlashArgs& a) {
   } else {
     return false;
   }
+  if (a.new_v != nullptr) {   // in-launch append: dense keys as stored (fp16), or packed keys; packed values
+    if (a.v_format != TQ_KV_POLAR || a.k_format == TQ_KV_AFFINE || a.new_k == nullptr) return false;
+    if (a.k_format == TQ_KV_DENSE &&
+        (a.new_dtype != TQ_F16 || !aligned16(a.new_k) || a.nk_batch_stride % 8 || a.nk_head_stride % 8))
+      return false;
+  }
   return true;
 }
 
 int flash_mma_chunk_multiple() { return kChunkMultiple; }
-int flash_mma_ctas_per_sm() { return 1; }
+int flash_mma_ctas_per_sm() { return kCtasPerSm; }
 
 int64_t flash_mma_header_bytes(int batch, int n_kv_heads) {
-  return ((16 + 4 * (int64_t)kCtrPerGroup * batch * n_kv_heads) + 15) / 16 * 16;
+  return ((16 + 4 * (int64_t)batch * n_kv_heads) + 15) / 16 * 16;
 }
-int flash_mma_max_splits() { return kMaxParts * kMaxGroups; }
-int flash_mma_level1_parts() { return kMaxGroups; }
+int flash_mma_max_splits() { return kMaxParts; }
 
 int launch_flash_mma(const FlashArgs& a, int splits, const MmaOutput& mo, cudaStream_t st) {
   MmaTables tb;
@@ -1166,11 +1187,6 @@ int launch_flash_mma(const FlashArgs& a, int splits, const MmaOutput& mo, cudaSt
   tb.status = mo.status;
   tb.counters = mo.counters;
   tb.splits = splits;
-  tb.n_groups = (splits + kMaxParts - 1) / kMaxParts;           // 1 up to kMaxParts splits
-  tb.group = (splits + tb.n_groups - 1) / tb.n_groups;
-  tb.l1_m = mo.l1_m;
-  tb.l1_l = mo.l1_l;
-  tb.l1_acc = mo.l1_acc;
   tb.out_mode = mo.out_mode;
   tb.out_dtype = mo.out_dtype;
   tb.out = mo.out;

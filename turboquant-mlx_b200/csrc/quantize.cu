@@ -8,6 +8,7 @@
 #include <stdlib.h>
 
 #include "common.cuh"
+#include "quantize_row.cuh"
 
 namespace tq {
 
@@ -44,7 +45,6 @@ template <typename T, int EPL, int BITS>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 quantize_warp_kernel(const QuantArgs a) {
   constexpr int DIM = EPL * 32;
-  constexpr int VPW = vals_per_word(BITS);
   constexpr int PDIM = packed_words(DIM, BITS);
   __shared__ uint8_t idx_s[kWarpsPerBlock][DIM];
   // A kernel launched behind this one with programmatic stream serialization (the decode
@@ -67,60 +67,14 @@ quantize_warp_kernel(const QuantArgs a) {
   const int64_t warp_global = (int64_t)blockIdx.x * kWarpsPerBlock + warp;
   const int64_t warp_stride = (int64_t)q_blocks * kWarpsPerBlock;
 
-  uint32_t sbit[EPL];
-#pragma unroll
-  for (int j = 0; j < EPL; ++j) sbit[j] = sign_bit_at(a.signs, lane * EPL + j);
-
   for (int64_t v = warp_global; v < a.n_vecs; v += warp_stride) {
     const int64_t o = v / a.n_inner, i = v - o * a.n_inner;
     const T* row = reinterpret_cast<const T*>(a.x) + o * a.x_outer_stride + i * DIM + lane * EPL;
     float x[EPL];
 #pragma unroll
     for (int j = 0; j < EPL; ++j) x[j] = to_f32<T>(row[j]);
-
-    // L2 norm: float32 squares, pairwise tree in natural index order.
-    float sq[EPL];
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) sq[j] = __fmul_rn(x[j], x[j]);
-#pragma unroll
-    for (int h = 1; h < EPL; h <<= 1) {
-#pragma unroll
-      for (int j = 0; j < EPL; j += 2 * h) sq[j] = __fadd_rn(sq[j], sq[j + h]);
-    }
-    float ss = sq[0];
-#pragma unroll
-    for (int k = 1; k < 32; k <<= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, k));
-    const float nrm = __fsqrt_rn(ss);
-    const float safe = fmaxf(nrm, 1e-8f);
-
-    float t[EPL];
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) {
-      float u = __fdiv_rn(x[j], safe);
-      t[j] = __uint_as_float(__float_as_uint(u) ^ sbit[j]);   // u * (+/-1), exact
-    }
-    warp_butterfly<EPL>(t, lane);
-
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) {
-      int idx = 0;
-#pragma unroll
-      for (int b = 0; b < (1 << BITS) - 1; ++b) idx += (t[j] > a.thr.v[b]) ? 1 : 0;
-      idx_s[warp][lane * EPL + j] = (uint8_t)idx;
-    }
-    __syncwarp();
-    uint32_t* prow = a.packed + o * a.packed_outer_stride + i * PDIM;
-    for (int w = lane; w < PDIM; w += 32) {
-      uint32_t word = 0;
-#pragma unroll
-      for (int k = 0; k < VPW; ++k) {
-        const int e = w * VPW + k;
-        if (e < DIM) word |= (uint32_t)idx_s[warp][e] << (k * BITS);
-      }
-      prow[w] = word;
-    }
-    if (lane == 0) a.norms[o * a.norms_outer_stride + i] = nrm;
-    __syncwarp();
+    quantize_row_warp<EPL, BITS>(x, a.signs, a.thr, idx_s[warp], a.packed + o * a.packed_outer_stride + i * PDIM,
+                                 a.norms + o * a.norms_outer_stride + i, lane);
   }
 }
 

@@ -50,9 +50,11 @@ def cache_kv_descriptors(cache):
     """K / V descriptors of a TurboQuantKVCache for `kernels.flash_decode`."""
     total = cache.offset
     k = dict(format="polar", packed=cache.k_packed[:, :, :total, :], norms=cache.k_norms[:, :, :total],
-             centroids=cache._k_q.centroids, signs=cache._k_q.signs, bits=cache._k_q.bits)
+             centroids=cache._k_q.centroids, signs=cache._k_q.signs, bits=cache._k_q.bits,
+             boundaries=cache._k_q.boundaries)
     v = dict(format="polar", packed=cache.v_packed[:, :, :total, :], norms=cache.v_norms[:, :, :total],
-             centroids=cache._v_q.centroids, signs=cache._v_q.signs, bits=cache._v_q.bits)
+             centroids=cache._v_q.centroids, signs=cache._v_q.signs, bits=cache._v_q.bits,
+             boundaries=cache._v_q.boundaries)
     return k, v
 
 
@@ -60,20 +62,28 @@ def turboquant_attention(queries, cache, attn_scale: float, mask=None, v_buffer=
                          sparse_v_threshold: float | None = None) -> torch.Tensor:
     """queries (B, n_heads, 1, dim) -> (B, n_heads, 1, dim) in queries.dtype."""
     B, n_q_heads, S_q, dim = queries.shape
-    total = cache.offset
     n_kv_heads = cache.k_packed.shape[1]
     n_rep = n_q_heads // n_kv_heads
     thr = sparse_v_threshold if (sparse_v_threshold is not None and sparse_v_threshold >= 0.0) else 0.0
+    has_mask = mask is not None and not isinstance(mask, str)
+    pending = getattr(cache, "_pending", None) is not None
+    if pending and (v_buffer is not None or thr != 0.0 or has_mask or n_rep > 8 or dim != 128):
+        cache.flush_pending()          # the in-launch insert needs the tensor-core decode kernel
+    total = cache.offset
 
     if v_buffer is None and thr == 0.0:
         k, v = cache_kv_descriptors(cache)
         m3 = None
-        if mask is not None and not isinstance(mask, str):
+        if has_mask:
             if mask.dtype == torch.bool:
                 mask = torch.where(mask, 0.0, float("-inf"))
             m3 = _mask_3d(mask, B, n_q_heads, total)
+        rows = cache.take_pending() if hasattr(cache, "take_pending") else None
+        new_k, new_v = rows if rows is not None else (None, None)
+        stable = bool(getattr(cache, "inputs_stable", False))
         out = flash_decode(queries[:, :, 0, :], k=k, v=v, attn_scale=attn_scale, mask=m3,
-                           out_dtype=queries.dtype)
+                           out_dtype=queries.dtype, kv_stable=stable, q_stable=stable,
+                           new_k=new_k, new_v=new_v)
         return out.unsqueeze(2)
 
     outputs = []

@@ -24,7 +24,7 @@ __all__ = [
     "prerotate_query", "prerot_fused_qk_scores", "prerot_packed_dequantize",
     "sparse_v_matvec", "count_active_positions", "flash_attention_turboquant",
     "flash_decode", "merge_partials", "FlashDecodePlan", "MergePlan",
-    "prefill_attention", "prefill_supported", "prefill_status",
+    "prefill_attention", "prefill_supported", "prefill_status", "flash_status",
 ]
 
 
@@ -252,6 +252,7 @@ def _strides3(t: torch.Tensor, batched: bool):
 def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerotated: bool = False,
                  mask: torch.Tensor | None = None, num_splits: int = 0, out_dtype=None,
                  partials: bool = False, partial_out=None, kv_stable: bool = False, out=None, peers=None,
+                 q_stable: bool = False, new_k: torch.Tensor | None = None, new_v: torch.Tensor | None = None,
                  _prepare_only: bool = False):
     """Split-K flash decoding for one query token per sequence.
 
@@ -269,9 +270,19 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
     optionally names the three tensors to write (e.g. slices of a send buffer).
     `out` optionally names the (B, n_q, dim) tensor to write.  `peers` (partials only, see
     distributed.PeerExchange.targets) makes the kernel also store the merged state into the
-    given peer buffers and bump their counters.  kv_stable=True promises that the kernel launched just before this call on the
-    stream does not write any K / V row this call reads (e.g. the new token was
-    appended earlier), which lets the kernel prefetch K / V while that kernel drains.
+    given peer buffers and bump their counters.
+
+    kv_stable=True promises that no kernel that may still be running when this call's kernel
+    starts (the decode kernel is launched with programmatic stream serialization, so the
+    kernels in front of it on the stream may still be draining) writes a K / V row this call
+    reads; q_stable=True promises the same for q (and new_k / new_v).  With both the kernel
+    reads its inputs at once and consecutive decode calls overlap on the GPU.
+
+    new_k / new_v (B, n_kv, dim): the step's own token.  The K / V descriptors must already
+    span it (S counts it, its row is the last one); the kernel stores / quantizes the two rows
+    into that position and attends over them in the same launch, replacing the separate cache
+    append.  The descriptors need "boundaries" (and polar keys "signs") for this.  Raises
+    ValueError when the call does not qualify for the tensor-core kernel.
     """
     _lib.require_cuda(q)
     B, n_q, dim = q.shape
@@ -351,6 +362,29 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
     P.n_kv_heads, P.seq_len = n_kv, S
     P.attn_scale, P.num_splits = float(attn_scale), int(num_splits)
     P.kv_stable = int(kv_stable)
+    P.q_stable = int(q_stable)
+    if (new_k is None) != (new_v is None):
+        raise ValueError("new_k and new_v must be given together")
+    if new_k is not None:
+        _lib.require_cuda(new_k, new_v)
+        if new_k.shape != (B, n_kv, dim) or new_v.shape != (B, n_kv, dim) or new_k.dtype != new_v.dtype:
+            raise ValueError(f"new_k / new_v must be ({B}, {n_kv}, {dim}) tensors of one dtype")
+        if new_k.stride(-1) != 1:
+            new_k = new_k.contiguous()
+        if new_v.stride(-1) != 1:
+            new_v = new_v.contiguous()
+        keep += [new_k, new_v]
+        P.new_dtype = _lib.dtype_code(new_k.dtype)
+        P.new_k, P.new_v = new_k.data_ptr(), new_v.data_ptr()
+        P.new_k_batch_stride, P.new_k_head_stride = new_k.stride(0), new_k.stride(1)
+        P.new_v_batch_stride, P.new_v_head_stride = new_v.stride(0), new_v.stride(1)
+        vb = _lib.host_floats(v.get("boundaries"))
+        kb = _lib.host_floats(k.get("boundaries")) if kf == "polar" else None
+        keep += [vb, kb]
+        if vb is not None:
+            P.v_boundaries_host = vb
+        if kb is not None:
+            P.k_boundaries_host = kb
 
     if mask is not None:
         m = mask.to(torch.float32)
@@ -428,6 +462,22 @@ class FlashDecodePlan:
         return self.result
 
 
+def flash_status(device, batch_kv_groups: int) -> int:
+    """Status word of the tensor-core decode kernel's workspace for calls with
+    batch * n_kv_heads == `batch_kv_groups` on this device and stream (synchronises):
+    0 unless a bounded wait inside the kernel gave up, in which case the outputs of
+    the calls since the last check are invalid.  Resets the word."""
+    key = (f"flash{batch_kv_groups}", str(torch.device(device)), torch.cuda.current_stream(device).cuda_stream)
+    ws = _lib._workspaces.get(key)
+    if ws is None:
+        return 0
+    word = ws[:4].view(torch.int32)
+    code = int(word.item())
+    if code:
+        word.zero_()
+    return code
+
+
 def flash_attention_turboquant(q_rot, k_packed, k_norms, v_packed, v_norms, k_centroids,
                                v_centroids, v_signs, dim: int, bits: int, attn_scale: float,
                                block_size: int = 16, n_rep: int = 1, v_bits: int | None = None):
@@ -495,10 +545,11 @@ class MergePlan:
             _lib.check(rc)
         return self.result
 
-    def run_after_peers(self, flags_ptr, n_ranks: int, epoch: int, status_ptr):
-        """The same merge, gated inside the kernel on the peers' flags (see PeerExchange)."""
-        rc = _lib.lib().tq_merge_partials_after_peers(flags_ptr, n_ranks, epoch, status_ptr, *self._args,
-                                                      _lib.stream_ptr(self._dev))
+    def run_after_peers(self, flags_ptr, n_ranks: int, epoch: int, status_ptr, reset_flags: bool = False):
+        """The same merge, gated inside the kernel on the peers' flags (see PeerExchange).  With
+        `reset_flags` the kernel zeroes the flags once it is past the gate (graph-replayable)."""
+        rc = _lib.lib().tq_merge_partials_after_peers(flags_ptr, n_ranks, epoch, status_ptr, int(reset_flags),
+                                                      *self._args, _lib.stream_ptr(self._dev))
         if rc:
             _lib.check(rc)
         return self.result

@@ -22,12 +22,24 @@ class VOnlyTurboQuantCache:
     as a plain cache unless `fused` is set."""
 
     def __init__(self, bits: int = 3, seed: int = 42, no_v_buffer: bool = False,
-                 fused: bool = False):
+                 fused: bool = False, defer_append: bool = False, inputs_stable: bool = False):
+        """`defer_append` (fused caches only, an addition to the reference's arguments): a
+        one-token `update_and_fetch` only records the new rows; the decode attention that
+        follows stores the key row and quantizes the value row inside its own launch, so a
+        decode step is one kernel per layer.  The rows handed to `update_and_fetch` must stay
+        unchanged until that attention call (or until anything else reads the cache, which
+        materialises them first).  `inputs_stable`: the caller promises that neither the queries and
+        new rows of a decode step nor this cache's storage are written by a kernel that may
+        still be running when the step's attention kernel starts (see `kv_stable` / `q_stable`
+        of `kernels.flash_decode`); the decode launches of consecutive layers then overlap."""
         self._k_cache = KVCache(keys_only=True)
         self._v_tq = TurboQuantKVCache(bits=bits, seed=seed, v_only=True, fused=fused)
         self._v_bits = bits
         self._no_v_buffer = no_v_buffer
         self.fused = fused
+        self.defer_append = defer_append and fused
+        self.inputs_stable = inputs_stable
+        self._pending = None      # (new K rows, new V rows) (B, H, D) awaiting the attention launch
 
     def reserve(self, B, H, n_positions, k_dim, v_dim, dtype=torch.float16, device=None):
         """Pre-size K and V storage for `n_positions` so inserts never reallocate."""
@@ -72,8 +84,55 @@ class VOnlyTurboQuantCache:
         from .cache import _zero
         return kc.keys[..., :kc.offset, :], _zero(values.dtype, values.device).expand(B, H, kc.offset, Dv)
 
+    def _defer(self, keys, values):
+        """Record a one-token append for the next decode attention; None when it does not qualify
+        (storage must exist with room, fp16 keys of the cache's type, head_dim 128)."""
+        kc, tq = self._k_cache, self._v_tq
+        B, H, S, Dk = keys.shape
+        if not (self.defer_append and S == 1 and keys.is_cuda and kc.keys is not None and tq.v_packed is not None):
+            return None
+        prev = kc.offset
+        if prev != tq.offset or prev + 1 > kc.keys.shape[2] or prev + 1 > tq.v_packed.shape[2]:
+            return None
+        if kc.keys.dtype != torch.float16 or keys.dtype != torch.float16 or values.dtype != torch.float16:
+            return None
+        if kc.keys.shape[:2] != (B, H) or Dk != 128 or values.shape[3] != 128 or tq._v_q is None:
+            return None
+        if tq._v_q.bits not in (3, 4) or keys.data_ptr() % 16 or any(st % 8 for st in keys.stride()[:2]):
+            return None
+        tq._dtype = keys.dtype
+        self._pending = (keys[:, :, 0, :], values[:, :, 0, :])
+        kc.offset = prev + 1
+        tq.offset = prev + 1
+        from .cache import _zero
+        return kc.keys[..., :kc.offset, :], _zero(values.dtype, values.device).expand(B, H, kc.offset, values.shape[3])
+
+    def flush_pending(self):
+        """Materialise a deferred append with the ordinary append kernel (anything that reads the
+        storage other than the decode attention calls this first)."""
+        if self._pending is None:
+            return
+        k_row, v_row = self._pending
+        self._pending = None
+        self._k_cache.offset -= 1
+        self._v_tq.offset -= 1
+        defer, self.defer_append = self.defer_append, False
+        try:
+            self.update_and_fetch(k_row.unsqueeze(2), v_row.unsqueeze(2))
+        finally:
+            self.defer_append = defer
+
+    def take_pending(self):
+        """The deferred rows (or None), handing responsibility for them to the caller."""
+        rows, self._pending = self._pending, None
+        return rows
+
     def update_and_fetch(self, keys, values):
         """Store K as is, compress V, return (K, V_dequant)."""
+        self.flush_pending()
+        deferred = self._defer(keys, values)
+        if deferred is not None:
+            return deferred
         fused = self._append_fused(keys, values)
         if fused is not None:
             return fused
@@ -98,6 +157,7 @@ class VOnlyTurboQuantCache:
 
     @property
     def state(self):
+        self.flush_pending()
         k_state = list(self._k_cache.state) if self._k_cache.state else []
         v_state = list(self._v_tq.state) if self._v_tq.state else []
         return k_state + v_state
@@ -130,6 +190,7 @@ class VOnlyTurboQuantCache:
         return True
 
     def trim(self, n):
+        self.flush_pending()
         self._k_cache.trim(n)
         return self._v_tq.trim(n)
 
@@ -138,21 +199,30 @@ class VOnlyTurboQuantCache:
 
 
 def v_only_attention(queries, cache: VOnlyTurboQuantCache, attn_scale: float, mask=None,
-                     kv_stable: bool = False, out=None):
+                     kv_stable: bool = False, out=None, q_stable: bool | None = None):
     """Decode attention for a fused V-only cache: queries (B, n_q, 1, dim),
-    dense K and packed V read once per KV head -> (B, n_q, 1, dim)."""
-    total = cache.offset
+    dense K and packed V read once per KV head -> (B, n_q, 1, dim).  A deferred
+    one-token append of the cache is carried out by the same launch."""
     tq = cache._v_tq
-    k = dict(format="dense", data=cache._k_cache.keys[:, :, :total, :])
-    v = dict(format="polar", packed=tq.v_packed[:, :, :total, :], norms=tq.v_norms[:, :, :total],
-             centroids=tq._v_q.centroids, signs=tq._v_q.signs, bits=tq._v_q.bits)
+    if q_stable is None:
+        q_stable = cache.inputs_stable
     m3 = None
     if mask is not None and not isinstance(mask, str):
         from .fused_attention import _mask_3d
         if mask.dtype == torch.bool:
             mask = torch.where(mask, 0.0, float("-inf"))
-        m3 = _mask_3d(mask, queries.shape[0], queries.shape[1], total)
+        m3 = _mask_3d(mask, queries.shape[0], queries.shape[1], cache.offset)
+    n_rep = queries.shape[1] // max(1, tq.v_packed.shape[1])
+    if cache._pending is not None and (m3 is not None or n_rep > 8 or queries.shape[-1] != 128):
+        cache.flush_pending()       # the in-launch append needs the tensor-core kernel
+    total = cache.offset
+    k = dict(format="dense", data=cache._k_cache.keys[:, :, :total, :])
+    v = dict(format="polar", packed=tq.v_packed[:, :, :total, :], norms=tq.v_norms[:, :, :total],
+             centroids=tq._v_q.centroids, signs=tq._v_q.signs, bits=tq._v_q.bits, boundaries=tq._v_q.boundaries)
+    rows = cache.take_pending()
+    new_k, new_v = rows if rows is not None else (None, None)
     res = flash_decode(queries[:, :, 0, :], k=k, v=v, attn_scale=attn_scale, mask=m3,
-                       out_dtype=queries.dtype, kv_stable=kv_stable,
+                       out_dtype=queries.dtype, kv_stable=kv_stable or q_stable,
+                       q_stable=q_stable, new_k=new_k, new_v=new_v,
                        out=None if out is None else out[:, :, 0, :])
     return res.unsqueeze(2)
