@@ -89,3 +89,63 @@ def test_gloo_gather_and_merge_equals_whole(empty_rank):
     for r in range(world):
         err, bad = ret[r]
         assert err < 1e-5 and bad
+
+
+def _failure_worker(rank, world, port, mode, ret):
+    """Host-made failures: `nan` - rank 1 sends a partial state with NaN in it; `late` - rank 1
+    joins the collective two seconds late; `dropped` - rank 1 never joins and rank 0's collective
+    ends with an error after the short process-group timeout."""
+    import datetime
+    import time
+    sys.path.insert(0, ROOT)
+    import __graft_entry__ as entry
+    entry.load_package()
+    from turboquant_mlx_b200.distributed import check_partials, gather_partials, partial_views
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=6))
+    try:
+        rows, D = 4, 32
+        send = torch.zeros(rows * (D + 2), dtype=torch.float32)
+        send[:rows] = 0.5 + rank
+        send[rows:2 * rows] = 1.0
+        send[2 * rows:] = float(rank + 1)
+        if mode == "nan" and rank == 1:
+            send[2 * rows + 7] = float("nan")
+        if mode == "late" and rank == 1:
+            time.sleep(2.0)
+        if mode == "dropped" and rank == 1:
+            time.sleep(10.0)              # leaves between steps: never joins the gather
+            ret[rank] = "left"
+            return
+        try:
+            recv = gather_partials(send)
+        except Exception as exc:          # the short timeout ended the collective
+            ret[rank] = f"collective failed: {type(exc).__name__}"
+            return
+        try:
+            check_partials(recv, rows, D)
+            m, l, acc = partial_views(recv, rows, D)
+            ret[rank] = ("ok", float(acc[1, 0, 0]), bool(torch.isfinite(acc).all()))
+        except RuntimeError as exc:
+            ret[rank] = str(exc)
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+@pytest.mark.parametrize("mode", ["nan", "late", "dropped"])
+def test_gloo_host_side_failures(mode):
+    world = 2
+    port = 31500 + (os.getpid() % 2000) + {"nan": 0, "late": 1, "dropped": 2}[mode]
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_failure_worker, args=(world, port, mode, ret), nprocs=world, join=True)
+    if mode == "nan":          # every rank learns which rank sent the bad block
+        assert all("rank 1 sent a non-finite" in ret[r] for r in range(world))
+    elif mode == "late":       # a late rank only delays the step
+        assert all(ret[r] == ("ok", 2.0, True) for r in range(world))
+    else:                      # the remaining rank gets an error instead of hanging
+        assert ret[1] == "left" and ret[0].startswith("collective failed")

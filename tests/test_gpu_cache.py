@@ -249,3 +249,52 @@ def test_v_only_fused_append_matches_two_step_append(tq, dev):
     keys, vals = fast.update_and_fetch(k, k)
     assert keys.shape == (B, H, n + 1, D) and vals.shape == (B, H, n + 1, D)
     assert torch.equal(keys[:, :, n], k[:, :, 0])
+
+
+def test_hybrid_cache_quantize_k_then_decode(tq, oracle, dev):
+    """HybridQuantCache (hybrid_cache.py:25-100): plain K + packed V during the prompt, then
+    `maybe_quantize_k()` and decode steps on 8-bit affine K + 3-bit packed V through the hook;
+    compared with the oracle's composed attention over the dequantized affine keys."""
+    import math
+    from turboquant_mlx_b200 import base
+    rng = np.random.default_rng(11)
+    B, n_kv, n_rep, S, D = 2, 2, 4, 300, 128
+    k_all = rng.standard_normal((B, n_kv, S + 2, D)).astype(np.float16)
+    v_all = (rng.standard_normal((B, n_kv, S + 2, D)) * rng.lognormal(0, 0.5, (B, n_kv, S + 2, 1))).astype(np.float16)
+    q = rng.standard_normal((B, n_kv * n_rep, 1, D)).astype(np.float16)
+    kd, vd, qd = (torch.from_numpy(a).to(dev) for a in (k_all, v_all, q))
+    scale = 1.0 / math.sqrt(D)
+    c = tq.HybridQuantCache(k_bits=8, k_group_size=64, v_bits=3, v_seed=42)
+    assert c.empty() and c.bits is None and c.group_size is None
+    k_out, v_out = c.update_and_fetch(kd[:, :, :S], vd[:, :, :S])
+    assert torch.equal(k_out, kd[:, :, :S]) and v_out.shape == (B, n_kv, S, D)     # reference behaviour before conversion
+    c.maybe_quantize_k()
+    assert c.bits == 8 and c.group_size == 64 and c.offset == S
+    fp16_bytes = B * n_kv * S * 2 * D * 2
+    assert 0.30 < c.nbytes / fp16_bytes < 0.40          # ~35 % of an fp16 cache (hybrid_cache.py:3-6)
+    tq.apply_patch()
+    try:
+        for step in range(2):
+            keys, values = c.update_and_fetch(kd[:, :, S + step:S + step + 1], vd[:, :, S + step:S + step + 1])
+            out = base.scaled_dot_product_attention(qd, keys, values, c, scale, None)
+    finally:
+        tq.remove_patch()
+    assert tq._lib.lib().tq_flash_decode_last_kernel() == 1 and c.offset == S + 2
+    signs = c._v_tq._v_q.signs.cpu().numpy()
+    codes, sc, bi = oracle.affine_quantize(k_all, 64, 8)
+    assert np.array_equal(c.k_codes[:, :, :S + 2].cpu().numpy(), codes)
+    k_deq = oracle.affine_dequantize(codes, sc, bi, 64, 8)
+    fn_out = tq.hybrid_quantized_attention(qd, tuple(c.state), c._v_tq.v_packed[:, :, :S + 2], c._v_tq.v_norms[:, :, :S + 2],
+                                           c._v_tq._v_q.centroids, c._v_tq._v_q.signs, scale, None)
+    thr_out = tq.hybrid_quantized_attention(qd, tuple(c.state), c._v_tq.v_packed[:, :, :S + 2], c._v_tq.v_norms[:, :, :S + 2],
+                                            c._v_tq._v_q.centroids, c._v_tq._v_q.signs, scale, None,
+                                            sparse_v_threshold=1e-6)
+    for b in range(B):
+        vp, vn = oracle.quantize_packed(v_all[b], signs, 3)
+        ref, _ = oracle.decode_attention(q[b, :, 0], k_dense=k_deq[b],
+                                         v_polar=dict(packed=vp, norms=vn, centroids=oracle.codebook(3), signs=signs, bits=3),
+                                         attn_scale=scale, n_rep=n_rep)
+        for got in (out, fn_out, thr_out):
+            err = np.abs(got[b, :, 0].float().cpu().numpy() - ref).max() / np.abs(ref).max()
+            assert err < 2e-3
+    assert c.trim(1) == 1 and c.offset == S + 1

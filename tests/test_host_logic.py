@@ -81,7 +81,7 @@ def test_meta_state_format(tq):
     assert v.meta_state.startswith("VOnlyTQ,3,")
     assert v.empty() and v.is_trimmable() and tq.TurboQuantKVCache().empty()
     with pytest.raises(ValueError, match="Expected 2"):
-        c.state = [torch.zeros(1)] * 3
+        c.state = [torch.zeros(1)] * 5
 
 
 def test_qwen2_module_cache_consistency():
@@ -102,3 +102,80 @@ def test_qwen2_module_cache_consistency():
     assert caches[0].offset == 9
     assert torch.allclose(step[:, 0], full[:, -1], atol=1e-4, rtol=1e-4)
     assert model.n_params() == sum(t.numel() for lw in model.layers for t in lw.values()) + 2 * cfg.vocab * cfg.hidden
+
+
+def test_host_float_cache_follows_the_tensor_object(tq):
+    """The host copy of a codebook-sized tensor is tied to the tensor object: a new tensor that
+    lands at a freed tensor's address, or an in-place change, is read again."""
+    from turboquant_mlx_b200 import _lib
+    a = torch.tensor([1.0, -1.0, 1.0, 1.0])
+    assert list(_lib.host_floats(a)) == [1.0, -1.0, 1.0, 1.0]
+    assert _lib.host_floats(a) is _lib.host_floats(a)            # cached while it lives
+    addr = a.data_ptr()
+    del a
+    for _ in range(8):                                           # the allocator reuses the block
+        b = torch.tensor([-1.0, -1.0, 1.0, -1.0])
+        assert list(_lib.host_floats(b)) == [-1.0, -1.0, 1.0, -1.0]
+        if b.data_ptr() == addr:
+            break
+        del b
+    c = torch.tensor([1.0, 1.0])
+    first = _lib.host_floats(c)
+    c.mul_(-1.0)
+    assert list(_lib.host_floats(c)) == [-1.0, -1.0] and list(first) == [1.0, 1.0]
+    n_before = len(_lib._host_cache)
+    del c
+    assert len(_lib._host_cache) == n_before - 1                 # evicted with the tensor
+
+
+def test_state_with_saved_sign_vectors_loads(tq):
+    """A saved state may carry its sign vectors (a library whose generator differs cannot rebuild
+    them from the seed): they replace the seed-derived ones; malformed vectors are refused."""
+    from turboquant_mlx_b200.rotation import sign_values
+    B, H, S, D = 1, 2, 5, 128
+    kp = torch.zeros((B, H, S, 16), dtype=torch.int32).view(torch.uint32)
+    vp = torch.zeros((B, H, S, 13), dtype=torch.int32).view(torch.uint32)
+    kn, vn = torch.ones((B, H, S)), torch.ones((B, H, S))
+    ks = torch.tensor(sign_values(D, 42))
+    vs = -torch.tensor(sign_values(D, 43))                       # not what seed 43 gives here
+    meta = f"{S},3,42,{D},{D},float16,4,3"
+    c = tq.TurboQuantKVCache.from_state([kp, kn, vp, vn, ks, vs], meta)
+    assert c.offset == S and c.k_bits == 4 and c.v_bits == 3
+    assert torch.equal(c._k_q.signs, ks) and torch.equal(c._v_q.signs, vs)
+    assert not c.signs_match_seed()
+    assert len(c.state) == 4 and len(c.state_with_signs) == 6
+    plain = tq.TurboQuantKVCache.from_state([kp, kn, vp, vn], meta)
+    assert plain.signs_match_seed()
+    with pytest.raises(ValueError, match=r"\+1 / -1"):
+        tq.TurboQuantKVCache.from_state([kp, kn, vp, vn, ks * 0.5, vs], meta)
+    with pytest.raises(ValueError, match="cache dimension"):
+        tq.TurboQuantKVCache.from_state([kp, kn, vp, vn, ks[:64], vs], meta)
+    with pytest.raises(ValueError, match="Expected 2"):
+        tq.TurboQuantKVCache.from_state([kp, kn, vp, vn, ks], meta)
+    # values-only forms: 2 arrays, or 3 with the V sign vector
+    v_only = tq.TurboQuantKVCache.from_state([vp, vn, vs], f"{S},3,42,0,{D},float16")
+    assert v_only.v_only and not v_only.empty() and torch.equal(v_only._v_q.signs, vs)
+    k16 = torch.zeros((B, H, S, D), dtype=torch.float16)
+    vo = tq.VOnlyTurboQuantCache.from_state([k16, k16[..., :0], vp, vn, vs], f"VOnlyTQ,3,42,{S},3,42,0,{D},float16")
+    assert vo.offset == S and torch.equal(vo._v_tq._v_q.signs, vs)
+    assert len(vo.state_with_signs) == 5
+
+
+def test_adaptive_cache_arguments_follow_the_reference(tq):
+    from turboquant_mlx_b200.base import KVCache
+    caches = tq.make_adaptive_cache(8, 3, 4, 3, 2)      # num_layers, bits, k_bits, v_bits, fp16_layers
+    assert [isinstance(c, KVCache) for c in caches] == [True, True] + [False] * 4 + [True, True]
+    mid = caches[3]
+    assert (mid.k_bits, mid.v_bits, mid.seed) == (4, 3, 42)
+
+    class Plain:
+        def make_cache(self):
+            return [KVCache()]
+
+    class Other:
+        def make_cache(self):
+            return [object()]
+
+    assert len(tq.make_adaptive_cache(4, model=Plain())) == 4
+    with pytest.raises(ValueError, match="Incompatible cache type"):
+        tq.make_adaptive_cache(4, model=Other())

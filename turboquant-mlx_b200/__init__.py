@@ -34,5 +34,6 @@ from .rotation import (
 )
 from .base import KVCache, scaled_dot_product_attention
 from .mixed_cache import MixedQuantKVCache
+from .hybrid_cache import HybridQuantCache, hybrid_quantized_attention
 
-__version__ = "0.4.0"
+__version__ = "0.5.0"

@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import weakref
 from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint32, c_void_p
 
 import torch
@@ -166,32 +167,40 @@ def stream_ptr(device=None) -> c_void_p:
 # ---------------------------------------------------------------------------
 # codebook-sized parameters: the C ABI takes them as host float arrays
 # ---------------------------------------------------------------------------
-_host_cache: dict = {}
+_host_cache: dict = {}     # id(tensor) -> (weak reference, tensor version, ctypes array)
+
+
+def _remember(t: torch.Tensor, arr) -> None:
+    key = id(t)
+
+    def _evict(_ref, key=key):
+        _host_cache.pop(key, None)
+
+    _host_cache[key] = (weakref.ref(t, _evict), t._version, arr)
 
 
 def register_host_values(t: torch.Tensor, values) -> None:
     """Remember the host copy of a small device tensor (signs, centroids,
     boundaries) so that passing the tensor later costs no device read."""
-    arr = (c_float * len(values))(*[float(v) for v in values])
-    _host_cache[(t.data_ptr(), t._version, t.numel(), str(t.device))] = arr
-    if len(_host_cache) > 4096:
-        for k in list(_host_cache)[:1024]:
-            del _host_cache[k]
+    _remember(t, (c_float * len(values))(*[float(v) for v in values]))
 
 
 def host_floats(x):
     """ctypes float array for a codebook-sized parameter given as a tensor,
     numpy array or sequence.  A device tensor seen for the first time is read
-    back once (this synchronises) and cached by (address, version)."""
+    back once (this synchronises) and the copy is kept for as long as that tensor
+    object lives and is not modified in place: the entry is keyed on the object
+    itself (not its address, which the allocator hands to the next tensor of the
+    same size) and dropped when the tensor is freed."""
     if x is None:
         return None
     if isinstance(x, torch.Tensor):
-        key = (x.data_ptr(), x._version, x.numel(), str(x.device))
-        arr = _host_cache.get(key)
-        if arr is None:
-            vals = x.detach().to(torch.float32).reshape(-1).cpu().tolist()
-            arr = (c_float * len(vals))(*vals)
-            _host_cache[key] = arr
+        hit = _host_cache.get(id(x))
+        if hit is not None and hit[0]() is x and hit[1] == x._version:
+            return hit[2]
+        vals = x.detach().to(torch.float32).reshape(-1).cpu().tolist()
+        arr = (c_float * len(vals))(*vals)
+        _remember(x, arr)
         return arr
     vals = [float(v) for v in x]
     return (c_float * len(vals))(*vals)

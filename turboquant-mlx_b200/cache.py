@@ -104,6 +104,7 @@ class TurboQuantKVCache:
             self._v_q = _Quantizer(v_dim, self.v_bits, self.seed + 1, device)
             self._v_dim = v_dim
             self._v_pdim = packed_dim(v_dim, self.v_bits)
+        self._adopt_loaded_signs()
 
     @staticmethod
     def _grow(old_p, old_n, B, H, n, pdim, prev, device):
@@ -285,9 +286,19 @@ class TurboQuantKVCache:
 
     @state.setter
     def state(self, v):
+        """2 (v_only) or 4 arrays as the reference stores them (cache.py:262-274), or the
+        `state_with_signs` form: the same followed by the sign vectors (one for v_only, K then V
+        otherwise).  Saved sign vectors replace the ones this process would derive from the seed,
+        so a cache written by a library with a different generator decodes correctly."""
         if not v:
             return
         v = [t.contiguous() for t in v]
+        if len(v) in (3, 6):
+            n_signs = 1 if len(v) == 3 else 2
+            signs = [self._check_signs(t) for t in v[-n_signs:]]
+            self._loaded_signs = (None, signs[0]) if n_signs == 1 else (signs[0], signs[1])
+            v = v[:-n_signs]
+            self._adopt_loaded_signs()
         if len(v) == 4:
             self.k_packed, self.k_norms, self.v_packed, self.v_norms = v
             self.offset = self.k_packed.shape[2]
@@ -295,7 +306,34 @@ class TurboQuantKVCache:
             self.v_packed, self.v_norms = v
             self.offset = self.v_packed.shape[2]
         else:
-            raise ValueError(f"Expected 2 (v_only) or 4 arrays in state, got {len(v)}")
+            raise ValueError(f"Expected 2 (v_only) or 4 arrays in state (plus 1 or 2 sign vectors), got {len(v)}")
+
+    @staticmethod
+    def _check_signs(t):
+        t = t.to(torch.float32).reshape(-1)
+        if t.numel() == 0 or t.numel() & (t.numel() - 1) or not bool(((t == 1.0) | (t == -1.0)).all()):
+            raise ValueError("a saved sign vector must hold +1 / -1 values and have a power-of-two length")
+        return t
+
+    def _adopt_loaded_signs(self):
+        """Put sign vectors that came with a saved state into the quantizers (once they exist)."""
+        loaded = getattr(self, "_loaded_signs", None)
+        if loaded is None:
+            return
+        for q, sg in ((self._k_q, loaded[0]), (self._v_q, loaded[1])):
+            if q is not None and sg is not None:
+                if sg.numel() != q.dim:
+                    raise ValueError(f"saved sign vector has {sg.numel()} entries, the cache dimension is {q.dim}")
+                q.signs = sg.to(q.signs.device)
+
+    def signs_match_seed(self) -> bool:
+        """True when the sign vectors in use are the ones this library derives from `seed`
+        (False after loading a state saved by a library with another generator)."""
+        from .rotation import sign_values
+        for q, sd in ((self._k_q, self.seed), (self._v_q, self.seed + 1)):
+            if q is not None and q.signs.cpu().tolist() != sign_values(q.dim, sd):
+                return False
+        return True
 
     @property
     def state_with_signs(self):
@@ -356,11 +394,14 @@ class TurboQuantKVCache:
         cls.__init__(obj)
         obj.meta_state = meta_state
         obj.state = state
+        if obj.k_packed is None and obj.v_packed is not None:
+            obj.v_only = True      # a values-only state (the reference leaves v_only False here and then
+                                   # reports such a cache as empty, cache.py:354-356 with :220-221)
         if obj.k_packed is not None:
             obj._k_pdim = obj.k_packed.shape[-1]
         if obj.v_packed is not None:
             obj._v_pdim = obj.v_packed.shape[-1]
-        if obj._k_dim is not None and obj._v_dim is not None:
+        if obj._v_dim is not None and (obj._k_dim is not None or obj.v_only):
             dev = obj.v_packed.device if obj.v_packed is not None else None
-            obj._ensure_quantizer(obj._k_dim, obj._v_dim, dev)
+            obj._ensure_quantizer(obj._k_dim or obj._v_dim, obj._v_dim, dev)
         return obj

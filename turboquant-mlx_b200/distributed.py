@@ -57,6 +57,18 @@ def gather_partials(send: torch.Tensor, group=None, recv: torch.Tensor | None = 
     return recv
 
 
+def check_partials(recv: torch.Tensor, rows: int, dim: int) -> None:
+    """Host-side guard for a gathered (world, rows * (dim + 2)) block (synchronises): raises
+    RuntimeError naming the first rank whose partial state holds a non-finite value where one
+    cannot occur (l or acc anywhere, m on a row with l > 0; m = -inf marks an empty chunk)."""
+    m, l, acc = partial_views(recv, rows, dim)
+    bad = (~torch.isfinite(l)).any(-1) | (~torch.isfinite(acc)).flatten(1).any(-1) | \
+        ((l > 0) & ~torch.isfinite(m)).any(-1) | torch.isnan(m).any(-1)
+    if bool(bad.any()):
+        rank = int(torch.nonzero(bad)[0])
+        raise RuntimeError(f"rank {rank} sent a non-finite partial attention state")
+
+
 class PeerExchange:
     """All-gather of one flat float32 block per rank through peer-to-peer stores over
     NVLink instead of a library collective: `tq_peer_push` writes this rank's block into
@@ -150,14 +162,18 @@ class PeerExchange:
 
 def sequence_parallel_decode(q, *, k, v, attn_scale: float, group=None, out_dtype=None,
                              q_prerotated: bool = False, mask=None, send_buf=None,
-                             recv_buf=None, exchange: "PeerExchange | None" = None) -> torch.Tensor:
+                             recv_buf=None, exchange: "PeerExchange | None" = None,
+                             check: bool = False) -> torch.Tensor:
     """Decode attention with the sequence split across the ranks of `group`.
 
     q (B, n_q, dim) is replicated; `k` / `v` describe this rank's chunk of
     positions (formats as in `kernels.flash_decode`).  Returns (B, n_q, dim) on
     every rank.  A rank whose chunk is empty passes k = v = None.  With `exchange`
     (a PeerExchange sized rows * (dim + 2) floats) the partial states travel by peer
-    stores instead of the all_gather."""
+    stores instead of the all_gather; its waits are bounded, and a wait that gave up leaves NaN in
+    the output and a code in `exchange.status`: call `exchange.check()` at your next host
+    synchronisation point, or pass check=True here (which synchronises on every call and also
+    validates the gathered block with `check_partials`)."""
     B, n_q, dim = q.shape
     rows = B * n_q
     dev = q.device
@@ -171,6 +187,10 @@ def sequence_parallel_decode(q, *, k, v, attn_scale: float, group=None, out_dtyp
                              partials=True,
                              partial_out=(m.view(B, n_q), l.view(B, n_q), acc.view(B, n_q, dim)))
     recv = exchange.exchange(send_buf) if exchange is not None else gather_partials(send_buf, group, recv_buf)
+    if check:
+        if exchange is not None:
+            exchange.check()
+        check_partials(recv, rows, dim)
     gm, gl, gacc = partial_views(recv, rows, dim)
     signs = v["signs"] if (v is not None and v.get("format") == "polar") else None
     out = kernels.merge_partials(gm, gl, gacc, signs, out_dtype or q.dtype)

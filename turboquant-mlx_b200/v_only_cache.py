@@ -163,6 +163,11 @@ class VOnlyTurboQuantCache:
         return k_state + v_state
 
     @property
+    def state_with_signs(self):
+        """`state` followed by the V sign vector (see TurboQuantKVCache.state_with_signs)."""
+        return self.state + [self._v_tq._v_q.signs]
+
+    @property
     def meta_state(self):
         return f"VOnlyTQ,{self._v_bits},{self._v_tq.seed},{self._v_tq.meta_state}"
 
@@ -175,9 +180,11 @@ class VOnlyTurboQuantCache:
             obj._k_cache.values = state[1].contiguous()
             obj._k_cache.offset = state[0].shape[2]
         if len(state) > 2:
-            obj._v_tq.state = state[2:]
             obj._v_tq.meta_state = parts[3]
+            obj._v_tq.state = state[2:]          # 2 arrays, or 3 with the saved V sign vector
             obj._v_tq._v_pdim = obj._v_tq.v_packed.shape[-1]
+            if obj._v_tq._v_dim:
+                obj._v_tq._ensure_quantizer(state[0].shape[-1], obj._v_tq._v_dim, obj._v_tq.v_packed.device)
         return obj
 
     def make_mask(self, *args, **kwargs):
