@@ -242,6 +242,18 @@ typedef struct tq_flash_params {
   int64_t new_k_batch_stride, new_k_head_stride, new_v_batch_stride, new_v_head_stride;
   const float* k_boundaries_host;
   const float* v_boundaries_host;
+  /* Value skipping inside the decode kernel (sparse_v.py:59-65, threshold plumbed at
+   * fused_attention.py:109-121).  The reference drops a position from the value sum when its
+   * softmax weight is below the threshold.  Here (tensor-core path, > 0 enables) a warp's tile of 16
+   * positions is dropped for a (batch, kv head) group when every weight in it is already certain to
+   * end below the threshold - weight <= exp(score - running max) / running sum - so nothing is
+   * dropped that the reference would keep, and everything still counts in the softmax sum.
+   * active_positions: optional device int32 (batch, n_kv_heads), zeroed by the caller; receives
+   * the number of positions whose values were accumulated (count_active_positions semantics per
+   * group, sparse_v.py:189-191). */
+  float sparse_v_threshold;
+  int32_t sparse_reserved;
+  int32_t* active_positions;
 } tq_flash_params;
 
 /* Workspace contract: 16-byte aligned, at least tq_flash_decode_workspace_bytes()

@@ -387,3 +387,59 @@ def test_prepared_calls_match_direct_calls(tq, golden, dev):
     mp = tq.MergePlan(pm, pl, pa, v["signs"], merged)
     mp.run()
     assert _rel(merged.cpu().numpy(), want[0].cpu().numpy()) < 1e-5   # two identical parts merge to the same result
+
+
+def test_flash_decode_value_skipping_is_conservative(tq, oracle, dev):
+    """sparse_v_threshold inside the decode kernel (sparse_v.py:59-65 semantics, conservative):
+    peaked attention over 4096 positions - most 16-position tiles are dropped, the result stays
+    within the attention tolerance of the oracle's exact rule, the count of accumulated positions
+    is never below the oracle's count of kept positions, and a threshold of 0 changes nothing."""
+    rng = np.random.default_rng(21)
+    n_kv, n_rep, S, D = 2, 4, 4096, 128
+    kq = tq.PolarQuantizer(D, 4, seed=42, device=dev)
+    vq = tq.PolarQuantizer(D, 3, seed=43, device=dev)
+    ks, vs = kq.signs.cpu().numpy(), vq.signs.cpu().numpy()
+    q = rng.standard_normal((n_kv * n_rep, D)).astype(np.float16)
+    kraw = rng.standard_normal((n_kv, S, D)).astype(np.float16)
+    # a few keys line up with the queries so that the softmax is peaked (as in a trained model)
+    for h in range(n_kv):
+        for j in range(6):
+            kraw[h, 97 * (j + 1) + 300 * h] = (q[h * n_rep + (j % n_rep)] * 6).astype(np.float16)
+    vraw = (rng.standard_normal((n_kv, S, D)) * rng.lognormal(0, 0.5, (n_kv, S, 1))).astype(np.float16)
+    kp, kn = oracle.quantize_packed(kraw, ks, 4)
+    vp, vn = oracle.quantize_packed(vraw, vs, 3)
+    scale = 1.0 / math.sqrt(D)
+    kdesc = dict(packed=kp, norms=kn, centroids=oracle.codebook(4), signs=ks, bits=4)
+    vdesc = dict(packed=vp, norms=vn, centroids=oracle.codebook(3), signs=vs, bits=3)
+    k = dict(format="polar", packed=_t(kp, dev).unsqueeze(0), norms=_t(kn, dev).unsqueeze(0), centroids=kq.centroids,
+             signs=kq.signs, bits=4)
+    v = dict(format="polar", packed=_t(vp, dev).unsqueeze(0), norms=_t(vn, dev).unsqueeze(0), centroids=vq.centroids,
+             signs=vq.signs, bits=3)
+    qd = _t(q, dev).unsqueeze(0)
+    dense = tq.flash_decode(qd, k=k, v=v, attn_scale=scale, out_dtype=torch.float32)
+    dense_ref, w = oracle.decode_attention(q, k_polar=kdesc, v_polar=vdesc, attn_scale=scale, n_rep=n_rep)
+    assert _rel(dense[0].cpu().numpy(), dense_ref) < ATT_TOL
+    for thr in (1e-5, 1e-3):
+        exact, _ = oracle.decode_attention(q, k_polar=kdesc, v_polar=vdesc, attn_scale=scale, n_rep=n_rep,
+                                           sparse_v_threshold=thr)
+        active = torch.empty((1, n_kv), dtype=torch.int32, device=dev)
+        got = tq.flash_decode(qd, k=k, v=v, attn_scale=scale, out_dtype=torch.float32, sparse_v_threshold=thr,
+                              active_out=active)
+        assert tq._lib.lib().tq_flash_decode_last_kernel() == 1
+        g0 = got[0].cpu().numpy()
+        # the kernel drops a subset of what the exact rule drops: it is at least as close to the
+        # un-thresholded result as the exact rule is
+        assert _rel(g0, dense_ref) <= _rel(exact, dense_ref) + ATT_TOL
+        if thr == 1e-5:                                            # the reference's own criterion at its default
+            cos = (g0 * dense_ref).sum(-1) / (np.linalg.norm(g0, axis=-1) * np.linalg.norm(dense_ref, axis=-1))
+            assert cos.min() > 0.999
+        kept = (w >= thr).reshape(n_kv, n_rep, S).any(1).sum(-1)   # positions the exact rule keeps for some head
+        act = active[0].cpu().numpy()
+        print(f"thr {thr}: positions accumulated per kv head {act.tolist()}, kept by the exact rule {kept.tolist()}")
+        assert (act >= kept).all() and (act <= S).all()
+        if thr == 1e-3:
+            assert (act < S).all()                                 # whole tiles were dropped
+    same = tq.flash_decode(qd, k=k, v=v, attn_scale=scale, out_dtype=torch.float32, sparse_v_threshold=0.0)
+    assert torch.equal(same, dense)
+    with pytest.raises(ValueError, match="value skipping"):
+        tq.flash_decode(qd, k=k, v=v, attn_scale=scale, sparse_v_threshold=1e-3, mask=torch.zeros((1, 1, S), device=dev))

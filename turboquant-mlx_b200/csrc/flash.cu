@@ -138,6 +138,8 @@ static int fill_args(const tq_flash_params* p, FlashArgs* a) {
   a->vs_batch_stride = p->vs_batch_stride;
   a->vs_head_stride = p->vs_head_stride;
   a->attn_scale = p->attn_scale;
+  a->sparse_thr = p->sparse_v_threshold > 0.f ? p->sparse_v_threshold : 0.f;
+  a->active_positions = p->active_positions;
   a->mask = p->mask;
   a->mask_batch_stride = p->mask_batch_stride;
   a->mask_head_stride = p->mask_head_stride;
@@ -291,6 +293,8 @@ extern "C" int tq_flash_decode(const tq_flash_params* p) {
     return launch_flash_mma(a, plan.splits, mo, st);
   }
   TQ_REQUIRE(p->n_peers == 0, TQ_ERR_UNSUPPORTED, "peer targets need the tensor-core decode path");
+  TQ_REQUIRE(!(p->sparse_v_threshold > 0.f) && p->active_positions == nullptr, TQ_ERR_UNSUPPORTED,
+             "value skipping (sparse_v_threshold, active_positions) needs the tensor-core decode path");
   TQ_REQUIRE(p->new_v == nullptr, TQ_ERR_UNSUPPORTED,
              "the in-launch append needs the tensor-core decode path (dim 128, n_rep <= 8, no mask, fp16 or "
              "packed keys, new_k of the keys' type)");

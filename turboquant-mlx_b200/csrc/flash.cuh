@@ -38,6 +38,8 @@ struct FlashArgs {
   SignMask v_signs;
 
   float attn_scale;
+  float sparse_thr;                // > 0: drop value tiles whose weights are certain to end below it
+  int* active_positions;           // optional (batch, n_kv_heads) count of positions accumulated
   const float* mask;
   int64_t mask_batch_stride, mask_head_stride;
 

@@ -764,6 +764,24 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
           l_run += ex2(s2[ng][c] - m_use);
         }
       }
+    // Value skipping: the final softmax weight of a position is at most exp(score - running max) /
+    // running sum (both only grow), so a tile whose every weight is below the threshold by that bound,
+    // for every head of the group, contributes nothing the reference would keep.
+    bool skip_values = false;
+    if (a.sparse_thr > 0.f) {
+      float wmax = 0.f;
+#pragma unroll
+      for (int ng = 0; ng < 2; ++ng)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) wmax = fmaxf(wmax, ex2(s2[ng][c] - m_use));
+      float lq = l_run;                                  // running sum of head g in this warp: the quad's lanes
+      lq += __shfl_xor_sync(0xffffffffu, lq, 1);
+      lq += __shfl_xor_sync(0xffffffffu, lq, 2);
+      skip_values = __all_sync(0xffffffffu, g >= a.n_rep || wmax < a.sparse_thr * lq);
+    }
+    if (a.active_positions != nullptr && !skip_values && lane == 0 && pw < nvp)
+      atomicAdd(a.active_positions + b * a.n_kv_heads + kvh, min(16, nvp - pw));
+    if (!skip_values) {
     const uint32_t pb0 = pack_h2(pv[0][0], pv[0][1]);   // k = 2t, 2t+1      (positions pw + 2t ..)
     const uint32_t pb1 = pack_h2(pv[1][0], pv[1][1]);   // k = 2t+8, 2t+9    (positions pw + 8 + 2t ..)
     // affine values: this lane's 16 elements lie in group g / 4; its scales for the two position pairs
@@ -823,6 +841,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       }
       mma16816(o[j], af, pb0, pb1);
     }
+    }   // !skip_values
     __syncwarp();
     if (lane == 0) mbar_arrive(empty_bar(s));
   }

@@ -5,8 +5,6 @@
 // five stages through warp shuffles.  All float32 steps that feed the index
 // compare use explicit round-to-nearest intrinsics (no FMA contraction) so the
 // packed words are bit-identical to a sequential float32 evaluation.
-#include <stdlib.h>
-
 #include "common.cuh"
 #include "quantize_row.cuh"
 
@@ -288,8 +286,7 @@ static int quantize_impl(const void* x, int x_dtype, int64_t n_outer, int64_t n_
   make_raw_thresholds(boundaries_host, a.n_thr, dim, &a.thr);
   cudaStream_t st = (cudaStream_t)stream;
   if (x_dtype < TQ_F32 || x_dtype > TQ_BF16) return set_error(TQ_ERR_BAD_ARG, "unknown dtype %d", x_dtype);
-  static const bool force_general = getenv("TQ_FORCE_GENERIC") != nullptr;   // debugging aid
-  if (!force_general && !copy) {   // large contiguous dim-128 batches: thread-per-vector kernel
+  if (!copy) {   // large contiguous dim-128 batches: split-per-vector kernel
     rc = try_launch_quantize_fast(x, x_dtype, n_outer, n_inner, x_outer_stride, dim, bits, a.signs, a.thr,
                                   packed, packed_outer_stride, norms, norms_outer_stride, st);
     if (rc != TQ_ERR_UNSUPPORTED) return rc;
@@ -356,8 +353,7 @@ extern "C" int tq_dequantize(const uint32_t* packed, int64_t packed_outer_stride
     a.cs.v[i] = cs;
   }
   cudaStream_t st = (cudaStream_t)stream;
-  static const bool force_general = getenv("TQ_FORCE_GENERIC") != nullptr;   // debugging aid
-  if (!force_general) {   // large contiguous dim-128 batches: split-per-vector kernel
+  {   // large contiguous dim-128 batches: split-per-vector kernel
     rc = try_launch_dequantize_fast(packed, packed_outer_stride, norms, norms_outer_stride, n_outer, n_inner,
                                     dim, bits, a.cs, a.s, a.signs, out, out_dtype, out_outer_stride, st);
     if (rc != TQ_ERR_UNSUPPORTED) return rc;

@@ -3,9 +3,11 @@ turboquant_mlx/fused_attention.py:20-125).
 
 The reference loops over the batch in Python and launches prerotate_query,
 prerot_fused_qk_scores, softmax and sparse_v_matvec per element.  Here the
-default route is one split-K flash-decode launch for the whole batch; the
-composed route is kept for `sparse_v_threshold > 0` (its skip rule needs the
-normalised weights) and for `v_buffer`."""
+default route is one split-K flash-decode launch for the whole batch, also with
+`sparse_v_threshold > 0`: the kernel then drops value tiles whose weights are
+certain to end below the threshold (a subset of what the reference's exact rule
+`w < threshold` drops, sparse_v.py:61).  The composed route is kept for
+`v_buffer`, and for thresholds on calls the tensor-core kernel does not cover."""
 
 from __future__ import annotations
 
@@ -67,11 +69,12 @@ def turboquant_attention(queries, cache, attn_scale: float, mask=None, v_buffer=
     thr = sparse_v_threshold if (sparse_v_threshold is not None and sparse_v_threshold >= 0.0) else 0.0
     has_mask = mask is not None and not isinstance(mask, str)
     pending = getattr(cache, "_pending", None) is not None
-    if pending and (v_buffer is not None or thr != 0.0 or has_mask or n_rep > 8 or dim != 128):
+    fused_ok = v_buffer is None and (thr == 0.0 or not (has_mask or n_rep > 8 or dim != 128))
+    if pending and (not fused_ok or has_mask or n_rep > 8 or dim != 128):
         cache.flush_pending()          # the in-launch insert needs the tensor-core decode kernel
     total = cache.offset
 
-    if v_buffer is None and thr == 0.0:
+    if fused_ok:
         k, v = cache_kv_descriptors(cache)
         m3 = None
         if has_mask:
@@ -81,9 +84,13 @@ def turboquant_attention(queries, cache, attn_scale: float, mask=None, v_buffer=
         rows = cache.take_pending() if hasattr(cache, "take_pending") else None
         new_k, new_v = rows if rows is not None else (None, None)
         stable = bool(getattr(cache, "inputs_stable", False))
+        active = None
+        if thr > 0.0 and getattr(cache, "track_active_positions", False):
+            active = torch.empty((B, n_kv_heads), dtype=torch.int32, device=queries.device)
+            cache.last_active_positions = active
         out = flash_decode(queries[:, :, 0, :], k=k, v=v, attn_scale=attn_scale, mask=m3,
                            out_dtype=queries.dtype, kv_stable=stable, q_stable=stable,
-                           new_k=new_k, new_v=new_v)
+                           new_k=new_k, new_v=new_v, sparse_v_threshold=thr, active_out=active)
         return out.unsqueeze(2)
 
     outputs = []

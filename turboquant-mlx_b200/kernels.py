@@ -253,6 +253,7 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
                  mask: torch.Tensor | None = None, num_splits: int = 0, out_dtype=None,
                  partials: bool = False, partial_out=None, kv_stable: bool = False, out=None, peers=None,
                  q_stable: bool = False, new_k: torch.Tensor | None = None, new_v: torch.Tensor | None = None,
+                 sparse_v_threshold: float = 0.0, active_out: torch.Tensor | None = None,
                  _prepare_only: bool = False):
     """Split-K flash decoding for one query token per sequence.
 
@@ -283,6 +284,12 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
     into that position and attends over them in the same launch, replacing the separate cache
     append.  The descriptors need "boundaries" (and polar keys "signs") for this.  Raises
     ValueError when the call does not qualify for the tensor-core kernel.
+
+    sparse_v_threshold > 0 (tensor-core kernel only, ValueError otherwise): values of positions
+    whose softmax weight is certain to end below the threshold are not accumulated (decided per
+    16-position tile and kv-head group from the running softmax state, so nothing is dropped
+    that the reference's `sparse_v_matvec` would keep); `active_out`, an int32 (B, n_kv) tensor,
+    receives the number of positions whose values were accumulated.
     """
     _lib.require_cuda(q)
     B, n_q, dim = q.shape
@@ -363,6 +370,14 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
     P.attn_scale, P.num_splits = float(attn_scale), int(num_splits)
     P.kv_stable = int(kv_stable)
     P.q_stable = int(q_stable)
+    P.sparse_v_threshold = max(float(sparse_v_threshold), 0.0)
+    if active_out is not None:
+        _lib.require_cuda(active_out)
+        if active_out.dtype != torch.int32 or tuple(active_out.shape) != (B, n_kv) or not active_out.is_contiguous():
+            raise ValueError(f"active_out must be a contiguous int32 ({B}, {n_kv}) tensor")
+        active_out.zero_()
+        keep.append(active_out)
+        P.active_positions = active_out.data_ptr()
     if (new_k is None) != (new_v is None):
         raise ValueError("new_k and new_v must be given together")
     if new_k is not None:
