@@ -254,6 +254,12 @@ typedef struct tq_flash_params {
   float sparse_v_threshold;
   int32_t sparse_reserved;
   int32_t* active_positions;
+  /* Optional device array of `batch` int32 (tensor-core path only): the number of valid
+   * positions of each sequence, read by the kernel when it runs, at most seq_len (which then is
+   * the capacity the launch is planned for).  Serves ragged batches without a mask tensor, and
+   * decode loops replayed from a CUDA graph whose lengths advance on the device.  With new_k /
+   * new_v the rows go to position seq_lens_dev[b] - 1.  No reference counterpart. */
+  const int32_t* seq_lens_dev;
 } tq_flash_params;
 
 /* Workspace contract: 16-byte aligned, at least tq_flash_decode_workspace_bytes()

@@ -443,3 +443,80 @@ def test_flash_decode_value_skipping_is_conservative(tq, oracle, dev):
     assert torch.equal(same, dense)
     with pytest.raises(ValueError, match="value skipping"):
         tq.flash_decode(qd, k=k, v=v, attn_scale=scale, sparse_v_threshold=1e-3, mask=torch.zeros((1, 1, S), device=dev))
+
+
+def test_flash_decode_device_side_lengths(tq, dev):
+    """seq_lens: a ragged batch in one launch equals per-sequence calls on the truncated views, for
+    dense and packed keys; with new_k / new_v each row lands at its own sequence's end; and a CUDA
+    graph replays with lengths that advance on the device."""
+    g = torch.Generator(device=dev).manual_seed(31)
+    B, n_kv, n_rep, S, D = 3, 2, 4, 1500, 128
+    vq = tq.PolarQuantizer(D, 3, seed=43, device=dev)
+    kq = tq.PolarQuantizer(D, 4, seed=42, device=dev)
+    lens = [1500, 777, 33]
+    kd = torch.randn((B, n_kv, S, D), generator=g, device=dev).half()
+    vraw = (torch.randn((B, n_kv, S, D), generator=g, device=dev) * 2).half()
+    vp, vn = tq.fused_quantize(vraw.reshape(-1, D), vq.signs, vq.boundaries, D, 3)
+    kp, kn = tq.fused_quantize(kd.reshape(-1, D), kq.signs, kq.boundaries, D, 4)
+    v = dict(format="polar", packed=vp.reshape(B, n_kv, S, 13), norms=vn.reshape(B, n_kv, S), centroids=vq.centroids,
+             signs=vq.signs, bits=3, boundaries=vq.boundaries)
+    k_dense = dict(format="dense", data=kd)
+    k_polar = dict(format="polar", packed=kp.reshape(B, n_kv, S, 16), norms=kn.reshape(B, n_kv, S),
+                   centroids=kq.centroids, signs=kq.signs, bits=4, boundaries=kq.boundaries)
+    q = torch.randn((B, n_kv * n_rep, D), generator=g, device=dev).half()
+    sl = torch.tensor(lens, dtype=torch.int32, device=dev)
+    scale = 0.09
+
+    def cut(desc, b, n):
+        return {key: (val[b:b + 1, :, :n] if isinstance(val, torch.Tensor) and val.ndim >= 3 else val)
+                for key, val in desc.items()}
+
+    for k in (k_dense, k_polar):
+        got = tq.flash_decode(q, k=k, v=v, attn_scale=scale, out_dtype=torch.float32, seq_lens=sl)
+        assert tq._lib.lib().tq_flash_decode_last_kernel() == 1
+        for b, n in enumerate(lens):
+            one = tq.flash_decode(q[b:b + 1], k=cut(k, b, n), v=cut(v, b, n), attn_scale=scale, out_dtype=torch.float32)
+            assert _rel(got[b].cpu().numpy(), one[0].cpu().numpy()) < 1e-5
+    # in-launch append at each sequence's own end
+    kd2, vp2, vn2 = kd.clone(), v["packed"].clone(), v["norms"].clone()
+    new_k = torch.randn((B, n_kv, D), generator=g, device=dev).half()
+    new_v = torch.randn((B, n_kv, D), generator=g, device=dev).half()
+    v2 = dict(v, packed=vp2, norms=vn2)
+    got = tq.flash_decode(q, k=dict(format="dense", data=kd2), v=v2, attn_scale=scale, out_dtype=torch.float32,
+                          seq_lens=sl, new_k=new_k, new_v=new_v)
+    rp, rn = tq.fused_quantize(new_v.reshape(-1, D), vq.signs, vq.boundaries, D, 3)
+    for b, n in enumerate(lens):
+        assert torch.equal(kd2[b, :, n - 1], new_k[b]) and torch.equal(vp2[b, :, n - 1], rp.reshape(B, n_kv, 13)[b])
+        assert torch.equal(vn2[b, :, n - 1], rn.reshape(B, n_kv)[b])
+        assert torch.equal(kd2[b, :, :n - 1], kd[b, :, :n - 1]) and torch.equal(kd2[b, :, n:], kd[b, :, n:])
+        one = tq.flash_decode(q[b:b + 1], k=dict(format="dense", data=kd2[b:b + 1, :, :n]), v=cut(v2, b, n),
+                              attn_scale=scale, out_dtype=torch.float32)
+        assert _rel(got[b].cpu().numpy(), one[0].cpu().numpy()) < 1e-5
+    # graph replay with a device-side length that grows by one per replay
+    out = torch.zeros((B, n_kv * n_rep, D), dtype=torch.float32, device=dev)
+    sl2 = torch.tensor([100, 200, 300], dtype=torch.int32, device=dev)
+
+    def step():
+        sl2.add_(1)
+        tq.flash_decode(q, k=k_dense, v=v, attn_scale=scale, out=out, seq_lens=sl2)
+
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    n_now = sl2.tolist()
+    assert n_now == [104, 204, 304]           # one eager run (capture itself runs nothing) + three replays
+    for b in range(B):
+        one = tq.flash_decode(q[b:b + 1], k=cut(k_dense, b, n_now[b]), v=cut(v, b, n_now[b]), attn_scale=scale,
+                              out_dtype=torch.float32)
+        assert _rel(out[b].cpu().numpy(), one[0].cpu().numpy()) < 1e-5
+    with pytest.raises(ValueError, match="seq_lens"):
+        tq.flash_decode(q, k=k_dense, v=v, attn_scale=scale, seq_lens=sl, mask=torch.zeros((1, 1, S), device=dev))

@@ -6,7 +6,7 @@ benchmark itself uses, with the decode kernel's choice and its status word check
   C2  V-only decode, 28 q / 4 kv heads, ctx 32768, through VOnlyTurboQuantCache + the hooked SDPA
   C3  full TurboQuant cache (K 4-bit, V 3-bit), B = 32, 32 q / 8 kv heads, ctx 8192
   C5  per-GPU shard: 64 q / 8 kv heads, 131072 positions, K 8-bit affine + V 3-bit, two chunks merged
-  and the general-kernel fallbacks (bf16 dense keys, a padding mask) at the C2 size.
+  and, at the C2 size, bf16 dense keys (tensor-core kernel) and a padding mask (general kernel).
 
 Tolerances (reference tests/test_flash_attention.py:38-137, test_core.py:70-109 and the
 stated targets): packed words bit-exact, norms <= 1e-6 relative, attention <= 2e-3 max
@@ -275,8 +275,9 @@ def test_c5_per_gpu_shape_two_chunks_merged(tq, oracle, dev):
 
 
 @pytest.mark.parametrize("case", ["bf16_keys", "padding_mask"])
-def test_c2_size_general_kernel_fallbacks(tq, oracle, dev, case):
-    """bf16 dense keys and an additive padding mask at the C2 size take the general float32 kernel."""
+def test_c2_size_bf16_keys_and_padding_mask(tq, oracle, dev, case):
+    """At the C2 size: bf16 dense keys (a bf16 model with the V-only cache) run on the tensor-core
+    kernel through the bf16 MMA; an additive padding mask takes the general float32 kernel."""
     rng = np.random.default_rng(606)
     n_q, n_kv, S = 28, 4, 32768
     n_rep = n_q // n_kv
@@ -298,12 +299,12 @@ def test_c2_size_general_kernel_fallbacks(tq, oracle, dev, case):
     out = tq.flash_decode(torch.from_numpy(q).to(dev).unsqueeze(0), k=k, v=v, attn_scale=scale, out_dtype=torch.float32,
                           mask=None if mask is None else torch.from_numpy(mask).to(dev))
     torch.cuda.synchronize()
-    assert tq._lib.lib().tq_flash_decode_last_kernel() == 0
+    assert tq._lib.lib().tq_flash_decode_last_kernel() == (1 if case == "bf16_keys" else 0)
     vdesc = dict(packed=vp, norms=vn, centroids=oracle.codebook(3), signs=signs, bits=3)
     m2 = None if mask is None else np.broadcast_to(mask[0], (n_q, S))
     ref = _oracle_dense_k(oracle, q, kt.float().numpy(), vdesc, scale, n_rep, mask=m2)
     err = _rel(out[0].cpu().numpy(), ref)
-    print(f"C2-size fallback ({case}): max rel err vs oracle {err:.2e}")
+    print(f"C2 size, {case}: max rel err vs oracle {err:.2e}")
     assert err < ATT_TOL
 
 

@@ -63,6 +63,7 @@ class FlashParams(ctypes.Structure):
         ("new_v_batch_stride", c_int64), ("new_v_head_stride", c_int64),
         ("k_boundaries_host", POINTER(c_float)), ("v_boundaries_host", POINTER(c_float)),
         ("sparse_v_threshold", c_float), ("sparse_reserved", c_int32), ("active_positions", c_void_p),
+        ("seq_lens_dev", c_void_p),
     ]
 
 

@@ -96,6 +96,7 @@ static int fill_args(const tq_flash_params* p, FlashArgs* a) {
   a->n_rep = p->n_q_heads / p->n_kv_heads;
   a->dim = p->dim;
   a->seq_len = p->seq_len;
+  a->seq_lens = p->seq_lens_dev;
   a->q = p->q;
   a->q_dtype = p->q_dtype;
   a->q_prerotated = p->q_prerotated;
@@ -293,6 +294,8 @@ extern "C" int tq_flash_decode(const tq_flash_params* p) {
     return launch_flash_mma(a, plan.splits, mo, st);
   }
   TQ_REQUIRE(p->n_peers == 0, TQ_ERR_UNSUPPORTED, "peer targets need the tensor-core decode path");
+  TQ_REQUIRE(p->seq_lens_dev == nullptr, TQ_ERR_UNSUPPORTED,
+             "device-side sequence lengths (seq_lens_dev) need the tensor-core decode path");
   TQ_REQUIRE(!(p->sparse_v_threshold > 0.f) && p->active_positions == nullptr, TQ_ERR_UNSUPPORTED,
              "value skipping (sparse_v_threshold, active_positions) needs the tensor-core decode path");
   TQ_REQUIRE(p->new_v == nullptr, TQ_ERR_UNSUPPORTED,

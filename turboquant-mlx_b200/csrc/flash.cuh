@@ -8,6 +8,7 @@ namespace tq {
 struct FlashArgs {
   int batch, n_q_heads, n_kv_heads, n_rep, dim;
   int64_t seq_len, chunk;          // chunk = positions per split
+  const int* seq_lens;             // optional per-sequence valid lengths on the device (<= seq_len)
 
   const void* q;
   int q_dtype, q_prerotated;

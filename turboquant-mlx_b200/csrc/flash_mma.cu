@@ -65,7 +65,9 @@ constexpr int kMaxParts = 96;               // splits of one (batch, kv head) gr
 constexpr int kMergeBatch = 20;             // 16-byte loads a merging lane keeps in flight
 constexpr int kXBatch = (kMaxParts + kConsumerWarps - 1) / kConsumerWarps;
 
-enum : int { KF_DENSE = 0, KF_POLAR3 = 3, KF_POLAR4 = 4, KF_AFFINE8 = 8 };
+enum : int { KF_DENSE = 0, KF_DENSE_BF16 = 1, KF_POLAR3 = 3, KF_POLAR4 = 4, KF_AFFINE8 = 8 };
+// dense keys: fp16 rows (KF_DENSE) or bf16 rows (KF_DENSE_BF16, scores by the bf16 MMA)
+__host__ __device__ constexpr bool is_dense(int kf) { return kf == KF_DENSE || kf == KF_DENSE_BF16; }
 
 struct MmaTables {
   uint16_t k_c16[16];   // beta_k-scaled centroids as f16 bits
@@ -90,6 +92,7 @@ struct MmaTables {
 
 template <int KF> struct KGeom;
 template <> struct KGeom<KF_DENSE> { static constexpr int row = kDenseRowBytes, lut = 0, norms = 0; };
+template <> struct KGeom<KF_DENSE_BF16> { static constexpr int row = kDenseRowBytes, lut = 0, norms = 0; };
 template <> struct KGeom<KF_POLAR3> { static constexpr int row = 52, lut = 64 * 32 * 4, norms = kTile * 4; };
 template <> struct KGeom<KF_POLAR4> { static constexpr int row = 64, lut = 256 * 32 * 4, norms = kTile * 4; };
 // group-affine 8-bit codes, two groups of 64: per row 128 code bytes; the "norms" slot holds the
@@ -178,6 +181,30 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void mma16816_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// a pair of floats as the score MMA's 16-bit operand type (high part) and what is left (residual)
+template <bool BF>
+__device__ __forceinline__ void split_pair(float x, float y, uint32_t& hi, uint32_t& lo) {
+  if (BF) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+    const float2 hf = __bfloat1622float2(h);
+    const __nv_bfloat162 l = __floats2bfloat162_rn(x - hf.x, y - hf.y);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    lo = *reinterpret_cast<const uint32_t*>(&l);
+  } else {
+    const __half2 h = __floats2half2_rn(x, y);
+    const float2 hf = __half22float2(h);
+    const __half2 l = __floats2half2_rn(x - hf.x, y - hf.y);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    lo = *reinterpret_cast<const uint32_t*>(&l);
+  }
+}
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -219,7 +246,7 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
 template <int KF>
 __device__ __forceinline__ int kslot_element(int ks, int s) {
   const int tt = (s & 7) >> 1, lo = s & 1, up = s >> 3;
-  if (KF == KF_DENSE) return 8 * (4 * (ks >> 1) + tt) + 4 * (ks & 1) + 2 * up + lo;
+  if (is_dense(KF)) return 8 * (4 * (ks >> 1) + tt) + 4 * (ks & 1) + 2 * up + lo;
   if (KF == KF_POLAR4) return 32 * tt + 4 * ks + 2 * up + lo;
   if (KF == KF_AFFINE8) return 16 * (4 * (ks >> 2) + tt) + 4 * (ks & 3) + 2 * up + lo;   // k-steps 0-3: group 0
   const int pi = 2 * ks + up;   // pair index within the thread: 15 pairs in words 3t..3t+2, one in word 12
@@ -284,8 +311,12 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  // valid positions of this sequence: the launch's seq_len, or the device-side length when given
+  // (an input like the query: unless the caller vouches for it, wait for the preceding grid first)
+  if (a.seq_lens != nullptr && !a.q_stable) grid_dependency_wait();
+  const int64_t seq = a.seq_lens != nullptr ? max((int64_t)0, min((int64_t)a.seq_lens[b], a.seq_len)) : a.seq_len;
   const int64_t pb = (int64_t)split * a.chunk;
-  const int64_t pe = min(a.seq_len, pb + a.chunk);
+  const int64_t pe = max(pb, min(seq, pb + a.chunk));
   const int n_tiles = (int)((pe - pb + kTile - 1) / kTile);
   const int h0 = kvh * a.n_rep;
 
@@ -362,11 +393,10 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         else
           v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const __nv_bfloat16*>(a.q) + off));
       }
-      const __half2 hi = __floats2half2_rn(v.x, v.y);
-      const float2 hf = __half22float2(hi);
-      const __half2 lo = __floats2half2_rn(v.x - hf.x, v.y - hf.y);
-      qf[(ks * 32 + ln) * 4 + 2 * up] = *reinterpret_cast<const uint32_t*>(&hi);
-      qf[(ks * 32 + ln) * 4 + 2 * up + 1] = *reinterpret_cast<const uint32_t*>(&lo);
+      uint32_t hi, lo;
+      split_pair<KF == KF_DENSE_BF16>(v.x, v.y, hi, lo);
+      qf[(ks * 32 + ln) * 4 + 2 * up] = hi;
+      qf[(ks * 32 + ln) * 4 + 2 * up + 1] = lo;
     }
     consumer_barrier();   // query fragments ready
   }
@@ -387,14 +417,18 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         for (int j = 0; j < 4; ++j) v[j] *= sign_at(a.k_signs, lane * 4 + j);
         warp_butterfly<4>(v, lane);
       }
-      float qsum = 0.f;   // sum of the f16 (hi + lo) query values this lane holds
+      float qsum = 0.f;   // sum of the 16-bit (hi + lo) query values this lane holds
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const __half hi = __float2half_rn(v[j]);
-        const __half lo = __float2half_rn(v[j] - __half2float(hi));
-        qs[r * kDim + lane * 4 + j] = hi;
-        qs[(8 + r) * kDim + lane * 4 + j] = lo;
-        qsum += __half2float(hi) + __half2float(lo);
+      for (int j = 0; j < 4; j += 2) {
+        uint32_t hi, lo;
+        split_pair<KF == KF_DENSE_BF16>(v[j], v[j + 1], hi, lo);
+        *reinterpret_cast<uint32_t*>(qs + r * kDim + lane * 4 + j) = hi;
+        *reinterpret_cast<uint32_t*>(qs + (8 + r) * kDim + lane * 4 + j) = lo;
+        if (KF == KF_AFFINE8) {
+          const float2 hf = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+          const float2 lf = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+          qsum += (hf.x + lf.x) + (hf.y + lf.y);
+        }
       }
       if (KF == KF_AFFINE8) {   // lanes 0-15 hold elements 0-63 (group 0), lanes 16-31 group 1
 #pragma unroll
@@ -406,7 +440,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   }
 
   const uint8_t* kbase;
-  if (KF == KF_DENSE)
+  if (is_dense(KF))
     kbase = reinterpret_cast<const uint8_t*>(a.k_data) + (b * a.k_batch_stride + kvh * a.k_head_stride) * 2;
   else if (KF == KF_AFFINE8)
     kbase = reinterpret_cast<const uint8_t*>(a.k_data) + (b * a.k_batch_stride + kvh * a.k_head_stride);
@@ -421,7 +455,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   // packed values: strides in 32-bit words; affine codes: strides in bytes
   const uint8_t* vbase = reinterpret_cast<const uint8_t*>(a.v_data) +
                          (b * a.v_batch_stride + kvh * a.v_head_stride) * (VAFF ? 1 : 4);
-  const float* knbase = (KF == KF_DENSE || KF == KF_AFFINE8)
+  const float* knbase = (is_dense(KF) || KF == KF_AFFINE8)
                             ? nullptr : a.k_norms + b * a.kn_batch_stride + kvh * a.kn_head_stride;
   const float* vnbase = VAFF ? nullptr : a.v_norms + b * a.vn_batch_stride + kvh * a.vn_head_stride;
   // affine values: per position two fp16 scales and two fp16 biases = one 32-bit word each
@@ -432,9 +466,9 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
 
   // =============================== producer ===============================
   if (warp == kConsumerWarps) {
-    // The step's own token (position seq_len - 1) is appended by the CTA that owns the last chunk of
-    // the group, just before it streams the tile that holds it.
-    const bool appends = a.new_v != nullptr && split == (int)gridDim.x - 1 && KF != KF_AFFINE8 && !VAFF;
+    // The step's own token (the sequence's last position) is appended by the CTA whose chunk holds
+    // it, just before it streams the tile that holds it.
+    const bool appends = a.new_v != nullptr && seq - 1 >= pb && seq - 1 < pe && KF != KF_AFFINE8 && !VAFF;
     // K / V may be fetched while preceding kernels are still running only if the caller vouches
     // that they do not write them (kv_stable); likewise the rows to append (q_stable).
     if (!a.kv_stable || (appends && !a.q_stable)) grid_dependency_wait();
@@ -446,10 +480,10 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         break;
       }
       if (appends && i == n_tiles - 1) {
-        const int64_t pn = a.seq_len - 1;
+        const int64_t pn = seq - 1;
         const int64_t koff = b * a.nk_batch_stride + (int64_t)kvh * a.nk_head_stride;
         const int64_t voff = b * a.nv_batch_stride + (int64_t)kvh * a.nv_head_stride;
-        if (KF == KF_DENSE) {          // key row stored as it is (same 16-bit type as the cache)
+        if (is_dense(KF)) {          // key row stored as it is (same 16-bit type as the cache)
           if (lane < 16)
             reinterpret_cast<uint4*>(const_cast<uint8_t*>(kbase) + pn * kDenseRowBytes)[lane] =
                 reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(a.new_k) + koff * 2)[lane];
@@ -484,10 +518,10 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       // byte counts moved by bulk copies (multiples of 16); ragged remainders by plain loads
       const uint32_t v_total = nvp * VGeom<VB>::row, v_bulk = v_total & ~15u;
       const uint32_t n_total = nvp * 4, n_bulk = n_total & ~15u;
-      const uint32_t k_total = (KF == KF_DENSE || KF == KF_AFFINE8) ? 0u : (uint32_t)nvp * KGeom<KF>::row;
+      const uint32_t k_total = (is_dense(KF) || KF == KF_AFFINE8) ? 0u : (uint32_t)nvp * KGeom<KF>::row;
       const uint32_t k_bulk = k_total & ~15u;
       const uint8_t* vsrc = vbase + p0 * VGeom<VB>::row;
-      const uint8_t* ksrc = kbase + p0 * (KF == KF_DENSE ? 256 : KGeom<KF>::row);
+      const uint8_t* ksrc = kbase + p0 * (is_dense(KF) ? 256 : KGeom<KF>::row);
       {
         const int w = lane;   // remainders are at most 3 words each
         if (v_bulk + 4 * w < v_total)
@@ -520,11 +554,11 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       __syncwarp();
       if (lane == 0) {
         uint32_t tx = v_bulk + (VAFF ? 2 * n_bulk : n_bulk);
-        if (KF == KF_DENSE) tx += (uint32_t)nvp * 256u;
+        if (is_dense(KF)) tx += (uint32_t)nvp * 256u;
         else if (KF == KF_AFFINE8) tx += (uint32_t)nvp * 128u + 2 * n_bulk;
         else tx += k_bulk + n_bulk;
         mbar_arrive_expect_tx(full_bar(s), tx);
-        if (KF == KF_DENSE) bulk_g2s(st + L::k_off, ksrc, (uint32_t)nvp * 256u, full_bar(s));
+        if (is_dense(KF)) bulk_g2s(st + L::k_off, ksrc, (uint32_t)nvp * 256u, full_bar(s));
         if (KF == KF_AFFINE8) {
           bulk_g2s(st + L::k_off, ksrc, (uint32_t)nvp * 128u, full_bar(s));
           if (n_bulk) bulk_g2s(st + L::kn_off, kscbase + p0, n_bulk, full_bar(s));
@@ -623,7 +657,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
     for (int ng = 0; ng < 2; ++ng) {
       sc[ng][0] = sc[ng][1] = sc[ng][2] = sc[ng][3] = 0.f;
       const int prow = pw + 8 * ng + g;
-      if (KF == KF_DENSE) {
+      if (is_dense(KF)) {
         const uint32_t row = st + L::k_off + prow * kDenseRowBytes + t * 16;
         float sc2[4] = {0.f, 0.f, 0.f, 0.f};   // second accumulator: two independent MMA chains
         uint4 r[4];
@@ -631,8 +665,13 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         for (int it = 0; it < 4; ++it) r[it] = lds128(row + it * 64);
 #pragma unroll
         for (int it = 0; it < 4; ++it) {
-          mma16816(sc[ng], aq[2 * it], r[it].x, r[it].y);
-          mma16816(sc2, aq[2 * it + 1], r[it].z, r[it].w);
+          if (KF == KF_DENSE_BF16) {
+            mma16816_bf16(sc[ng], aq[2 * it], r[it].x, r[it].y);
+            mma16816_bf16(sc2, aq[2 * it + 1], r[it].z, r[it].w);
+          } else {
+            mma16816(sc[ng], aq[2 * it], r[it].x, r[it].y);
+            mma16816(sc2, aq[2 * it + 1], r[it].z, r[it].w);
+          }
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) sc[ng][c] += sc2[c];
@@ -1168,7 +1207,7 @@ bool flash_mma_supported(const FlashArgs& a) {
     return false;
   }
   if (a.k_format == TQ_KV_DENSE) {
-    if (a.k_dtype != TQ_F16) return false;
+    if (a.k_dtype != TQ_F16 && a.k_dtype != TQ_BF16) return false;
     if (!aligned16(a.k_data) || a.k_batch_stride % 8 || a.k_head_stride % 8) return false;
   } else if (a.k_format == TQ_KV_POLAR) {
     if (a.k_bits != 3 && a.k_bits != 4) return false;
@@ -1186,7 +1225,7 @@ bool flash_mma_supported(const FlashArgs& a) {
   if (a.new_v != nullptr) {   // in-launch append: dense keys as stored (fp16), or packed keys; packed values
     if (a.v_format != TQ_KV_POLAR || a.k_format == TQ_KV_AFFINE || a.new_k == nullptr) return false;
     if (a.k_format == TQ_KV_DENSE &&
-        (a.new_dtype != TQ_F16 || !aligned16(a.new_k) || a.nk_batch_stride % 8 || a.nk_head_stride % 8))
+        (a.new_dtype != a.k_dtype || !aligned16(a.new_k) || a.nk_batch_stride % 8 || a.nk_head_stride % 8))
       return false;
   }
   return true;
@@ -1240,11 +1279,15 @@ int launch_flash_mma(const FlashArgs& a, int splits, const MmaOutput& mo, cudaSt
     tb.k_post = a.attn_scale * kLog2e / ((float)kDim * kb.beta);
     kf = a.k_bits == 3 ? KF_POLAR3 : KF_POLAR4;
   }
-  if (v_affine)
-    return a.k_format == TQ_KV_AFFINE ? launch_variant<KF_AFFINE8, 40>(a, tb, splits, st)
-                                      : launch_variant<KF_DENSE, 40>(a, tb, splits, st);
+  const bool k_bf16 = a.k_format == TQ_KV_DENSE && a.k_dtype == TQ_BF16;
+  if (v_affine) {
+    if (a.k_format == TQ_KV_AFFINE) return launch_variant<KF_AFFINE8, 40>(a, tb, splits, st);
+    return k_bf16 ? launch_variant<KF_DENSE_BF16, 40>(a, tb, splits, st) : launch_variant<KF_DENSE, 40>(a, tb, splits, st);
+  }
   if (a.k_format == TQ_KV_AFFINE)
     return a.v_bits == 3 ? launch_variant<KF_AFFINE8, 3>(a, tb, splits, st) : launch_variant<KF_AFFINE8, 4>(a, tb, splits, st);
+  if (kf == KF_DENSE && k_bf16)
+    return a.v_bits == 3 ? launch_variant<KF_DENSE_BF16, 3>(a, tb, splits, st) : launch_variant<KF_DENSE_BF16, 4>(a, tb, splits, st);
   if (kf == KF_DENSE) return a.v_bits == 3 ? launch_variant<KF_DENSE, 3>(a, tb, splits, st) : launch_variant<KF_DENSE, 4>(a, tb, splits, st);
   if (kf == KF_POLAR3) return a.v_bits == 3 ? launch_variant<KF_POLAR3, 3>(a, tb, splits, st) : launch_variant<KF_POLAR3, 4>(a, tb, splits, st);
   return a.v_bits == 3 ? launch_variant<KF_POLAR4, 3>(a, tb, splits, st) : launch_variant<KF_POLAR4, 4>(a, tb, splits, st);

@@ -254,7 +254,7 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
                  partials: bool = False, partial_out=None, kv_stable: bool = False, out=None, peers=None,
                  q_stable: bool = False, new_k: torch.Tensor | None = None, new_v: torch.Tensor | None = None,
                  sparse_v_threshold: float = 0.0, active_out: torch.Tensor | None = None,
-                 _prepare_only: bool = False):
+                 seq_lens: torch.Tensor | None = None, _prepare_only: bool = False):
     """Split-K flash decoding for one query token per sequence.
 
     q: (B, n_q, dim).  k / v: dicts describing the stored keys / values:
@@ -290,6 +290,11 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
     16-position tile and kv-head group from the running softmax state, so nothing is dropped
     that the reference's `sparse_v_matvec` would keep); `active_out`, an int32 (B, n_kv) tensor,
     receives the number of positions whose values were accumulated.
+
+    seq_lens (tensor-core kernel only): int32 (B,) device tensor with the number of valid positions
+    of each sequence (<= S), read by the kernel when it runs: ragged batches without a mask, and
+    decode steps replayed from a CUDA graph whose lengths advance on the device.  With new_k /
+    new_v the rows go to position seq_lens[b] - 1.
     """
     _lib.require_cuda(q)
     B, n_q, dim = q.shape
@@ -371,6 +376,12 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
     P.kv_stable = int(kv_stable)
     P.q_stable = int(q_stable)
     P.sparse_v_threshold = max(float(sparse_v_threshold), 0.0)
+    if seq_lens is not None:
+        _lib.require_cuda(seq_lens)
+        if seq_lens.dtype != torch.int32 or tuple(seq_lens.shape) != (B,) or not seq_lens.is_contiguous():
+            raise ValueError(f"seq_lens must be a contiguous int32 ({B},) tensor")
+        keep.append(seq_lens)
+        P.seq_lens_dev = seq_lens.data_ptr()
     if active_out is not None:
         _lib.require_cuda(active_out)
         if active_out.dtype != torch.int32 or tuple(active_out.shape) != (B, n_kv) or not active_out.is_contiguous():
