@@ -246,8 +246,10 @@ typedef struct tq_flash_params {
    * fused_attention.py:109-121).  The reference drops a position from the value sum when its
    * softmax weight is below the threshold.  Here (tensor-core path, > 0 enables) a warp's tile of 16
    * positions is dropped for a (batch, kv head) group when every weight in it is already certain to
-   * end below the threshold - weight <= exp(score - running max) / running sum - so nothing is
-   * dropped that the reference would keep, and everything still counts in the softmax sum.
+   * end below the threshold - weight <= exp(score - running max) / running sum, and weight <=
+   * exp(score - largest score the CTA has seen) - so nothing is dropped that the reference would
+   * keep, and everything still counts in the softmax sum.  The bounds only know what the CTA's own
+   * chunk of the sequence has shown so far: chunks without a dominant key drop little.
    * active_positions: optional device int32 (batch, n_kv_heads), zeroed by the caller; receives
    * the number of positions whose values were accumulated (count_active_positions semantics per
    * group, sparse_v.py:189-191). */

@@ -391,9 +391,11 @@ def test_prepared_calls_match_direct_calls(tq, golden, dev):
 
 def test_flash_decode_value_skipping_is_conservative(tq, oracle, dev):
     """sparse_v_threshold inside the decode kernel (sparse_v.py:59-65 semantics, conservative):
-    peaked attention over 4096 positions - most 16-position tiles are dropped, the result stays
-    within the attention tolerance of the oracle's exact rule, the count of accumulated positions
-    is never below the oracle's count of kept positions, and a threshold of 0 changes nothing."""
+    peaked attention over 4096 positions.  The kernel drops a subset of what the exact rule drops
+    (it only knows the running state of the chunk it has seen), so its result lies between the exact
+    rule's and the un-thresholded one, the count of accumulated positions is never below the
+    oracle's count of kept positions, a single chunk whose dominant keys come early drops most
+    tiles, and a threshold of 0 changes nothing."""
     rng = np.random.default_rng(21)
     n_kv, n_rep, S, D = 2, 4, 4096, 128
     kq = tq.PolarQuantizer(D, 4, seed=42, device=dev)
@@ -424,9 +426,11 @@ def test_flash_decode_value_skipping_is_conservative(tq, oracle, dev):
                                            sparse_v_threshold=thr)
         active = torch.empty((1, n_kv), dtype=torch.int32, device=dev)
         got = tq.flash_decode(qd, k=k, v=v, attn_scale=scale, out_dtype=torch.float32, sparse_v_threshold=thr,
-                              active_out=active)
+                              active_out=active, num_splits=1)
         assert tq._lib.lib().tq_flash_decode_last_kernel() == 1
         g0 = got[0].cpu().numpy()
+        split = tq.flash_decode(qd, k=k, v=v, attn_scale=scale, out_dtype=torch.float32, sparse_v_threshold=thr)
+        assert _rel(split[0].cpu().numpy(), dense_ref) <= _rel(exact, dense_ref) + ATT_TOL
         # the kernel drops a subset of what the exact rule drops: it is at least as close to the
         # un-thresholded result as the exact rule is
         assert _rel(g0, dense_ref) <= _rel(exact, dense_ref) + ATT_TOL
@@ -438,7 +442,7 @@ def test_flash_decode_value_skipping_is_conservative(tq, oracle, dev):
         print(f"thr {thr}: positions accumulated per kv head {act.tolist()}, kept by the exact rule {kept.tolist()}")
         assert (act >= kept).all() and (act <= S).all()
         if thr == 1e-3:
-            assert (act < S).all()                                 # whole tiles were dropped
+            assert (act < S // 2).all()                            # one chunk, dominant keys in its first quarter
     same = tq.flash_decode(qd, k=k, v=v, attn_scale=scale, out_dtype=torch.float32, sparse_v_threshold=0.0)
     assert torch.equal(same, dense)
     with pytest.raises(ValueError, match="value skipping"):

@@ -253,6 +253,13 @@ __device__ __forceinline__ int kslot_element(int ks, int s) {
   return (pi < 15 ? 30 * tt + 2 * pi : 120 + 2 * tt) + lo;
 }
 
+// float <-> int with the same ordering (for atomicMax on shared memory); an involution
+__device__ __forceinline__ int ordered_int(float f) {
+  const int i = __float_as_int(f);
+  return i ^ ((i >> 31) & 0x7fffffff);
+}
+__device__ __forceinline__ float from_ordered_int(int i) { return __int_as_float(i ^ ((i >> 31) & 0x7fffffff)); }
+
 template <typename T>
 __device__ __forceinline__ float load_q(const void* base, int64_t idx) {
   return to_f32<T>(reinterpret_cast<const T*>(base)[idx]);
@@ -323,7 +330,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   // Programmatic dependent launch: let the next kernel on the stream be scheduled as
   // soon as resources free up; its own griddepcontrol.wait keeps it from consuming
   // anything this grid produces before this grid has completed.
-  if (tid == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   auto full_bar = [&](int s) { return sbase + L::bars + 8 * s; };
   auto empty_bar = [&](int s) { return sbase + L::bars + 8 * (kStages + s); };
 
@@ -332,6 +339,8 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   __shared__ int abort_s;          // a bounded wait of this CTA gave up
   __shared__ int elected_s;        // this CTA completed its group's counter
   __shared__ uint8_t idx_s[kDim];  // producer warp: codes of the row being appended
+  __shared__ int hint_s[8];        // value skipping: per head, the largest score any warp of the CTA has seen
+  if (tid < 8) hint_s[tid] = (int)0x80000000;   // ordered image of -inf, see ordered_int()
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(full_bar(s), 1);
@@ -808,15 +817,23 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
     // for every head of the group, contributes nothing the reference would keep.
     bool skip_values = false;
     if (a.sparse_thr > 0.f) {
-      float wmax = 0.f;
+      float smax = -INFINITY;                            // largest score among this thread's positions
 #pragma unroll
       for (int ng = 0; ng < 2; ++ng)
 #pragma unroll
-        for (int c = 0; c < 2; ++c) wmax = fmaxf(wmax, ex2(s2[ng][c] - m_use));
+        for (int c = 0; c < 2; ++c) smax = fmaxf(smax, s2[ng][c]);
       float lq = l_run;                                  // running sum of head g in this warp: the quad's lanes
       lq += __shfl_xor_sync(0xffffffffu, lq, 1);
       lq += __shfl_xor_sync(0xffffffffu, lq, 2);
-      skip_values = __all_sync(0xffffffffu, g >= a.n_rep || wmax < a.sparse_thr * lq);
+      // the log-sum-exp of a head is at least any single score: the largest one seen by any warp of
+      // the CTA so far is a second lower bound (shared through hint_s)
+      float sq = fmaxf(smax, __shfl_xor_sync(0xffffffffu, smax, 1));
+      sq = fmaxf(sq, __shfl_xor_sync(0xffffffffu, sq, 2));
+      if (t == 0 && g < a.n_rep && sq > -INFINITY) atomicMax(&hint_s[g], ordered_int(sq));
+      __syncwarp();
+      const float hint = from_ordered_int(*reinterpret_cast<volatile int*>(&hint_s[g]));
+      const bool below = smax == -INFINITY || ex2(smax - m_use) < a.sparse_thr * lq || ex2(smax - hint) < a.sparse_thr;
+      skip_values = __all_sync(0xffffffffu, g >= a.n_rep || below);
     }
     if (a.active_positions != nullptr && !skip_values && lane == 0 && pw < nvp)
       atomicAdd(a.active_positions + b * a.n_kv_heads + kvh, min(16, nvp - pw));
