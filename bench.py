@@ -553,13 +553,25 @@ def workload_c1(args):
 
 def workload_c3(args):
     """Config 3: full TurboQuantKVCache (K 4-bit, V 3-bit), 32 q / 8 kv heads, batch 32,
-    context 8192, one decode token per sequence; 260.0 MB of packed KV per layer-step."""
+    context 8192, one decode token per sequence; 260.0 MB of packed KV per layer-step.
+    Under torchrun the KV heads are sharded across the ranks (8 heads -> N ranks, each rank keeps
+    its GQA groups whole, no exchange on the data path): strong scaling of one workload."""
     import torch
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
     tq = entry.load_package()
-    B, nq, nkv, ctx, layers = 32, 32, 8, 8192, 2
-    gen = torch.Generator(device=dev).manual_seed(9)
+    from turboquant_mlx_b200.distributed import shard_range
+    B, nq_all, nkv_all, ctx, layers = 32, 32, 8, 8192, 2
+    h0, h1 = shard_range(nkv_all, world, rank)
+    nkv = h1 - h0
+    nq = nkv * (nq_all // nkv_all)
+    gen = torch.Generator(device=dev).manual_seed(9 + rank)
     caches = []
     for _ in range(layers):
         c = tq.TurboQuantKVCache(bits=3, k_bits=4, v_bits=3, fused=True)
@@ -571,7 +583,6 @@ def workload_c3(args):
         caches.append(c)
     q = torch.randn((layers, B, nq, 1, DIM), generator=gen, device=dev).half()
     scale = 1.0 / math.sqrt(DIM)
-
     from turboquant_mlx_b200.fused_attention import cache_kv_descriptors
     outs = [torch.empty((B, nq, DIM), dtype=torch.float16, device=dev) for _ in range(layers)]
 
@@ -583,15 +594,24 @@ def workload_c3(args):
             else:
                 tq.turboquant_attention(q[l], caches[l], scale)
 
-    ms = _time_graph(torch, step, args.steps) / layers
-    nbytes = B * nkv * ctx * (68 + 56)
+    g = _capture(torch, step, dev)
+    ms = _timed(torch, dist, world, dev, g.replay, max(args.steps, 20), 3) / layers
+    nbytes = B * nkv_all * ctx * (68 + 56)
     peak, kind = measured_peaks()
-    print(json.dumps({"metric": METRIC, "unit": "GB/s", "n_gpus": 1, "value": nbytes / ms / 1e6,
-                      "us_per_layer_step": ms * 1e3, "frac_of_peak": nbytes / ms / 1e6 / peak, "peak": peak,
-                      "peak_kind": kind, "tensor_core_path": tq._lib.lib().tq_flash_decode_last_kernel() == 1,
-                      "decode_kernel_status": tq.kernels.flash_status(dev, B * nkv), "splits_forced": args.splits,
-                      "config": {"workload": "C3 full TurboQuant cache decode: B=32, 32q/8kv, ctx 8192, K 4-bit + V 3-bit",
-                                 "bytes_per_layer_step": nbytes}}))
+    status = tq.kernels.flash_status(dev, B * nkv)
+    if rank == 0:
+        print(json.dumps({"metric": METRIC, "unit": "GB/s", "n_gpus": world, "value": nbytes / ms / 1e6,
+                          "scaling": "strong" if world > 1 else "weak",
+                          "us_per_layer_step": ms * 1e3, "frac_of_peak_per_gpu": nbytes / world / ms / 1e6 / peak,
+                          "peak": peak, "peak_kind": kind,
+                          "tensor_core_path": tq._lib.lib().tq_flash_decode_last_kernel() == 1,
+                          "decode_kernel_status": status, "splits_forced": args.splits,
+                          "config": {"workload": "C3 full TurboQuant cache decode: B=32, 32q/8kv, ctx 8192, K 4-bit + V 3-bit",
+                                     "bytes_per_layer_step": nbytes,
+                                     "sharding": f"kv heads {nkv_all} -> {world} ranks, no exchange" if world > 1 else "one GPU"}}))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def workload_c4_prefill(args):

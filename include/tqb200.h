@@ -284,6 +284,10 @@ int tq_flash_decode(const tq_flash_params* p);
  * once; a kernel whose bounded wait gives up writes a non-zero word there (and its
  * output is invalid).  Diagnostic, no reference counterpart. */
 int tq_flash_decode_last_kernel(void);
+/* CTAs of the tensor-core decode kernel the runtime keeps resident per SM (occupancy query made
+ * when a kernel variant is first set up on a device; the design needs 2); -1 before that.
+ * Diagnostic, no reference counterpart. */
+int tq_flash_decode_resident_ctas_per_sm(void);
 
 /* Merge n_parts partial states (split-K chunks or ranks): part i of row r is at
  * part_m[i * m_part_stride + r], part_l[i * l_part_stride + r] and

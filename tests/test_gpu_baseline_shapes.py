@@ -138,8 +138,14 @@ def test_c2_pipelined_launches_match_serial(tq, dev):
                        norms=torch.exp(0.5 * torch.randn((1, n_kv, S), generator=g, device=dev)) * 11.3))
         qs.append(torch.randn((1, n_q, D), generator=g, device=dev).half())
     scale = 1.0 / math.sqrt(D)
-    serial = [tq.flash_decode(qs[l], k=ks[l], v=vs[l], attn_scale=scale, out_dtype=torch.float32) for l in range(layers)]
-    torch.cuda.synchronize()
+    # the same launches (same flags, hence the same split plan) one at a time
+    serial = []
+    for l in range(layers):
+        serial.append(tq.flash_decode(qs[l], k=ks[l], v=vs[l], attn_scale=scale, out_dtype=torch.float32,
+                                      kv_stable=True, q_stable=True))
+        torch.cuda.synchronize()
+    alone = tq.flash_decode(qs[0], k=ks[0], v=vs[0], attn_scale=scale, out_dtype=torch.float32)
+    assert _rel(alone.cpu().numpy(), serial[0].cpu().numpy()) < 1e-3     # another split plan: equal to fp16 rounding of P
     outs = [torch.zeros_like(o) for o in serial]
 
     def step():
@@ -161,8 +167,7 @@ def test_c2_pipelined_launches_match_serial(tq, dev):
         graph.replay()
         torch.cuda.synchronize()
         for l in range(layers):
-            # split counts differ between the two plans, so the merge order does: equal to rounding
-            assert _rel(outs[l].cpu().numpy(), serial[l].cpu().numpy()) < 1e-5
+            assert torch.equal(outs[l], serial[l])       # overlapping launches change nothing, bit for bit
     assert flash_status(dev, n_kv) == 0
 
 

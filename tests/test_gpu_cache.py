@@ -294,7 +294,7 @@ def test_hybrid_cache_quantize_k_then_decode(tq, oracle, dev):
         ref, _ = oracle.decode_attention(q[b, :, 0], k_dense=k_deq[b],
                                          v_polar=dict(packed=vp, norms=vn, centroids=oracle.codebook(3), signs=signs, bits=3),
                                          attn_scale=scale, n_rep=n_rep)
-        for got in (out, fn_out, thr_out):
+        for name, got in (("hook", out), ("function", fn_out), ("function with threshold", thr_out)):
             err = np.abs(got[b, :, 0].float().cpu().numpy() - ref).max() / np.abs(ref).max()
-            assert err < 2e-3
+            assert err < 2e-3, f"{name}, batch element {b}: max rel err {err:.3e}"
     assert c.trim(1) == 1 and c.offset == S + 1

@@ -98,6 +98,7 @@ _SIGNATURES = {
     "tq_flash_decode_workspace_bytes": (c_int64, [POINTER(FlashParams)]),
     "tq_flash_decode": (c_int, [POINTER(FlashParams)]),
     "tq_flash_decode_last_kernel": (c_int, []),
+    "tq_flash_decode_resident_ctas_per_sm": (c_int, []),
     "tq_merge_partials": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int,
                                   c_int64, c_int, _FP, c_void_p, c_int, c_int64, c_void_p]),
     "tq_affine_quantize": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p,

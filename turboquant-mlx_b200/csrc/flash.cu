@@ -227,6 +227,7 @@ using namespace tq;
 static thread_local int g_last_kernel = -1;
 
 extern "C" int tq_flash_decode_last_kernel(void) { return g_last_kernel; }
+extern "C" int tq_flash_decode_resident_ctas_per_sm(void) { return flash_mma_resident_ctas_per_sm(); }
 
 extern "C" int64_t tq_flash_decode_header_bytes(int batch, int n_kv_heads) {
   if (batch <= 0 || n_kv_heads <= 0) return 0;

@@ -67,6 +67,7 @@ int launch_flash_generic(const FlashArgs& a, int splits, cudaStream_t st);
 bool flash_mma_supported(const FlashArgs& a);
 int flash_mma_chunk_multiple();
 int flash_mma_ctas_per_sm();
+int flash_mma_resident_ctas_per_sm();   // what the runtime's occupancy query returned (-1: not queried yet)
 struct MmaOutput {       // where the tensor-core kernel's fused merge writes
   int* status;           // workspace header word 0
   int* counters;         // one int per (batch, kv head) after the status block, zero between calls

@@ -1173,6 +1173,8 @@ static void scale_codebook(const float* c, int n, ScaledBook* out) {
   *out = sb;
 }
 
+static int g_ctas_per_sm_seen = -1;   // occupancy the runtime reports for the variant set up last
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 template <int KF, int VB>
@@ -1189,6 +1191,9 @@ static int launch_variant(const FlashArgs& a, const MmaTables& tb, int splits, c
                                cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return set_error(TQ_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     attr_done[dev] = true;
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, flash_mma_kernel<KF, VB>, kThreads, L::total) == cudaSuccess)
+      g_ctas_per_sm_seen = n;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(splits, a.n_kv_heads, a.batch);
@@ -1248,6 +1253,7 @@ bool flash_mma_supported(const FlashArgs& a) {
   return true;
 }
 
+int flash_mma_resident_ctas_per_sm() { return g_ctas_per_sm_seen; }
 int flash_mma_chunk_multiple() { return kChunkMultiple; }
 int flash_mma_ctas_per_sm() { return kCtasPerSm; }
 
