@@ -243,11 +243,14 @@ class ShardedLayers:
             m, lsum, acc = partial_views(self.sends[l], rows, DIM)
             po = (m.view(1, n_q), lsum.view(1, n_q), acc.view(1, n_q, DIM))
             kw = {} if new_rows is None else dict(new_k=new_rows[l][0], new_v=new_rows[l][1])
+            # every layer's call has a workspace of its own: the launches depend on nothing still running
             self.plans.append(tq.FlashDecodePlan(qs[l], k=ks[l], v=vs[l], attn_scale=scale, partials=True,
                                                  peers=self.ex.targets(slot, rows, DIM), partial_out=po,
-                                                 kv_stable=True, q_stable=True, **kw))
+                                                 kv_stable=True, q_stable=True,
+                                                 workspace=tq.kernels.decode_workspace(dev), **kw))
             self.local_plans.append(tq.FlashDecodePlan(qs[l], k=ks[l], v=vs[l], attn_scale=scale, partials=True,
-                                                       partial_out=po, kv_stable=True, q_stable=True))
+                                                       partial_out=po, kv_stable=True, q_stable=True,
+                                                       workspace=tq.kernels.decode_workspace(dev)))
             gm, gl, gacc = partial_views(self.ex.data[slot], rows, DIM)
             self.merges.append(tq.MergePlan(gm, gl, gacc, v_signs, self.outs[l]))
         self.flag_ptrs = [tq._lib.ptr(self.ex.flags[slot]) for slot in range(2)]
@@ -261,6 +264,10 @@ class ShardedLayers:
     def kernels_only(self):
         for l in range(self.layers):
             self.local_plans[l].run()
+
+    def status(self):
+        """Largest status word of the decode workspaces (synchronises)."""
+        return max(int(p._keep_ws[:4].view(__import__("torch").int32).item()) for p in self.plans + self.local_plans)
 
 
 def gpu_arm(args):
@@ -331,7 +338,7 @@ def gpu_arm(args):
         launch_ms = ms_calls / N_LAYERS
         launches_per_step = N_LAYERS
         sharding = "one GPU, no collective"
-        status = flash_status(dev, N_KV)
+        status = max(tq.kernels.workspace_status(c._decode_ws) for c in caches)
     else:
         # ---- one sequence of world x CTX tokens, sharded along the sequence ----
         ks = [dict(format="dense", data=c._k_cache.keys[:, :, :CTX, :]) for c in caches]
@@ -362,11 +369,11 @@ def gpu_arm(args):
         sharding = (f"one sequence of {world * CTX} tokens split along the sequence, {CTX} positions per GPU; per "
                     "layer: partial-mode decode -> (m, l, acc) rows stored to every rank over NVLink by the decode "
                     "kernel -> gated merge; one CUDA graph per step")
+        status = sh.status()
         extra_cfg = {"us_per_layer_kernel_only": launch_ms * 1e3, "us_per_layer_total": ms_total / N_LAYERS * 1e3,
                      "us_per_layer_exchange_and_merge": (ms_total - ms_calls) / N_LAYERS * 1e3,
                      "exchange_bytes_per_rank_per_layer": N_Q * (DIM + 2) * 4,
                      "max_abs_diff_vs_nccl_allgather_path": diff, "max_abs_diff_across_ranks": rank_diff}
-        status = flash_status(dev, N_KV)
 
     value = world * step_bytes / (ms_step * 1e-3) / 1e9
     toks = 1.0 / (ms_step * 1e-3)
@@ -438,9 +445,10 @@ def gpu_arm(args):
     ms_e2e = _timed(torch, dist, world, dev, e2e_step, args.steps, args.warmup)
     if world == 1:
         tq.remove_patch()
+        status = status or max(tq.kernels.workspace_status(c._decode_ws) for c in caches)
     else:
         sh2.ex.check()
-    status = status or flash_status(dev, N_KV)
+        status = status or sh2.status()
     e2e_val = world * step_bytes / (ms_e2e * 1e-3) / 1e9
     h2d = h_in.numel() * 2
     d2h = h_out.numel() * 2
@@ -574,7 +582,7 @@ def workload_c3(args):
     gen = torch.Generator(device=dev).manual_seed(9 + rank)
     caches = []
     for _ in range(layers):
-        c = tq.TurboQuantKVCache(bits=3, k_bits=4, v_bits=3, fused=True)
+        c = tq.TurboQuantKVCache(bits=3, k_bits=4, v_bits=3, fused=True, inputs_stable=True)
         c.reserve(B, nkv, ctx + 256, DIM, DIM, dev)
         for s0 in range(0, ctx, 2048):
             k = (torch.randn((B, nkv, 2048, DIM), generator=gen, device=dev) *
@@ -598,7 +606,8 @@ def workload_c3(args):
     ms = _timed(torch, dist, world, dev, g.replay, max(args.steps, 20), 3) / layers
     nbytes = B * nkv_all * ctx * (68 + 56)
     peak, kind = measured_peaks()
-    status = tq.kernels.flash_status(dev, B * nkv)
+    status = max([tq.kernels.flash_status(dev, B * nkv)] +
+                 [tq.kernels.workspace_status(c._decode_ws) for c in caches if c._decode_ws is not None])
     if rank == 0:
         print(json.dumps({"metric": METRIC, "unit": "GB/s", "n_gpus": world, "value": nbytes / ms / 1e6,
                           "scaling": "strong" if world > 1 else "weak",
@@ -756,16 +765,18 @@ def c5_measure(args, tq, torch, dist, dev, world, rank):
         sh.ex.check()
     else:
         outs = [torch.empty((1, nq, DIM), dtype=torch.float16, device=dev) for _ in range(layers)]
+        wss = [tq.kernels.decode_workspace(dev) for _ in range(layers)]
 
         def step():
             for l in range(layers):
-                tq.flash_decode(q[l], k=ks[l], v=vs[l], attn_scale=scale, kv_stable=True, q_stable=True, out=outs[l])
+                tq.flash_decode(q[l], k=ks[l], v=vs[l], attn_scale=scale, kv_stable=True, q_stable=True, out=outs[l],
+                                workspace=wss[l])
         g = _capture(torch, step, dev)
         ms = ms_k = _timed(torch, dist, world, dev, g.replay, max(args.steps, 50), 3) / layers
     rec.update({"GBs_aggregate": world * nbytes / ms / 1e6, "us_per_layer_step": ms * 1e3,
                 "us_kernel_only": ms_k * 1e3, "per_gpu_frac_of_peak": nbytes / ms / 1e6 / peak, "peak": peak,
                 "peak_kind": kind, "tensor_core_path": tq._lib.lib().tq_flash_decode_last_kernel() == 1,
-                "decode_kernel_status": tq.kernels.flash_status(dev, nkv)})
+                "decode_kernel_status": sh.status() if world > 1 else max(tq.kernels.workspace_status(w) for w in wss)})
     return rec
 
 

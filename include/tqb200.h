@@ -262,6 +262,14 @@ typedef struct tq_flash_params {
    * decode loops replayed from a CUDA graph whose lengths advance on the device.  With new_k /
    * new_v the rows go to position seq_lens_dev[b] - 1.  No reference counterpart. */
   const int32_t* seq_lens_dev;
+  /* 1: no call that may be in flight together with this one uses this workspace (e.g. one
+   * workspace per layer, reused at the next decode step).  With kv_stable and q_stable the kernel
+   * then waits for nothing before it finishes its work (only its last CTA waits, at its end, for
+   * the preceding launch to complete, so that launches still complete in stream order), and the
+   * hand-over and merge of consecutive launches overlap as well.  0: the workspace may be shared
+   * with the preceding call on the stream; the kernel waits for that call before writing it. */
+  int32_t workspace_exclusive;
+  int32_t reserved_tail;
 } tq_flash_params;
 
 /* Workspace contract: 16-byte aligned, at least tq_flash_decode_workspace_bytes()
@@ -271,8 +279,8 @@ typedef struct tq_flash_params {
  * zero, so a workspace can be reused by later calls with the same batch * n_kv_heads.
  * Zero the header again before reusing the memory with a different
  * batch * n_kv_heads or after any other use.  Calls on one stream may share a
- * workspace (the kernel orders its workspace accesses after the preceding launch);
- * calls on different streams must not. */
+ * workspace (the kernel orders its workspace accesses after the preceding launch) unless
+ * they set workspace_exclusive; calls on different streams must not. */
 int64_t tq_flash_decode_header_bytes(int batch, int n_kv_heads);
 int64_t tq_flash_decode_workspace_bytes(const tq_flash_params* p);
 int tq_flash_decode(const tq_flash_params* p);

@@ -109,6 +109,7 @@ def test_c2_exact_shape_through_cache_and_hook(tq, oracle, dev, deferred):
     assert cache._pending is None and cache.offset == S
     assert tq._lib.lib().tq_flash_decode_last_kernel() == 1
     assert flash_status(dev, n_kv) == 0
+    assert cache._decode_ws is None or tq.kernels.workspace_status(cache._decode_ws) == 0
     signs = cache._v_tq._v_q.signs.cpu().numpy()
     ref_p, ref_n = oracle.quantize_packed(v_all[0], signs, 3)
     # the stored rows (including the one appended by the decode launch) are the oracle's, bit for bit
@@ -122,9 +123,11 @@ def test_c2_exact_shape_through_cache_and_hook(tq, oracle, dev, deferred):
     assert err < ATT_TOL
 
 
-def test_c2_pipelined_launches_match_serial(tq, dev):
-    """Six layers of the C2 shape replayed from one CUDA graph with kv_stable and q_stable (the
-    launches overlap, one workspace): every layer's output equals its stand-alone result."""
+@pytest.mark.parametrize("own_workspaces", [False, True])
+def test_c2_pipelined_launches_match_serial(tq, dev, own_workspaces):
+    """Six layers of the C2 shape replayed from one CUDA graph with kv_stable and q_stable: the
+    launches overlap, sharing one workspace (each waits for its predecessor before writing it) or
+    with a workspace each (nothing waits); every layer's output equals its stand-alone result."""
     from turboquant_mlx_b200.kernels import flash_status
     g = torch.Generator(device=dev).manual_seed(7)
     n_q, n_kv, S, layers = 28, 4, 32768, 6
@@ -138,11 +141,12 @@ def test_c2_pipelined_launches_match_serial(tq, dev):
                        norms=torch.exp(0.5 * torch.randn((1, n_kv, S), generator=g, device=dev)) * 11.3))
         qs.append(torch.randn((1, n_q, D), generator=g, device=dev).half())
     scale = 1.0 / math.sqrt(D)
+    wss = [tq.kernels.decode_workspace(dev) if own_workspaces else None for _ in range(layers)]
     # the same launches (same flags, hence the same split plan) one at a time
     serial = []
     for l in range(layers):
         serial.append(tq.flash_decode(qs[l], k=ks[l], v=vs[l], attn_scale=scale, out_dtype=torch.float32,
-                                      kv_stable=True, q_stable=True))
+                                      kv_stable=True, q_stable=True, workspace=wss[l]))
         torch.cuda.synchronize()
     alone = tq.flash_decode(qs[0], k=ks[0], v=vs[0], attn_scale=scale, out_dtype=torch.float32)
     assert _rel(alone.cpu().numpy(), serial[0].cpu().numpy()) < 1e-3     # another split plan: equal to fp16 rounding of P
@@ -150,7 +154,8 @@ def test_c2_pipelined_launches_match_serial(tq, dev):
 
     def step():
         for l in range(layers):
-            tq.flash_decode(qs[l], k=ks[l], v=vs[l], attn_scale=scale, kv_stable=True, q_stable=True, out=outs[l])
+            tq.flash_decode(qs[l], k=ks[l], v=vs[l], attn_scale=scale, kv_stable=True, q_stable=True, out=outs[l],
+                            workspace=wss[l])
 
     side = torch.cuda.Stream(device=dev)
     side.wait_stream(torch.cuda.current_stream())
@@ -169,6 +174,7 @@ def test_c2_pipelined_launches_match_serial(tq, dev):
         for l in range(layers):
             assert torch.equal(outs[l], serial[l])       # overlapping launches change nothing, bit for bit
     assert flash_status(dev, n_kv) == 0
+    assert all(w is None or tq.kernels.workspace_status(w) == 0 for w in wss)
 
 
 @pytest.mark.parametrize("deferred", [False, True])
@@ -204,6 +210,7 @@ def test_c3_exact_shape_batch32(tq, oracle, dev, deferred):
     assert cache.offset == S and cache._pending is None
     assert tq._lib.lib().tq_flash_decode_last_kernel() == 1
     assert flash_status(dev, B * n_kv) == 0
+    assert cache._decode_ws is None or tq.kernels.workspace_status(cache._decode_ws) == 0
     ks, vs = cache._k_q.signs.cpu().numpy(), cache._v_q.signs.cpu().numpy()
     for b in checked:
         kb = np.concatenate([a for a, _ in kept[b]] + [k1[b].cpu().numpy()], axis=1)

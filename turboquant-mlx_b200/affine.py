@@ -55,10 +55,13 @@ def affine_dequantize(codes, scales, biases, group: int = 64, bits: int = 8,
     dim = codes.shape[-1] * (1 if bits == 8 else 2)
     lead = codes.shape[:-1]
     c2 = codes.reshape(-1, codes.shape[-1]).contiguous()
+    # the contiguous copies must outlive the launch call: a temporary dropped right after its
+    # pointer is taken hands its block to the next temporary of the same size
+    s2, b2 = scales.contiguous(), biases.contiguous()
     n = c2.shape[0]
     out = torch.empty((n, dim), dtype=dtype, device=codes.device)
-    _lib.check(_lib.lib().tq_affine_dequantize(_lib.ptr(c2), _lib.ptr(scales.contiguous()),
-                                               _lib.ptr(biases.contiguous()), n, dim, group, bits,
+    _lib.check(_lib.lib().tq_affine_dequantize(_lib.ptr(c2), _lib.ptr(s2), _lib.ptr(b2), n, dim, group, bits,
                                                _lib.ptr(out), _lib.dtype_code(dtype),
                                                _lib.stream_ptr(codes.device)))
+    del s2, b2
     return out.reshape(*lead, dim)

@@ -67,6 +67,7 @@ class TurboQuantKVCache:
         self.defer_append = defer_append and fused and not v_only
         self.inputs_stable = inputs_stable
         self._pending = None
+        self._decode_ws = None
         self.quant_bits = bits
         self.k_bits = bits if k_bits is None else k_bits
         self.v_bits = bits if v_bits is None else v_bits

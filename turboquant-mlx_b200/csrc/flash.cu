@@ -121,6 +121,7 @@ static int fill_args(const tq_flash_params* p, FlashArgs* a) {
   a->v_group = p->v_group > 0 ? p->v_group : p->dim;
   a->kv_stable = p->kv_stable;
   a->q_stable = p->q_stable;
+  a->ws_exclusive = p->workspace_exclusive;
   a->new_k = p->new_k;
   a->new_v = p->new_v;
   a->new_dtype = p->new_dtype;
@@ -167,14 +168,28 @@ static void make_plan(const tq_flash_params* p, const FlashArgs& a, Plan* plan) 
   int64_t splits = p->num_splits;
   if (splits <= 0) {
     const int64_t sms = num_sms();
-    // Tensor-core kernel: two CTAs fit on an SM.  A call that may overlap its neighbours on the
-    // stream (kv_stable and q_stable) takes one CTA per SM, so that the next launch's CTAs run
-    // beside this one's and its prologue and epilogue hide behind their streaming; a call that
-    // runs alone fills both halves of every SM.
-    const int per_sm = plan->mma ? ((a.kv_stable && a.q_stable) ? 1 : flash_mma_ctas_per_sm()) : 2;
-    const int64_t target = per_sm * sms;
+    int64_t target;
+    if (!plan->mma) {
+      target = 2 * sms;
+    } else if (a.kv_stable && a.q_stable) {
+      // A call that may overlap its neighbours on the stream runs as few, long CTAs (half an SM count
+      // of them): the CTAs of several launches share every SM (up to four), so prologues, hand-over
+      // and merge hide behind the other launches' streaming, and fewer partial states are merged.
+      target = sms / 2;
+    } else {
+      // A call that runs on its own: one CTA per SM.  The CTA that merges a group outlives the others;
+      // leaving one SM per group spare for the next launch's CTAs pays off when the chunks barely grow.
+      target = sms;
+      if ((target - groups) / groups >= 32) target -= groups;
+    }
     splits = target / groups;                          // round down: the grid fits one wave
-    if (splits < 1) {
+    if (splits < 1 && plan->mma && a.kv_stable && a.q_stable) {
+      // overlapping launches with more groups than the target: the next launch fills the SMs as this
+      // one drains, so wave rounding does not matter; two CTAs per group keep each group's tail short
+      // without multiplying prologues (measured at 256 groups of 8192 positions: 1 / 2 / 4 splits =
+      // 143 / 121 / 123 us)
+      splits = a.seq_len >= 4096 ? 2 : 1;
+    } else if (splits < 1) {
       // more groups than CTA slots: several waves.  Pick the split count whose CTA count comes
       // closest to a whole number of CTAs per SM (e.g. 256 groups on 148 SMs: 4 splits = 1024
       // CTAs = 6.9 per SM instead of 1.7), keeping at least 1024 positions per CTA.

@@ -28,6 +28,7 @@ struct FlashArgs {
   int v_format, v_bits, v_group;
   int kv_stable;                   // K / V are not written by kernels that may still run when this one starts
   int q_stable;                    // likewise the query and the rows to append
+  int ws_exclusive;                // no call that may overlap with this one uses this workspace
   const void* v_data;
   int64_t v_batch_stride, v_head_stride;
   const float* v_norms;
@@ -66,7 +67,7 @@ int launch_flash_generic(const FlashArgs& a, int splits, cudaStream_t st);
 // the arguments qualify; otherwise the caller takes the general kernel.
 bool flash_mma_supported(const FlashArgs& a);
 int flash_mma_chunk_multiple();
-int flash_mma_ctas_per_sm();
+int flash_mma_ctas_per_sm(const FlashArgs& a);   // CTAs of this call's kernel variant that fit on one SM
 int flash_mma_resident_ctas_per_sm();   // what the runtime's occupancy query returned (-1: not queried yet)
 struct MmaOutput {       // where the tensor-core kernel's fused merge writes
   int* status;           // workspace header word 0

@@ -84,13 +84,15 @@ def turboquant_attention(queries, cache, attn_scale: float, mask=None, v_buffer=
         rows = cache.take_pending() if hasattr(cache, "take_pending") else None
         new_k, new_v = rows if rows is not None else (None, None)
         stable = bool(getattr(cache, "inputs_stable", False))
+        # a workspace of the cache's own: decode launches of different layers overlap end to end
+        owner = cache if (stable and m3 is None) else None
         active = None
         if thr > 0.0 and getattr(cache, "track_active_positions", False):
             active = torch.empty((B, n_kv_heads), dtype=torch.int32, device=queries.device)
             cache.last_active_positions = active
         out = flash_decode(queries[:, :, 0, :], k=k, v=v, attn_scale=attn_scale, mask=m3,
                            out_dtype=queries.dtype, kv_stable=stable, q_stable=stable,
-                           new_k=new_k, new_v=new_v, sparse_v_threshold=thr, active_out=active)
+                           new_k=new_k, new_v=new_v, sparse_v_threshold=thr, active_out=active, workspace_owner=owner)
         return out.unsqueeze(2)
 
     outputs = []

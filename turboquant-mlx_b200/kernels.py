@@ -24,7 +24,8 @@ __all__ = [
     "prerotate_query", "prerot_fused_qk_scores", "prerot_packed_dequantize",
     "sparse_v_matvec", "count_active_positions", "flash_attention_turboquant",
     "flash_decode", "merge_partials", "FlashDecodePlan", "MergePlan",
-    "prefill_attention", "prefill_supported", "prefill_status", "flash_status",
+    "prefill_attention", "prefill_supported", "prefill_status", "flash_status", "decode_workspace",
+    "workspace_status",
 ]
 
 
@@ -254,7 +255,8 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
                  partials: bool = False, partial_out=None, kv_stable: bool = False, out=None, peers=None,
                  q_stable: bool = False, new_k: torch.Tensor | None = None, new_v: torch.Tensor | None = None,
                  sparse_v_threshold: float = 0.0, active_out: torch.Tensor | None = None,
-                 seq_lens: torch.Tensor | None = None, _prepare_only: bool = False):
+                 seq_lens: torch.Tensor | None = None, workspace: torch.Tensor | None = None,
+                 workspace_owner=None, _prepare_only: bool = False):
     """Split-K flash decoding for one query token per sequence.
 
     q: (B, n_q, dim).  k / v: dicts describing the stored keys / values:
@@ -295,6 +297,13 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
     of each sequence (<= S), read by the kernel when it runs: ragged batches without a mask, and
     decode steps replayed from a CUDA graph whose lengths advance on the device.  With new_k /
     new_v the rows go to position seq_lens[b] - 1.
+
+    workspace: a zero-initialised uint8 CUDA tensor owned by the caller and used by no other call
+    that may be in flight together with this one (`decode_workspace` makes one; e.g. one per
+    layer).  With kv_stable and q_stable such a call depends on nothing that is still running, so
+    consecutive decode launches overlap from start to end.  Without it the calls of a stream share
+    one workspace and each waits for its predecessor before writing it.  `workspace_owner`: any
+    object (a cache, say); its attribute `_decode_ws` holds such a workspace, made or grown here.
     """
     _lib.require_cuda(q)
     B, n_q, dim = q.shape
@@ -457,7 +466,19 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
     need = L.tq_flash_decode_workspace_bytes(ctypes.byref(P))
     if need < 0:
         _lib.check(int(need))
-    ws = _lib.workspace(need, dev, tag=f"flash{B * n_kv}")   # counters: one layout per batch * n_kv
+    if workspace is None and workspace_owner is not None:
+        workspace = getattr(workspace_owner, "_decode_ws", None)
+        if workspace is None or workspace.numel() < need or workspace.device != dev:
+            workspace = decode_workspace(dev, max(int(need), 1 << 20))
+            workspace_owner._decode_ws = workspace
+    if workspace is not None:
+        _lib.require_cuda(workspace)
+        if workspace.dtype != torch.uint8 or not workspace.is_contiguous() or workspace.numel() < need:
+            raise ValueError(f"workspace must be a contiguous uint8 tensor of at least {need} bytes")
+        ws = workspace
+        P.workspace_exclusive = 1
+    else:
+        ws = _lib.workspace(need, dev, tag=f"flash{B * n_kv}")   # counters: one layout per batch * n_kv
     if ws is not None:
         P.workspace, P.workspace_bytes = ws.data_ptr(), ws.numel()
     result = (pm, pl, pa) if partials else out
@@ -476,6 +497,7 @@ class FlashDecodePlan:
     time per layer matters.  Same keyword arguments as `flash_decode`."""
 
     def __init__(self, q, **kwargs):
+        self._keep_ws = kwargs.get("workspace")          # a caller-owned workspace, if any (status word in front)
         self._P, self._keep, self.result, self._dev = flash_decode(q, _prepare_only=True, **kwargs)
         self._fn = _lib.lib().tq_flash_decode
         self._ref = ctypes.byref(self._P)
@@ -486,6 +508,22 @@ class FlashDecodePlan:
         if rc:
             _lib.check(rc)
         return self.result
+
+
+def decode_workspace(device, nbytes: int = 4 << 20) -> torch.Tensor:
+    """A zero-filled workspace for `flash_decode(..., workspace=...)`: give every call that may
+    overlap with others (one per layer, say) its own.  4 MiB covers 96 splits of 64 heads."""
+    return torch.zeros((int(nbytes),), dtype=torch.uint8, device=device)
+
+
+def workspace_status(ws: torch.Tensor) -> int:
+    """Status word of a caller-owned decode workspace (synchronises; resets the word): 0 unless
+    a bounded wait inside the kernel gave up."""
+    word = ws[:4].view(torch.int32)
+    code = int(word.item())
+    if code:
+        word.zero_()
+    return code
 
 
 def flash_status(device, batch_kv_groups: int) -> int:

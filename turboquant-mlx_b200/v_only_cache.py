@@ -40,6 +40,7 @@ class VOnlyTurboQuantCache:
         self.defer_append = defer_append and fused
         self.inputs_stable = inputs_stable
         self._pending = None      # (new K rows, new V rows) (B, H, D) awaiting the attention launch
+        self._decode_ws = None    # this cache's own decode workspace (inputs_stable: launches of different layers overlap)
 
     def reserve(self, B, H, n_positions, k_dim, v_dim, dtype=torch.float16, device=None):
         """Pre-size K and V storage for `n_positions` so inserts never reallocate."""
@@ -228,8 +229,10 @@ def v_only_attention(queries, cache: VOnlyTurboQuantCache, attn_scale: float, ma
              centroids=tq._v_q.centroids, signs=tq._v_q.signs, bits=tq._v_q.bits, boundaries=tq._v_q.boundaries)
     rows = cache.take_pending()
     new_k, new_v = rows if rows is not None else (None, None)
+    # a workspace of the cache's own: decode launches of different layers overlap end to end
+    owner = cache if (q_stable and (kv_stable or cache.inputs_stable) and m3 is None) else None
     res = flash_decode(queries[:, :, 0, :], k=k, v=v, attn_scale=attn_scale, mask=m3,
                        out_dtype=queries.dtype, kv_stable=kv_stable or q_stable,
-                       q_stable=q_stable, new_k=new_k, new_v=new_v,
+                       q_stable=q_stable, new_k=new_k, new_v=new_v, workspace_owner=owner,
                        out=None if out is None else out[:, :, 0, :])
     return res.unsqueeze(2)
