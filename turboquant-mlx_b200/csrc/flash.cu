@@ -183,6 +183,11 @@ static void make_plan(const tq_flash_params* p, const FlashArgs& a, Plan* plan) 
       if ((target - groups) / groups >= 32) target -= groups;
     }
     splits = target / groups;                          // round down: the grid fits one wave
+    if (plan->mma && a.kv_stable && a.q_stable) {
+      // ... but a long sequence still gets a CTA per 4096 positions: such launches fill the GPU alone
+      const int64_t by_work = (a.seq_len + 4095) / 4096;
+      if (groups <= target && splits < by_work) splits = by_work;
+    }
     if (splits < 1 && plan->mma && a.kv_stable && a.q_stable) {
       // overlapping launches with more groups than the target: the next launch fills the SMs as this
       // one drains, so wave rounding does not matter; two CTAs per group keep each group's tail short
