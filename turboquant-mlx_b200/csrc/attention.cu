@@ -512,6 +512,8 @@ __global__ void merge_partials_kernel(const float* pm, int64_t sm, const float* 
   if (gate_failed) res = __int_as_float(0x7fc00000);   // a rank never pushed: do not hand out a partial merge
   const int64_t bb = row / rows_per_batch, hh2 = row - bb * rows_per_batch;
   out[bb * out_batch_stride + hh2 * out_row_stride + e] = from_f32<T>(res);
+  // launched ahead of its predecessor's completion (see launch_merge): do not complete before it does
+  if (gate.flags != nullptr && gate.reset) asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 int launch_merge(const float* pm, int64_t sm, const float* pl, int64_t sl, const float* pacc,
@@ -522,23 +524,31 @@ int launch_merge(const float* pm, int64_t sm, const float* pl, int64_t sl, const
   if (n_rows <= 0) return TQ_OK;
   PeerGate gate = {nullptr, 0, 0u, nullptr, 0, nullptr, 0ull};
   if (gate_in) gate = *gate_in;
-  const dim3 grid((unsigned)n_rows), block(dim);
-  if (!finalize || out_dtype == TQ_F32)
-    merge_partials_kernel<float><<<grid, block, 0, st>>>(pm, sm, pl, sl, pacc, sa, n_parts, n_rows, dim, rotate,
-                                                         signs, finalize, (float*)out,
-                                                         out_row_stride, rows_per_batch,
-                                                         out_batch_stride, om, ol, oacc, gate);
-  else if (out_dtype == TQ_F16)
-    merge_partials_kernel<__half><<<grid, block, 0, st>>>(pm, sm, pl, sl, pacc, sa, n_parts, n_rows, dim, rotate,
-                                                          signs, finalize, (__half*)out,
-                                                          out_row_stride, rows_per_batch,
-                                                          out_batch_stride, om, ol, oacc, gate);
-  else if (out_dtype == TQ_BF16)
-    merge_partials_kernel<__nv_bfloat16><<<grid, block, 0, st>>>(
-        pm, sm, pl, sl, pacc, sa, n_parts, n_rows, dim, rotate, signs, finalize, (__nv_bfloat16*)out,
-        out_row_stride, rows_per_batch, out_batch_stride, om, ol, oacc, gate);
-  else
-    return set_error(TQ_ERR_BAD_ARG, "unknown dtype %d", out_dtype);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)n_rows);
+  cfg.blockDim = dim3(dim);
+  cfg.stream = st;
+  // A merge that resets its gate (the replayed, all-device-side exchange) depends on nothing but the
+  // flags and the parts they guard, so it may start while the kernel in front of it is still running;
+  // it waits for that kernel only before it ends.  Every other merge is an ordinary launch.
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  if (gate.flags != nullptr && gate.reset) {
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  cudaError_t e;
+#define TQ_MERGE(T)                                                                                        \
+  e = cudaLaunchKernelEx(&cfg, merge_partials_kernel<T>, pm, sm, pl, sl, pacc, sa, n_parts, n_rows, dim, rotate, \
+                         signs, finalize, (T*)out, out_row_stride, rows_per_batch, out_batch_stride, om, ol, \
+                         oacc, gate)
+  if (!finalize || out_dtype == TQ_F32) TQ_MERGE(float);
+  else if (out_dtype == TQ_F16) TQ_MERGE(__half);
+  else if (out_dtype == TQ_BF16) TQ_MERGE(__nv_bfloat16);
+  else return set_error(TQ_ERR_BAD_ARG, "unknown dtype %d", out_dtype);
+#undef TQ_MERGE
+  if (e != cudaSuccess) return set_error(TQ_ERR_LAUNCH, "tq_merge_partials: %s", cudaGetErrorString(e));
   return check_launch("tq_merge_partials");
 }
 
