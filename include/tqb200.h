@@ -365,9 +365,8 @@ int tq_peer_wait(const void* flags, int n_ranks, uint32_t epoch, int* status, vo
  * instead of a partial result; word 1 is scratch.  With reset_flags != 0 the kernel sets the
  * n_ranks flag words back to zero once all of its blocks are past the wait, so a launch with a
  * constant `epoch` (the additions expected per exchange) can be replayed from a CUDA graph; such
- * a launch may also start while the kernel in front of it on the stream is still running (it reads
- * nothing but the flags and the parts they guard, and waits for that kernel before it ends), so
- * `out` must not be written by that kernel. */
+ * a launch also lets the launch behind it on the stream start at once (programmatic dependent
+ * launch: the next layer's decode call overlaps this merge and the decode call in front of it). */
 int tq_merge_partials_after_peers(void* flags, int n_ranks, uint32_t epoch, int* status, int reset_flags,
                                   const float* part_m, int64_t m_part_stride, const float* part_l,
                                   int64_t l_part_stride, const float* part_acc, int64_t acc_part_stride,

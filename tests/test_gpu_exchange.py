@@ -114,9 +114,8 @@ def test_gated_merge_resets_its_flags_for_graph_replay(tq):
     status = torch.zeros(4, dtype=torch.int32, device=dev)
     plan = tq.MergePlan(m, l, acc, pq.signs, out)
     for _ in range(3):
-        out.zero_()                   # not by the kernel right in front of the merge: that one may still run
-        torch.cuda.synchronize()
         flags.add_(4)                 # what the peers' decode kernels would add (4 groups each)
+        out.zero_()
         plan.run_after_peers(tq._lib.ptr(flags), parts, 4, tq._lib.ptr(status), reset_flags=True)
         torch.cuda.synchronize()
         assert int(status[0]) == 0 and int(status[1]) == 0 and torch.equal(out, ref)

@@ -408,6 +408,11 @@ __global__ void merge_partials_kernel(const float* pm, int64_t sm, const float* 
   // now; it waits for this grid's completion before it reads the query or touches its workspace
   if (e == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   bool gate_failed = false;
+  // A merge that resets its gate is launched with programmatic stream serialization (see launch_merge):
+  // it is resident early only so that the decode launch behind it may start; its own work begins once
+  // the kernel in front of it has completed, like an ordinary launch (two merges that share a gate must
+  // never wait on it at the same time).
+  if (gate.flags != nullptr && gate.reset) asm volatile("griddepcontrol.wait;" ::: "memory");
   if (gate.flags != nullptr) {
     // parts pushed by peer GPUs: one thread per rank waits for that rank's flag, bounded by a time
     // limit on the GPU-wide nanosecond timer (and by an iteration count as a second bound)
@@ -512,8 +517,6 @@ __global__ void merge_partials_kernel(const float* pm, int64_t sm, const float* 
   if (gate_failed) res = __int_as_float(0x7fc00000);   // a rank never pushed: do not hand out a partial merge
   const int64_t bb = row / rows_per_batch, hh2 = row - bb * rows_per_batch;
   out[bb * out_batch_stride + hh2 * out_row_stride + e] = from_f32<T>(res);
-  // launched ahead of its predecessor's completion (see launch_merge): do not complete before it does
-  if (gate.flags != nullptr && gate.reset) asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 int launch_merge(const float* pm, int64_t sm, const float* pl, int64_t sl, const float* pacc,
@@ -528,9 +531,10 @@ int launch_merge(const float* pm, int64_t sm, const float* pl, int64_t sl, const
   cfg.gridDim = dim3((unsigned)n_rows);
   cfg.blockDim = dim3(dim);
   cfg.stream = st;
-  // A merge that resets its gate (the replayed, all-device-side exchange) depends on nothing but the
-  // flags and the parts they guard, so it may start while the kernel in front of it is still running;
-  // it waits for that kernel only before it ends.  Every other merge is an ordinary launch.
+  // A merge that resets its gate (the replayed, all-device-side exchange) is launched with programmatic
+  // stream serialization: it becomes resident while the decode kernel in front of it runs, releases the
+  // launch behind it at once (the next layer's decode, which depends on neither) and then waits for its
+  // predecessor's completion before it touches the gate.  Every other merge is an ordinary launch.
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
