@@ -225,27 +225,28 @@ class ShardedLayers:
     stores the merged (m, l, acc) rows into every rank's receive slot (plain peer stores over NVLink
     + one system-scope counter add per (batch, kv head) group and peer); a merge gated on those
     counters (bounded wait) combines the ranks' states and zeroes the counters again, so the whole
-    step replays from one CUDA graph.  Two receive slots alternate by layer."""
+    step replays from one CUDA graph.  Every layer has a receive slot of its own (reused one step
+    later), so no launch waits for another: the ranks' decode kernels and merges overlap freely."""
 
     def __init__(self, tq, qs, ks, vs, scale, v_signs, dev, world, n_q, n_kv, out_dtype, new_rows=None):
         import torch
         from turboquant_mlx_b200.distributed import PeerExchange, partial_buffer, partial_views
         self.layers = len(ks)
         rows = n_q
-        self.ex = PeerExchange(rows * (DIM + 2), dev)
+        self.ex = PeerExchange(rows * (DIM + 2), dev, slots=self.layers)
         self.world, self.n_kv = world, n_kv
         self.status_ptr = tq._lib.ptr(self.ex.status)
         self.outs = [torch.empty((rows, DIM), dtype=out_dtype, device=dev) for _ in range(self.layers)]
         self.sends = [partial_buffer(rows, DIM, dev)[0] for _ in range(self.layers)]
         self.plans, self.merges, self.local_plans = [], [], []
         for l in range(self.layers):
-            slot = l & 1
+            slot = l
             m, lsum, acc = partial_views(self.sends[l], rows, DIM)
             po = (m.view(1, n_q), lsum.view(1, n_q), acc.view(1, n_q, DIM))
             kw = {} if new_rows is None else dict(new_k=new_rows[l][0], new_v=new_rows[l][1])
             # every layer's call has a workspace of its own: the launches depend on nothing still running
             self.plans.append(tq.FlashDecodePlan(qs[l], k=ks[l], v=vs[l], attn_scale=scale, partials=True,
-                                                 peers=self.ex.targets(slot, rows, DIM), partial_out=po,
+                                                 peers=self.ex.targets(slot, rows, DIM, exclusive=True), partial_out=po,
                                                  kv_stable=True, q_stable=True,
                                                  workspace=tq.kernels.decode_workspace(dev), **kw))
             self.local_plans.append(tq.FlashDecodePlan(qs[l], k=ks[l], v=vs[l], attn_scale=scale, partials=True,
@@ -253,12 +254,12 @@ class ShardedLayers:
                                                        workspace=tq.kernels.decode_workspace(dev)))
             gm, gl, gacc = partial_views(self.ex.data[slot], rows, DIM)
             self.merges.append(tq.MergePlan(gm, gl, gacc, v_signs, self.outs[l]))
-        self.flag_ptrs = [tq._lib.ptr(self.ex.flags[slot]) for slot in range(2)]
+        self.flag_ptrs = [tq._lib.ptr(self.ex.flags[slot]) for slot in range(self.layers)]
 
     def step(self):
         for l in range(self.layers):
             self.plans[l].run()
-            self.merges[l].run_after_peers(self.flag_ptrs[l & 1], self.world, self.n_kv, self.status_ptr,
+            self.merges[l].run_after_peers(self.flag_ptrs[l], self.world, self.n_kv, self.status_ptr,
                                            reset_flags=True)
 
     def kernels_only(self):

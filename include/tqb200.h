@@ -219,7 +219,10 @@ typedef struct tq_flash_params {
    * batch * n_kv_heads additions all rows are in place (sequence-sharded decode: the push of
    * tq_peer_push done by the decode kernel itself).  No reference counterpart. */
   int32_t n_peers;             /* 0 .. 8 */
-  int32_t peer_reserved;
+  int32_t peer_slots_exclusive; /* 1: no exchange that may still be in flight uses these peer slots (one slot
+                                   per layer, say), so a call that waits for nothing (kv_stable, q_stable,
+                                   workspace_exclusive) may store into them at once; 0: it first waits for the
+                                   launch in front of it (the gated merge that reads a small ring of slots) */
   float* peer_m[8];
   float* peer_l[8];
   float* peer_acc[8];

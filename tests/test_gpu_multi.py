@@ -84,46 +84,59 @@ for it in range(4):
     tq.MergePlan(gm, gl, gacc, pq.signs, out4).run_after_peers(flags_ptr, world, want, tq._lib.ptr(ex2.status))
     err2 = max(err2, float((out4.view(B, -1, D) - full).abs().max() / full.abs().max()))
 ex2.check()
-# one CUDA graph per step: four layers of decode-with-push (stable inputs, a workspace each, so the
-# launches overlap) + merges gated on the peers' counters, which they reset for the next replay
-ex3 = PeerExchange(rows * (D + 2), dev)
-plans, merges, outs5 = [], [], []
-for l in range(4):
-    slot = l & 1
-    sb = partial_buffer(rows, D, dev)[0]
-    m5, l5, a5 = partial_views(sb, rows, D)
-    plans.append(tq.FlashDecodePlan(
-        q, k=dict(format="dense", data=kd[:, :, a:b]),
-        v=dict(format="polar", packed=vp[:, :, a:b], norms=vn[:, :, a:b], centroids=pq.centroids, signs=pq.signs, bits=3),
-        attn_scale=scale, partials=True, peers=ex3.targets(slot, rows, D), kv_stable=True, q_stable=True,
-        workspace=tq.kernels.decode_workspace(dev),
-        partial_out=(m5.view(B, -1), l5.view(B, -1), a5.view(B, -1, D))))
-    gm, gl, gacc = partial_views(ex3.data[slot], rows, D)
-    outs5.append(torch.zeros((rows, D), dtype=torch.float32, device=dev))
-    merges.append(tq.MergePlan(gm, gl, gacc, pq.signs, outs5[-1]))
-def step():
-    for l in range(4):
-        plans[l].run()
-        merges[l].run_after_peers(tq._lib.ptr(ex3.flags[l & 1]), world, B * n_kv, tq._lib.ptr(ex3.status), reset_flags=True)
-side = torch.cuda.Stream(device=dev)
-side.wait_stream(torch.cuda.current_stream())
-with torch.cuda.stream(side):
-    step(); step()
-torch.cuda.current_stream().wait_stream(side)
-torch.cuda.synchronize()
-dist.barrier()
-graph = torch.cuda.CUDAGraph()
-with torch.cuda.graph(graph):
-    step()
-for it in range(5):
-    for o5 in outs5:
-        o5.zero_()
-    graph.replay()
+# one CUDA graph per step: four layers (different queries) of decode-with-push (stable inputs, a
+# workspace each, so the launches overlap) + merges gated on the peers' counters, which they reset for
+# the next replay; the receive slots are a ring of two (pushes wait for the merge in front) or one per
+# layer (nothing waits)
+kdesc = dict(format="dense", data=kd[:, :, a:b])
+vdesc = dict(format="polar", packed=vp[:, :, a:b], norms=vn[:, :, a:b], centroids=pq.centroids, signs=pq.signs, bits=3)
+kfull = dict(format="dense", data=kd)
+vfull = dict(format="polar", packed=vp, norms=vn, centroids=pq.centroids, signs=pq.signs, bits=3)
+n_layers = 6
+qs = [(q.float() * (1.0 + 0.25 * l)).half() for l in range(n_layers)]
+fulls = [tq.flash_decode(qs[l], k=kfull, v=vfull, attn_scale=scale, out_dtype=torch.float32) for l in range(n_layers)]
+for ring in (True, False):
+    ex3 = PeerExchange(rows * (D + 2), dev, slots=2 if ring else n_layers)
+    plans, merges, outs5, slots = [], [], [], []
+    for l in range(n_layers):
+        slot = l & 1 if ring else l
+        slots.append(slot)
+        sb = partial_buffer(rows, D, dev)[0]
+        m5, l5, a5 = partial_views(sb, rows, D)
+        plans.append(tq.FlashDecodePlan(
+            qs[l], k=kdesc, v=vdesc, attn_scale=scale, partials=True,
+            peers=ex3.targets(slot, rows, D, exclusive=not ring), kv_stable=True, q_stable=True,
+            workspace=tq.kernels.decode_workspace(dev),
+            partial_out=(m5.view(B, -1), l5.view(B, -1), a5.view(B, -1, D))))
+        gm, gl, gacc = partial_views(ex3.data[slot], rows, D)
+        outs5.append(torch.zeros((rows, D), dtype=torch.float32, device=dev))
+        merges.append(tq.MergePlan(gm, gl, gacc, pq.signs, outs5[-1]))
+    def step():
+        for l in range(n_layers):
+            plans[l].run()
+            merges[l].run_after_peers(tq._lib.ptr(ex3.flags[slots[l]]), world, B * n_kv, tq._lib.ptr(ex3.status),
+                                      reset_flags=True)
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step(); step()
+    torch.cuda.current_stream().wait_stream(side)
     torch.cuda.synchronize()
-    for o5 in outs5:
-        err2 = max(err2, float((o5.view(B, -1, D) - full).abs().max() / full.abs().max()))
-ex3.check()
-assert int(ex3.flags.abs().sum()) == 0          # the merges left the counters at zero
+    dist.barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    for it in range(8):
+        for o5 in outs5:
+            o5.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        for l in range(n_layers):
+            err2 = max(err2, float((outs5[l].view(B, -1, D) - fulls[l]).abs().max() / fulls[l].abs().max()))
+    ex3.check()
+    assert int(ex3.flags.abs().sum()) == 0          # the merges left the counters at zero
+    assert all(tq.kernels.workspace_status(p._keep_ws) == 0 for p in plans)
+    dist.barrier()
 print(f"rank {rank} peer exchange rel err {err2:.3e}")
 dist.barrier()
 dist.destroy_process_group()

@@ -54,7 +54,7 @@ class FlashParams(ctypes.Structure):
         ("out", c_void_p), ("out_batch_stride", c_int64), ("out_head_stride", c_int64),
         ("part_m", c_void_p), ("part_l", c_void_p), ("part_acc", c_void_p),
         ("stream", c_void_p),
-        ("n_peers", c_int32), ("peer_reserved", c_int32),
+        ("n_peers", c_int32), ("peer_slots_exclusive", c_int32),
         ("peer_m", c_void_p * 8), ("peer_l", c_void_p * 8), ("peer_acc", c_void_p * 8),
         ("peer_counter", c_void_p * 8),
         ("q_stable", c_int32), ("new_dtype", c_int32),

@@ -306,6 +306,7 @@ extern "C" int tq_flash_decode(const tq_flash_params* p) {
     mo.ol = p->part_l;
     mo.oacc = p->part_acc;
     mo.n_peers = p->out_mode == 1 ? p->n_peers : 0;
+    mo.peer_unordered = p->peer_slots_exclusive;
     for (int i = 0; i < 8; ++i) {
       mo.peer_m[i] = p->peer_m[i];
       mo.peer_l[i] = p->peer_l[i];

@@ -79,6 +79,7 @@ struct MmaOutput {       // where the tensor-core kernel's fused merge writes
   float* ol;
   float* oacc;
   int n_peers;           // out_mode 1: peers that also receive the merged state (0: none)
+  int peer_unordered;    // the peer slots are used by no exchange that may still be in flight
   float* peer_m[8];
   float* peer_l[8];
   float* peer_acc[8];

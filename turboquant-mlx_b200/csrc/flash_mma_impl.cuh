@@ -99,6 +99,7 @@ struct MmaTables {
   float* ol;
   float* oacc;
   int n_peers;          // out_mode 1: the merged state also goes to these peers (other GPUs' memory)
+  int peer_unordered;   // the peer slots are not shared with an exchange that may still be in flight
   float* peer_m[8];
   float* peer_l[8];
   float* peer_acc[8];
@@ -1038,6 +1039,9 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   }
   consumer_barrier();
   if (!elected_s) return;
+  // A push into peer slots that an exchange still in flight may be reading (a small ring of slots) has to
+  // come after the launch in front of this one - the gated merge that reads them - has completed.
+  if (independent && tb.n_peers > 0 && !tb.peer_unordered) grid_dependency_wait();
 
   // The merge reads every split's state straight from L2 into registers.  Shared scratch
   // (the ring is free): weights [8][kMaxParts], m* [8], l* [8].
@@ -1094,9 +1098,6 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
     }
     write_row<VAFF>(a, tb, b, h0 + r, row0 + r, acc4, mst[r], lst[r], lane);
   }
-  // An independent launch still must not complete before its predecessor has: later work on the
-  // stream is ordered after this grid only.  The CTA that merged is the last to leave; it waits.
-  if (independent && tid == 0) grid_dependency_wait();
   if (tb.out_mode == 1 && tb.n_peers > 0) {
     // every row of this (batch, kv head) group is on its way: one thread fences at system scope (the
     // barrier makes the other threads' stores precede it) and tells each peer
@@ -1108,6 +1109,9 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         if (p < tb.n_peers) atomicAdd_system(tb.peer_counter[p], 1u);
     }
   }
+  // An independent launch still must not complete before its predecessor has: later work on the
+  // stream is ordered after this grid only.  The CTA that merged is the last to leave; it waits.
+  if (independent && tid == 0) grid_dependency_wait();
 }
 
 // ---- host side: scaled f16 codebooks --------------------------------------------------
@@ -1230,6 +1234,7 @@ int TQ_CAT(launch_flash_mma_, TQ_GEOM)(const FlashArgs& a, int splits, const Mma
   tb.ol = mo.ol;
   tb.oacc = mo.oacc;
   tb.n_peers = mo.n_peers;
+  tb.peer_unordered = mo.peer_unordered;
   for (int i = 0; i < 8; ++i) {
     tb.peer_m[i] = mo.peer_m[i];
     tb.peer_l[i] = mo.peer_l[i];

@@ -79,7 +79,10 @@ class PeerExchange:
     block that is still being merged.  All ranks must call `exchange` the same number
     of times.  Multicast mappings are not used (and switched off before the rendezvous)."""
 
-    def __init__(self, n_floats: int, device, group=None):
+    def __init__(self, n_floats: int, device, group=None, slots: int = 2):
+        """`slots`: receive slots per rank.  Two alternate by exchange (the default protocol of
+        `exchange` / `push` / `next_fused`); a caller that addresses slots itself through `targets`
+        (one per layer of a replayed decode step, say) may ask for more."""
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
         if n_floats % 4:
@@ -89,8 +92,9 @@ class PeerExchange:
         self.rank = dist.get_rank(self.group)
         self.n = n_floats
         self.device = torch.device(device)
-        self.data = symm.empty((2, self.world, n_floats), dtype=torch.float32, device=self.device)
-        self.flags = symm.empty((2, 64), dtype=torch.int32, device=self.device)
+        self.slots = max(2, int(slots))
+        self.data = symm.empty((self.slots, self.world, n_floats), dtype=torch.float32, device=self.device)
+        self.flags = symm.empty((self.slots, 64), dtype=torch.int32, device=self.device)
         self.data.zero_()
         self.flags.zero_()
         self._hd = symm.rendezvous(self.data, self.group)
@@ -133,16 +137,19 @@ class PeerExchange:
         return self.data[slot], _lib.ptr(self.flags[slot]), self.epoch
 
     # ---- push done by the decode kernel itself -------------------------------------------------
-    def targets(self, slot: int, rows: int, dim: int) -> dict:
+    def targets(self, slot: int, rows: int, dim: int, exclusive: bool = False) -> dict:
         """Peer addresses of this rank's block in `slot` for `flash_decode(..., peers=...)`: the block
         is laid out [m (rows) | l (rows) | acc (rows * dim)] as in `partial_buffer`.  The decode
         kernel adds 1 to every rank's flag word per (batch, kv head) group it completes, so an
-        exchange object must be used either this way or through `push` / `exchange`, not both."""
+        exchange object must be used either this way or through `push` / `exchange`, not both.
+        `exclusive`: the slot is used by no other exchange that may be in flight at the same time
+        (one slot per layer), so a decode call that waits for nothing may store into it at once."""
         if rows * (dim + 2) != self.n:
             raise ValueError("rows * (dim + 2) must equal the block size given at construction")
         base = [int(self._hd.buffer_ptrs[p]) + (slot * self.world + self.rank) * self.n * 4 for p in range(self.world)]
         return dict(m=base, l=[b + rows * 4 for b in base], acc=[b + 2 * rows * 4 for b in base],
-                    counter=[int(self._hf.buffer_ptrs[p]) + (slot * 64 + self.rank) * 4 for p in range(self.world)])
+                    counter=[int(self._hf.buffer_ptrs[p]) + (slot * 64 + self.rank) * 4 for p in range(self.world)],
+                    exclusive=exclusive)
 
     def next_fused(self, groups: int):
         """Bookkeeping of one exchange whose push is done by the decode kernel: returns (slot, block

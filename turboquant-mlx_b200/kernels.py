@@ -450,6 +450,7 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
             if not (1 <= n_peers <= 8) or any(len(peers[key]) != n_peers for key in ("m", "l", "counter")):
                 raise ValueError("peers: 1..8 entries in each of m, l, acc, counter")
             P.n_peers = n_peers
+            P.peer_slots_exclusive = int(bool(peers.get("exclusive", False)))
             for i in range(n_peers):
                 P.peer_m[i], P.peer_l[i] = int(peers["m"][i]), int(peers["l"][i])
                 P.peer_acc[i], P.peer_counter[i] = int(peers["acc"][i]), int(peers["counter"][i])
