@@ -260,7 +260,7 @@ class ShardedLayers:
         for l in range(self.layers):
             self.plans[l].run()
             self.merges[l].run_after_peers(self.flag_ptrs[l], self.world, self.n_kv, self.status_ptr,
-                                           reset_flags=True)
+                                           reset_flags=True, exclusive_flags=True)
 
     def kernels_only(self):
         for l in range(self.layers):

@@ -115,7 +115,7 @@ for ring in (True, False):
         for l in range(n_layers):
             plans[l].run()
             merges[l].run_after_peers(tq._lib.ptr(ex3.flags[slots[l]]), world, B * n_kv, tq._lib.ptr(ex3.status),
-                                      reset_flags=True)
+                                      reset_flags=True, exclusive_flags=not ring)
     side = torch.cuda.Stream(device=dev)
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):

@@ -412,7 +412,9 @@ __global__ void merge_partials_kernel(const float* pm, int64_t sm, const float* 
   // it is resident early only so that the decode launch behind it may start; its own work begins once
   // the kernel in front of it has completed, like an ordinary launch (two merges that share a gate must
   // never wait on it at the same time).
-  if (gate.flags != nullptr && gate.reset) asm volatile("griddepcontrol.wait;" ::: "memory");
+  // (reset == 2: the flags are this merge's alone - one set per layer - so nothing has to be waited for
+  // up front; the merge only must not complete before its predecessor, see the end of the kernel.)
+  if (gate.flags != nullptr && gate.reset == 1) asm volatile("griddepcontrol.wait;" ::: "memory");
   if (gate.flags != nullptr) {
     // parts pushed by peer GPUs: one thread per rank waits for that rank's flag, bounded by a time
     // limit on the GPU-wide nanosecond timer (and by an iteration count as a second bound)
@@ -517,6 +519,7 @@ __global__ void merge_partials_kernel(const float* pm, int64_t sm, const float* 
   if (gate_failed) res = __int_as_float(0x7fc00000);   // a rank never pushed: do not hand out a partial merge
   const int64_t bb = row / rows_per_batch, hh2 = row - bb * rows_per_batch;
   out[bb * out_batch_stride + hh2 * out_row_stride + e] = from_f32<T>(res);
+  if (gate.flags != nullptr && gate.reset == 2) asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 int launch_merge(const float* pm, int64_t sm, const float* pl, int64_t sl, const float* pacc,
@@ -756,7 +759,8 @@ extern "C" int tq_merge_partials_after_peers(void* flags, int n_ranks, uint32_t 
   int rc;
   if (v_signs_host && (rc = make_sign_mask(v_signs_host, dim, &sg))) return rc;
   // status[0]: give-up code; status[1]: blocks past the gate (reset_flags only), zero between calls
-  const PeerGate gate = {static_cast<uint32_t*>(flags), n_ranks, epoch, status, reset_flags != 0, status + 1,
+  TQ_REQUIRE(reset_flags >= 0 && reset_flags <= 2, TQ_ERR_BAD_ARG, "reset_flags must be 0, 1 or 2");
+  const PeerGate gate = {static_cast<uint32_t*>(flags), n_ranks, epoch, status, reset_flags, status + 1,
                          peer_wait_limit_ns()};
   return launch_merge(part_m, m_part_stride, part_l, l_part_stride, part_acc, acc_part_stride,
                       n_parts, n_rows, dim, v_signs_host != nullptr, sg, 1, out, out_dtype,

@@ -93,7 +93,8 @@ int launch_flash_mma(const FlashArgs& a, int splits, const MmaOutput& mo, cudaSt
 // (the parts were pushed by peer GPUs, see exchange.cu); flags == nullptr: no wait.  When the wait
 // gives up the status word is set and the merge writes NaN.  With `reset` the block that is last to
 // pass the gate sets the flags back to zero (`done` counts the blocks), so the same launch can be
-// replayed from a CUDA graph with a constant `epoch`.
+// replayed from a CUDA graph with a constant `epoch` (1: the flags are shared with other merges of a
+// slot ring; 2: they are this merge's alone).
 struct PeerGate {
   uint32_t* flags;
   int n;

@@ -610,10 +610,14 @@ class MergePlan:
             _lib.check(rc)
         return self.result
 
-    def run_after_peers(self, flags_ptr, n_ranks: int, epoch: int, status_ptr, reset_flags: bool = False):
+    def run_after_peers(self, flags_ptr, n_ranks: int, epoch: int, status_ptr, reset_flags: bool = False,
+                        exclusive_flags: bool = False):
         """The same merge, gated inside the kernel on the peers' flags (see PeerExchange).  With
-        `reset_flags` the kernel zeroes the flags once it is past the gate (graph-replayable)."""
-        rc = _lib.lib().tq_merge_partials_after_peers(flags_ptr, n_ranks, epoch, status_ptr, int(reset_flags),
+        `reset_flags` the kernel zeroes the flags once it is past the gate (graph-replayable);
+        `exclusive_flags`: no other merge waits on these flag words (a slot per layer), so this one
+        need not wait for the launch in front of it."""
+        rc = _lib.lib().tq_merge_partials_after_peers(flags_ptr, n_ranks, epoch, status_ptr,
+                                                      (2 if exclusive_flags else 1) if reset_flags else 0,
                                                       *self._args, _lib.stream_ptr(self._dev))
         if rc:
             _lib.check(rc)
