@@ -372,7 +372,8 @@ int tq_peer_wait(const void* flags, int n_ranks, uint32_t epoch, int* status, vo
  * launch: the next layer's decode call overlaps this merge and the decode call in front of it).
  * reset_flags 1: the flag words belong to a ring of slots that other merges also wait on, so this
  * merge starts its wait only after the launch in front of it has completed; 2: the flag words are
- * waited on by this merge alone (a slot per layer), it waits for nothing but them. */
+ * waited on by this merge alone (a slot per layer), it waits for nothing but them, and `flags` has
+ * one more zero-initialised word behind the n_ranks flag words (its block count, scratch). */
 int tq_merge_partials_after_peers(void* flags, int n_ranks, uint32_t epoch, int* status, int reset_flags,
                                   const float* part_m, int64_t m_part_stride, const float* part_l,
                                   int64_t l_part_stride, const float* part_acc, int64_t acc_part_stride,

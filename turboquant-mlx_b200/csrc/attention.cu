@@ -760,7 +760,10 @@ extern "C" int tq_merge_partials_after_peers(void* flags, int n_ranks, uint32_t 
   if (v_signs_host && (rc = make_sign_mask(v_signs_host, dim, &sg))) return rc;
   // status[0]: give-up code; status[1]: blocks past the gate (reset_flags only), zero between calls
   TQ_REQUIRE(reset_flags >= 0 && reset_flags <= 2, TQ_ERR_BAD_ARG, "reset_flags must be 0, 1 or 2");
-  const PeerGate gate = {static_cast<uint32_t*>(flags), n_ranks, epoch, status, reset_flags, status + 1,
+  // blocks past the gate are counted in status[1] (merges that follow one another) or, for a merge that
+  // may run beside others (reset_flags 2), in the word behind its own flag words
+  int* done = reset_flags == 2 ? reinterpret_cast<int*>(static_cast<uint32_t*>(flags) + n_ranks) : status + 1;
+  const PeerGate gate = {static_cast<uint32_t*>(flags), n_ranks, epoch, status, reset_flags, done,
                          peer_wait_limit_ns()};
   return launch_merge(part_m, m_part_stride, part_l, l_part_stride, part_acc, acc_part_stride,
                       n_parts, n_rows, dim, v_signs_host != nullptr, sg, 1, out, out_dtype,
