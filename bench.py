@@ -220,13 +220,13 @@ def _capture(torch, fn, dev):
 
 
 class ShardedLayers:
-    """One decode step of `layers` attention layers with the sequence sharded across the ranks:
-    per layer the decode kernel attends over this rank's chunk in partial mode and its final step
-    stores the merged (m, l, acc) rows into every rank's receive slot (plain peer stores over NVLink
-    + one system-scope counter add per (batch, kv head) group and peer); a merge gated on those
-    counters (bounded wait) combines the ranks' states and zeroes the counters again, so the whole
-    step replays from one CUDA graph.  Every layer has a receive slot of its own (reused one step
-    later), so no launch waits for another: the ranks' decode kernels and merges overlap freely."""
+    """One decode step of `layers` attention layers with the sequence sharded across the ranks, one
+    launch per layer: the decode kernel attends over this rank's chunk in partial mode; the CTA that
+    completes a (batch, kv head) group stores its merged (m, l, acc) rows into every rank's receive
+    slot (plain peer stores over NVLink + one system-scope counter add per peer), then waits (bounded)
+    for the other ranks' rows in its own slot, merges them and writes the layer's output.  Every layer
+    has a receive slot and a workspace of its own (reused one step later), so no launch waits for
+    another and the whole step replays from one CUDA graph."""
 
     def __init__(self, tq, qs, ks, vs, scale, v_signs, dev, world, n_q, n_kv, out_dtype, new_rows=None):
         import torch
@@ -235,40 +235,36 @@ class ShardedLayers:
         rows = n_q
         self.ex = PeerExchange(rows * (DIM + 2), dev, slots=self.layers)
         self.world, self.n_kv = world, n_kv
-        self.status_ptr = tq._lib.ptr(self.ex.status)
         self.outs = [torch.empty((rows, DIM), dtype=out_dtype, device=dev) for _ in range(self.layers)]
         self.sends = [partial_buffer(rows, DIM, dev)[0] for _ in range(self.layers)]
-        self.plans, self.merges, self.local_plans = [], [], []
+        self.plans, self.local_plans = [], []
         for l in range(self.layers):
-            slot = l
             m, lsum, acc = partial_views(self.sends[l], rows, DIM)
             po = (m.view(1, n_q), lsum.view(1, n_q), acc.view(1, n_q, DIM))
             kw = {} if new_rows is None else dict(new_k=new_rows[l][0], new_v=new_rows[l][1])
-            # every layer's call has a workspace of its own: the launches depend on nothing still running
             self.plans.append(tq.FlashDecodePlan(qs[l], k=ks[l], v=vs[l], attn_scale=scale, partials=True,
-                                                 peers=self.ex.targets(slot, rows, DIM, exclusive=True), partial_out=po,
+                                                 peers=self.ex.targets(l, rows, DIM, exclusive=True),
+                                                 gather=self.ex.gather_spec(l, rows, DIM),
+                                                 out=self.outs[l].view(1, n_q, DIM), partial_out=po,
                                                  kv_stable=True, q_stable=True,
                                                  workspace=tq.kernels.decode_workspace(dev), **kw))
             self.local_plans.append(tq.FlashDecodePlan(qs[l], k=ks[l], v=vs[l], attn_scale=scale, partials=True,
                                                        partial_out=po, kv_stable=True, q_stable=True,
                                                        workspace=tq.kernels.decode_workspace(dev)))
-            gm, gl, gacc = partial_views(self.ex.data[slot], rows, DIM)
-            self.merges.append(tq.MergePlan(gm, gl, gacc, v_signs, self.outs[l]))
-        self.flag_ptrs = [tq._lib.ptr(self.ex.flags[slot]) for slot in range(self.layers)]
 
     def step(self):
         for l in range(self.layers):
             self.plans[l].run()
-            self.merges[l].run_after_peers(self.flag_ptrs[l], self.world, self.n_kv, self.status_ptr,
-                                           reset_flags=True, exclusive_flags=True)
 
     def kernels_only(self):
         for l in range(self.layers):
             self.local_plans[l].run()
 
     def status(self):
-        """Largest status word of the decode workspaces (synchronises)."""
-        return max(int(p._keep_ws[:4].view(__import__("torch").int32).item()) for p in self.plans + self.local_plans)
+        """Largest status word of the decode workspaces (synchronises): non-zero when a bounded wait
+        (a tile that never arrived, a rank that never pushed) gave up."""
+        import torch
+        return max(int(p._keep_ws[:4].view(torch.int32).item()) for p in self.plans + self.local_plans)
 
 
 def gpu_arm(args):
@@ -364,12 +360,11 @@ def gpu_arm(args):
             ms_step = _timed(torch, dist, world, dev, graph.replay, args.steps, args.warmup)
             ms_calls = _timed(torch, dist, world, dev, gk.replay, max(args.steps, 100), 3)
             ms_total = _timed(torch, dist, world, dev, graph.replay, max(args.steps, 100), 3)
-        sh.ex.check()
         launch_ms = ms_calls / N_LAYERS
-        launches_per_step = 2 * N_LAYERS
+        launches_per_step = N_LAYERS
         sharding = (f"one sequence of {world * CTX} tokens split along the sequence, {CTX} positions per GPU; per "
-                    "layer: partial-mode decode -> (m, l, acc) rows stored to every rank over NVLink by the decode "
-                    "kernel -> gated merge; one CUDA graph per step")
+                    "layer ONE launch: partial-mode decode -> (m, l, acc) rows stored to every rank over NVLink -> "
+                    "bounded wait for the other ranks' rows -> merge; one CUDA graph per step")
         status = sh.status()
         extra_cfg = {"us_per_layer_kernel_only": launch_ms * 1e3, "us_per_layer_total": ms_total / N_LAYERS * 1e3,
                      "us_per_layer_exchange_and_merge": (ms_total - ms_calls) / N_LAYERS * 1e3,
@@ -433,9 +428,9 @@ def gpu_arm(args):
             sh2.step()
             torch.stack(sh2.outs, out=d_out.view(N_LAYERS, N_Q, DIM))
             h_out.copy_(d_out, non_blocking=True)
-        e2e_launches = 2 * N_LAYERS + 1
-        e2e_path = ("CUDA-graph replay of H2D(q,k,v) -> per layer: decode launch (the last rank's appends the token) "
-                    "with peer push + gated merge -> D2H, ctx held")
+        e2e_launches = N_LAYERS + 1
+        e2e_path = ("CUDA-graph replay of H2D(q,k,v) -> per layer one decode launch (the last rank's appends the "
+                    "token) with peer push, gather and merge -> D2H, ctx held")
 
     g3 = _capture(torch, e2e_body, dev)
 
@@ -448,7 +443,6 @@ def gpu_arm(args):
         tq.remove_patch()
         status = status or max(tq.kernels.workspace_status(c._decode_ws) for c in caches)
     else:
-        sh2.ex.check()
         status = status or sh2.status()
     e2e_val = world * step_bytes / (ms_e2e * 1e-3) / 1e9
     h2d = h_in.numel() * 2
@@ -763,7 +757,6 @@ def c5_measure(args, tq, torch, dist, dev, world, rank):
         gk = _capture(torch, sh.kernels_only, dev)
         ms = _timed(torch, dist, world, dev, g.replay, max(args.steps, 50), 3) / layers
         ms_k = _timed(torch, dist, world, dev, gk.replay, max(args.steps, 50), 3) / layers
-        sh.ex.check()
     else:
         outs = [torch.empty((1, nq, DIM), dtype=torch.float16, device=dev) for _ in range(layers)]
         wss = [tq.kernels.decode_workspace(dev) for _ in range(layers)]

@@ -204,13 +204,14 @@ typedef struct tq_flash_params {
   void* workspace;             /* tq_flash_decode_workspace_bytes() */
   int64_t workspace_bytes;
 
-  int32_t out_mode;            /* 0: final output; 1: merged partials (m, l, S) */
+  int32_t out_mode;            /* 0: final output; 1: merged partials (m, l, S); 2: partials pushed to the peers,
+                                  gathered from them and merged into the final output (see gather_*) */
   int32_t out_dtype;
-  void* out;                   /* mode 0: (batch, n_q_heads, dim) */
+  void* out;                   /* modes 0 and 2: (batch, n_q_heads, dim) */
   int64_t out_batch_stride, out_head_stride;
-  float* part_m;               /* mode 1: (batch * n_q_heads) */
-  float* part_l;               /* mode 1: (batch * n_q_heads) */
-  float* part_acc;             /* mode 1: (batch * n_q_heads, dim), before the butterfly */
+  float* part_m;               /* modes 1 and 2: (batch * n_q_heads) */
+  float* part_l;               /* modes 1 and 2: (batch * n_q_heads) */
+  float* part_acc;             /* modes 1 and 2: (batch * n_q_heads, dim), before the butterfly */
   void* stream;
   /* mode 1, optional (n_peers 0: off; tensor-core path only): the CTA that completes a (batch, kv head)
    * group also stores its rows of the merged state into each peer_m / peer_l / peer_acc [p] (same row
@@ -272,7 +273,22 @@ typedef struct tq_flash_params {
    * hand-over and merge of consecutive launches overlap as well.  0: the workspace may be shared
    * with the preceding call on the stream; the kernel waits for that call before writing it. */
   int32_t workspace_exclusive;
-  int32_t reserved_tail;
+  /* out_mode 2 (tensor-core path; no reference counterpart): the all-gather and merge of the
+   * sequence-sharded decode inside the decode launch.  As in mode 1 with peers the CTA that
+   * completes a (batch, kv head) group stores its merged rows into every rank's receive slot (one of
+   * the peer targets is this rank's own slot) and adds 1 to every rank's counter; it then waits -
+   * bounded by tq_set_peer_wait_limit_ms - until the gather_ranks counters at gather_flags (this
+   * rank's own, one per rank) have each received batch * n_kv_heads additions, merges the ranks' rows
+   * found at gather_m / gather_l / gather_acc (rank 0's block of this GPU's slot; rank p's block is
+   * gather_part_stride floats further) and writes the final output to `out`.  gather_flags has
+   * gather_ranks + 1 zero-initialised words; the kernel leaves them at zero.  A wait that gives up
+   * writes 21 + the missing rank to the workspace's status word and NaN to `out`. */
+  int32_t gather_ranks;
+  const float* gather_m;
+  const float* gather_l;
+  const float* gather_acc;
+  int64_t gather_part_stride;
+  uint32_t* gather_flags;
 } tq_flash_params;
 
 /* Workspace contract: 16-byte aligned, at least tq_flash_decode_workspace_bytes()

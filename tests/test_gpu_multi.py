@@ -137,6 +137,42 @@ for ring in (True, False):
     assert int(ex3.flags.abs().sum()) == 0          # the merges left the counters at zero
     assert all(tq.kernels.workspace_status(p._keep_ws) == 0 for p in plans)
     dist.barrier()
+# the whole exchange inside the decode launch (push, bounded wait for the other ranks' rows, merge):
+# one launch per layer, a slot per layer, replayed from a graph
+ex4 = PeerExchange(rows * (D + 2), dev, slots=n_layers)
+plans, outs6 = [], []
+for l in range(n_layers):
+    sb = partial_buffer(rows, D, dev)[0]
+    m5, l5, a5 = partial_views(sb, rows, D)
+    outs6.append(torch.zeros((B, n_kv * n_rep, D), dtype=torch.float32, device=dev))
+    plans.append(tq.FlashDecodePlan(
+        qs[l], k=kdesc, v=vdesc, attn_scale=scale, partials=True, peers=ex4.targets(l, rows, D, exclusive=True),
+        gather=ex4.gather_spec(l, rows, D), out=outs6[-1], kv_stable=True, q_stable=True,
+        workspace=tq.kernels.decode_workspace(dev),
+        partial_out=(m5.view(B, -1), l5.view(B, -1), a5.view(B, -1, D))))
+def step2():
+    for l in range(n_layers):
+        plans[l].run()
+side = torch.cuda.Stream(device=dev)
+side.wait_stream(torch.cuda.current_stream())
+with torch.cuda.stream(side):
+    step2(); step2()
+torch.cuda.current_stream().wait_stream(side)
+torch.cuda.synchronize()
+dist.barrier()
+graph = torch.cuda.CUDAGraph()
+with torch.cuda.graph(graph):
+    step2()
+for it in range(8):
+    for o6 in outs6:
+        o6.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    for l in range(n_layers):
+        err2 = max(err2, float((outs6[l] - fulls[l]).abs().max() / fulls[l].abs().max()))
+assert int(ex4.flags.abs().sum()) == 0              # the kernels left their counters at zero
+assert all(tq.kernels.workspace_status(p._keep_ws) == 0 for p in plans)
+dist.barrier()
 print(f"rank {rank} peer exchange rel err {err2:.3e}")
 dist.barrier()
 dist.destroy_process_group()

@@ -64,7 +64,9 @@ class FlashParams(ctypes.Structure):
         ("k_boundaries_host", POINTER(c_float)), ("v_boundaries_host", POINTER(c_float)),
         ("sparse_v_threshold", c_float), ("sparse_reserved", c_int32), ("active_positions", c_void_p),
         ("seq_lens_dev", c_void_p),
-        ("workspace_exclusive", c_int32), ("reserved_tail", c_int32),
+        ("workspace_exclusive", c_int32), ("gather_ranks", c_int32),
+        ("gather_m", c_void_p), ("gather_l", c_void_p), ("gather_acc", c_void_p),
+        ("gather_part_stride", c_int64), ("gather_flags", c_void_p),
     ]
 
 

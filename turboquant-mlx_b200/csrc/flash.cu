@@ -27,7 +27,7 @@ static int validate(const tq_flash_params* p) {
   TQ_REQUIRE(p->seq_len > 0, TQ_ERR_BAD_ARG, "seq_len must be positive, got %lld",
              (long long)p->seq_len);
   TQ_REQUIRE(p->n_peers >= 0 && p->n_peers <= 8, TQ_ERR_BAD_ARG, "n_peers must be 0..8, got %d", p->n_peers);
-  TQ_REQUIRE(p->n_peers == 0 || p->out_mode == 1, TQ_ERR_BAD_ARG, "peer targets need out_mode 1");
+  TQ_REQUIRE(p->n_peers == 0 || p->out_mode != 0, TQ_ERR_BAD_ARG, "peer targets need out_mode 1 or 2");
   for (int i = 0; i < p->n_peers; ++i)
     TQ_REQUIRE(p->peer_m[i] && p->peer_l[i] && p->peer_acc[i] && p->peer_counter[i] &&
                    (reinterpret_cast<uintptr_t>(p->peer_acc[i]) & 15) == 0,
@@ -66,11 +66,19 @@ static int validate(const tq_flash_params* p) {
     default: return set_error(TQ_ERR_BAD_ARG, "unknown v_format %d", p->v_format);
   }
   TQ_REQUIRE(p->q && p->k_data && p->v_data, TQ_ERR_BAD_ARG, "NULL tensor pointer");
-  TQ_REQUIRE(p->out_mode == 0 || p->out_mode == 1, TQ_ERR_BAD_ARG, "bad out_mode %d", p->out_mode);
-  if (p->out_mode == 0)
+  TQ_REQUIRE(p->out_mode >= 0 && p->out_mode <= 2, TQ_ERR_BAD_ARG, "bad out_mode %d", p->out_mode);
+  if (p->out_mode != 1)
     TQ_REQUIRE(p->out && p->out_dtype >= TQ_F32 && p->out_dtype <= TQ_BF16, TQ_ERR_BAD_ARG,
-               "mode 0 needs out and a valid out_dtype");
-  else {
+               "modes 0 and 2 need out and a valid out_dtype");
+  if (p->out_mode == 2) {
+    TQ_REQUIRE(p->n_peers > 0, TQ_ERR_BAD_ARG, "mode 2 needs peer targets (its own slot among them)");
+    TQ_REQUIRE(p->gather_m && p->gather_l && p->gather_acc && p->gather_flags && p->gather_ranks >= 1 &&
+                   p->gather_ranks <= 16,
+               TQ_ERR_BAD_ARG, "mode 2 needs the local receive slot, its flag words and 1..16 ranks");
+    TQ_REQUIRE((reinterpret_cast<uintptr_t>(p->gather_acc) & 15) == 0 && p->gather_part_stride % 4 == 0,
+               TQ_ERR_MISALIGNED, "gather_acc must be 16-byte aligned and gather_part_stride a multiple of 4 floats");
+  }
+  if (p->out_mode != 0) {
     TQ_REQUIRE(p->part_m && p->part_l && p->part_acc, TQ_ERR_BAD_ARG,
                "mode 1 needs part_m, part_l and part_acc");
     TQ_REQUIRE((reinterpret_cast<uintptr_t>(p->part_acc) & 15) == 0, TQ_ERR_MISALIGNED,
@@ -305,7 +313,14 @@ extern "C" int tq_flash_decode(const tq_flash_params* p) {
     mo.om = p->part_m;
     mo.ol = p->part_l;
     mo.oacc = p->part_acc;
-    mo.n_peers = p->out_mode == 1 ? p->n_peers : 0;
+    mo.n_peers = p->out_mode != 0 ? p->n_peers : 0;
+    mo.g_m = p->gather_m;
+    mo.g_l = p->gather_l;
+    mo.g_acc = p->gather_acc;
+    mo.g_stride = p->gather_part_stride;
+    mo.g_flags = p->gather_flags;
+    mo.g_ranks = p->gather_ranks;
+    mo.g_limit_ns = peer_wait_limit_ns();
     mo.peer_unordered = p->peer_slots_exclusive;
     for (int i = 0; i < 8; ++i) {
       mo.peer_m[i] = p->peer_m[i];

@@ -80,6 +80,13 @@ struct MmaOutput {       // where the tensor-core kernel's fused merge writes
   float* oacc;
   int n_peers;           // out_mode 1: peers that also receive the merged state (0: none)
   int peer_unordered;    // the peer slots are used by no exchange that may still be in flight
+  const float* g_m;      // out_mode 2: this GPU's receive slot (rank 0's block; g_stride floats between ranks)
+  const float* g_l;
+  const float* g_acc;
+  int64_t g_stride;
+  uint32_t* g_flags;
+  int g_ranks;
+  unsigned long long g_limit_ns;
   float* peer_m[8];
   float* peer_l[8];
   float* peer_acc[8];

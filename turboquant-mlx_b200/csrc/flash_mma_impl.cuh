@@ -100,6 +100,17 @@ struct MmaTables {
   float* oacc;
   int n_peers;          // out_mode 1: the merged state also goes to these peers (other GPUs' memory)
   int peer_unordered;   // the peer slots are not shared with an exchange that may still be in flight
+  // out_mode 2: after the push the CTA waits (bounded) for every rank's rows of this exchange in this
+  // GPU's own receive slot, merges them and writes the final output: the all-gather + merge of the
+  // sequence-sharded decode inside the decode launch
+  const float* g_m;     // rank 0's block of the local slot; rank p's block is g_stride floats further
+  const float* g_l;
+  const float* g_acc;
+  int64_t g_stride;
+  uint32_t* g_flags;    // [n_ranks] counters the ranks' pushes add to, then one word counting this rank's CTAs past the wait
+  int g_ranks;
+  int g_expect;         // additions per rank and exchange = batch * n_kv_heads
+  unsigned long long g_limit_ns;
   float* peer_m[8];
   float* peer_l[8];
   float* peer_acc[8];
@@ -298,8 +309,8 @@ __device__ __forceinline__ float load_any(const void* base, int dtype, int64_t i
 // go to peer GPUs by plain stores.
 template <bool VAFF>
 __device__ __forceinline__ void write_row(const FlashArgs& a, const MmaTables& tb, int b, int head, int64_t row,
-                                          float4 acc4, float m_star, float l_star, int lane) {
-  if (tb.out_mode == 1) {
+                                          float4 acc4, float m_star, float l_star, int lane, bool final_out) {
+  if (!final_out) {
     reinterpret_cast<float4*>(tb.oacc + row * kDim)[lane] = acc4;
     if (lane == 0) {
       tb.om[row] = m_star;
@@ -1043,62 +1054,67 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   // come after the launch in front of this one - the gated merge that reads them - has completed.
   if (independent && tb.n_peers > 0 && !tb.peer_unordered) grid_dependency_wait();
 
-  // The merge reads every split's state straight from L2 into registers.  Shared scratch
+  // The merge reads every part's state straight from L2 into registers.  Shared scratch
   // (the ring is free): weights [8][kMaxParts], m* [8], l* [8].
   float* wgt = reinterpret_cast<float*>(smem + L::stage0);
   float* mst = wgt + 8 * kMaxParts;
   float* lst = mst + 8;
-  for (int r = warp; r < a.n_rep; r += kConsumerWarps) {
-    // lane i (+32, +64) holds part i: m* = max over parts with l > 0, weight = e^(m - m*)
-    float mi[3], li[3];
-#pragma unroll
-    for (int s3 = 0; s3 < 3; ++s3) {
-      const int i = lane + 32 * s3;
-      const bool on = i < count;
-      li[s3] = on ? __ldcg(a.part_l + (int64_t)i * n_rows + row0 + r) : 0.f;
-      mi[s3] = on ? __ldcg(a.part_m + (int64_t)i * n_rows + row0 + r) : -INFINITY;
-    }
-    float mx = -INFINITY;
-#pragma unroll
-    for (int s3 = 0; s3 < 3; ++s3)
-      if (li[s3] > 0.f) mx = fmaxf(mx, mi[s3]);
-    mx = warp_max(mx);
-    float lsum = 0.f;
-#pragma unroll
-    for (int s3 = 0; s3 < 3; ++s3) {
-      const int i = lane + 32 * s3;
-      const float w = li[s3] > 0.f ? __expf(mi[s3] - mx) : 0.f;
-      if (i < count) wgt[r * kMaxParts + i] = w;
-      lsum += li[s3] * w;
-    }
-    lsum = warp_sum(lsum);
-    if (lane == 0) {
-      mst[r] = mx;
-      lst[r] = lsum;
-    }
-  }
-  consumer_barrier();
-  const int64_t pstride = n_rows * (kDim / 4);          // float4s between consecutive parts
   const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-  // warp w owns rows w, w + kConsumerWarps, ...; a lane owns elements 4*lane .. 4*lane+3 of its row
-  for (int r = warp; r < a.n_rep; r += kConsumerWarps) {
-    float4 acc4 = zero4;
-    const float4* src = reinterpret_cast<const float4*>(a.part_acc + (row0 + r) * kDim) + lane;
-    const float* wr = wgt + r * kMaxParts;
-    for (int i0 = 0; i0 < count; i0 += kMergeBatch) {
-      float4 v[kMergeBatch];
+  // parts: m / l at pm / pl + i * ml_stride + row, acc rows at pacc + i * acc_stride + row * 128
+  auto merge_pass = [&](const float* pm, const float* pl, const float* pacc, int64_t ml_stride, int64_t acc_stride,
+                        int cnt, bool final_out, bool poisoned) {
+    for (int r = warp; r < a.n_rep; r += kConsumerWarps) {
+      // lane i (+32, +64) holds part i: m* = max over parts with l > 0, weight = e^(m - m*)
+      float mi[3], li[3];
 #pragma unroll
-      for (int j = 0; j < kMergeBatch; ++j)
-        v[j] = i0 + j < count ? __ldcg(src + (int64_t)(i0 + j) * pstride) : zero4;
+      for (int s3 = 0; s3 < 3; ++s3) {
+        const int i = lane + 32 * s3;
+        const bool on = i < cnt;
+        li[s3] = on ? __ldcg(pl + (int64_t)i * ml_stride + row0 + r) : 0.f;
+        mi[s3] = on ? __ldcg(pm + (int64_t)i * ml_stride + row0 + r) : -INFINITY;
+      }
+      float mx = -INFINITY;
 #pragma unroll
-      for (int j = 0; j < kMergeBatch; ++j) {
-        const float wi = i0 + j < count ? wr[i0 + j] : 0.f;
-        acc4.x += v[j].x * wi; acc4.y += v[j].y * wi; acc4.z += v[j].z * wi; acc4.w += v[j].w * wi;
+      for (int s3 = 0; s3 < 3; ++s3)
+        if (li[s3] > 0.f) mx = fmaxf(mx, mi[s3]);
+      mx = warp_max(mx);
+      float lsum = 0.f;
+#pragma unroll
+      for (int s3 = 0; s3 < 3; ++s3) {
+        const int i = lane + 32 * s3;
+        const float w = li[s3] > 0.f ? __expf(mi[s3] - mx) : 0.f;
+        if (i < cnt) wgt[r * kMaxParts + i] = w;
+        lsum += li[s3] * w;
+      }
+      lsum = warp_sum(lsum);
+      if (lane == 0) {
+        mst[r] = mx;
+        lst[r] = poisoned ? __int_as_float(0x7fc00000) : lsum;   // a rank never pushed: hand out NaN, not a partial merge
       }
     }
-    write_row<VAFF>(a, tb, b, h0 + r, row0 + r, acc4, mst[r], lst[r], lane);
-  }
-  if (tb.out_mode == 1 && tb.n_peers > 0) {
+    consumer_barrier();
+    const int64_t pstride = acc_stride / 4;               // float4s between consecutive parts
+    // warp w owns rows w, w + kConsumerWarps, ...; a lane owns elements 4*lane .. 4*lane+3 of its row
+    for (int r = warp; r < a.n_rep; r += kConsumerWarps) {
+      float4 acc4 = zero4;
+      const float4* src = reinterpret_cast<const float4*>(pacc + (row0 + r) * kDim) + lane;
+      const float* wr = wgt + r * kMaxParts;
+      for (int i0 = 0; i0 < cnt; i0 += kMergeBatch) {
+        float4 v[kMergeBatch];
+#pragma unroll
+        for (int j = 0; j < kMergeBatch; ++j)
+          v[j] = i0 + j < cnt ? __ldcg(src + (int64_t)(i0 + j) * pstride) : zero4;
+#pragma unroll
+        for (int j = 0; j < kMergeBatch; ++j) {
+          const float wi = i0 + j < cnt ? wr[i0 + j] : 0.f;
+          acc4.x += v[j].x * wi; acc4.y += v[j].y * wi; acc4.z += v[j].z * wi; acc4.w += v[j].w * wi;
+        }
+      }
+      write_row<VAFF>(a, tb, b, h0 + r, row0 + r, acc4, mst[r], lst[r], lane, final_out);
+    }
+  };
+  merge_pass(a.part_m, a.part_l, a.part_acc, n_rows, n_rows * kDim, count, tb.out_mode == 0, false);
+  if (tb.out_mode != 0 && tb.n_peers > 0) {
     // every row of this (batch, kv head) group is on its way: one thread fences at system scope (the
     // barrier makes the other threads' stores precede it) and tells each peer
     consumer_barrier();
@@ -1108,6 +1124,43 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       for (int p = 0; p < 8; ++p)
         if (p < tb.n_peers) atomicAdd_system(tb.peer_counter[p], 1u);
     }
+  }
+  if (tb.out_mode == 2) {
+    // The ranks' rows of this exchange arrive in this GPU's own slot; thread e waits for rank e's counter
+    // (bounded by a time limit on the GPU-wide timer and by an iteration count).
+    __shared__ int gather_failed_s;
+    if (tid == 0) gather_failed_s = 0;
+    consumer_barrier();
+    if (tid < tb.g_ranks) {
+      bool seen = false;
+      unsigned long long t0;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+      for (uint32_t it = 0; it < (1u << 28) && !seen; ++it) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(tb.g_flags + tid) : "memory");
+        seen = v >= (uint32_t)tb.g_expect;
+        if (!seen) {
+          __nanosleep(40);
+          unsigned long long t1;
+          asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+          if (t1 - t0 > tb.g_limit_ns) break;
+        }
+      }
+      if (!seen) {
+        atomicExch(tb.status, 21 + tid);
+        gather_failed_s = 1;
+      }
+    }
+    consumer_barrier();
+    // the CTA of this rank that is last past the wait puts the counters back to zero for the next use
+    if (tid == 0) {
+      const uint32_t prev = atomicAdd(tb.g_flags + tb.g_ranks, 1u);
+      if (prev == (uint32_t)tb.g_expect - 1) {
+        for (int i = 0; i <= tb.g_ranks; ++i)
+          asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(tb.g_flags + i), "r"(0u) : "memory");
+      }
+    }
+    merge_pass(tb.g_m, tb.g_l, tb.g_acc, tb.g_stride, tb.g_stride, tb.g_ranks, true, gather_failed_s != 0);
   }
   // An independent launch still must not complete before its predecessor has: later work on the
   // stream is ordered after this grid only.  The CTA that merged is the last to leave; it waits.
@@ -1235,6 +1288,14 @@ int TQ_CAT(launch_flash_mma_, TQ_GEOM)(const FlashArgs& a, int splits, const Mma
   tb.oacc = mo.oacc;
   tb.n_peers = mo.n_peers;
   tb.peer_unordered = mo.peer_unordered;
+  tb.g_m = mo.g_m;
+  tb.g_l = mo.g_l;
+  tb.g_acc = mo.g_acc;
+  tb.g_stride = mo.g_stride;
+  tb.g_flags = mo.g_flags;
+  tb.g_ranks = mo.g_ranks;
+  tb.g_expect = a.batch * a.n_kv_heads;
+  tb.g_limit_ns = mo.g_limit_ns;
   for (int i = 0; i < 8; ++i) {
     tb.peer_m[i] = mo.peer_m[i];
     tb.peer_l[i] = mo.peer_l[i];

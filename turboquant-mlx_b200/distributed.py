@@ -151,6 +151,16 @@ class PeerExchange:
                     counter=[int(self._hf.buffer_ptrs[p]) + (slot * 64 + self.rank) * 4 for p in range(self.world)],
                     exclusive=exclusive)
 
+    def gather_spec(self, slot: int, rows: int, dim: int) -> dict:
+        """This rank's own view of `slot` for `flash_decode(..., peers=..., gather=...)`: where the
+        ranks' blocks arrive, and the counters their pushes add to (the decode kernel waits on them,
+        merges the blocks and puts the counters back to zero)."""
+        if rows * (dim + 2) != self.n:
+            raise ValueError("rows * (dim + 2) must equal the block size given at construction")
+        base = self.data[slot].data_ptr()
+        return dict(m=base, l=base + rows * 4, acc=base + 2 * rows * 4, part_stride=self.n,
+                    flags=self.flags[slot].data_ptr(), n_ranks=self.world)
+
     def next_fused(self, groups: int):
         """Bookkeeping of one exchange whose push is done by the decode kernel: returns (slot, block
         view, flags pointer, counter value to wait for).  `groups` = batch * n_kv_heads additions

@@ -256,7 +256,7 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
                  q_stable: bool = False, new_k: torch.Tensor | None = None, new_v: torch.Tensor | None = None,
                  sparse_v_threshold: float = 0.0, active_out: torch.Tensor | None = None,
                  seq_lens: torch.Tensor | None = None, workspace: torch.Tensor | None = None,
-                 workspace_owner=None, _prepare_only: bool = False):
+                 workspace_owner=None, gather=None, _prepare_only: bool = False):
     """Split-K flash decoding for one query token per sequence.
 
     q: (B, n_q, dim).  k / v: dicts describing the stored keys / values:
@@ -304,6 +304,11 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
     consecutive decode launches overlap from start to end.  Without it the calls of a stream share
     one workspace and each waits for its predecessor before writing it.  `workspace_owner`: any
     object (a cache, say); its attribute `_decode_ws` holds such a workspace, made or grown here.
+
+    gather (with partials=True and peers; see distributed.PeerExchange.gather_spec): after the
+    push the same launch waits (bounded) for every rank's rows in this GPU's own receive slot,
+    merges them and writes the final (B, n_q, dim) result to `out`, which is returned: the
+    sequence-sharded decode step in one launch per layer.
     """
     _lib.require_cuda(q)
     B, n_q, dim = q.shape
@@ -435,8 +440,20 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
         P.mask_head_stride = 0 if m.shape[1] == 1 else m.stride(1)
 
     dev = q.device
+    if gather is not None and (not partials or peers is None):
+        raise ValueError("gather needs partials=True and peers")
     if partials:
-        P.out_mode = 1
+        P.out_mode = 1 if gather is None else 2
+        if gather is not None:
+            if out is None:
+                out = torch.empty((B, n_q, dim), dtype=out_dtype or q.dtype, device=dev)
+            elif tuple(out.shape) != (B, n_q, dim) or out.stride(-1) != 1:
+                raise ValueError(f"out must be ({B}, {n_q}, {dim}) with a contiguous last dimension")
+            P.out, P.out_dtype = out.data_ptr(), _lib.dtype_code(out.dtype)
+            P.out_batch_stride, P.out_head_stride = out.stride(0), out.stride(1)
+            P.gather_ranks = int(gather["n_ranks"])
+            P.gather_m, P.gather_l, P.gather_acc = int(gather["m"]), int(gather["l"]), int(gather["acc"])
+            P.gather_part_stride, P.gather_flags = int(gather["part_stride"]), int(gather["flags"])
         if partial_out is not None:     # contiguous float32 views (B, n_q), (B, n_q), (B, n_q, dim)
             pm, pl, pa = partial_out
             assert pm.is_contiguous() and pl.is_contiguous() and pa.is_contiguous()
@@ -482,7 +499,7 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
         ws = _lib.workspace(need, dev, tag=f"flash{B * n_kv}")   # counters: one layout per batch * n_kv
     if ws is not None:
         P.workspace, P.workspace_bytes = ws.data_ptr(), ws.numel()
-    result = (pm, pl, pa) if partials else out
+    result = out if (not partials or gather is not None) else (pm, pl, pa)
     if _prepare_only:
         keep += [q, ws, result]
         return P, keep, result, dev
