@@ -526,7 +526,10 @@ def workload_c1(args):
     peak, kind = measured_peaks()
     pq = tq.PolarQuantizer(DIM, 3, seed=43, device=dev)
     res = {}
-    for name, n, nbuf in (("c1_16384", 4 * 4096, 64), ("sat_2M", 1 << 21, 3)):
+    sizes = (("c1_16384", 4 * 4096, 64), ("sat_2M", 1 << 21, 3))
+    if args.vectors > 0:        # one size only (profiling aid): few launches in front of the captured one
+        sizes = (("sat_2M", args.vectors, 3),)
+    for name, n, nbuf in sizes:
         gen = torch.Generator(device=dev).manual_seed(5)
         xs = [(torch.randn((1, n, DIM), generator=gen, device=dev) *
                torch.exp(0.5 * torch.randn((1, n, 1), generator=gen, device=dev))).half() for _ in range(nbuf)]
@@ -810,6 +813,7 @@ def main():
                     help="plain launches of the flash-decode kernel only (no graph, no e2e): profiler case")
     ap.add_argument("--ctx", type=int, default=0, help="c4p: prompt length (default 32768)")
     ap.add_argument("--no-c5", action="store_true", help="N > 1: skip the secondary config-5 record")
+    ap.add_argument("--vectors", type=int, default=0, help="c1: run this many vectors only (default: 16384 and 2^21)")
     ap.add_argument("--splits", type=int, default=0, help="c3: force the split count of the decode kernel (0 = planner)")
     ap.add_argument("--workload", default="c2", choices=["c2", "c1", "c3", "c5", "c4p", "c4"],
                     help="c2 = the headline benchmark; c1 / c3 = secondary measurements of other configurations")

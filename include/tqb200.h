@@ -289,6 +289,16 @@ typedef struct tq_flash_params {
   const float* gather_acc;
   int64_t gather_part_stride;
   uint32_t* gather_flags;
+  /* Several query tokens per sequence (tensor-core path, out_mode 0; the reference intercepts
+   * single-token steps only, patch.py:19-21, and sends every other step to dense attention over the
+   * dequantized cache).  q_tokens in 2..8 with n_rep * q_tokens <= 8: the queries are the LAST
+   * q_tokens positions of the sequence, already stored in the cache (seq_len counts them), and
+   * attend causally: token t sees positions 0 .. seq_len - q_tokens + t.  q and out gain a token
+   * axis with the strides below (in elements); 0 or 1: one token, strides ignored. */
+  int32_t q_tokens;
+  int32_t q_tokens_reserved;
+  int64_t q_token_stride;
+  int64_t out_token_stride;
 } tq_flash_params;
 
 /* Workspace contract: 16-byte aligned, at least tq_flash_decode_workspace_bytes()

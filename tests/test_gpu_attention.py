@@ -524,3 +524,62 @@ def test_flash_decode_device_side_lengths(tq, dev):
         assert _rel(out[b].cpu().numpy(), one[0].cpu().numpy()) < 1e-5
     with pytest.raises(ValueError, match="seq_lens"):
         tq.flash_decode(q, k=k_dense, v=v, attn_scale=scale, seq_lens=sl, mask=torch.zeros((1, 1, S), device=dev))
+
+
+@pytest.mark.parametrize("n_rep,T,S,kind", [(2, 4, 1531, "polar4"), (4, 2, 700, "dense"), (1, 8, 2300, "polar3"),
+                                            (2, 3, 5000, "dense"), (7, 1, 300, "dense")])
+def test_short_multi_token_step_is_causal_and_matches_oracle(tq, oracle, dev, n_rep, T, S, kind):
+    """T query tokens per sequence (the last T stored positions) in one launch over the packed rows:
+    token t must equal a single-token decode over the first S - T + 1 + t positions (the oracle's
+    composed path), for dense and packed keys, with several splits and a ragged last tile.  The
+    reference sends such steps to dense attention (patch.py:19-21)."""
+    L = tq._lib.lib()
+    rng = np.random.default_rng(77 + T)
+    B, n_kv, D = 2, 2, 128
+    scale = 1.0 / math.sqrt(D)
+    vq = tq.PolarQuantizer(D, 3, seed=43, device=dev)
+    vs = vq.signs.cpu().numpy()
+    vraw = (rng.standard_normal((B, n_kv, S, D)) * rng.lognormal(0, 0.5, (B, n_kv, S, 1))).astype(np.float32)
+    vp, vn = oracle.quantize_packed(vraw, vs, 3)
+    n_alloc = (S + 255) // 256 * 256
+
+    def alloc(x):   # rows live in a longer allocation, as in a cache
+        full = np.zeros(x.shape[:2] + (n_alloc,) + x.shape[3:], x.dtype)
+        full[:, :, :S] = x
+        return _t(full, dev)[:, :, :S]
+
+    v = dict(format="polar", packed=alloc(vp), norms=alloc(vn), centroids=vq.centroids, signs=vq.signs, bits=3)
+    if kind == "dense":
+        kd = rng.standard_normal((B, n_kv, S, D)).astype(np.float16)
+        k = dict(format="dense", data=alloc(kd))
+    else:
+        kbits = int(kind[-1])
+        kq = tq.PolarQuantizer(D, kbits, seed=42, device=dev)
+        ks = kq.signs.cpu().numpy()
+        kraw = rng.standard_normal((B, n_kv, S, D)).astype(np.float16)
+        kp, kn = oracle.quantize_packed(kraw, ks, kbits)
+        k = dict(format="polar", packed=alloc(kp), norms=alloc(kn), centroids=kq.centroids, signs=kq.signs, bits=kbits)
+    q = rng.standard_normal((B, n_kv * n_rep, T, D)).astype(np.float16)
+    for splits in (0, 3):
+        out = tq.flash_decode(_t(q, dev) if T > 1 else _t(q, dev)[:, :, 0], k=k, v=v, attn_scale=scale,
+                              out_dtype=torch.float32, num_splits=splits)
+        assert L.tq_flash_decode_last_kernel() == 1
+        out = out.cpu().numpy().reshape(B, n_kv * n_rep, T, D)
+        for b in range(B):
+            for t in range(T):
+                n = S - T + 1 + t
+                vdesc = dict(packed=vp[b, :, :n], norms=vn[b, :, :n], centroids=oracle.codebook(3), signs=vs, bits=3)
+                if kind == "dense":
+                    ref, _ = oracle.decode_attention(q[b, :, t], k_dense=kd[b, :, :n], v_polar=vdesc,
+                                                     attn_scale=scale, n_rep=n_rep)
+                else:
+                    ref, _ = oracle.decode_attention(
+                        q[b, :, t], k_polar=dict(packed=kp[b, :, :n], norms=kn[b, :, :n],
+                                                 centroids=oracle.codebook(kbits), signs=ks, bits=kbits),
+                        v_polar=vdesc, attn_scale=scale, n_rep=n_rep)
+                assert _rel(out[b, :, t], ref) < ATT_TOL, (b, t, splits)
+    assert tq.kernels.flash_status(dev, B * n_kv) == 0
+    if T > 1:
+        with pytest.raises(ValueError):      # rows beyond the MMA tile: refused, not silently wrong
+            tq.flash_decode(_t(np.zeros((B, n_kv * n_rep, 9 // n_rep + 1, D), np.float16), dev), k=k, v=v,
+                            attn_scale=scale)

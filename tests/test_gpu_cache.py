@@ -75,6 +75,57 @@ def test_state_round_trip_and_extend(tq, dev):
     assert torch.equal(r.k_packed[:, :, :10].view(torch.int32), st[0].view(torch.int32))
 
 
+def test_state_with_signs_on_disk_round_trip(tq, oracle, dev, tmp_path):
+    """A cache written with sign vectors that this library's generator would NOT derive from the seed
+    (the situation of a file saved by the reference: its signs come from another PRNG) goes to disk as
+    safetensors, comes back through `from_state`, decodes with the saved signs and can be extended
+    (tests/test_v_only_cache.py:98-134 of the reference, plus the sign vectors)."""
+    from safetensors.torch import load_file, save_file
+    torch.manual_seed(21)
+    B, n_kv, S = 1, 2, 40
+    k = torch.randn(B, n_kv, S, 128, device=dev, dtype=torch.float16)
+    v = torch.randn(B, n_kv, S, 128, device=dev, dtype=torch.float16)
+    g = torch.Generator().manual_seed(77)
+    foreign_k = (torch.randint(0, 2, (128,), generator=g) * 2 - 1).float()
+    foreign_v = (torch.randint(0, 2, (128,), generator=g) * 2 - 1).float()
+    # the writer: packed rows produced with the foreign signs (oracle arithmetic), as the other library would
+    kp, kn = oracle.quantize_packed(k.cpu().numpy(), foreign_k.numpy(), 3)
+    vp, vn = oracle.quantize_packed(v.cpu().numpy(), foreign_v.numpy(), 3)
+    arrays = [torch.from_numpy(kp.view(np.int32)), torch.from_numpy(kn), torch.from_numpy(vp.view(np.int32)),
+              torch.from_numpy(vn), foreign_k, foreign_v]
+    path = str(tmp_path / "cache.safetensors")
+    save_file({f"a{i}": t.contiguous() for i, t in enumerate(arrays)}, path,
+              metadata={"meta_state": f"{S},3,42,128,128,float16"})
+    loaded = load_file(path, device=str(dev))
+    from safetensors import safe_open
+    with safe_open(path, framework="pt") as f:
+        meta = f.metadata()["meta_state"]
+    state = [loaded[f"a{i}"] for i in range(6)]
+    state[0], state[2] = state[0].view(torch.uint32), state[2].view(torch.uint32)
+    r = tq.TurboQuantKVCache.from_state(state, meta)
+    assert r.offset == S and not r.signs_match_seed()
+    kd, vd = r.dequantized(dtype=torch.float32)
+    want_k = oracle.packed_dequantize(kp, kn, oracle.codebook(3), foreign_k.numpy(), 128, 3)
+    want_v = oracle.packed_dequantize(vp, vn, oracle.codebook(3), foreign_v.numpy(), 128, 3)
+    assert np.array_equal(kd.cpu().numpy(), want_k) and np.array_equal(vd.cpu().numpy(), want_v)
+    # the loaded cache keeps quantizing with the saved signs
+    k2 = torch.randn(B, n_kv, 3, 128, device=dev, dtype=torch.float16)
+    ko, vo = r.update_and_fetch(k2, k2)
+    assert r.offset == S + 3 and ko.shape == (B, n_kv, S + 3, 128)
+    kp2, kn2 = oracle.quantize_packed(k2.cpu().numpy(), foreign_k.numpy(), 3)
+    assert np.array_equal(r.k_packed[:, :, S:S + 3].cpu().numpy().view(np.uint32), kp2)
+    # its own state with signs survives a second trip through a file unchanged
+    st2 = r.state_with_signs
+    save_file({f"a{i}": (t.view(torch.int32) if t.dtype == torch.uint32 else t).contiguous().cpu()
+               for i, t in enumerate(st2)}, path, metadata={"meta_state": r.meta_state})
+    again = load_file(path, device=str(dev))
+    st3 = [again[f"a{i}"] for i in range(6)]
+    st3[0], st3[2] = st3[0].view(torch.uint32), st3[2].view(torch.uint32)
+    r2 = tq.TurboQuantKVCache.from_state(st3, r.meta_state)
+    assert r2.offset == S + 3 and torch.equal(r2.k_packed.view(torch.int32), r.k_packed[:, :, :S + 3].view(torch.int32))
+    assert torch.equal(r2._v_q.signs.cpu(), foreign_v)
+
+
 def _filled_cache(tq, dev, B, n_kv, S, fused=True, **kw):
     torch.manual_seed(3)
     c = tq.TurboQuantKVCache(bits=3, fused=fused, **kw)

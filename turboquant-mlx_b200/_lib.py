@@ -67,6 +67,7 @@ class FlashParams(ctypes.Structure):
         ("workspace_exclusive", c_int32), ("gather_ranks", c_int32),
         ("gather_m", c_void_p), ("gather_l", c_void_p), ("gather_acc", c_void_p),
         ("gather_part_stride", c_int64), ("gather_flags", c_void_p),
+        ("q_tokens", c_int32), ("q_tokens_reserved", c_int32), ("q_token_stride", c_int64), ("out_token_stride", c_int64),
     ]
 
 

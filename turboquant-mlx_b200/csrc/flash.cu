@@ -26,6 +26,15 @@ static int validate(const tq_flash_params* p) {
              "n_q_heads (%d) must equal n_kv_heads (%d) * n_rep", p->n_q_heads, p->n_kv_heads);
   TQ_REQUIRE(p->seq_len > 0, TQ_ERR_BAD_ARG, "seq_len must be positive, got %lld",
              (long long)p->seq_len);
+  TQ_REQUIRE(p->q_tokens >= 0 && p->q_tokens <= 8, TQ_ERR_BAD_ARG, "q_tokens must be 0..8, got %d", p->q_tokens);
+  if (p->q_tokens > 1) {
+    TQ_REQUIRE(p->seq_len >= p->q_tokens, TQ_ERR_BAD_ARG, "seq_len (%lld) counts the q_tokens (%d) new positions",
+               (long long)p->seq_len, p->q_tokens);
+    TQ_REQUIRE(p->out_mode == 0 && p->n_peers == 0, TQ_ERR_UNSUPPORTED, "several query tokens need out_mode 0");
+    TQ_REQUIRE(p->new_k == nullptr && p->new_v == nullptr, TQ_ERR_UNSUPPORTED,
+               "the in-launch append takes one token; store a multi-token step's rows before the call");
+    TQ_REQUIRE(p->mask == nullptr, TQ_ERR_UNSUPPORTED, "several query tokens are causal; no additive mask");
+  }
   TQ_REQUIRE(p->n_peers >= 0 && p->n_peers <= 8, TQ_ERR_BAD_ARG, "n_peers must be 0..8, got %d", p->n_peers);
   TQ_REQUIRE(p->n_peers == 0 || p->out_mode != 0, TQ_ERR_BAD_ARG, "peer targets need out_mode 1 or 2");
   for (int i = 0; i < p->n_peers; ++i)
@@ -110,6 +119,10 @@ static int fill_args(const tq_flash_params* p, FlashArgs* a) {
   a->q_prerotated = p->q_prerotated;
   a->q_batch_stride = p->q_batch_stride;
   a->q_head_stride = p->q_head_stride;
+  a->q_tokens = p->q_tokens > 1 ? p->q_tokens : 1;
+  a->rows = a->n_rep * a->q_tokens;
+  a->q_token_stride = p->q_token_stride;
+  a->out_token_stride = p->out_token_stride;
   a->k_format = p->k_format;
   a->k_bits = (p->k_format == TQ_KV_POLAR || p->k_format == TQ_KV_AFFINE) ? p->k_bits : 4;
   a->k_dtype = p->k_dtype;
@@ -239,7 +252,7 @@ static int64_t header_bytes(const tq_flash_params* p, const Plan&) {
 }
 static int64_t partial_bytes(const tq_flash_params* p, const Plan& plan) {
   if (!plan.mma && p->out_mode == 1 && plan.splits == 1) return 0;
-  const int64_t rows = (int64_t)p->batch * p->n_q_heads;
+  const int64_t rows = (int64_t)p->batch * p->n_q_heads * (p->q_tokens > 1 ? p->q_tokens : 1);
   const int64_t parts = plan.splits;
   return parts * rows * (p->dim + 2) * (int64_t)sizeof(float);
 }
@@ -286,7 +299,7 @@ extern "C" int tq_flash_decode(const tq_flash_params* p) {
   TQ_REQUIRE(need == 0 || (p->workspace && p->workspace_bytes >= need), TQ_ERR_WORKSPACE,
              "workspace of %lld bytes required, got %lld", (long long)need,
              (long long)p->workspace_bytes);
-  const int64_t rows = (int64_t)p->batch * p->n_q_heads;
+  const int64_t rows = (int64_t)p->batch * p->n_q_heads * a.q_tokens;
   const bool direct = partial_bytes(p, plan) == 0;
   if (direct) {
     a.part_m = p->part_m;
@@ -331,6 +344,8 @@ extern "C" int tq_flash_decode(const tq_flash_params* p) {
     return launch_flash_mma(a, plan.splits, mo, st);
   }
   TQ_REQUIRE(p->n_peers == 0, TQ_ERR_UNSUPPORTED, "peer targets need the tensor-core decode path");
+  TQ_REQUIRE(a.q_tokens == 1, TQ_ERR_UNSUPPORTED,
+             "several query tokens need the tensor-core decode path (dim 128, n_rep * q_tokens <= 8, no mask)");
   TQ_REQUIRE(p->seq_lens_dev == nullptr, TQ_ERR_UNSUPPORTED,
              "device-side sequence lengths (seq_lens_dev) need the tensor-core decode path");
   TQ_REQUIRE(!(p->sparse_v_threshold > 0.f) && p->active_positions == nullptr, TQ_ERR_UNSUPPORTED,

@@ -13,6 +13,10 @@ struct FlashArgs {
   const void* q;
   int q_dtype, q_prerotated;
   int64_t q_batch_stride, q_head_stride;
+  // several query tokens per sequence (the last q_tokens positions, causal): token t of head h is MMA
+  // row t * n_rep + (h mod n_rep) of its kv head's group; rows = n_rep * q_tokens <= 8
+  int q_tokens, rows;
+  int64_t q_token_stride, out_token_stride;
 
   int k_format, k_bits, k_dtype, k_group;
   const void* k_data;

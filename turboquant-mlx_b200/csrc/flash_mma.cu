@@ -23,7 +23,7 @@ static bool overlapping(const FlashArgs& a) { return a.kv_stable && a.q_stable; 
 static int g_last_geometry = 0;   // warps of the geometry launched last (diagnostic)
 
 bool flash_mma_supported(const FlashArgs& a) {
-  if (a.dim != 128 || a.n_rep > 8 || a.mask != nullptr) return false;
+  if (a.dim != 128 || a.rows > 8 || a.mask != nullptr) return false;
   if (a.v_format == TQ_KV_POLAR) {
     if (a.v_bits != 3 && a.v_bits != 4) return false;
     if (!aligned16(a.v_data) || a.v_batch_stride % 4 || a.v_head_stride % 4) return false;

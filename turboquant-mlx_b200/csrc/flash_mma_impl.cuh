@@ -308,7 +308,7 @@ __device__ __forceinline__ float load_any(const void* base, int dtype, int64_t i
 // final output (butterfly * signs / dim / l) or the merged partial state, which may also
 // go to peer GPUs by plain stores.
 template <bool VAFF>
-__device__ __forceinline__ void write_row(const FlashArgs& a, const MmaTables& tb, int b, int head, int64_t row,
+__device__ __forceinline__ void write_row(const FlashArgs& a, const MmaTables& tb, int b, int h0, int r, int64_t row,
                                           float4 acc4, float m_star, float l_star, int lane, bool final_out) {
   if (!final_out) {
     reinterpret_cast<float4*>(tb.oacc + row * kDim)[lane] = acc4;
@@ -331,7 +331,8 @@ __device__ __forceinline__ void write_row(const FlashArgs& a, const MmaTables& t
   float v[4] = {acc4.x, acc4.y, acc4.z, acc4.w};
   if (!VAFF) warp_butterfly<4>(v, lane);      // packed values are summed in the rotated domain
   const float inv = l_star > 0.f ? (VAFF ? 1.0f : 1.0f / kDim) / l_star : 0.f;
-  const int64_t ooff = b * tb.out_batch_stride + (int64_t)head * tb.out_head_stride + lane * 4;
+  const int tok = r / a.n_rep, head = h0 + r - tok * a.n_rep;   // row r of the group = (query token, head)
+  const int64_t ooff = b * tb.out_batch_stride + (int64_t)head * tb.out_head_stride + tok * a.out_token_stride + lane * 4;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const float res = v[j] * (VAFF ? 1.0f : sign_at(a.v_signs, lane * 4 + j)) * inv;
@@ -418,7 +419,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   const int q_esize = a.q_dtype == TQ_F32 ? 4 : 2;
   const bool q_direct = ((KF != KF_POLAR3 && KF != KF_POLAR4) || a.q_prerotated) &&
                         reinterpret_cast<uintptr_t>(a.q) % (2 * q_esize) == 0 &&
-                        a.q_batch_stride % 2 == 0 && a.q_head_stride % 2 == 0;
+                        a.q_batch_stride % 2 == 0 && a.q_head_stride % 2 == 0 && a.q_token_stride % 2 == 0;
   if (warp < kConsumerWarps && q_direct) {
     // staged in fragment order [k-step][lane][4 registers]: every element pair is fetched once per
     // CTA, split into f16 high part + residual, and read back with one conflict-free 16-byte load
@@ -427,9 +428,10 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       const int ln = task & 31, up = (task >> 5) & 1, ks = task >> 6;
       const int gg = ln >> 2, tt = ln & 3;
       float2 v = make_float2(0.f, 0.f);
-      if (gg < a.n_rep) {
-        const int64_t off = b * a.q_batch_stride + (int64_t)(h0 + gg) * a.q_head_stride +
-                            kslot_element<KF>(ks, 2 * tt + 8 * up);
+      if (gg < a.rows) {
+        const int tok = gg / a.n_rep;
+        const int64_t off = b * a.q_batch_stride + (int64_t)(h0 + gg - tok * a.n_rep) * a.q_head_stride +
+                            tok * a.q_token_stride + kslot_element<KF>(ks, 2 * tt + 8 * up);
         if (a.q_dtype == TQ_F32) v = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(a.q) + off);
         else if (a.q_dtype == TQ_F16)
           v = __half22float2(*reinterpret_cast<const __half2*>(reinterpret_cast<const __half*>(a.q) + off));
@@ -451,8 +453,9 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         float x = 0.f;
-        if (r < a.n_rep)
-          x = load_any(a.q, a.q_dtype, b * a.q_batch_stride + (int64_t)(h0 + r) * a.q_head_stride + lane * 4 + j);
+        if (r < a.rows)
+          x = load_any(a.q, a.q_dtype, b * a.q_batch_stride + (int64_t)(h0 + r % a.n_rep) * a.q_head_stride +
+                                           (r / a.n_rep) * a.q_token_stride + lane * 4 + j);
         v[j] = x;
       }
       if ((KF == KF_POLAR3 || KF == KF_POLAR4) && !a.q_prerotated) {
@@ -693,6 +696,14 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
     }
     const uint32_t st = sbase + L::stage0 + s * L::stage_bytes;
     const int nvp = (int)min((int64_t)kTile, pe - (pb + (int64_t)i * kTile));
+    // several query tokens: token t (row g's) does not see the sequence's last q_tokens - 1 - t positions
+    // (recomputed per tile so that the one-token path carries nothing extra through the loop)
+    int nvp_row = nvp;
+    if (a.q_tokens > 1 && g < a.rows) {
+      const int64_t sq = a.seq_lens != nullptr ? max((int64_t)0, min((int64_t)a.seq_lens[blockIdx.z], a.seq_len)) : a.seq_len;
+      const int64_t tile0 = (int64_t)blockIdx.x * a.chunk + (int64_t)i * kTile;
+      nvp_row = min(nvp, (int)min((int64_t)(2 * kTile), sq - tile0) - (a.q_tokens - 1 - g / a.n_rep));
+    }
 
     // ---------------- scores ----------------
     float sc[2][4];
@@ -798,7 +809,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         const int pos = pw + 8 * ng + 2 * t + c;
         float v = (sc[ng][c] + sc[ng][c + 2]) * tb.k_post;
         if (KF == KF_POLAR3 || KF == KF_POLAR4) v *= lds_f32(st + L::kn_off + pos * 4);
-        const bool valid = pos < nvp;
+        const bool valid = pos < nvp_row;
         s2[ng][c] = valid ? v : -INFINITY;
         if (VAFF) {
           vscw[ng][c] = valid ? lds32(st + L::vn_off + pos * 4) : 0u;   // stale words past the end must not reach the MMA
@@ -863,11 +874,11 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       // the CTA so far is a second lower bound (shared through hint_s)
       float sq = fmaxf(smax, __shfl_xor_sync(0xffffffffu, smax, 1));
       sq = fmaxf(sq, __shfl_xor_sync(0xffffffffu, sq, 2));
-      if (t == 0 && g < a.n_rep && sq > -INFINITY) atomicMax(&hint_s[g], ordered_int(sq));
+      if (t == 0 && g < a.rows && sq > -INFINITY) atomicMax(&hint_s[g], ordered_int(sq));
       __syncwarp();
       const float hint = from_ordered_int(*reinterpret_cast<volatile int*>(&hint_s[g]));
       const bool below = smax == -INFINITY || ex2(smax - m_use) < a.sparse_thr * lq || ex2(smax - hint) < a.sparse_thr;
-      skip_values = __all_sync(0xffffffffu, g >= a.n_rep || below);
+      skip_values = __all_sync(0xffffffffu, g >= a.rows || below);
     }
     if (a.active_positions != nullptr && !skip_values && lane == 0 && pw < nvp)
       atomicAdd(a.active_positions + b * a.n_kv_heads + kvh, min(16, nvp - pw));
@@ -968,8 +979,8 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   // of consecutive launches (hand-over, merge) overlap like their main loops do.
   const bool independent = a.kv_stable && a.q_stable && a.ws_exclusive;
   if (a.q_stable && !independent) grid_dependency_wait();
-  const int64_t n_rows = (int64_t)a.batch * a.n_q_heads;
-  const int64_t row0 = (int64_t)b * a.n_q_heads + h0;
+  const int64_t n_rows = (int64_t)a.batch * a.n_kv_heads * a.rows;
+  const int64_t row0 = ((int64_t)b * a.n_kv_heads + kvh) * a.rows;
   {
     constexpr int R = L::xch_rows;
     // rescale factors of the source warps for this thread's two heads (2t, 2t+1)
@@ -1007,7 +1018,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         for (int sw = 0; sw < kConsumerWarps; ++sw)
           v += xch[(sw * R + k) * 32 + lane] * ((c & 1) ? f1[sw] : f0[sw]);
         const int head = 2 * t + (c & 1);
-        if (head < a.n_rep)
+        if (head < a.rows)
           acc0[head * kDim + 16 * g + 2 * j + (c >> 1)] = v * tb.v_post + (VAFF ? ((c & 1) ? bias1 : bias0) : 0.f);
       }
     }
@@ -1024,7 +1035,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       }
       lg += __shfl_xor_sync(0xffffffffu, lg, 1);
       lg += __shfl_xor_sync(0xffffffffu, lg, 2);
-      if (t == 0 && g < a.n_rep) {
+      if (t == 0 && g < a.rows) {
         a.part_m[(int64_t)split * n_rows + row0 + g] = mg == -INFINITY ? -INFINITY : mg * 0.6931471805599453f;
         a.part_l[(int64_t)split * n_rows + row0 + g] = lg;
       }
@@ -1063,7 +1074,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   // parts: m / l at pm / pl + i * ml_stride + row, acc rows at pacc + i * acc_stride + row * 128
   auto merge_pass = [&](const float* pm, const float* pl, const float* pacc, int64_t ml_stride, int64_t acc_stride,
                         int cnt, bool final_out, bool poisoned) {
-    for (int r = warp; r < a.n_rep; r += kConsumerWarps) {
+    for (int r = warp; r < a.rows; r += kConsumerWarps) {
       // lane i (+32, +64) holds part i: m* = max over parts with l > 0, weight = e^(m - m*)
       float mi[3], li[3];
 #pragma unroll
@@ -1095,7 +1106,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
     consumer_barrier();
     const int64_t pstride = acc_stride / 4;               // float4s between consecutive parts
     // warp w owns rows w, w + kConsumerWarps, ...; a lane owns elements 4*lane .. 4*lane+3 of its row
-    for (int r = warp; r < a.n_rep; r += kConsumerWarps) {
+    for (int r = warp; r < a.rows; r += kConsumerWarps) {
       float4 acc4 = zero4;
       const float4* src = reinterpret_cast<const float4*>(pacc + (row0 + r) * kDim) + lane;
       const float* wr = wgt + r * kMaxParts;
@@ -1110,7 +1121,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
           acc4.x += v[j].x * wi; acc4.y += v[j].y * wi; acc4.z += v[j].z * wi; acc4.w += v[j].w * wi;
         }
       }
-      write_row<VAFF>(a, tb, b, h0 + r, row0 + r, acc4, mst[r], lst[r], lane, final_out);
+      write_row<VAFF>(a, tb, b, h0, r, row0 + r, acc4, mst[r], lst[r], lane, final_out);
     }
   };
   merge_pass(a.part_m, a.part_l, a.part_acc, n_rows, n_rows * kDim, count, tb.out_mode == 0, false);

@@ -60,13 +60,32 @@ def cache_kv_descriptors(cache):
     return k, v
 
 
+def short_step_supported(queries, n_kv_heads: int, mask) -> bool:
+    """A multi-token step the decode kernel takes as it is: the T new tokens (already stored) attend
+    causally, and their n_rep * T (token, head) rows fit the eight rows of the kernel's MMA tile."""
+    B, n_q_heads, T, dim = queries.shape
+    n_rep = n_q_heads // max(1, n_kv_heads)
+    return (T > 1 and isinstance(mask, str) and mask == "causal" and dim == 128 and n_rep * T <= 8
+            and queries.dtype in (torch.float16, torch.bfloat16, torch.float32))
+
+
 def turboquant_attention(queries, cache, attn_scale: float, mask=None, v_buffer=None,
                          sparse_v_threshold: float | None = None) -> torch.Tensor:
-    """queries (B, n_heads, 1, dim) -> (B, n_heads, 1, dim) in queries.dtype."""
+    """queries (B, n_heads, 1, dim) -> (B, n_heads, 1, dim) in queries.dtype; also a short causal
+    multi-token step (B, n_heads, T, dim) with n_rep * T <= 8 (`short_step_supported`), which the
+    reference leaves to dense attention (patch.py:19-21)."""
     B, n_q_heads, S_q, dim = queries.shape
     n_kv_heads = cache.k_packed.shape[1]
     n_rep = n_q_heads // n_kv_heads
     thr = sparse_v_threshold if (sparse_v_threshold is not None and sparse_v_threshold >= 0.0) else 0.0
+    if S_q > 1:
+        if v_buffer is not None or not short_step_supported(queries, n_kv_heads, mask):
+            raise ValueError("a multi-token step needs mask='causal', dim 128, n_rep * tokens <= 8 and no v_buffer")
+        if hasattr(cache, "flush_pending"):
+            cache.flush_pending()
+        k, v = cache_kv_descriptors(cache)
+        return flash_decode(queries, k=k, v=v, attn_scale=attn_scale, out_dtype=queries.dtype,
+                            sparse_v_threshold=thr)
     has_mask = mask is not None and not isinstance(mask, str)
     pending = getattr(cache, "_pending", None) is not None
     fused_ok = v_buffer is None and (thr == 0.0 or not (has_mask or n_rep > 8 or dim != 128))

@@ -257,9 +257,13 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
                  sparse_v_threshold: float = 0.0, active_out: torch.Tensor | None = None,
                  seq_lens: torch.Tensor | None = None, workspace: torch.Tensor | None = None,
                  workspace_owner=None, gather=None, _prepare_only: bool = False):
-    """Split-K flash decoding for one query token per sequence.
+    """Split-K flash decoding for one query token per sequence (or a few, see below).
 
-    q: (B, n_q, dim).  k / v: dicts describing the stored keys / values:
+    q: (B, n_q, dim), or (B, n_q, T, dim) with n_rep * T <= 8 for a short multi-token step: the T
+    queries are the last T positions of the sequence (their K / V rows are already stored, S counts
+    them) and attend causally; the result is (B, n_q, T, dim).  The reference sends such steps to
+    dense attention over the dequantized cache (patch.py:19-21); here they read the packed rows once.
+    k / v: dicts describing the stored keys / values:
       polar : dict(format="polar", packed (B, n_kv, S, pdim) uint32, norms (B, n_kv, S),
                    centroids, signs, bits)
       dense : dict(format="dense", data (B, n_kv, S, dim) fp16/bf16/fp32)       [keys only]
@@ -311,14 +315,24 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
     sequence-sharded decode step in one launch per layer.
     """
     _lib.require_cuda(q)
-    B, n_q, dim = q.shape
+    q_tokens = 1
+    if q.ndim == 4:                       # (B, n_q, T, dim): the last T positions of each sequence, causal
+        q_tokens = q.shape[2]
+        if q_tokens == 1:
+            q = q[:, :, 0]
+        elif partials or new_k is not None or mask is not None:
+            raise ValueError("several query tokens: no partials, no in-launch append, no mask (causal is implied)")
     if q.stride(-1) != 1:
         q = q.contiguous()
+    B, n_q, dim = q.shape[0], q.shape[1], q.shape[-1]
     P = _lib.FlashParams()
     P.struct_bytes = ctypes.sizeof(_lib.FlashParams)
     P.batch, P.n_q_heads, P.dim = B, n_q, dim
     P.q, P.q_dtype, P.q_prerotated = q.data_ptr(), _lib.dtype_code(q.dtype), int(q_prerotated)
     P.q_batch_stride, P.q_head_stride = q.stride(0), q.stride(1)
+    if q_tokens > 1:
+        P.q_tokens, P.q_token_stride = q_tokens, q.stride(2)
+    out_shape = (B, n_q, dim) if q_tokens == 1 else (B, n_q, q_tokens, dim)
     keep = []  # keeps converted tensors / host arrays alive until the launch returns
 
     def rows(t):
@@ -474,11 +488,13 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
     else:
         P.out_mode = 0
         if out is None:
-            out = torch.empty((B, n_q, dim), dtype=out_dtype or q.dtype, device=dev)
-        elif tuple(out.shape) != (B, n_q, dim) or out.stride(-1) != 1:
-            raise ValueError(f"out must be ({B}, {n_q}, {dim}) with a contiguous last dimension")
+            out = torch.empty(out_shape, dtype=out_dtype or q.dtype, device=dev)
+        elif tuple(out.shape) != out_shape or out.stride(-1) != 1:
+            raise ValueError(f"out must be {out_shape} with a contiguous last dimension")
         P.out, P.out_dtype = out.data_ptr(), _lib.dtype_code(out.dtype)
         P.out_batch_stride, P.out_head_stride = out.stride(0), out.stride(1)
+        if q_tokens > 1:
+            P.out_token_stride = out.stride(2)
     P.stream = torch.cuda.current_stream(dev).cuda_stream
     L = _lib.lib()
     need = L.tq_flash_decode_workspace_bytes(ctypes.byref(P))

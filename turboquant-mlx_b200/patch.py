@@ -30,7 +30,8 @@ def _patched_sdpa(queries, keys, values, cache, scale, mask, sinks=None):
 
     is_decode = queries.shape[2] == 1
     if isinstance(cache, TurboQuantKVCache) and cache.offset > 0 and cache.fused and not cache.v_only:
-        if is_decode:
+        from .fused_attention import short_step_supported
+        if is_decode or short_step_supported(queries, cache.k_packed.shape[1], mask):
             from .fused_attention import turboquant_attention
             return turboquant_attention(queries, cache, scale, mask,
                                         sparse_v_threshold=cache.sparse_v_threshold)
@@ -39,7 +40,8 @@ def _patched_sdpa(queries, keys, values, cache, scale, mask, sinks=None):
         k, v = cache.dequantized(queries.dtype)
         return _prefill_sdpa(queries, k, v, scale, mask)
     if isinstance(cache, VOnlyTurboQuantCache) and cache.fused and cache.offset > 0:
-        if is_decode:
+        from .fused_attention import short_step_supported
+        if is_decode or short_step_supported(queries, cache._v_tq.v_packed.shape[1], mask):
             from .v_only_cache import v_only_attention
             return v_only_attention(queries, cache, scale, mask)
         _, v = cache._v_tq.dequantized(queries.dtype)

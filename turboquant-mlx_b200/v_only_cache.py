@@ -210,8 +210,19 @@ def v_only_attention(queries, cache: VOnlyTurboQuantCache, attn_scale: float, ma
                      kv_stable: bool = False, out=None, q_stable: bool | None = None):
     """Decode attention for a fused V-only cache: queries (B, n_q, 1, dim),
     dense K and packed V read once per KV head -> (B, n_q, 1, dim).  A deferred
-    one-token append of the cache is carried out by the same launch."""
+    one-token append of the cache is carried out by the same launch.  A short multi-token step
+    (queries (B, n_q, T, dim), `short_step_supported`) attends causally over the same packed rows."""
     tq = cache._v_tq
+    if queries.shape[2] > 1:
+        from .fused_attention import short_step_supported
+        if not short_step_supported(queries, tq.v_packed.shape[1], mask):
+            raise ValueError("a multi-token step needs mask='causal', dim 128 and n_rep * tokens <= 8")
+        cache.flush_pending()
+        total = cache.offset
+        k = dict(format="dense", data=cache._k_cache.keys[:, :, :total, :])
+        v = dict(format="polar", packed=tq.v_packed[:, :, :total, :], norms=tq.v_norms[:, :, :total],
+                 centroids=tq._v_q.centroids, signs=tq._v_q.signs, bits=tq._v_q.bits)
+        return flash_decode(queries, k=k, v=v, attn_scale=attn_scale, out_dtype=queries.dtype, out=out)
     if q_stable is None:
         q_stable = cache.inputs_stable
     m3 = None
