@@ -680,7 +680,7 @@ def workload_c4(args):
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     tq = entry.load_package()
-    from turboquant_mlx_b200.qwen2 import Qwen2Config, Qwen2Model
+    from turboquant_mlx_b200.qwen2 import Qwen2Config, Qwen2Model, StaticDecoder
     cfg = Qwen2Config()
     if args.layers != 28:
         cfg.n_layers = args.layers
@@ -697,24 +697,37 @@ def workload_c4(args):
         e1.record()
         caches = [tq.MixedQuantKVCache.from_kvcache(c, k_bits=8, v_bits=4, group_size=64) for c in caches]
         tok = logits[:, -1].argmax(-1, keepdim=True)
-        e2.record()
-        toks = [tok]
+        ec = torch.cuda.Event(enable_timing=True)
+        ec.record()
+        # decode: one CUDA-graph replay per token (position and length live on the device); the first
+        # two tokens (one eager step that warms the host-side caches, the capture, one replay) are not timed
+        dec = StaticDecoder(model, caches, S + n_new + 8)
+        warm = dec.generate(tok, 2) if not args.eager else None
+        toks = [tok] + ([warm] if warm is not None else [])
+        n_timed = n_new - 1 - (2 if warm is not None else 0)
+        torch.cuda.synchronize()
         with ClockSampler(0) as clk:
-            for _ in range(n_new - 1):
-                tok = model.forward(tok, caches)[:, -1].argmax(-1, keepdim=True)
-                toks.append(tok)
+            e2.record()
+            rest = dec.generate(toks[-1][:, -1:], n_timed, use_graph=not args.eager)
             e3.record()
             torch.cuda.synchronize()
+        toks.append(rest)
+        decode_status = tq.kernels.flash_status(dev, cfg.n_kv_heads)
         prefill_status = tq.kernels.prefill_status(dev)
     finally:
         tq.remove_patch()
-    t_prefill, t_convert, t_decode = e0.elapsed_time(e1), e1.elapsed_time(e2), e2.elapsed_time(e3)
+    t_prefill, t_convert, t_decode = e0.elapsed_time(e1), e1.elapsed_time(ec), e2.elapsed_time(e3)
     kv_bytes_per_token = cfg.n_layers * cfg.n_kv_heads * (S + n_new // 2) * (136 + 72)
+    weight_bytes = 2 * (model.n_params() - model.emb.numel())      # read once per token (bf16)
+    peak, _ = measured_peaks()
     print(json.dumps({"metric": "K8/V4 end-to-end decode tok/s", "unit": "tok/s", "n_gpus": 1,
-                      "value": (n_new - 1) / (t_decode / 1e3), "decode_ms_per_token": t_decode / (n_new - 1),
+                      "value": n_timed / (t_decode / 1e3), "decode_ms_per_token": t_decode / n_timed,
+                      "decode_mode": "eager" if args.eager else "one CUDA-graph replay per token",
+                      "decode_kernel_status": decode_status,
+                      "hbm_floor_ms_per_token": (weight_bytes + kv_bytes_per_token) / peak / 1e6,
                       "prefill_ms": t_prefill, "prefill_tok_per_s": S / (t_prefill / 1e3), "convert_ms": t_convert,
                       "prefill_kernel_status": prefill_status, "tokens": [int(t) for t in torch.cat(toks, 1)[0, :8]],
-                      "kv_GBs_during_decode": kv_bytes_per_token / (t_decode / (n_new - 1)) / 1e6,
+                      "kv_GBs_during_decode": kv_bytes_per_token / (t_decode / n_timed) / 1e6,
                       "cache_bytes": sum(c.nbytes for c in caches), "params": model.n_params(), "dtype": "bf16",
                       "data": "synthetic", "clocks": clk.summary(),
                       "config": {"workload": f"C4: prompt {S}, {n_new} greedy tokens, K8/V4 group 64", **cfg.describe()}}))
@@ -813,6 +826,7 @@ def main():
                     help="plain launches of the flash-decode kernel only (no graph, no e2e): profiler case")
     ap.add_argument("--ctx", type=int, default=0, help="c4p: prompt length (default 32768)")
     ap.add_argument("--no-c5", action="store_true", help="N > 1: skip the secondary config-5 record")
+    ap.add_argument("--eager", action="store_true", help="c4: decode steps launched eagerly instead of graph replay")
     ap.add_argument("--vectors", type=int, default=0, help="c1: run this many vectors only (default: 16384 and 2^21)")
     ap.add_argument("--splits", type=int, default=0, help="c3: force the split count of the decode kernel (0 = planner)")
     ap.add_argument("--workload", default="c2", choices=["c2", "c1", "c3", "c5", "c4p", "c4"],

@@ -352,6 +352,15 @@ int tq_affine_quantize(const void* x, int x_dtype, int64_t n_rows, int dim, int 
 int tq_affine_quantize_rows(const void* x, int x_dtype, int64_t n_rows, int dim, int group, int bits,
                             int64_t x_row_stride, uint8_t* codes, int64_t codes_row_stride,
                             void* scales_f16, void* biases_f16, int64_t sb_row_stride, void* stream);
+/* The same with the destination position on the device: the rows go to codes + *position_dev *
+ * codes_pos_stride (bytes) and scales / biases + *position_dev * sb_pos_stride (halfs), read when the
+ * kernel runs, so that a decode step captured in a CUDA graph appends at a position that advances
+ * from replay to replay.  position_dev NULL: as tq_affine_quantize_rows. */
+int tq_affine_quantize_rows_at(const void* x, int x_dtype, int64_t n_rows, int dim, int group, int bits,
+                               int64_t x_row_stride, uint8_t* codes, int64_t codes_row_stride,
+                               void* scales_f16, void* biases_f16, int64_t sb_row_stride,
+                               const int32_t* position_dev, int64_t codes_pos_stride, int64_t sb_pos_stride,
+                               void* stream);
 int tq_affine_dequantize(const uint8_t* codes, const void* scales_f16, const void* biases_f16,
                          int64_t n_rows, int dim, int group, int bits, void* out, int out_dtype,
                          void* stream);

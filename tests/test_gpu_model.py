@@ -122,3 +122,51 @@ def test_turboquant_caches_drive_the_same_model(tq, dev):
         assert cos_v > 0.85 and cos_f > 0.6      # 3-bit values (and 4-bit keys) on random weights: the point is the path, not quality
     finally:
         tq.remove_patch()
+
+
+def test_static_decode_graph_replay_matches_eager_steps(tq, dev):
+    """The K8 / V4 decode step with position and length on the device: replaying one captured CUDA
+    graph per token must produce exactly the tokens and cache rows of the same steps run eagerly, and
+    its first step must agree with the ordinary `forward` path (host-side offset) on the logits."""
+    from turboquant_mlx_b200.qwen2 import Qwen2Config, Qwen2Model, StaticDecoder
+    cfg = Qwen2Config(n_layers=3, hidden=512, n_q_heads=8, n_kv_heads=2, head_dim=128, ffn=1024, vocab=1000,
+                      init_std=0.05)
+    model = Qwen2Model(cfg, dev, torch.bfloat16, seed=4)
+    prompt = torch.randint(0, cfg.vocab, (1, 300), generator=torch.Generator().manual_seed(5)).to(dev)
+    n_new = 20
+    tq.apply_patch()
+    try:
+        def prefilled():
+            caches = [tq.KVCache() for _ in range(cfg.n_layers)]
+            logits = model.forward(prompt, caches)
+            return logits[:, -1].argmax(-1, keepdim=True), [tq.MixedQuantKVCache.from_kvcache(c) for c in caches]
+
+        first, c_eager = prefilled()
+        _, c_graph = prefilled()
+        _, c_fwd = prefilled()
+        # the fused-projection step against the ordinary forward pass, same token, same cache
+        lg_fwd = model.forward(first, c_fwd)[:, -1].float()
+        dec_e = StaticDecoder(model, c_eager, 300 + n_new + 8)
+        lg_step = model.decode_step(first, c_eager, dec_e.counters[:1]).float()
+        cos = F.cosine_similarity(lg_step, lg_fwd, dim=-1).min().item()
+        assert cos > 0.999, cos
+        # that call appended a row without advancing the counter: the next step overwrites it, as intended
+        tok_e = dec_e.generate(first, n_new, use_graph=False)
+        dec_g = StaticDecoder(model, c_graph, 300 + n_new + 8)
+        tok_g = dec_g.generate(first, n_new, use_graph=True)
+        assert dec_g.graph is not None
+        assert torch.equal(tok_e, tok_g)
+        assert c_graph[0].offset == 300 + n_new == c_eager[0].offset
+        for a, b in zip(c_eager, c_graph):
+            t = a.offset
+            assert torch.equal(a.k_codes[:, :, :t], b.k_codes[:, :, :t])
+            assert torch.equal(a.v_codes[:, :, :t], b.v_codes[:, :, :t])
+            assert torch.equal(a.k_scales[:, :, :t], b.k_scales[:, :, :t])
+        assert tq.kernels.flash_status(dev, cfg.n_kv_heads) == 0
+        # a second call replays the same graph from the advanced position
+        more = dec_g.generate(tok_g[:, -1:], 4)
+        assert more.shape == (1, 4) and c_graph[0].offset == 300 + n_new + 4
+        dec_g.close()
+        assert c_graph[0]._static is None
+    finally:
+        tq.remove_patch()

@@ -101,7 +101,11 @@ def test_qwen2_module_cache_consistency():
     step = model.forward(toks[:, 8:], caches)
     assert caches[0].offset == 9
     assert torch.allclose(step[:, 0], full[:, -1], atol=1e-4, rtol=1e-4)
-    assert model.n_params() == sum(t.numel() for lw in model.layers for t in lw.values()) + 2 * cfg.vocab * cfg.hidden
+    per_layer = 2 * cfg.hidden * cfg.n_q_heads * cfg.head_dim + 2 * cfg.hidden * cfg.n_kv_heads * cfg.head_dim + \
+        3 * cfg.hidden * cfg.ffn
+    assert model.n_params() == cfg.n_layers * per_layer + 2 * cfg.vocab * cfg.hidden
+    lw = model.layers[0]      # the separate projection names are views of the fused matrices
+    assert lw["wq"].data_ptr() == lw["wqkv"].data_ptr() and lw["w3"].shape == (cfg.hidden, cfg.ffn)
 
 
 def test_host_float_cache_follows_the_tensor_object(tq):

@@ -109,6 +109,8 @@ _SIGNATURES = {
                                    c_void_p, c_void_p, c_void_p]),
     "tq_affine_quantize_rows": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int64, c_void_p, c_int64,
                                         c_void_p, c_void_p, c_int64, c_void_p]),
+    "tq_affine_quantize_rows_at": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int64, c_void_p, c_int64,
+                                           c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p]),
     "tq_affine_dequantize": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,
                                      c_void_p, c_int, c_void_p]),
     "tq_merge_partials_after_peers": (c_int, [c_void_p, c_int, c_uint32, c_void_p, c_int, c_void_p, c_int64, c_void_p,

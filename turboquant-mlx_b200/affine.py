@@ -33,19 +33,26 @@ def affine_quantize(x: torch.Tensor, group: int = 64, bits: int = 8):
 
 
 def affine_quantize_rows_into(x: torch.Tensor, codes: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor,
-                              group: int, bits: int) -> bool:
+                              group: int, bits: int, position: torch.Tensor | None = None,
+                              pos_strides: tuple[int, int] = (0, 0)) -> bool:
     """Quantize the rows of x (n, dim) straight into codes / scales / biases (n, width), views whose
     rows may be far apart (one decode step's rows inside a pre-sized cache).  Returns False, writing
-    nothing, when a view does not have unit-stride rows at one uniform row distance."""
+    nothing, when a view does not have unit-stride rows at one uniform row distance.
+    `position`: an int32 device tensor whose first element, read when the kernel runs, moves the
+    destination by `pos_strides` = (bytes of codes, halfs of scales / biases) per unit: the views
+    then name position 0, and a CUDA graph of the step appends where the device counter points."""
     for t in (x, codes, scales, biases):
         if t.ndim != 2 or t.stride(1) != 1:
             return False
     if scales.stride(0) != biases.stride(0) or not x.is_cuda:
         return False
+    if position is not None and (position.dtype != torch.int32 or not position.is_cuda):
+        raise ValueError("position must be an int32 CUDA tensor")
     n, dim = x.shape
-    _lib.check(_lib.lib().tq_affine_quantize_rows(
+    _lib.check(_lib.lib().tq_affine_quantize_rows_at(
         _lib.ptr(x), _lib.dtype_code(x.dtype), n, dim, group, bits, x.stride(0), _lib.ptr(codes), codes.stride(0),
-        _lib.ptr(scales), _lib.ptr(biases), scales.stride(0), _lib.stream_ptr(x.device)))
+        _lib.ptr(scales), _lib.ptr(biases), scales.stride(0), _lib.ptr(position), int(pos_strides[0]),
+        int(pos_strides[1]), _lib.stream_ptr(x.device)))
     return True
 
 

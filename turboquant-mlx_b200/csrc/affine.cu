@@ -10,8 +10,15 @@ __global__ void __launch_bounds__(256)
 affine_quantize_kernel(const T* __restrict__ x, int64_t n_groups, int bits,
                        uint8_t* __restrict__ codes, __half* __restrict__ scales,
                        __half* __restrict__ biases, int gpr /* groups per row */, int64_t x_row_stride,
-                       int64_t codes_row_stride /* bytes */, int64_t sb_row_stride) {
+                       int64_t codes_row_stride /* bytes */, int64_t sb_row_stride,
+                       const int* __restrict__ pos_dev, int64_t codes_pos_stride, int64_t sb_pos_stride) {
   constexpr int GROUP = EPG * 32;
+  if (pos_dev != nullptr) {   // destination rows start at a position that lives on the device
+    const int64_t pos = *pos_dev;
+    codes += pos * codes_pos_stride;
+    scales += pos * sb_pos_stride;
+    biases += pos * sb_pos_stride;
+  }
   const int lane = threadIdx.x & 31;
   const int64_t warp_global = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   const int64_t warp_stride = (int64_t)gridDim.x * 8;
@@ -78,15 +85,16 @@ __global__ void affine_dequantize_kernel(const uint8_t* __restrict__ codes,
 
 template <typename T>
 static int launch_affine_q(const void* x, int64_t n_groups, int group, int bits, uint8_t* codes,
-                           void* sc, void* bi, int gpr, int64_t xs, int64_t cs, int64_t ss, cudaStream_t st) {
+                           void* sc, void* bi, int gpr, int64_t xs, int64_t cs, int64_t ss, cudaStream_t st,
+                           const int* pos = nullptr, int64_t cps = 0, int64_t sps = 0) {
   int64_t blocks = (n_groups + 7) / 8;
   const int64_t cap = (int64_t)num_sms() * 8;
   const int grid = (int)(blocks > cap ? cap : blocks);
   const T* xt = reinterpret_cast<const T*>(x);
   switch (group) {
-    case 32: affine_quantize_kernel<T, 1><<<grid, 256, 0, st>>>(xt, n_groups, bits, codes, (__half*)sc, (__half*)bi, gpr, xs, cs, ss); break;
-    case 64: affine_quantize_kernel<T, 2><<<grid, 256, 0, st>>>(xt, n_groups, bits, codes, (__half*)sc, (__half*)bi, gpr, xs, cs, ss); break;
-    default: affine_quantize_kernel<T, 4><<<grid, 256, 0, st>>>(xt, n_groups, bits, codes, (__half*)sc, (__half*)bi, gpr, xs, cs, ss); break;
+    case 32: affine_quantize_kernel<T, 1><<<grid, 256, 0, st>>>(xt, n_groups, bits, codes, (__half*)sc, (__half*)bi, gpr, xs, cs, ss, pos, cps, sps); break;
+    case 64: affine_quantize_kernel<T, 2><<<grid, 256, 0, st>>>(xt, n_groups, bits, codes, (__half*)sc, (__half*)bi, gpr, xs, cs, ss, pos, cps, sps); break;
+    default: affine_quantize_kernel<T, 4><<<grid, 256, 0, st>>>(xt, n_groups, bits, codes, (__half*)sc, (__half*)bi, gpr, xs, cs, ss, pos, cps, sps); break;
   }
   return check_launch("tq_affine_quantize");
 }
@@ -106,6 +114,15 @@ static int affine_check(int dim, int group, int bits) {
 extern "C" int tq_affine_quantize_rows(const void* x, int x_dtype, int64_t n_rows, int dim, int group,
                                        int bits, int64_t x_row_stride, uint8_t* codes, int64_t codes_row_stride,
                                        void* scales_f16, void* biases_f16, int64_t sb_row_stride, void* stream) {
+  return tq_affine_quantize_rows_at(x, x_dtype, n_rows, dim, group, bits, x_row_stride, codes, codes_row_stride,
+                                    scales_f16, biases_f16, sb_row_stride, nullptr, 0, 0, stream);
+}
+
+extern "C" int tq_affine_quantize_rows_at(const void* x, int x_dtype, int64_t n_rows, int dim, int group,
+                                          int bits, int64_t x_row_stride, uint8_t* codes, int64_t codes_row_stride,
+                                          void* scales_f16, void* biases_f16, int64_t sb_row_stride,
+                                          const int32_t* position_dev, int64_t codes_pos_stride,
+                                          int64_t sb_pos_stride, void* stream) {
   int rc = affine_check(dim, group, bits);
   if (rc) return rc;
   if (n_rows <= 0) return TQ_OK;
@@ -118,13 +135,14 @@ extern "C" int tq_affine_quantize_rows(const void* x, int x_dtype, int64_t n_row
   switch (x_dtype) {
     case TQ_F32:
       return launch_affine_q<float>(x, n_groups, group, bits, codes, scales_f16, biases_f16, gpr, x_row_stride,
-                                    codes_row_stride, sb_row_stride, st);
+                                    codes_row_stride, sb_row_stride, st, position_dev, codes_pos_stride, sb_pos_stride);
     case TQ_F16:
       return launch_affine_q<__half>(x, n_groups, group, bits, codes, scales_f16, biases_f16, gpr, x_row_stride,
-                                     codes_row_stride, sb_row_stride, st);
+                                     codes_row_stride, sb_row_stride, st, position_dev, codes_pos_stride, sb_pos_stride);
     case TQ_BF16:
       return launch_affine_q<__nv_bfloat16>(x, n_groups, group, bits, codes, scales_f16, biases_f16, gpr,
-                                            x_row_stride, codes_row_stride, sb_row_stride, st);
+                                            x_row_stride, codes_row_stride, sb_row_stride, st, position_dev,
+                                            codes_pos_stride, sb_pos_stride);
     default: return set_error(TQ_ERR_BAD_ARG, "unknown dtype %d", x_dtype);
   }
 }

@@ -37,6 +37,41 @@ class MixedQuantKVCache:
         self.k_codes = self.k_scales = self.k_biases = None
         self.v_codes = self.v_scales = self.v_biases = None
         self._dtype = torch.float16
+        self._static = None                # device-side length / position of the static decode mode
+
+    # ---- static decode: lengths on the device, steps replayable from a CUDA graph -----------
+    def enable_static_decode(self, max_len: int, counters: torch.Tensor | None = None) -> torch.Tensor:
+        """Pre-size the storage for `max_len` positions and keep the sequence length on the device:
+        one-token `update_and_fetch` calls then write at the device-side position and the decode
+        kernel reads the device-side length, so a whole decode step can be captured once in a CUDA
+        graph and replayed while the sequence grows (host-side `offset` goes stale during replays;
+        `sync_offset()` reads it back).  `counters`: int32 (1 + B,) tensor [position, length per
+        sequence] shared by the caches of all layers (made here when None); the caller advances it
+        once per step with `counters += 1` after the last layer.  Returns the counters."""
+        if self.k_codes is None:
+            raise ValueError("static decode starts from a filled cache (prefill or convert first)")
+        B, H = self.k_codes.shape[:2]
+        dk = self.k_codes.shape[3]
+        dv = self.v_codes.shape[3] * (1 if self.v_bits == 8 else 2)
+        if max_len > self.k_codes.shape[2]:
+            self._ensure(B, H, max_len - self.offset, dk, dv, self.k_codes.device)
+        if counters is None:
+            counters = torch.tensor([self.offset] + [self.offset + 1] * B, dtype=torch.int32,
+                                    device=self.k_codes.device)
+        elif counters.dtype != torch.int32 or counters.numel() != 1 + B:
+            raise ValueError(f"counters must be an int32 tensor of {1 + B} elements")
+        self._static = counters
+        return counters
+
+    def disable_static_decode(self):
+        self.sync_offset()
+        self._static = None
+
+    def sync_offset(self) -> int:
+        """Static decode: read the device-side position back into `offset` (synchronises)."""
+        if self._static is not None:
+            self.offset = int(self._static[0].item())
+        return self.offset
 
     # ---- construction ---------------------------------------------------------
     @classmethod
@@ -76,6 +111,12 @@ class MixedQuantKVCache:
         self._dtype = keys.dtype
         self._ensure(B, H, S, dk, dv, keys.device)
         p = self.offset
+        if self._static is not None:
+            if S != 1 or not self._append_one(keys, values, 0, self._static):
+                raise ValueError("static decode takes one token per step with row-uniform views")
+            self.offset = p + 1            # host copy; the device counter is what the kernels read
+            return (_zero(keys.dtype, keys.device).expand(B, H, self.offset, dk),
+                    _zero(values.dtype, values.device).expand(B, H, self.offset, dv))
         if S == 1 and self._append_one(keys, values, p):
             self.offset = p + 1
             return (_zero(keys.dtype, keys.device).expand(B, H, self.offset, dk),
@@ -89,9 +130,10 @@ class MixedQuantKVCache:
         zv = _zero(values.dtype, values.device).expand(B, H, self.offset, dv)
         return zk, zv
 
-    def _append_one(self, keys, values, p) -> bool:
+    def _append_one(self, keys, values, p, position=None) -> bool:
         """One decode step: the (batch, head) rows are quantized straight into position p of the
-        storage (two launches, no intermediate tensors).  False when a view is not row-uniform."""
+        storage (two launches, no intermediate tensors).  False when a view is not row-uniform.
+        With `position` (device counter) the rows go to p + position[0], read on the device."""
         from .affine import affine_quantize_rows_into
 
         def rows(t):            # (B, H, 1 or n, W) at position -> (B * H, W) view, or None
@@ -108,12 +150,15 @@ class MixedQuantKVCache:
         kx, kc, ks, kb, vx, vc, vs, vb = views
         if H_stride_zero(kx) or H_stride_zero(vx):
             return False
-        return (affine_quantize_rows_into(kx, kc, ks, kb, self.group_size, self.k_bits) and
-                affine_quantize_rows_into(vx, vc, vs, vb, self.group_size, self.v_bits))
+        kps = (self.k_codes.stride(2), self.k_scales.stride(2))
+        vps = (self.v_codes.stride(2), self.v_scales.stride(2))
+        return (affine_quantize_rows_into(kx, kc, ks, kb, self.group_size, self.k_bits, position, kps) and
+                affine_quantize_rows_into(vx, vc, vs, vb, self.group_size, self.v_bits, position, vps))
 
     # ---- attention --------------------------------------------------------------
     def descriptors(self):
-        t = self.offset
+        # static decode: the whole allocation, the valid length comes from the device counter
+        t = self.offset if self._static is None else self.k_codes.shape[2]
         k = dict(format="affine", codes=self.k_codes[:, :, :t], scales=self.k_scales[:, :, :t],
                  biases=self.k_biases[:, :, :t], bits=self.k_bits, group=self.group_size)
         v = dict(format="affine", codes=self.v_codes[:, :, :t], scales=self.v_scales[:, :, :t],
@@ -140,7 +185,13 @@ class MixedQuantKVCache:
                 if mask.dtype == torch.bool:
                     mask = torch.where(mask, 0.0, float("-inf"))
                 m3 = _mask_3d(mask, queries.shape[0], queries.shape[1], self.offset)
-            out = flash_decode(queries[:, :, 0, :], k=k, v=v, attn_scale=scale, mask=m3, out_dtype=queries.dtype)
+            lens = None
+            if self._static is not None:
+                if m3 is not None:
+                    raise ValueError("static decode does not take a mask")
+                lens = self._static[1:]
+            out = flash_decode(queries[:, :, 0, :], k=k, v=v, attn_scale=scale, mask=m3, out_dtype=queries.dtype,
+                               seq_lens=lens)
             return out.unsqueeze(2)
         from .base import _dense_sdpa
         k, v = self.dequantized(queries.dtype)
