@@ -97,14 +97,17 @@ class Qwen2Model:
         cos, sin = rope_tables(pos, D, cfg.rope_theta, x.dtype)
         for lw, cache in zip(self.layers, caches):
             h = F.rms_norm(x, (cfg.hidden,), eps=cfg.rms_eps)
-            q = apply_rope((h @ lw["wq"]).view(B, L, cfg.n_q_heads, D).transpose(1, 2), cos, sin)
-            k = apply_rope((h @ lw["wk"]).view(B, L, cfg.n_kv_heads, D).transpose(1, 2), cos, sin)
-            v = (h @ lw["wv"]).view(B, L, cfg.n_kv_heads, D).transpose(1, 2)
+            qd, kvd = cfg.n_q_heads * D, cfg.n_kv_heads * D
+            qkv = h @ lw["wqkv"]
+            q = apply_rope(qkv[..., :qd].view(B, L, cfg.n_q_heads, D).transpose(1, 2), cos, sin)
+            k = apply_rope(qkv[..., qd:qd + kvd].view(B, L, cfg.n_kv_heads, D).transpose(1, 2), cos, sin)
+            v = qkv[..., qd + kvd:].view(B, L, cfg.n_kv_heads, D).transpose(1, 2)
             keys, values = cache.update_and_fetch(k, v)
             att = base.scaled_dot_product_attention(q, keys, values, cache, scale, mask)
             x = x + att.transpose(1, 2).reshape(B, L, cfg.n_q_heads * D) @ lw["wo"]
             h = F.rms_norm(x, (cfg.hidden,), eps=cfg.rms_eps)
-            x = x + (F.silu(h @ lw["w1"]) * (h @ lw["w3"])) @ lw["w2"]
+            gu = h @ lw["w13"]
+            x = x + (F.silu(gu[..., :cfg.ffn]) * gu[..., cfg.ffn:]) @ lw["w2"]
         if last_only:
             x = x[:, -1:]
         return F.rms_norm(x, (cfg.hidden,), eps=cfg.rms_eps) @ self.head
