@@ -84,12 +84,10 @@ __device__ __forceinline__ void warp_butterfly(float (&v)[EPL], int lane) {
   }
 #pragma unroll
   for (int k = 1; k < 32; k <<= 1) {
-    const bool upper = (lane & k) != 0;
+    // upper partner: o - v = fma(v, -1, o), which rounds exactly like the subtraction it replaces
+    const float sg = (lane & k) ? -1.0f : 1.0f;
 #pragma unroll
-    for (int j = 0; j < EPL; ++j) {
-      float o = __shfl_xor_sync(0xffffffffu, v[j], k);
-      v[j] = upper ? __fsub_rn(o, v[j]) : __fadd_rn(v[j], o);
-    }
+    for (int j = 0; j < EPL; ++j) v[j] = __fmaf_rn(v[j], sg, __shfl_xor_sync(0xffffffffu, v[j], k));
   }
 }
 

@@ -196,6 +196,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   }
   return false;
 }
+// The same for the producer warp, which is usually a whole ring ahead of the consumers: it polls at a
+// low rate, so that its polling takes no issue slots from the warps that do the work.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity) {
+  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+    __nanosleep(256);
+  }
+  return false;
+}
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
@@ -521,7 +538,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
     for (int i = 0; i < n_tiles; ++i) {
       const int s = i % kStages;
       const uint32_t ph = (i / kStages) & 1;
-      if (i >= kStages && !mbar_wait(empty_bar(s), ph ^ 1)) {
+      if (i >= kStages && !mbar_wait_relaxed(empty_bar(s), ph ^ 1)) {
         if (lane == 0) atomicExch(tb.status, 1);
         break;
       }
