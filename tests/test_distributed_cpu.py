@@ -24,6 +24,17 @@ def test_shard_range_covers_everything(tq):
         assert max(sizes) - min(sizes) <= 1
 
 
+def test_send_buffer_keeps_the_accumulator_on_a_16_byte_boundary(tq):
+    """The decode kernel writes accumulator rows as 16-byte vectors: the send buffer of a rank must put
+    `acc` on a 16-byte boundary for odd row counts too (one kv-head shard with 7 query heads, say)."""
+    from turboquant_mlx_b200.distributed import partial_buffer, partial_views
+    for rows in (1, 7, 8, 21, 28, 63, 64):
+        buf = partial_buffer(rows, 128, "cpu")[0]
+        m, l, acc = partial_views(buf, rows, 128)
+        assert acc.data_ptr() % 16 == 0, rows
+        assert m.shape == (rows,) and l.data_ptr() - m.data_ptr() == 4 * rows and acc.shape == (rows, 128)
+
+
 def test_partial_views_layout(tq):
     from turboquant_mlx_b200.distributed import partial_buffer, partial_views
     rows, dim, world = 6, 32, 3

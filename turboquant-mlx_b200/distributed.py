@@ -30,8 +30,14 @@ def shard_range(n_items: int, world: int, rank: int):
 
 
 def partial_buffer(rows: int, dim: int, device, world: int = 1) -> torch.Tensor:
-    """(world, rows * (dim + 2)) float32: per rank [m (rows) | l (rows) | acc (rows * dim)]."""
-    return torch.empty((world, rows * (dim + 2)), dtype=torch.float32, device=device)
+    """(world, rows * (dim + 2)) float32: per rank [m (rows) | l (rows) | acc (rows * dim)].
+    The decode kernel stores accumulator rows as 16-byte vectors; acc starts 8 * rows bytes into a
+    block, so a one-block buffer (a rank's send buffer) with an odd row count is placed 8 bytes into
+    its allocation, which puts acc on a 16-byte boundary."""
+    n = rows * (dim + 2)
+    if world == 1 and rows % 2:
+        return torch.empty((n + 2,), dtype=torch.float32, device=device)[2:].view(1, n)
+    return torch.empty((world, n), dtype=torch.float32, device=device)
 
 
 def partial_views(buf: torch.Tensor, rows: int, dim: int):
