@@ -573,7 +573,8 @@ def workload_c3(args):
         dist.init_process_group("nccl", device_id=dev)
     tq = entry.load_package()
     from turboquant_mlx_b200.distributed import shard_range
-    B, nq_all, nkv_all, ctx, layers = 32, 32, 8, 8192, 2
+    # layers per CUDA graph: enough launches in flight to fill a GPU that holds only 1 / world of the kv heads
+    B, nq_all, nkv_all, ctx, layers = 32, 32, 8, 8192, 2 * world
     h0, h1 = shard_range(nkv_all, world, rank)
     nkv = h1 - h0
     nq = nkv * (nq_all // nkv_all)
