@@ -88,7 +88,9 @@ def test_prefill_convert_decode_matches_fp16_cache(tq, dev):
         agree = (tok84 == ref_tok).float().mean().item()
         print(f"\nK8/V4 vs fp16 cache (teacher forced): min logits cosine {cos:.5f}, argmax agreement {agree:.3f}")
         assert torch.equal(tok84[:, 0], ref_tok[:, 0])            # identical fp16 prefill
-        assert cos > 0.95 and agree >= 0.5      # 4-bit values on random weights: small but visible logit noise
+        # 4-bit values on random weights: small but visible logit noise (observed: 0.90 agreement); the
+        # reference's "identical greedy text" (README.md:21-24) is a statement about a trained model
+        assert cos > 0.95 and agree >= 0.8
         tok88, lg88, _ = _generate(model, plain(), prompt, n_new, base, forced=ref_tok,
                                    convert=lambda c: c.to_quantized(group_size=64, bits=8))
         cos88 = F.cosine_similarity(lg88, ref_logits, dim=-1).min().item()
