@@ -121,7 +121,11 @@ template <int KF> struct KGeom;
 template <> struct KGeom<KF_DENSE> { static constexpr int row = kDenseRowBytes, lut = 0, norms = 0; };
 template <> struct KGeom<KF_DENSE_BF16> { static constexpr int row = kDenseRowBytes, lut = 0, norms = 0; };
 template <> struct KGeom<KF_POLAR3> { static constexpr int row = 52, lut = 64 * 32 * 4, norms = kTile * 4; };
-template <> struct KGeom<KF_POLAR4> { static constexpr int row = 64, lut = 256 * 32 * 4, norms = kTile * 4; };
+// 4-bit keys: the 256-entry pair table is kept once per kK4Rep lanes (lane l reads copy l mod kK4Rep).  With 16
+// copies two lanes share a copy and collide when their entries differ in the same bank half: ~2 wavefronts per
+// lookup instead of 1, in exchange for 16 KB of shared memory per CTA (one CTA more per SM).
+constexpr int kK4Rep = 16;
+template <> struct KGeom<KF_POLAR4> { static constexpr int row = 64, lut = 256 * kK4Rep * 4, norms = kTile * 4; };
 // group-affine 8-bit codes, two groups of 64: per row 128 code bytes; the "norms" slot holds the
 // row's two fp16 scales (4 B) followed, kTile * 4 bytes later, by its two fp16 biases
 template <> struct KGeom<KF_AFFINE8> { static constexpr int row = 128, lut = 0, norms = 2 * kTile * 4; };
@@ -418,8 +422,9 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       constexpr int KB = KF == KF_POLAR3 ? 3 : 4;
       uint32_t* kl = reinterpret_cast<uint32_t*>(smem + L::klut);
       constexpr int nk = 1 << (2 * KB);
-      for (int i = tid; i < nk * 32; i += kCT) {
-        const int e = i >> 5;
+      constexpr int rep = KF == KF_POLAR4 ? kK4Rep : 32;     // copies of the table (one per lane, or per lane mod rep)
+      for (int i = tid; i < nk * rep; i += kCT) {
+        const int e = i / rep;
         kl[i] = (uint32_t)c16_s[16 + (e & ((1 << KB) - 1))] | ((uint32_t)c16_s[16 + (e >> KB)] << 16);
       }
     }
@@ -777,10 +782,14 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         float sc2[4] = {0.f, 0.f, 0.f, 0.f};   // second accumulator: two independent MMA chains
 #pragma unroll
         for (int wi = 0; wi < 4; ++wi) {
-          const uint32_t a0 = ((w[wi] << 7) & 0x7F80u) | lane4;
-          const uint32_t a1 = ((w[wi] >> 1) & 0x7F80u) | lane4;
-          const uint32_t a2 = ((w[wi] >> 9) & 0x7F80u) | lane4;
-          const uint32_t a3 = ((w[wi] >> 17) & 0x7F80u) | lane4;
+          // byte address of pair entry e in this lane's copy: e * (kK4Rep * 4) + (lane mod kK4Rep) * 4
+          constexpr int esh = kK4Rep == 32 ? 7 : 6;
+          constexpr uint32_t emask = 0xFFu << esh;
+          const uint32_t lk = (lane & (kK4Rep - 1)) * 4;
+          const uint32_t a0 = ((w[wi] << esh) & emask) | lk;
+          const uint32_t a1 = ((w[wi] >> (8 - esh)) & emask) | lk;
+          const uint32_t a2 = ((w[wi] >> (16 - esh)) & emask) | lk;
+          const uint32_t a3 = ((w[wi] >> (24 - esh)) & emask) | lk;
           mma16816(sc[ng], aq[2 * wi], lds32(klut + a0), lds32(klut + a1));
           mma16816(sc2, aq[2 * wi + 1], lds32(klut + a2), lds32(klut + a3));
         }
