@@ -275,6 +275,11 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
   return v;
 }
+// Table lookups go through the shared array itself, so that the table's offset inside the shared window
+// becomes the load's immediate instead of an add per lookup.
+__device__ __forceinline__ uint32_t lut_ld(const uint8_t* table, uint32_t byte_off) {
+  return *reinterpret_cast<const uint32_t*>(table + byte_off);
+}
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -692,7 +697,6 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   }
   // V side: this thread's 16 elements are 16g .. 16g+15 (8 pairs)
   const uint32_t lane4 = lane * 4;
-  const uint32_t vlut = sbase + L::vlut, klut = sbase + L::klut;
   const int v_w0 = (16 * g) / 10;                       // first word holding element 16g (3-bit rows)
   const int v_s0 = 3 * ((16 * g) % 10);                 // its bit offset inside that word
   const int v_w2 = min(v_w0 + 2, 12);
@@ -704,6 +708,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   float bias_run[2] = {0.f, 0.f};   // affine values: sum of weight x bias per element group (head g, this lane's positions)
   const int pw = 16 * warp;   // first position of this warp inside a tile
 
+  const int span = (int)(pe - pb);          // positions of this chunk (at most one chunk: fits 32 bits)
   for (int i = 0; i < n_tiles; ++i) {
     const int s = i % kStages;
     if (!mbar_wait(full_bar(s), (i / kStages) & 1)) {
@@ -717,7 +722,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       break;
     }
     const uint32_t st = sbase + L::stage0 + s * L::stage_bytes;
-    const int nvp = (int)min((int64_t)kTile, pe - (pb + (int64_t)i * kTile));
+    const int nvp = min(kTile, span - i * kTile);
     // several query tokens: token t (row g's) does not see the sequence's last q_tokens - 1 - t positions
     // (recomputed per tile so that the one-token path carries nothing extra through the loop)
     int nvp_row = nvp;
@@ -790,8 +795,8 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
           const uint32_t a1 = ((w[wi] >> (8 - esh)) & emask) | lk;
           const uint32_t a2 = ((w[wi] >> (16 - esh)) & emask) | lk;
           const uint32_t a3 = ((w[wi] >> (24 - esh)) & emask) | lk;
-          mma16816(sc[ng], aq[2 * wi], lds32(klut + a0), lds32(klut + a1));
-          mma16816(sc2, aq[2 * wi + 1], lds32(klut + a2), lds32(klut + a3));
+          mma16816(sc[ng], aq[2 * wi], lut_ld(smem + L::klut, a0), lut_ld(smem + L::klut, a1));
+          mma16816(sc2, aq[2 * wi + 1], lut_ld(smem + L::klut, a2), lut_ld(smem + L::klut, a3));
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) sc[ng][c] += sc2[c];
@@ -813,8 +818,8 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
         float sc2[4] = {0.f, 0.f, 0.f, 0.f};   // second accumulator: two independent MMA chains
 #pragma unroll
         for (int ks = 0; ks < 8; ks += 2) {
-          mma16816(sc[ng], aq[ks], lds32(klut + bq[2 * ks]), lds32(klut + bq[2 * ks + 1]));
-          mma16816(sc2, aq[ks + 1], lds32(klut + bq[2 * ks + 2]), lds32(klut + bq[2 * ks + 3]));
+          mma16816(sc[ng], aq[ks], lut_ld(smem + L::klut, bq[2 * ks]), lut_ld(smem + L::klut, bq[2 * ks + 1]));
+          mma16816(sc2, aq[ks + 1], lut_ld(smem + L::klut, bq[2 * ks + 2]), lut_ld(smem + L::klut, bq[2 * ks + 3]));
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) sc[ng][c] += sc2[c];
@@ -953,7 +958,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
           const int sh = 8 * (j & 3) - 7;
           addr = (sh >= 0 ? (w >> sh) : (w << 7)) & 0x7F80u;
         }
-        lv[q4] = lds32(vlut + (addr | lane4));
+        lv[q4] = lut_ld(smem + L::vlut, addr | lane4);
       }
       uint32_t af[4];
       af[0] = __byte_perm(lv[0], lv[1], 0x5410);   // element 16g+2j,   positions 2t, 2t+1
