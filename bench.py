@@ -278,6 +278,7 @@ def gpu_arm(args):
     dev = torch.device("cuda", local)
     if world > 1:
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")    # plain peer stores / loads only: no multicast objects
         dist.init_process_group("nccl", device_id=dev)
     tq = entry.load_package()
     from turboquant_mlx_b200 import base
@@ -570,6 +571,7 @@ def workload_c3(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
     tq = entry.load_package()
     from turboquant_mlx_b200.distributed import shard_range
@@ -802,6 +804,7 @@ def workload_c5(args):
     dev = torch.device("cuda", local)
     if world > 1:
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")    # plain peer stores / loads only: no multicast objects
         dist.init_process_group("nccl", device_id=dev)
     tq = entry.load_package()
     rec = c5_measure(args, tq, torch, dist, dev, world, rank)
