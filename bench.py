@@ -599,7 +599,8 @@ def workload_c3(args):
         for l in range(layers):
             if args.splits > 0:      # tuning aid: a fixed split count instead of the planner's
                 k, v = cache_kv_descriptors(caches[l])
-                tq.flash_decode(q[l, :, :, 0, :], k=k, v=v, attn_scale=scale, num_splits=args.splits, out=outs[l])
+                tq.flash_decode(q[l, :, :, 0, :], k=k, v=v, attn_scale=scale, num_splits=args.splits, out=outs[l],
+                                kv_stable=True, q_stable=True, workspace_owner=caches[l])
             else:
                 tq.turboquant_attention(q[l], caches[l], scale)
 
