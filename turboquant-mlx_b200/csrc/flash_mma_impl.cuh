@@ -3,14 +3,15 @@
 // One CTA = one (batch, kv head, sequence chunk).  All n_rep <= 8 query heads of
 // the group consume the same K/V bytes, so every KV byte is read once.
 //
-// A CTA is half an SM: 6 consumer warps + 1 producer warp, at most ~112 KB of shared
-// memory, two CTAs resident per SM.  The launcher normally asks for one CTA per SM, so
-// the CTAs of the NEXT launch on the stream (programmatic dependent launch) take the
-// other half of every SM and stream their K/V while this launch is in its tail
-// (partial-state hand-over, merge); in steady state the HBM pipe and the issue slots
-// never wait for a prologue or an epilogue.
+// The CTA geometry comes from the including file (TQ_FLASH_WARPS consumer warps + 1 producer warp, up to
+// TQ_FLASH_MAX_CTAS CTAs per SM): small CTAs, several per SM, for calls whose launches overlap on the
+// stream (the CTAs of three to four consecutive launches share every SM, so one launch's prologue, partial-state
+// hand-over and merge run while the others stream), one large CTA per SM for a call that runs on its own.
+// Every launch is a programmatic dependent launch and releases its successor at entry; what it waits for
+// (nothing, when the caller vouches for stable inputs and a workspace of the call's own) is decided per
+// argument in the kernel body.
 //
-//   producer warp : streams 96-position tiles of K / V (and their norms) into a
+//   producer warp : streams tiles of 16 positions per consumer warp of K / V (and their norms) into a
 //                   shared-memory ring with cp.async.bulk (TMA, 1-D) and mbarrier
 //                   transaction counts; every copy reads this GPU's own memory into
 //                   this CTA only.  It also performs the optional in-launch cache
