@@ -230,8 +230,8 @@ typedef struct tq_flash_params {
   uint32_t* peer_counter[8];
   /* 1: the same promise as kv_stable for the query (and new_k / new_v): with both set the kernel
    * reads its inputs without waiting for the launches in front of it and only waits before it
-   * first writes the workspace, so consecutive decode launches overlap (each takes half of every
-   * SM).  0: wait before reading the query. */
+   * first writes the workspace (not even then with workspace_exclusive), so consecutive decode
+   * launches overlap (the CTAs of several launches share every SM).  0: wait before reading the query. */
   int32_t q_stable;
   /* Optional in-launch cache append (no reference counterpart; it takes the place of the
    * quantize-on-insert launch of cache.py:131-150 / v_only_cache.py:46-60 in front of a decode
