@@ -279,8 +279,8 @@ def gpu_arm(args):
     if world > 1:
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")    # plain peer stores / loads only: no multicast objects
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-            os.environ["NCCL_DEBUG"] = "WARN"             # keeps NCCL's version banner off stdout (one JSON line)
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "WARN"):
+            del os.environ["NCCL_DEBUG"]                  # keeps NCCL's version banner off stdout (one JSON line)
         dist.init_process_group("nccl", device_id=dev)
     tq = entry.load_package()
     from turboquant_mlx_b200 import base
