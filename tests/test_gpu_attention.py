@@ -578,8 +578,31 @@ def test_short_multi_token_step_is_causal_and_matches_oracle(tq, oracle, dev, n_
                                                  centroids=oracle.codebook(kbits), signs=ks, bits=kbits),
                         v_polar=vdesc, attn_scale=scale, n_rep=n_rep)
                 assert _rel(out[b, :, t], ref) < ATT_TOL, (b, t, splits)
+    # the small-CTA geometry (launches that overlap their neighbours) takes the same rows
+    ws = tq.kernels.decode_workspace(dev)
+    out4 = tq.flash_decode(_t(q, dev) if T > 1 else _t(q, dev)[:, :, 0], k=k, v=v, attn_scale=scale,
+                           out_dtype=torch.float32, kv_stable=True, q_stable=True, workspace=ws)
+    assert L.tq_flash_decode_last_kernel() == 1 and tq.kernels.workspace_status(ws) == 0
+    assert _rel(out4.cpu().numpy().reshape(out.shape), out) < 1e-3
     assert tq.kernels.flash_status(dev, B * n_kv) == 0
     if T > 1:
+        # device-side lengths: sequence 1 is 5 positions shorter, its T queries are the last T of those
+        lens = torch.tensor([S, S - 5], dtype=torch.int32, device=dev)
+        outl = tq.flash_decode(_t(q, dev), k=k, v=v, attn_scale=scale, out_dtype=torch.float32,
+                               seq_lens=lens).cpu().numpy()
+        assert np.array_equal(outl[0], out[0])
+        for t in range(T):
+            n = S - 5 - T + 1 + t
+            vdesc = dict(packed=vp[1, :, :n], norms=vn[1, :, :n], centroids=oracle.codebook(3), signs=vs, bits=3)
+            if kind == "dense":
+                ref, _ = oracle.decode_attention(q[1, :, t], k_dense=kd[1, :, :n], v_polar=vdesc, attn_scale=scale,
+                                                 n_rep=n_rep)
+            else:
+                ref, _ = oracle.decode_attention(
+                    q[1, :, t], k_polar=dict(packed=kp[1, :, :n], norms=kn[1, :, :n],
+                                             centroids=oracle.codebook(kbits), signs=ks, bits=kbits),
+                    v_polar=vdesc, attn_scale=scale, n_rep=n_rep)
+            assert _rel(outl[1, :, t], ref) < ATT_TOL, t
         with pytest.raises(ValueError):      # rows beyond the MMA tile: refused, not silently wrong
             tq.flash_decode(_t(np.zeros((B, n_kv * n_rep, 9 // n_rep + 1, D), np.float16), dev), k=k, v=v,
                             attn_scale=scale)
