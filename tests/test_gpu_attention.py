@@ -590,7 +590,7 @@ def test_short_multi_token_step_is_causal_and_matches_oracle(tq, oracle, dev, n_
         lens = torch.tensor([S, S - 5], dtype=torch.int32, device=dev)
         outl = tq.flash_decode(_t(q, dev), k=k, v=v, attn_scale=scale, out_dtype=torch.float32,
                                seq_lens=lens).cpu().numpy()
-        assert np.array_equal(outl[0], out[0])
+        assert _rel(outl[0], out[0]) < 1e-3          # sequence 0 at full length: the result above
         for t in range(T):
             n = S - 5 - T + 1 + t
             vdesc = dict(packed=vp[1, :, :n], norms=vn[1, :, :n], centroids=oracle.codebook(3), signs=vs, bits=3)
