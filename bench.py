@@ -325,7 +325,7 @@ def gpu_arm(args):
     if world == 1:
         # ---- device-resident step: 28 flash-decode launches, one graph.  The caches and queries are
         # static here, so each launch may read its inputs while the launches in front of it drain
-        # (kv_stable, q_stable): consecutive layers overlap, each on one half of every SM.
+        # (kv_stable, q_stable): consecutive layers overlap, the CTAs of three to four launches sharing every SM.
         def device_step():
             for layer in range(N_LAYERS):
                 v_only_attention(q_dev[layer], caches[layer], scale, kv_stable=True, q_stable=True, out=out_dev[layer])
@@ -334,7 +334,7 @@ def gpu_arm(args):
         with sampler:
             ms_step = _timed(torch, dist, world, dev, graph.replay, args.steps, args.warmup)
             # roofline of the dominant kernel: the same launches, event-timed over a longer region
-            ms_calls = _timed(torch, dist, world, dev, graph.replay, max(args.steps, 200), 3)
+            ms_calls = _timed(torch, dist, world, dev, graph.replay, max(args.steps, 600), 3)   # ~120 ms: > 50 clock samples
         launch_ms = ms_calls / N_LAYERS
         launches_per_step = N_LAYERS
         sharding = "one GPU, no collective"
@@ -361,8 +361,8 @@ def gpu_arm(args):
         gk = _capture(torch, sh.kernels_only, dev)
         with sampler:
             ms_step = _timed(torch, dist, world, dev, graph.replay, args.steps, args.warmup)
-            ms_calls = _timed(torch, dist, world, dev, gk.replay, max(args.steps, 100), 3)
-            ms_total = _timed(torch, dist, world, dev, graph.replay, max(args.steps, 100), 3)
+            ms_calls = _timed(torch, dist, world, dev, gk.replay, max(args.steps, 300), 3)
+            ms_total = _timed(torch, dist, world, dev, graph.replay, max(args.steps, 300), 3)
         launch_ms = ms_calls / N_LAYERS
         launches_per_step = N_LAYERS
         sharding = (f"one sequence of {world * CTX} tokens split along the sequence, {CTX} positions per GPU; per "
