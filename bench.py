@@ -334,7 +334,9 @@ def gpu_arm(args):
         with sampler:
             ms_step = _timed(torch, dist, world, dev, graph.replay, args.steps, args.warmup)
             # roofline of the dominant kernel: the same launches, event-timed over a longer region
-            ms_calls = _timed(torch, dist, world, dev, graph.replay, max(args.steps, 600), 3)   # ~120 ms: > 50 clock samples
+            # 200 replays = 40 ms: long enough for ~20 clock samples, short enough that the SM clock holds its
+            # boost (over 120 ms of this load it settled at 1830 MHz with no throttle reason reported)
+            ms_calls = _timed(torch, dist, world, dev, graph.replay, max(args.steps, 200), 3)
         launch_ms = ms_calls / N_LAYERS
         launches_per_step = N_LAYERS
         sharding = "one GPU, no collective"
@@ -361,8 +363,8 @@ def gpu_arm(args):
         gk = _capture(torch, sh.kernels_only, dev)
         with sampler:
             ms_step = _timed(torch, dist, world, dev, graph.replay, args.steps, args.warmup)
-            ms_calls = _timed(torch, dist, world, dev, gk.replay, max(args.steps, 300), 3)
-            ms_total = _timed(torch, dist, world, dev, graph.replay, max(args.steps, 300), 3)
+            ms_calls = _timed(torch, dist, world, dev, gk.replay, max(args.steps, 100), 3)
+            ms_total = _timed(torch, dist, world, dev, graph.replay, max(args.steps, 100), 3)
         launch_ms = ms_calls / N_LAYERS
         launches_per_step = N_LAYERS
         sharding = (f"one sequence of {world * CTX} tokens split along the sequence, {CTX} positions per GPU; per "
