@@ -349,3 +349,37 @@ def test_hybrid_cache_quantize_k_then_decode(tq, oracle, dev):
             err = np.abs(got[b, :, 0].float().cpu().numpy() - ref).max() / np.abs(ref).max()
             assert err < 2e-3, f"{name}, batch element {b}: max rel err {err:.3e}"
     assert c.trim(1) == 1 and c.offset == S + 1
+
+
+def test_mixed_cache_static_append_matches_host_side_append(tq, dev):
+    """One-token appends at a position read from a device counter (static decode mode) write the same
+    codes, scales and biases as appends at the host-side offset, and the decode over the device-side
+    length equals the decode over the sliced views."""
+    torch.manual_seed(31)
+    B, n_kv, n_q, S, D = 1, 2, 8, 70, 128
+    k0 = torch.randn(B, n_kv, S, D, device=dev, dtype=torch.bfloat16)
+    v0 = torch.randn(B, n_kv, S, D, device=dev, dtype=torch.bfloat16)
+    steps = [(torch.randn(B, n_kv, 1, D, device=dev, dtype=torch.bfloat16),
+              torch.randn(B, n_kv, 1, D, device=dev, dtype=torch.bfloat16)) for _ in range(5)]
+    q = torch.randn(B, n_q, 1, D, device=dev, dtype=torch.bfloat16)
+    a, b = tq.MixedQuantKVCache(), tq.MixedQuantKVCache()
+    a.update_and_fetch(k0, v0)
+    b.update_and_fetch(k0, v0)
+    counters = b.enable_static_decode(S + 16)
+    assert counters.tolist() == [S, S + 1]
+    for ks, vs in steps:
+        a.update_and_fetch(ks, vs)
+        out_a = a.quantized_attention(q, 1.0 / math.sqrt(D))
+        b.update_and_fetch(ks, vs)
+        out_b = b.quantized_attention(q, 1.0 / math.sqrt(D))     # reads the length from the device counter
+        counters += 1
+        assert (out_a.float() - out_b.float()).abs().max().item() < 2e-3 * out_a.float().abs().max().item()
+    t = S + len(steps)
+    assert b.sync_offset() == t == a.offset
+    for name in ("k_codes", "k_scales", "k_biases", "v_codes", "v_scales", "v_biases"):
+        assert torch.equal(getattr(a, name)[:, :, :t], getattr(b, name)[:, :, :t]), name
+    with pytest.raises(ValueError):
+        b.update_and_fetch(k0[:, :, :2], v0[:, :, :2])           # static decode takes one token per step
+    b.disable_static_decode()
+    b.update_and_fetch(k0[:, :, :2], v0[:, :, :2])
+    assert b.offset == t + 2
