@@ -374,7 +374,10 @@ def gpu_arm(args):
         extra_cfg = {"us_per_layer_kernel_only": launch_ms * 1e3, "us_per_layer_total": ms_total / N_LAYERS * 1e3,
                      "us_per_layer_exchange_and_merge": (ms_total - ms_calls) / N_LAYERS * 1e3,
                      "exchange_bytes_per_rank_per_layer": N_Q * (DIM + 2) * 4,
-                     "max_abs_diff_vs_nccl_allgather_path": diff, "max_abs_diff_across_ranks": rank_diff}
+                     "max_abs_diff_vs_nccl_allgather_path": diff, "max_abs_diff_across_ranks": rank_diff,
+                     "what_limits_the_rest": "not NVLink bytes (14.6 KB per rank and layer): every layer is an all-to-all "
+                                             "dependency, so the CTA that completes a kv head waits one NVLink trip after "
+                                             "the slowest rank, and each graph replay drains that wait once"}
 
     value = world * step_bytes / (ms_step * 1e-3) / 1e9
     toks = 1.0 / (ms_step * 1e-3)
