@@ -10,16 +10,18 @@ One step = one decode token = 28 layers, each layer with its own KV buffers
            (the 28-layer step replayed as one CUDA graph);
   e2e    : the same metric through the public cache / attention-hook API with
            HOST inputs: per step the new token's q, k, v for all layers are
-           copied from pinned host memory, appended (K copy, V quantize) and
-           attended, and the outputs are copied back to the host;
+           copied from pinned host memory, appended (K copy, V quantize: done by
+           the decode launch itself) and attended, and the outputs are copied
+           back to the host;
   roofline: flash-decode launch time from CUDA events vs the measured HBM peak;
   cpu_baseline: the numpy oracle of the same composed path on the host cores.
 
 With --gpus N > 1 (torchrun, one rank per GPU) ONE sequence of N x 32768 tokens is
 sharded along the sequence: every rank holds 32768 positions of every KV head, runs
 the decode kernel in partial mode on its chunk, the (m, l, acc) partial states cross
-NVLink (peer stores issued by the decode kernel's final step) and every rank merges
-them, per layer, inside the timed region: weak scaling, N = 1 is the plain workload.
+NVLink (peer stores issued by the decode kernel's final step) and the same launch waits
+(bounded) for the other ranks' states and merges them, per layer, inside the timed
+region: weak scaling, N = 1 is the plain workload.
 --impl reference times the CPU oracle only.
 """
 
