@@ -405,7 +405,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   __shared__ int elected_s;        // this CTA completed its group's counter
   __shared__ uint8_t idx_s[kDim];  // producer warp: codes of the row being appended
   __shared__ int hint_s[8];        // value skipping: per head, the largest score any warp of the CTA has seen
-  if (tid < 8) hint_s[tid] = (int)0x80000000;   // ordered image of -inf, see ordered_int()
+  if (tid < 8) hint_s[tid] = (int)0x807FFFFF;   // ordered_int(-inf): decodes to -inf, below every score
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(full_bar(s), 1);
@@ -709,6 +709,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
 #pragma unroll
   for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
   float m_run = -INFINITY, l_run = 0.f;
+  int active_count = 0;             // positions whose values this warp accumulated (reported when asked for)
   float bias_run[2] = {0.f, 0.f};   // affine values: sum of weight x bias per element group (head g, this lane's positions)
   const int pw = 16 * warp;   // first position of this warp inside a tile
 
@@ -909,14 +910,13 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       // the CTA so far is a second lower bound (shared through hint_s)
       float sq = fmaxf(smax, __shfl_xor_sync(0xffffffffu, smax, 1));
       sq = fmaxf(sq, __shfl_xor_sync(0xffffffffu, sq, 2));
-      if (t == 0 && g < a.rows && sq > -INFINITY) atomicMax(&hint_s[g], ordered_int(sq));
-      __syncwarp();
-      const float hint = from_ordered_int(*reinterpret_cast<volatile int*>(&hint_s[g]));
+      float hint = from_ordered_int(*reinterpret_cast<volatile int*>(&hint_s[g]));
+      if (t == 0 && g < a.rows && sq > hint) atomicMax(&hint_s[g], ordered_int(sq));   // rare once the large scores are in
+      hint = fmaxf(hint, sq);
       const bool below = smax == -INFINITY || ex2(smax - m_use) < a.sparse_thr * lq || ex2(smax - hint) < a.sparse_thr;
       skip_values = __all_sync(0xffffffffu, g >= a.rows || below);
     }
-    if (!PLAIN && a.active_positions != nullptr && !skip_values && lane == 0 && pw < nvp)
-      atomicAdd(a.active_positions + b * a.n_kv_heads + kvh, min(16, nvp - pw));
+    if (!PLAIN && !skip_values && pw < nvp) active_count += min(16, nvp - pw);   // one atomic per warp, after the loop
     if (!skip_values) {
     const uint32_t pb0 = pack_h2(pv[0][0], pv[0][1]);   // k = 2t, 2t+1      (positions pw + 2t ..)
     const uint32_t pb1 = pack_h2(pv[1][0], pv[1][1]);   // k = 2t+8, 2t+9    (positions pw + 8 + 2t ..)
@@ -981,6 +981,9 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
     __syncwarp();
     if (lane == 0) mbar_arrive(empty_bar(s));
   }
+
+  if (!PLAIN && a.active_positions != nullptr && lane == 0 && active_count > 0)
+    atomicAdd(a.active_positions + b * a.n_kv_heads + kvh, active_count);
 
   // ---------------- CTA epilogue: one exchange through shared memory ----------------
   // Every warp writes its (o[32], m, l) once, [warp][value][lane] (conflict free);
