@@ -303,9 +303,9 @@ typedef struct tq_flash_params {
 
 /* Workspace contract: 16-byte aligned, at least tq_flash_decode_workspace_bytes()
  * bytes.  It starts with a header of tq_flash_decode_header_bytes(batch,
- * n_kv_heads) bytes (a status block and one split counter per (batch, kv head)) that
- * must be zero the first time the workspace is used; every call leaves the counters at
- * zero, so a workspace can be reused by later calls with the same batch * n_kv_heads.
+ * n_kv_heads) bytes (a status block, and per (batch, kv head) one split counter and eight
+ * value-skipping hint words) that must be zero the first time the workspace is used; every
+ * call leaves counters and hint words at zero, so a workspace can be reused by later calls with the same batch * n_kv_heads.
  * Zero the header again before reusing the memory with a different
  * batch * n_kv_heads or after any other use.  Calls on one stream may share a
  * workspace (the kernel orders its workspace accesses after the preceding launch) unless

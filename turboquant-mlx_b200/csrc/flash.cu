@@ -318,6 +318,7 @@ extern "C" int tq_flash_decode(const tq_flash_params* p) {
     MmaOutput mo;
     mo.status = (int*)p->workspace;
     mo.counters = (int*)p->workspace + 4;
+    mo.hints = (uint32_t*)p->workspace + 4 + (int64_t)p->batch * p->n_kv_heads;
     mo.out_mode = p->out_mode;
     mo.out_dtype = p->out_dtype;
     mo.out = p->out;

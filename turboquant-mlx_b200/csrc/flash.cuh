@@ -76,6 +76,7 @@ int flash_mma_resident_ctas_per_sm();   // what the runtime's occupancy query re
 struct MmaOutput {       // where the tensor-core kernel's fused merge writes
   int* status;           // workspace header word 0
   int* counters;         // one int per (batch, kv head) after the status block, zero between calls
+  uint32_t* hints;       // eight words per (batch, kv head) after the counters (value skipping), zero between calls
   int out_mode, out_dtype;
   void* out;
   int64_t out_batch_stride, out_head_stride;

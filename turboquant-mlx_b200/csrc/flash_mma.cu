@@ -72,7 +72,8 @@ int flash_mma_resident_ctas_per_sm() {
   return g_last_geometry == 4 ? flash_mma_resident_ctas_w4() : g_last_geometry == 12 ? flash_mma_resident_ctas_w12() : -1;
 }
 int64_t flash_mma_header_bytes(int batch, int n_kv_heads) {
-  return ((16 + 4 * (int64_t)batch * n_kv_heads) + 15) / 16 * 16;
+  // status block, one split counter per (batch, kv head), eight value-skipping hint words per (batch, kv head)
+  return ((16 + (4 + 32) * (int64_t)batch * n_kv_heads) + 15) / 16 * 16;
 }
 int flash_mma_max_splits() { return 96; }
 

@@ -92,6 +92,8 @@ struct MmaTables {
   float v_post;         // multiplies the accumulator when it is written: 1 / beta_v
   int* status;          // set non-zero if a bounded wait gives up
   int* counters;        // one per (batch, kv head); zero between calls
+  uint32_t* hints;      // value skipping: 8 words per (batch, kv head), the largest score any CTA of the group has
+                        // seen per head as a biased ordered key (0 = none yet); zero between calls
   int splits;           // partials per (batch, kv head)
   int out_mode, out_dtype;
   void* out;
@@ -710,6 +712,11 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
   float m_run = -INFINITY, l_run = 0.f;
   int active_count = 0;             // positions whose values this warp accumulated (reported when asked for)
+  // value skipping across splits: the hint words are shared by the CTAs of the group and put back to zero by the
+  // CTA that merges it, so they may only be used by a call that is alone on its workspace while it runs (its own
+  // workspace, or a call that has already waited for its predecessor)
+  const bool use_group_hint = !PLAIN && a.sparse_thr > 0.f && tb.hints != nullptr && (a.ws_exclusive || !a.q_stable);
+  uint32_t* group_hint = tb.hints + 8 * (b * a.n_kv_heads + kvh);
   float bias_run[2] = {0.f, 0.f};   // affine values: sum of weight x bias per element group (head g, this lane's positions)
   const int pw = 16 * warp;   // first position of this warp inside a tile
 
@@ -736,6 +743,12 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       const int64_t tile0 = (int64_t)blockIdx.x * a.chunk + (int64_t)i * kTile;
       nvp_row = min(nvp, (int)min((int64_t)(2 * kTile), sq - tile0) - (a.q_tokens - 1 - g / a.n_rep));
     }
+
+    // value skipping: what the other CTAs of the group have seen so far, fetched now so that the latency is
+    // gone by the time the tile's own scores exist (only real scores are ever written there, so whatever a
+    // relaxed read returns is a valid lower bound of the head's largest score)
+    uint32_t group_key = 0u;
+    if (use_group_hint) asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(group_key) : "l"(group_hint + g));
 
     // ---------------- scores ----------------
     float sc[2][4];
@@ -911,7 +924,11 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
       float sq = fmaxf(smax, __shfl_xor_sync(0xffffffffu, smax, 1));
       sq = fmaxf(sq, __shfl_xor_sync(0xffffffffu, sq, 2));
       float hint = from_ordered_int(*reinterpret_cast<volatile int*>(&hint_s[g]));
-      if (t == 0 && g < a.rows && sq > hint) atomicMax(&hint_s[g], ordered_int(sq));   // rare once the large scores are in
+      if (group_key != 0u) hint = fmaxf(hint, from_ordered_int((int)(group_key ^ 0x80000000u)));
+      if (t == 0 && g < a.rows && sq > hint) {           // rare once the large scores are in
+        atomicMax(&hint_s[g], ordered_int(sq));
+        if (use_group_hint) atomicMax(group_hint + g, (uint32_t)ordered_int(sq) ^ 0x80000000u);
+      }
       hint = fmaxf(hint, sq);
       const bool below = smax == -INFINITY || ex2(smax - m_use) < a.sparse_thr * lq || ex2(smax - hint) < a.sparse_thr;
       skip_values = __all_sync(0xffffffffu, g >= a.rows || below);
@@ -1099,6 +1116,7 @@ flash_mma_kernel(const FlashArgs a, const MmaTables tb) {
   }
   consumer_barrier();
   if (!elected_s) return;
+  if (use_group_hint && tid < 8) group_hint[tid] = 0u;   // every CTA of the group is past its loop: zero between calls
   // A push into peer slots that an exchange still in flight may be reading (a small ring of slots) has to
   // come after the launch in front of this one - the gated merge that reads them - has completed.
   if (independent && tb.n_peers > 0 && !tb.peer_unordered) grid_dependency_wait();
@@ -1332,6 +1350,7 @@ int TQ_CAT(launch_flash_mma_, TQ_GEOM)(const FlashArgs& a, int splits, const Mma
   memset(&tb, 0, sizeof(tb));
   tb.status = mo.status;
   tb.counters = mo.counters;
+  tb.hints = mo.hints;
   tb.splits = splits;
   tb.out_mode = mo.out_mode;
   tb.out_dtype = mo.out_dtype;
