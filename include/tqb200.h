@@ -252,8 +252,10 @@ typedef struct tq_flash_params {
    * positions is dropped for a (batch, kv head) group when every weight in it is already certain to
    * end below the threshold - weight <= exp(score - running max) / running sum, and weight <=
    * exp(score - largest score the CTA has seen) - so nothing is dropped that the reference would
-   * keep, and everything still counts in the softmax sum.  The bounds only know what the CTA's own
-   * chunk of the sequence has shown so far: chunks without a dominant key drop little.
+   * keep, and everything still counts in the softmax sum.  The largest score is shared by all CTAs of
+   * a (batch, kv head) group through hint words in the workspace header when the call has its
+   * workspace to itself while it runs (workspace_exclusive, or q_stable = 0: it has waited for its
+   * predecessor); otherwise a CTA only knows what its own chunk of the sequence has shown so far.
    * active_positions: optional device int32 (batch, n_kv_heads), zeroed by the caller; receives
    * the number of positions whose values were accumulated (count_active_positions semantics per
    * group, sparse_v.py:189-191). */
