@@ -293,9 +293,11 @@ def flash_decode(q: torch.Tensor, *, k=None, v=None, attn_scale: float, q_prerot
 
     sparse_v_threshold > 0 (tensor-core kernel only, ValueError otherwise): values of positions
     whose softmax weight is certain to end below the threshold are not accumulated (decided per
-    16-position tile and kv-head group from the running softmax state, so nothing is dropped
-    that the reference's `sparse_v_matvec` would keep); `active_out`, an int32 (B, n_kv) tensor,
-    receives the number of positions whose values were accumulated.
+    16-position tile and kv-head group from the running softmax state and the largest score the
+    group's CTAs have seen so far, so nothing is dropped that the reference's `sparse_v_matvec`
+    would keep); `active_out`, an int32 (B, n_kv) tensor, receives the number of positions whose
+    values were accumulated (it is zeroed here with a launch of its own: leave it out where decode
+    launches are meant to overlap).
 
     seq_lens (tensor-core kernel only): int32 (B,) device tensor with the number of valid positions
     of each sequence (<= S), read by the kernel when it runs: ragged batches without a mask, and
